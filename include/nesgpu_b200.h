@@ -1,0 +1,249 @@
+/*
+ * nesgpu_b200 -- C ABI of the B200 (sm_100a) population-batched perturbed-layer kernels.
+ *
+ * Every entry point:
+ *   - takes plain DEVICE pointers and sizes (no framework types), all tensors contiguous;
+ *   - launches on the CUDA stream it is given (a cudaStream_t passed as void*), never
+ *     synchronises the device, never allocates or frees memory;
+ *   - returns NES_OK (0) or a negative nes_status; nes_last_error() gives the detail.
+ * Kernels that need workspace take a caller-owned `scratch` pointer; the matching
+ * *_scratch_bytes() function says how much.
+ *
+ * The reference project (jamesal1/NESgpu) has no C ABI: its layers are PyTorch modules
+ * (modules/base.py, modules/binary.py) over ATen library calls, cupy RawKernels
+ * (extensions/src/*.cu launched by extensions/booleanOperations.py) and a pybind
+ * extension (extensions/booleanOperations.cpp, booleanUtilities.cpp).  Each declaration
+ * below names the reference code it replaces as file:line within that project.
+ *
+ * Index conventions shared by the fp32 entry points (modules/base.py:357,368,490 and
+ * :377-378,504-505,584-585): batch row b = r * D + d for member d in [0, D) and repeat r in
+ * [0, R); when `antithetic` is non-zero the perturbation of rows with r >= (R + 1) / 2 is
+ * negated.  Noise tensors already carry their scale (modules/base.py:83,206).
+ */
+#ifndef NESGPU_B200_H
+#define NESGPU_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NES_ABI_VERSION 1
+
+typedef void* nes_stream_t; /* cudaStream_t */
+
+enum nes_status {
+  NES_OK = 0,
+  NES_ERR_BAD_ARG = -1,      /* null pointer, negative extent, misaligned buffer            */
+  NES_ERR_UNSUPPORTED = -2,  /* a size or option outside what the kernels implement          */
+  NES_ERR_LAUNCH = -3,       /* the CUDA runtime rejected a launch (see nes_last_error)      */
+  NES_ERR_TIMEOUT = -4,      /* a bounded device-side wait ran out                           */
+  NES_ERR_SCRATCH = -5       /* scratch buffer missing or smaller than *_scratch_bytes()     */
+};
+
+int nes_abi_version(void);
+const char* nes_status_string(int status);
+/* Detail of the last failure on the calling thread ("" if none). */
+const char* nes_last_error(void);
+/* Kernel launches issued by this library in the calling process so far (diagnostic counter; it has
+ * no counterpart in the reference). */
+int64_t nes_launch_count(void);
+
+/* ------------------------------------------------------------------ fp32: plain layers */
+
+/* y[M,N] = x[M,K] . weight[N,K]^T + bias[N] (bias may be NULL).
+ * Replaces F.linear at modules/base.py:366,381,488. */
+int nes_linear_fwd(const float* x, const float* weight, const float* bias, float* y,
+                   int64_t M, int64_t N, int64_t K, nes_stream_t stream);
+
+/* NCHW convolution, groups == 1, zero padding.  x (B,Cin,H,W), weight (Cout,Cin,kh,kw),
+ * y (B,Cout,Ho,Wo).  Replaces F.conv2d at modules/base.py:411,558. */
+int nes_conv2d_fwd(const float* x, const float* weight, const float* bias, float* y,
+                   int64_t B, int Cin, int H, int W, int Cout, int kh, int kw,
+                   int sh, int sw, int ph, int pw, int dh, int dw, nes_stream_t stream);
+
+/* ------------------------------------------------- fp32: dense per-member (IID) noise */
+
+/* PerturbedLinear.forward with the perturbed flag set (modules/base.py:355-381):
+ *   y[b,o] = x[b].weight[o] + bias[o] + s(r) * (x[b].noise[d,o] + bias_noise[d,o]).
+ * x (R*D,in), weight (out,in), noise (D,out,in), bias_noise (D,out) or NULL, y (R*D,out).
+ * direct != 0 follows modules/base.py:356-364: noise holds W+E, bias_noise holds b+beta,
+ * weight/bias are ignored and no sign is applied. */
+int nes_perturbed_linear_fwd(const float* x, const float* weight, const float* bias,
+                             const float* noise, const float* bias_noise, float* y,
+                             int64_t D, int64_t R, int64_t in, int64_t out,
+                             int antithetic, int direct, nes_stream_t stream);
+
+/* PerturbedConv2d.forward, non-direct branch (modules/base.py:410-425): per member a
+ * convolution with weight + s(r)*noise[d] and bias + s(r)*bias_noise[d].
+ * noise (D,Cout,Cin,kh,kw); bias/bias_noise may be NULL. */
+int nes_perturbed_conv2d_fwd(const float* x, const float* weight, const float* bias,
+                             const float* noise, const float* bias_noise, float* y,
+                             int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                             int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                             int antithetic, nes_stream_t stream);
+
+/* Perturbed.weight_grad plus the l1/l2 terms of Perturbed.update (modules/base.py:110-125):
+ *   grad[i] = sum_d w[d] * noise[d,i] + l1 * sign(weight[i]) + l2 * weight[i],  i in [0,n).
+ * `weight` may be NULL when l1 == l2 == 0.  Also used for the bias gradient
+ * `weights @ bias_noise` (modules/base.py:135) with n = out.
+ * The members are split over thread blocks; partial sums go through `scratch`. */
+int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n);
+int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
+                         int64_t D, int64_t n, float l1, float l2,
+                         void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* Sparse Gaussian noise ("SparsePerturbedLinear", README.md:12,29-30; the layer has no
+ * source in the reference snapshot): k (index,value) pairs per member and output row,
+ *   y[b,o] = x[b].weight[o] + bias[o] + s(r) * (sum_t x[b, idx[d,o,t]] * val[d,o,t] + bias_noise[d,o]),
+ * which equals PerturbedLinear.forward (modules/base.py:365-381) on the densified noise.
+ * idx (D,out,k) int32 in [0,in); val (D,out,k). */
+int nes_sparse_perturbed_linear_fwd(const float* x, const float* weight, const float* bias,
+                                    const int32_t* idx, const float* val, const float* bias_noise,
+                                    float* y, int64_t D, int64_t R, int64_t in, int64_t out,
+                                    int k, int antithetic, nes_stream_t stream);
+
+/* grad[o, idx[d,o,t]] += w[d] * val[d,o,t] over a zeroed grad, then + l1*sign(W) + l2*W:
+ * Perturbed.update (modules/base.py:110-125) on the densified sparse noise. */
+int nes_sparse_perturbed_update(const int32_t* idx, const float* val, const float* w,
+                                const float* weight, float* grad, int64_t D, int64_t in,
+                                int64_t out, int k, float l1, float l2, nes_stream_t stream);
+
+/* ------------------------------------------- fp32: shared noise + member permutations */
+
+/* PermutedLinear.forward, default branch (modules/base.py:487-508):
+ *   xg[b,j] = x[b, pin[d,j]]            (j < in_sp; identity when pin == NULL)
+ *   p[b,s]  = sum_j xg[b,j] * eps[s,j]  (s < out_sp)
+ *   q[b,k]  = p[b, pout[d,k]] if pout[d,k] < out_sp else 0   (identity when pout == NULL)
+ *   y[b,k]  = x[b].weight[k] + bias[k] + s(r) * (q[b,k] + bias_noise[d,k]).
+ * eps (out_sp,in_sp); pin (D,in_sp) int16 or NULL; pout (D,out) int16 or NULL.
+ * p goes through `scratch`. */
+int64_t nes_permuted_linear_fwd_scratch_bytes(int64_t D, int64_t R, int64_t out_sp);
+int nes_permuted_linear_fwd(const float* x, const float* weight, const float* bias,
+                            const float* eps, const float* bias_noise,
+                            const int16_t* pin, const int16_t* pout, float* y,
+                            int64_t D, int64_t R, int64_t in, int64_t out,
+                            int64_t in_sp, int64_t out_sp, int antithetic,
+                            void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* PermutedConv2d.forward, default branch (modules/base.py:557-588), evaluated as one
+ * convolution per member with the effective filter
+ *   W_d[k,c,:,:] = weight[k,c] + s(r) * eps[pout[d,k], j]  for the j with pin[d,j] == c
+ * (zero where pout[d,k] >= out_sp or no such j), which is algebraically the same sum.
+ * pin must not repeat a channel within a member (allow_repeats is handled by the caller
+ * through nes_permuted_dense_noise + nes_perturbed_conv2d_fwd).
+ * eps (out_sp,in_sp,kh,kw).  `scratch` holds the per-member channel maps. */
+int64_t nes_permuted_conv2d_fwd_scratch_bytes(int64_t D, int Cin, int Cout);
+int nes_permuted_conv2d_fwd(const float* x, const float* weight, const float* bias,
+                            const float* eps, const float* bias_noise,
+                            const int16_t* pin, const int16_t* pout, float* y,
+                            int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                            int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                            int in_sp, int out_sp, int antithetic,
+                            void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* The dense noise a Permuted layer is equal to (derived from modules/base.py:487-508):
+ *   E[d,k,m,t] = sum_j [pin[d,j] == m] * eps[pout[d,k], j, t]   (0 where pout[d,k] >= out_sp).
+ * E (D,out,in,ksize) is fully overwritten.  Repeated pin entries add. */
+int nes_permuted_dense_noise(const float* eps, const int16_t* pin, const int16_t* pout, float* E,
+                             int64_t D, int in, int out, int in_sp, int out_sp, int ksize,
+                             nes_stream_t stream);
+
+/* Permuted.get_permutation_weights + PermutedLinear/PermutedConv2d.weight_grad
+ * (modules/base.py:242-267, 511-518, 590-599) plus the l1/l2 terms of update (:122-125):
+ *   out-only: G[k,s] = sum_d w_d [pout[d,k] == s];  grad[k,m,t] = sum_s G[k,s] eps[s,m,t]
+ *   in-only:  H[j,m] = sum_d w_d [pin[d,j] == m];   grad[k,m,t] = sum_j eps[k,j,t] H[j,m]
+ *   both:     grad = sum_d w_d E_d  with E_d as in nes_permuted_dense_noise.
+ * grad (out,in,ksize); ksize = kh*kw (1 for linear).  `perm_weights_out`, if not NULL,
+ * receives G (out,out_sp) or H (in_sp,in) for the single-sided modes. */
+int64_t nes_permuted_update_scratch_bytes(int in, int out, int in_sp, int out_sp);
+int nes_permuted_update(const float* eps, const float* w, const int16_t* pin, const int16_t* pout,
+                        const float* weight, float* grad, float* perm_weights_out,
+                        int64_t D, int in, int out, int in_sp, int out_sp, int ksize,
+                        float l1, float l2, void* scratch, int64_t scratch_bytes,
+                        nes_stream_t stream);
+
+/* ---------------------------------------------------------------- noise set-up (device) */
+
+/* out[i] = mean + std * N(0,1), Philox-4x32-10 keyed by (seed, offset + i/4).
+ * Replaces Tensor.normal_ at modules/base.py:83-85,206-208. */
+int nes_fill_normal(float* out, int64_t n, float mean, float std, uint64_t seed, uint64_t offset,
+                    nes_stream_t stream);
+/* out[i] = lo + (hi - lo) * U(0,1].  Replaces torch.rand at modules/binary.py:63. */
+int nes_fill_uniform(float* out, int64_t n, float lo, float hi, uint64_t seed, uint64_t offset,
+                     nes_stream_t stream);
+/* D independent uniform permutations of [0,n), first `keep` entries of each stored
+ * (out is (D,keep) int16); with_replacement != 0 draws keep independent indices instead.
+ * Replaces the per-member CPU randperm loop / randint at modules/base.py:209-227.  n <= 16384
+ * without replacement (the sort runs in shared memory), n <= 32767 with replacement. */
+int nes_sample_permutations(int16_t* out, int64_t D, int n, int keep, int with_replacement,
+                            uint64_t seed, nes_stream_t stream);
+
+/* ---------------------------------------------------------------------- bit-packed ops
+ * word_bits is 64 (int64 words) or 32 (int32 words), as the reference's KernelWrapper
+ * substitutes (extensions/booleanOperations.py:10-36).  bool tensors are one byte per value. */
+
+/* (rows,cols) bool -> (rows, ceil(cols/word_bits)) words, LSB first.
+ * Replaces pack_kernel (extensions/src/pack.cu:4-30) and cuda_pack (booleanUtilitiesCuda.cu:54-74,163-177). */
+int nes_bin_pack(const uint8_t* in, void* out, int64_t rows, int64_t cols, int word_bits,
+                 nes_stream_t stream);
+/* (rows,cols) uint8 -> words, byte i -> bits 8i..8i+7.  Replaces int8pack_kernel (extensions/src/int8pack.cu:4-30). */
+int nes_bin_int8pack(const uint8_t* in, void* out, int64_t rows, int64_t cols, int word_bits,
+                     nes_stream_t stream);
+/* (rows,cols) bool -> (rows, ceil(cols/8)) int8.  Replaces cuda_pack8 (booleanUtilitiesCuda.cu:31-50,148-158). */
+int nes_bin_pack8(const uint8_t* in, int8_t* out, int64_t rows, int64_t cols, nes_stream_t stream);
+/* (rows,words) words -> (rows, words*word_bits) bool.  Replaces cuda_unpack (booleanUtilitiesCuda.cu:77-90,182-195). */
+int nes_bin_unpack(const void* in, uint8_t* out, int64_t rows, int64_t words, int word_bits,
+                   nes_stream_t stream);
+
+/* out[x,y,z] bit i = float(p[y, word_bits*z + i]) > u, for x in [0,n): Bernoulli(p) bits.
+ * p (rows,cols) fp16.  If `uniforms` (n,rows,cols) fp32 is given it supplies u; otherwise
+ * u in (0,1] comes from Philox keyed by (seed, x, y, column).
+ * Replaces sample_bits_kernel (extensions/src/sample_bits.cu:9-60) and cuda_sample_bits
+ * (booleanUtilitiesCuda.cu:95-122,199-223). */
+int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms, void* out, int64_t n,
+                        int64_t rows, int64_t cols, int word_bits, uint64_t seed,
+                        nes_stream_t stream);
+
+/* C[z,x,y] = sum_k popcount(A[z,x,k] ^ B[z,k,y]) as int32.  A (P,M,K), B (P,K,N), C (P,M,N).
+ * Replaces bmm_kernel (extensions/src/bmm.cu:5-58) and cuda_binary_bmm (booleanOperationsCuda.cu:33-100,206-238). */
+int nes_bin_bmm(const void* A, const void* B, int32_t* C, int64_t P, int64_t M, int64_t K,
+                int64_t N, int word_bits, nes_stream_t stream);
+/* C[z,x,y] = 2*acc > thresh[z,y] as bool.  Replaces bmm_act_kernel (extensions/src/bmm_act.cu:5-63). */
+int nes_bin_bmm_act(const void* A, const void* B, const int32_t* thresh, uint8_t* C, int64_t P,
+                    int64_t M, int64_t K, int64_t N, int word_bits, nes_stream_t stream);
+
+/* Packed NHWC (P,H,W,Cw) -> columns (P, h*w, fx*fy*Cw); out-of-bounds taps give the zero word.
+ * Replaces batch_im2col_kernel (extensions/src/batch_im2col.cu:3-33) and cuda_batch_im2col
+ * (booleanOperationsCuda.cu:121-168,243-291). */
+int nes_bin_im2col(const void* in, void* out, int64_t P, int H, int W, int Cw, int fx, int fy,
+                   int px, int py, int sx, int sy, int word_bits, nes_stream_t stream);
+/* out[p,xo,yo,n] = sum over window taps and channel words of popcount(in ^ filter), without
+ * materialising the columns.  filter (P, fx*fy*Cw, N).  thresh == NULL: int32 counts to
+ * `out_counts`; otherwise 2*acc > thresh[p,n] as bool to `out_bool`.
+ * Replaces booleanOperations.conv / conv_act (extensions/booleanOperations.py:162-172) and
+ * cuda_binary_batch_conv2d (booleanOperationsCuda.cu:295-298). */
+int nes_bin_conv(const void* in, const void* filter, const int32_t* thresh, int32_t* out_counts,
+                 uint8_t* out_bool, int64_t P, int H, int W, int Cw, int N, int fx, int fy,
+                 int px, int py, int sx, int sy, int word_bits, nes_stream_t stream);
+
+/* out[y,z] = half(sum_d float(w[d]) * bit_d[y,z]), fp32 accumulation.  in (D,rows,words),
+ * w (D) fp16, out (rows,zbits) fp16.  Members are split over thread blocks; the fp32
+ * partial sums go through `scratch`.
+ * Replaces weighted_sum_kernel (extensions/src/weighted_sum.cu:8-48) and
+ * cuda_binary_weighted_sum (booleanUtilitiesCuda.cu:125-145,225-240). */
+int64_t nes_bin_weighted_sum_scratch_bytes(int64_t D, int64_t rows, int64_t words, int word_bits);
+int nes_bin_weighted_sum(const void* in, const uint16_t* w_half, uint16_t* out_half, int64_t D,
+                         int64_t rows, int64_t words, int64_t zbits, int word_bits,
+                         void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* Bitwise OR over the 2x2 window starting at (xo*sx-px, yo*sy-py) of packed NHWC input;
+ * fx, fy only enter the output size, as in max_pool2d_kernel (extensions/src/max_pool2d.cu:3-36). */
+int nes_bin_maxpool2d(const void* in, void* out, int64_t P, int H, int W, int Cw, int fx, int fy,
+                      int px, int py, int sx, int sy, int word_bits, nes_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NESGPU_B200_H */

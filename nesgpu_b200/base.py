@@ -1,0 +1,553 @@
+"""Population-batched perturbed layers on B200 kernels.
+
+Host-side mirror of the reference's ``modules/base.py`` (NESgpu): the same class names,
+constructor signatures, public attributes (``weight_noise``, ``bias_noise``,
+``input_permutations``, ``output_permutations``, ``perturbed_flag`` ...) and methods
+(``set_noise``, ``forward``, ``update`` ...), so user code written for the reference runs
+unchanged.  All arithmetic happens in the CUDA library behind ``include/nesgpu_b200.h``;
+this file only keeps state, validates shapes and launches.  Tensors must live on a CUDA
+device and be fp32 -- there is no CPU path.
+
+Batch layout (reference ``modules/base.py:357,368,490``): row ``b = r * directions + d``.
+"""
+import random
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+from torch.nn.modules.utils import _pair
+
+from . import _cabi as C
+
+_F32 = torch.float32
+
+
+def _opt(t):
+    return None if t is None else C.require_cuda(t.detach(), "parameter", _F32)
+
+
+class PerturbedModel:
+    """Wraps a model whose layers derive from :class:`Perturbed` (reference ``base.py:9-41``).
+
+    ``forward`` runs the model with every perturbed layer switched to population mode; a
+    method name that :class:`Perturbed` defines is broadcast to all perturbed layers; any
+    other attribute is looked up on the model and called in population mode."""
+
+    def __init__(self, model, directions):
+        self.model = model
+        self.directions = directions
+        self.perturbed_layers = [m for m in model.modules() if isinstance(m, Perturbed)]
+
+    def _population_mode(self, on):
+        for layer in self.perturbed_layers:
+            layer.perturbed_flag = on
+
+    def forward(self, input, *args):
+        self._population_mode(True)
+        try:
+            return self.model.forward(input, *args)
+        finally:
+            self._population_mode(False)
+
+    def __getattr__(self, name):
+        if hasattr(Perturbed, name):
+            def broadcast(*args, **kwargs):
+                for layer in self.perturbed_layers:
+                    getattr(layer, name)(*args, **kwargs)
+            return broadcast
+
+        def in_population_mode(*args, **kwargs):
+            self._population_mode(True)
+            try:
+                return getattr(self.model, name)(*args, **kwargs)
+            finally:
+                self._population_mode(False)
+        return in_population_mode
+
+
+class Perturbed:
+    """Dense per-member Gaussian noise (reference ``base.py:44-138``).
+
+    ``weight_noise`` is ``(directions, *weight.shape)``, ``bias_noise`` ``(directions, *bias.shape)``,
+    both already scaled by ``noise_scale``.  ``options["direct"]`` stores ``weight + noise``
+    instead (reference ``base.py:67-81``)."""
+
+    def __init__(self, directions, antithetic=False, options={}):
+        self.directions = directions
+        self.perturbed_flag = False
+        self.noise_scale = None
+        self.seed = None
+        self.antithetic = antithetic
+        self.options = options
+        self.free_memory()
+
+    # -- state ---------------------------------------------------------------------------
+    def set_noise_scale(self, noise_scale):
+        self.noise_scale = noise_scale
+
+    def set_seed(self, seed=None):
+        self.seed = random.randrange(100000000) if seed is None else seed
+
+    def allocate_weight(self):
+        self.weight_noise = torch.empty((self.directions,) + tuple(self.weight.shape),
+                                        device=self.weight.device, dtype=self.weight.dtype)
+
+    def allocate_bias(self):
+        if self.bias is not None:
+            self.bias_noise = torch.empty((self.directions,) + tuple(self.bias.shape),
+                                          device=self.bias.device, dtype=self.bias.dtype)
+
+    def allocate_memory(self):
+        self.allocate_weight()
+        self.allocate_bias()
+
+    def free_memory(self):
+        self.weight_noise = None
+        if getattr(self, "bias", None) is not None:
+            self.bias_noise = None
+
+    def _prepare_noise(self, noise_scale):
+        if self.seed is None:
+            self.set_seed()
+        if noise_scale is not None:
+            self.set_noise_scale(noise_scale)
+        if self.weight_noise is None:
+            self.allocate_memory()
+
+    @staticmethod
+    def _fill_normal(t, std, seed, stream_id):
+        """N(0, std^2) from the device generator; ``stream_id`` separates the tensors of a layer."""
+        C.require_cuda(t, "noise tensor", _F32)
+        C.call("nes_fill_normal", C.ptr(t), t.numel(), 0.0, float(std), int(seed) & (2 ** 64 - 1),
+               int(stream_id) << 40, C.stream())
+
+    def set_noise(self, noise_scale=None):
+        """Draw fresh noise on the device (reference ``base.py:59-85``)."""
+        self._prepare_noise(noise_scale)
+        direct = bool(self.options.get("direct"))
+        pairs = [(self.weight_noise, self.weight, 0)]
+        if self.bias is not None:
+            pairs.append((self.bias_noise, self.bias, 1))
+        for noise, param, sid in pairs:
+            if direct and self.antithetic:
+                half = self.directions // 2
+                self._fill_normal(noise[:half], self.noise_scale, self.seed, sid)
+                noise[half:] = -noise[:half]
+            else:
+                self._fill_normal(noise, self.noise_scale, self.seed, sid)
+            if direct:
+                noise += param.detach()
+
+    # -- update --------------------------------------------------------------------------
+    def _direct_param(self, param):
+        """With "direct" storage the tensors hold ``param + noise`` (reference ``base.py:111-117``):
+        sum_d w_d (N_d - P) = sum_d w_d N_d - (sum_d w_d) P, so the parameter is taken out after
+        the reduction instead of materialising ``noise - param``."""
+        if not self.options.get("direct"):
+            return None
+        if self.antithetic:
+            raise NotImplementedError("direct + antithetic update is inconsistent in the reference "
+                                      "(modules/base.py:113-118) and is not provided")
+        return param.detach()
+
+    @staticmethod
+    def _weighted_sum(noise, weights, param, l1, l2, direct_param=None):
+        """sum_d weights[d] * noise[d] (+ l1 sign(param) + l2 param) as a tensor shaped like noise[0]."""
+        noise = C.require_cuda(noise, "noise", _F32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        D = noise.shape[0]
+        n = noise[0].numel() if D else 0
+        if weights.numel() != D:
+            raise RuntimeError("update weights must have one entry per direction")
+        out = torch.empty(noise.shape[1:], device=noise.device, dtype=_F32)
+        nbytes = C.call("nes_perturbed_update_scratch_bytes", D, n)
+        buf = C.scratch(nbytes, noise.device)
+        C.call("nes_perturbed_update", C.ptr(noise), C.ptr(weights), C.ptr(_opt(param)) if (l1 or l2) else None,
+               C.ptr(out), D, n, float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
+        if direct_param is not None:
+            out.sub_(direct_param * weights.sum())
+        return out
+
+    def weight_grad(self, weights):
+        return self._weighted_sum(self.weight_noise, weights, None, 0, 0, self._direct_param(self.weight))
+
+    def _weight_grad_regularised(self, weights, l1, l2):
+        return self._weighted_sum(self.weight_noise, weights, self.weight, l1, l2, self._direct_param(self.weight))
+
+    def update(self, weights, l1=0, l2=0):
+        """Accumulate the fitness-weighted noise sum into ``.grad`` (reference ``base.py:120-138``)."""
+        grad = self._weight_grad_regularised(weights, l1, l2)
+        self.weight.grad = grad if self.weight.grad is None else self.weight.grad + grad
+        if self.bias is None:
+            return grad
+        bias_grad = self._weighted_sum(self.bias_noise, weights, None, 0, 0, self._direct_param(self.bias))
+        self.bias.grad = bias_grad if self.bias.grad is None else self.bias.grad + bias_grad
+        return grad, bias_grad
+
+    # -- helpers shared by the layer classes ------------------------------------------------
+    def _repeats(self, batch):
+        if batch % self.directions:
+            raise RuntimeError("batch size %d is not a multiple of directions %d" % (batch, self.directions))
+        return batch // self.directions
+
+
+def _resolve_permutation(in_degree, out_degree, permutation, in_sparsity, out_sparsity):
+    """Which sides are permuted and how many noise rows/columns exist (reference ``base.py:148-184``)."""
+    if permutation == "auto":
+        if in_sparsity:
+            permutation = "both" if out_sparsity else "in"
+        elif out_sparsity:
+            permutation = "out"
+        elif 1 < in_degree < 32 and 1 < out_degree < 32:
+            permutation = "both"
+        else:
+            permutation = "in" if in_degree > out_degree else "out"
+    if permutation not in ("in", "out", "both"):
+        raise NotImplementedError("Permutation setting not recognized")
+    sides = {"in": permutation != "out", "out": permutation != "in"}
+    kept = {}
+    for side, degree, sp in (("in", in_degree, in_sparsity), ("out", out_degree, out_sparsity)):
+        if isinstance(sp, float):
+            sp = max(1, int(sp * degree))
+        if sp:
+            sides[side] = True
+        kept[side] = sp if sp else degree
+    return sides["in"], sides["out"], kept["in"], kept["out"]
+
+
+class Permuted(Perturbed):
+    """One shared noise tensor ``(out_sparsity, in_sparsity, ...)`` re-used by every member
+    through per-member int16 permutations of the inputs and/or outputs (reference
+    ``base.py:142-267``)."""
+
+    def __init__(self, in_degree, out_degree, directions, antithetic=False, options={},
+                 permutation="auto", in_sparsity=0, out_sparsity=0):
+        Perturbed.__init__(self, directions, antithetic, options)
+        (self.permute_inputs, self.permute_outputs,
+         self.in_sparsity, self.out_sparsity) = _resolve_permutation(in_degree, out_degree, permutation,
+                                                                     in_sparsity, out_sparsity)
+        self.in_degree = in_degree
+        self.out_degree = out_degree
+        if max(in_degree, out_degree) > 32767:
+            raise NotImplementedError("permutation tables are int16: degrees above 32767 are not supported")
+        if options.get("combined") and self.permute_inputs and self.permute_outputs:
+            raise NotImplementedError("Can't do combined multiplication with both input and output permutations")
+
+    def allocate_weight(self):
+        self.weight_noise = torch.empty((self.out_sparsity, self.in_sparsity) + tuple(self.weight.shape[2:]),
+                                        device=self.weight.device, dtype=self.weight.dtype)
+
+    def free_memory(self):
+        Perturbed.free_memory(self)
+        self.input_permutations = None
+        self.output_permutations = None
+
+    def _sample_permutations(self, n, keep, stream_id):
+        out = torch.empty((self.directions, keep), dtype=torch.int16, device=self.weight.device)
+        C.call("nes_sample_permutations", C.ptr(out), self.directions, n, keep,
+               1 if self.options.get("allow_repeats") else 0,
+               (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1), C.stream())
+        return out
+
+    def set_noise(self, noise_scale=None):
+        """Shared noise, bias noise and permutations, all drawn on the device (reference
+        ``base.py:197-227``, which loops ``torch.randperm`` on the CPU once per member)."""
+        self._prepare_noise(noise_scale)
+        rescale = (self.out_degree * self.in_degree / self.out_sparsity / self.in_sparsity) ** .5
+        self._fill_normal(self.weight_noise, self.noise_scale * rescale, self.seed, 0)
+        if self.bias is not None:
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+        if self.permute_outputs:
+            self.output_permutations = self._sample_permutations(self.out_degree, self.out_degree, 2)
+        if self.permute_inputs:
+            self.input_permutations = self._sample_permutations(self.in_degree, self.in_sparsity, 3)
+
+    # index_select helpers kept for API parity (reference base.py:229-240); not on the fused path
+    def _flat_index(self, perms, degree, device):
+        return (perms.long() + (torch.arange(self.directions, device=device) * degree).unsqueeze(1)).flatten()
+
+    def apply_input_permutation(self, input):
+        if not self.permute_inputs:
+            return input
+        return torch.index_select(input, 1, self._flat_index(self.input_permutations, self.in_degree, input.device))
+
+    def apply_output_permutation(self, output):
+        if not self.permute_outputs:
+            return output
+        return torch.index_select(output, 1, self._flat_index(self.output_permutations, self.out_degree, output.device))
+
+    def _perms(self):
+        pin = C.require_cuda(self.input_permutations, "input_permutations", torch.int16) if self.permute_inputs else None
+        pout = C.require_cuda(self.output_permutations, "output_permutations", torch.int16) if self.permute_outputs else None
+        return pin, pout
+
+    def _permuted_update(self, weights, l1, l2, want_perm_weights=False):
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        if weights.numel() != self.directions:
+            raise RuntimeError("update weights must have one entry per direction")
+        pin, pout = self._perms()
+        ksize = 1
+        for s in self.weight.shape[2:]:
+            ksize *= s
+        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        pw = None
+        if want_perm_weights:
+            shape = (self.in_sparsity, self.in_degree) if pin is not None else (self.out_degree, self.out_sparsity)
+            pw = torch.empty(shape, device=eps.device, dtype=_F32)
+        nbytes = C.call("nes_permuted_update_scratch_bytes", self.in_degree, self.out_degree,
+                        self.in_sparsity, self.out_sparsity)
+        buf = C.scratch(nbytes, eps.device)
+        C.call("nes_permuted_update", C.ptr(eps), C.ptr(weights), C.ptr(pin), C.ptr(pout),
+               C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), C.ptr(pw),
+               self.directions, self.in_degree, self.out_degree, self.in_sparsity, self.out_sparsity, ksize,
+               float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
+        return grad, pw
+
+    def get_permutation_weights(self, weights):
+        """The scatter-add matrix of reference ``base.py:254-267`` for the single-sided modes."""
+        if self.permute_inputs and self.permute_outputs:
+            raise NotImplementedError("two-sided permutation weights are O((out*in)^2) in the reference "
+                                      "(modules/base.py:243-253); weight_grad computes the gradient directly")
+        return self._permuted_update(weights, 0, 0, want_perm_weights=True)[1]
+
+    def weight_grad(self, weights):
+        return self._permuted_update(weights, 0, 0)[0]
+
+    def _weight_grad_regularised(self, weights, l1, l2):
+        return self._permuted_update(weights, l1, l2)[0]
+
+
+class _LinearMixin:
+    def _flatten_rows(self, input):
+        x = C.require_cuda(input, "input", _F32)
+        if x.shape[-1] != self.in_features:
+            raise RuntimeError("expected last dimension %d, got %d" % (self.in_features, x.shape[-1]))
+        return x.reshape(-1, self.in_features), x.shape[:-1]
+
+    def _plain_forward(self, input):
+        x, lead = self._flatten_rows(input)
+        y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        C.call("nes_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(y),
+               x.shape[0], self.out_features, self.in_features, C.stream())
+        return y.view(*lead, self.out_features)
+
+
+class PerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
+    """``y = x W^T + b + s * (x E_d^T + beta_d)`` with one dense noise matrix per member
+    (reference ``base.py:349-381``)."""
+
+    def __init__(self, in_features, out_features, directions, bias=True, antithetic=False, options={}):
+        nn.Linear.__init__(self, in_features, out_features, bias)
+        Perturbed.__init__(self, directions, antithetic, options)
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x, lead = self._flatten_rows(input)
+        R = self._repeats(x.shape[0])
+        direct = 1 if self.options.get("direct") else 0
+        noise = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        C.call("nes_perturbed_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+               C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, self.in_features, self.out_features,
+               1 if self.antithetic else 0, direct, C.stream())
+        if direct:
+            return y.view(R, self.directions, self.out_features)
+        return y.view(*lead, self.out_features)
+
+
+class SparsePerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
+    """Sparse Gaussian noise: ``k`` non-zero noise entries per member and output row
+    (reference ``README.md:12,29-30``; the reference snapshot ships no source for it).
+
+    ``noise_indices`` is ``(directions, out, k)`` int32, ``weight_noise`` ``(directions, out, k)``
+    with standard deviation ``noise_scale * sqrt(in / k)`` so that the per-row noise energy
+    matches the dense layer.  Forward and update equal :class:`PerturbedLinear` on the
+    densified noise."""
+
+    def __init__(self, in_features, out_features, directions, bias=True, antithetic=False, options={}, k=1):
+        nn.Linear.__init__(self, in_features, out_features, bias)
+        self.k = k
+        Perturbed.__init__(self, directions, antithetic, options)
+        if options.get("direct"):
+            raise NotImplementedError("direct storage is not defined for sparse noise")
+
+    def allocate_weight(self):
+        shape = (self.directions, self.out_features, self.k)
+        self.weight_noise = torch.empty(shape, device=self.weight.device, dtype=self.weight.dtype)
+        self.noise_indices = torch.empty(shape, device=self.weight.device, dtype=torch.int32)
+
+    def free_memory(self):
+        Perturbed.free_memory(self)
+        self.noise_indices = None
+
+    def set_noise(self, noise_scale=None):
+        self._prepare_noise(noise_scale)
+        self._fill_normal(self.weight_noise, self.noise_scale * (self.in_features / self.k) ** .5, self.seed, 0)
+        if self.bias is not None:
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+        u = torch.empty(self.noise_indices.shape, device=self.weight.device, dtype=_F32)
+        C.call("nes_fill_uniform", C.ptr(u), u.numel(), 0.0, 1.0, (int(self.seed) * 4 + 2) & (2 ** 64 - 1), 0, C.stream())
+        self.noise_indices = (u * self.in_features).clamp_(max=self.in_features - 1).to(torch.int32)
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x, lead = self._flatten_rows(input)
+        R = self._repeats(x.shape[0])
+        val = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        idx = C.require_cuda(self.noise_indices, "noise_indices", torch.int32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        C.call("nes_sparse_perturbed_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+               C.ptr(idx), C.ptr(val), C.ptr(beta), C.ptr(y), self.directions, R, self.in_features,
+               self.out_features, self.k, 1 if self.antithetic else 0, C.stream())
+        return y.view(*lead, self.out_features)
+
+    def _weight_grad_regularised(self, weights, l1, l2):
+        val = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        idx = C.require_cuda(self.noise_indices, "noise_indices", torch.int32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        grad = torch.empty_like(self.weight)
+        C.call("nes_sparse_perturbed_update", C.ptr(idx), C.ptr(val), C.ptr(weights),
+               C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), self.directions,
+               self.in_features, self.out_features, self.k, float(l1), float(l2), C.stream())
+        return grad
+
+    def weight_grad(self, weights):
+        return self._weight_grad_regularised(weights, 0, 0)
+
+
+class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
+    """``y = x W^T + b + s * (gather_out(gather_in(x) eps^T) + beta_d)`` (reference
+    ``base.py:447-518``).  ``options["combined"]`` selects the same fused kernels: the
+    reference's combined branches are algebraic re-arrangements of this sum (its combined
+    input branch additionally drops ``beta`` and the antithetic sign, ``base.py:458-464``;
+    that omission is not reproduced)."""
+
+    def __init__(self, in_features, out_features, directions, bias=True, antithetic=False, options={},
+                 permutation="auto", in_sparsity=0, out_sparsity=0):
+        nn.Linear.__init__(self, in_features, out_features, bias)
+        Permuted.__init__(self, in_features, out_features, directions, antithetic=antithetic, options=options,
+                          permutation=permutation, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x, lead = self._flatten_rows(input)
+        R = self._repeats(x.shape[0])
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        pin, pout = self._perms()
+        y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        nbytes = C.call("nes_permuted_linear_fwd_scratch_bytes", self.directions, R, self.out_sparsity)
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_permuted_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, self.in_features,
+               self.out_features, self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0,
+               C.ptr(buf), nbytes, C.stream())
+        return y.view(*lead, self.out_features)
+
+
+class _ConvMixin:
+    def _geometry(self, x):
+        if self.groups != 1:
+            raise NotImplementedError("groups != 1 is not supported")
+        if x.dim() != 4 or x.shape[1] != self.in_channels:
+            raise RuntimeError("expected (B, %d, H, W) input, got %s" % (self.in_channels, tuple(x.shape)))
+        if self.padding_mode != "zeros":
+            x = F.pad(x, self._reversed_padding_repeated_twice, mode=self.padding_mode).contiguous()
+            pad = (0, 0)
+        else:
+            pad = _pair(self.padding)
+        kh, kw = self.kernel_size
+        sh, sw = _pair(self.stride)
+        dh, dw = _pair(self.dilation)
+        H, W = x.shape[-2:]
+        Ho = (H + 2 * pad[0] - dh * (kh - 1) - 1) // sh + 1
+        Wo = (W + 2 * pad[1] - dw * (kw - 1) - 1) // sw + 1
+        geom = (self.in_channels, H, W, self.out_channels, kh, kw, sh, sw, pad[0], pad[1], dh, dw)
+        return x, geom, (Ho, Wo)
+
+    def _plain_forward(self, input):
+        x = C.require_cuda(input, "input", _F32)
+        x, geom, (Ho, Wo) = self._geometry(x)
+        y = torch.empty((x.shape[0], self.out_channels, Ho, Wo), device=x.device, dtype=_F32)
+        C.call("nes_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(y),
+               x.shape[0], *geom, C.stream())
+        return y
+
+    def _dense_forward(self, x, geom, out_hw, noise):
+        R = self._repeats(x.shape[0])
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
+        C.call("nes_perturbed_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+               C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, *geom,
+               1 if self.antithetic else 0, C.stream())
+        return y
+
+
+class PerturbedConv2d(nn.Conv2d, _ConvMixin, Perturbed):
+    """Per member a convolution with ``weight + s * noise[d]`` (reference ``base.py:384-425``,
+    which evaluates the noise term as one grouped convolution with ``groups * directions``
+    groups)."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, directions, stride=1, padding=0, dilation=1,
+                 groups=1, bias=True, antithetic=False, options={}, padding_mode='zeros'):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups,
+                           bias, padding_mode)
+        Perturbed.__init__(self, directions, antithetic, options)
+        if options.get("direct"):
+            raise NotImplementedError("direct storage for PerturbedConv2d drops the bias noise in the reference "
+                                      "(modules/base.py:401-409) and is not provided")
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x = C.require_cuda(input, "input", _F32)
+        x, geom, out_hw = self._geometry(x)
+        return self._dense_forward(x, geom, out_hw, C.require_cuda(self.weight_noise, "weight_noise", _F32))
+
+
+class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
+    """Shared noise filter with per-member channel permutations (reference ``base.py:521-599``).
+    Evaluated as one convolution per member with the effective filter
+    ``W + s * eps[pi_out[d, k], pi_in^-1[d, c]]`` formed inside the kernel."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, directions, stride=1, padding=0, dilation=1,
+                 groups=1, bias=True, antithetic=False, options={}, padding_mode='zeros', permutation="auto",
+                 in_sparsity=0, out_sparsity=0):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups,
+                           bias, padding_mode)
+        Permuted.__init__(self, in_channels, out_channels, directions, antithetic=antithetic, options=options,
+                          permutation=permutation, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
+
+    def _dense_noise(self, eps, pin, pout):
+        ksize = self.kernel_size[0] * self.kernel_size[1]
+        E = torch.empty((self.directions, self.out_channels, self.in_channels) + tuple(self.kernel_size),
+                        device=eps.device, dtype=_F32)
+        C.call("nes_permuted_dense_noise", C.ptr(eps), C.ptr(pin), C.ptr(pout), C.ptr(E), self.directions,
+               self.in_channels, self.out_channels, self.in_sparsity, self.out_sparsity, ksize, C.stream())
+        return E
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x = C.require_cuda(input, "input", _F32)
+        x, geom, out_hw = self._geometry(x)
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        pin, pout = self._perms()
+        if pin is not None and self.options.get("allow_repeats"):
+            # a repeated input channel makes the member's filter a sum of noise columns
+            return self._dense_forward(x, geom, out_hw, self._dense_noise(eps, pin, pout))
+        R = self._repeats(x.shape[0])
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
+        nbytes = C.call("nes_permuted_conv2d_fwd_scratch_bytes", self.directions, self.in_channels, self.out_channels)
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_permuted_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, *geom,
+               self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+        return y

@@ -1,0 +1,138 @@
+// On-device noise set-up: Gaussian / uniform fills and per-member permutations (Philox-4x32-10).
+#include "common.cuh"
+
+namespace nes {
+
+__global__ void fill_normal_kernel(float* __restrict__ out, int64_t n, float mean, float std,
+                                   uint64_t seed, uint64_t offset) {
+  const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;   // group of four outputs
+  if (q * 4 >= n) return;
+  const uint64_t ctr = offset + uint64_t(q);
+  uint32_t r[4];
+  Philox ph(seed);
+  ph(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 0u, r);
+  float z[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {     // Box-Muller on two uniform pairs
+    const float u1 = u32_to_unit(r[2 * h]);
+    const float u2 = u32_to_unit(r[2 * h + 1]);
+    const float rad = sqrtf(-2.0f * logf(u1));
+    float s, c;
+    sincospif(2.0f * u2, &s, &c);
+    z[2 * h] = rad * c;
+    z[2 * h + 1] = rad * s;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (q * 4 + j < n) out[q * 4 + j] = fmaf(std, z[j], mean);
+}
+
+__global__ void fill_uniform_kernel(float* __restrict__ out, int64_t n, float lo, float hi,
+                                    uint64_t seed, uint64_t offset) {
+  const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (q * 4 >= n) return;
+  const uint64_t ctr = offset + uint64_t(q);
+  uint32_t r[4];
+  Philox ph(seed);
+  ph(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 2u, r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (q * 4 + j < n) out[q * 4 + j] = fmaf(hi - lo, u32_to_unit(r[j]), lo);
+}
+
+// One block per member: draw a 32-bit key per position, sort (key, position) pairs with a
+// bitonic network in shared memory, emit the positions of the `keep` smallest keys.  Ties in
+// the key are broken by position (probability ~ n^2 / 2^33 per member).
+__global__ void sample_permutations_kernel(int16_t* __restrict__ out, int n, int n_pow2, int keep, uint64_t seed) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  uint64_t* keys = reinterpret_cast<uint64_t*>(dyn);
+  const int64_t d = blockIdx.x;
+  Philox ph(seed);
+  for (int q = threadIdx.x; q * 4 < n_pow2; q += blockDim.x) {
+    uint32_t r[4];
+    ph(uint32_t(q), uint32_t(d), uint32_t(uint64_t(d) >> 32), 1u, r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = q * 4 + j;
+      if (i < n_pow2) keys[i] = (i < n) ? ((uint64_t(r[j]) << 16) | uint64_t(i)) : ~uint64_t(0);
+    }
+  }
+  __syncthreads();
+  for (int size = 2; size <= n_pow2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < n_pow2 / 2; i += blockDim.x) {
+        const int lo = 2 * i - (i & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = ((lo & size) == 0);
+        const uint64_t a = keys[lo], b = keys[hi];
+        if ((a > b) == up) { keys[lo] = b; keys[hi] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < keep; i += blockDim.x) out[d * keep + i] = int16_t(keys[i] & 0xFFFFu);
+}
+
+__global__ void sample_indices_kernel(int16_t* __restrict__ out, int64_t total, int n, uint64_t seed) {
+  const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (q * 4 >= total) return;
+  uint32_t r[4];
+  Philox ph(seed);
+  ph(uint32_t(q), uint32_t(uint64_t(q) >> 32), 0u, 3u, r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (q * 4 + j < total) out[q * 4 + j] = int16_t((uint64_t(r[j]) * uint64_t(n)) >> 32);
+}
+
+}  // namespace nes
+
+using namespace nes;
+
+extern "C" int nes_fill_normal(float* out, int64_t n, float mean, float std, uint64_t seed, uint64_t offset,
+                               nes_stream_t stream) {
+  NES_REQUIRE(n >= 0, NES_ERR_BAD_ARG, "fill_normal: negative extent");
+  if (n == 0) return NES_OK;
+  NES_REQUIRE(out, NES_ERR_BAD_ARG, "fill_normal: null pointer");
+  const int64_t groups = ceil_div<int64_t>(n, 4);
+  NES_REQUIRE(ceil_div<int64_t>(groups, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "fill_normal: n too large");
+  fill_normal_kernel<<<(unsigned)ceil_div<int64_t>(groups, 256), 256, 0, as_stream(stream)>>>(out, n, mean, std, seed, offset);
+  return check_launch("fill_normal");
+}
+
+extern "C" int nes_fill_uniform(float* out, int64_t n, float lo, float hi, uint64_t seed, uint64_t offset,
+                                nes_stream_t stream) {
+  NES_REQUIRE(n >= 0, NES_ERR_BAD_ARG, "fill_uniform: negative extent");
+  if (n == 0) return NES_OK;
+  NES_REQUIRE(out, NES_ERR_BAD_ARG, "fill_uniform: null pointer");
+  const int64_t groups = ceil_div<int64_t>(n, 4);
+  NES_REQUIRE(ceil_div<int64_t>(groups, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "fill_uniform: n too large");
+  fill_uniform_kernel<<<(unsigned)ceil_div<int64_t>(groups, 256), 256, 0, as_stream(stream)>>>(out, n, lo, hi, seed, offset);
+  return check_launch("fill_uniform");
+}
+
+extern "C" int nes_sample_permutations(int16_t* out, int64_t D, int n, int keep, int with_replacement,
+                                       uint64_t seed, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && n > 0 && keep >= 0, NES_ERR_BAD_ARG, "sample_permutations: bad extent");
+  NES_REQUIRE(n <= 32767, NES_ERR_UNSUPPORTED, "sample_permutations: n=%d does not fit int16", n);
+  if (D == 0 || keep == 0) return NES_OK;
+  NES_REQUIRE(out, NES_ERR_BAD_ARG, "sample_permutations: null pointer");
+  cudaStream_t st = as_stream(stream);
+  if (with_replacement) {
+    const int64_t total = D * keep;
+    sample_indices_kernel<<<(unsigned)ceil_div<int64_t>(ceil_div<int64_t>(total, 4), 256), 256, 0, st>>>(out, total, n, seed);
+    return check_launch("sample_permutations(indices)");
+  }
+  NES_REQUIRE(keep <= n, NES_ERR_BAD_ARG, "sample_permutations: keep > n without replacement");
+  NES_REQUIRE(n <= 16384, NES_ERR_UNSUPPORTED, "sample_permutations: n=%d > 16384 not implemented", n);
+  NES_REQUIRE(D <= INT32_MAX, NES_ERR_UNSUPPORTED, "sample_permutations: D too large");
+  int n_pow2 = 1;
+  while (n_pow2 < n) n_pow2 <<= 1;
+  const size_t smem = size_t(n_pow2) * sizeof(uint64_t);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(sample_permutations_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(NES_ERR_UNSUPPORTED, "sample_permutations: %zu B of shared memory refused", smem);
+  }
+  const int threads = n_pow2 / 2 < 32 ? 32 : (n_pow2 / 2 > 512 ? 512 : n_pow2 / 2);
+  sample_permutations_kernel<<<(unsigned)D, threads, smem, st>>>(out, n, n_pow2, keep, seed);
+  return check_launch("sample_permutations");
+}

@@ -1,0 +1,309 @@
+// Fitness-weighted noise reductions that form the weight update.
+#include "common.cuh"
+
+namespace nes {
+
+// ---- sum_d w[d] * noise[d, :] : dense per-member noise ----------------------------------
+//
+// Streams the (D, n) noise once (HBM-bound).  A thread owns one 128-bit column group and walks
+// a slice of the members with eight independent evict-first loads in flight.  The member
+// range is split over blockIdx.y so that the grid fills the machine with an even number of
+// waves; each split writes an fp32 partial row to scratch and a second kernel adds the
+// partials in split order (deterministic) together with the l1 / l2 terms.
+constexpr int UPD_THREADS = 256;
+constexpr int UPD_BLOCKS_PER_SM = 4;
+constexpr int UPD_MAX_SPLITS = 16;
+
+template <bool VEC>
+__global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise_sum_kernel(
+    const float* __restrict__ noise, const float* __restrict__ w, float* __restrict__ out,
+    int64_t D, int64_t n, int64_t d_per_split) {
+  const int64_t d0 = blockIdx.y * d_per_split;
+  const int64_t d1 = (d0 + d_per_split < D) ? d0 + d_per_split : D;
+  float* dst = out + blockIdx.y * n;
+  if (VEC) {
+    const int64_t i4 = int64_t(blockIdx.x) * UPD_THREADS + threadIdx.x;
+    if (i4 * 4 >= n) return;
+    const float4* src = reinterpret_cast<const float4*>(noise) + i4;
+    const int64_t stride = n / 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int64_t d = d0;
+    for (; d + 8 <= d1; d += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcs(src + (d + u) * stride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float wd = __ldg(w + d + u);
+        acc.x = fmaf(wd, v[u].x, acc.x); acc.y = fmaf(wd, v[u].y, acc.y);
+        acc.z = fmaf(wd, v[u].z, acc.z); acc.w = fmaf(wd, v[u].w, acc.w);
+      }
+    }
+    for (; d < d1; ++d) {
+      const float4 v = __ldcs(src + d * stride);
+      const float wd = __ldg(w + d);
+      acc.x = fmaf(wd, v.x, acc.x); acc.y = fmaf(wd, v.y, acc.y);
+      acc.z = fmaf(wd, v.z, acc.z); acc.w = fmaf(wd, v.w, acc.w);
+    }
+    reinterpret_cast<float4*>(dst)[i4] = acc;
+  } else {
+    const int64_t i = int64_t(blockIdx.x) * UPD_THREADS + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), __ldcs(noise + d * n + i), acc);
+    dst[i] = acc;
+  }
+}
+
+// grad = sum_s partial[s] (+ l1 sign(W) + l2 W); splits == 0 means "grad already holds the sum"
+__global__ void finish_update_kernel(const float* __restrict__ partial, int splits, const float* __restrict__ weight,
+                                     float* __restrict__ grad, int64_t n, float l1, float l2) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = splits ? 0.f : grad[i];
+  for (int s = 0; s < splits; ++s) acc += partial[s * n + i];
+  if (weight) {
+    const float wv = weight[i];
+    if (l1 != 0.f) acc += l1 * ((wv > 0.f) - (wv < 0.f));
+    if (l2 != 0.f) acc += l2 * wv;
+  }
+  grad[i] = acc;
+}
+
+struct UpdatePlan { int splits; int64_t d_per_split; int64_t bx; bool vec; };
+
+static UpdatePlan plan_update(int64_t D, int64_t n, bool vec) {
+  UpdatePlan p;
+  p.vec = vec;
+  const int64_t cols = vec ? n / 4 : n;
+  p.bx = ceil_div<int64_t>(cols, UPD_THREADS);
+  const int64_t slots = int64_t(sm_count()) * UPD_BLOCKS_PER_SM;
+  int best = 1;
+  if (p.bx < 4 * slots) {
+    // smallest split count that gives at least two waves with a last wave >= 95 % full;
+    // failing that, the candidate with the fullest last wave
+    const int64_t cap = D / 8;
+    const int max_s = int(cap > UPD_MAX_SPLITS ? UPD_MAX_SPLITS : (cap > 1 ? cap : 1));
+    double best_score = -1.0;
+    for (int s = 1; s <= max_s; ++s) {
+      const int64_t items = p.bx * s;
+      const double eff = double(items) / double(ceil_div(items, slots) * slots);
+      const bool enough = items >= 2 * slots;
+      if (enough && eff >= 0.95) { best = s; break; }
+      const double score = (enough ? 1.0 : 0.0) + eff;
+      if (score > best_score) { best_score = score; best = s; }
+    }
+  }
+  p.splits = best;
+  p.d_per_split = ceil_div<int64_t>(D, best);
+  p.splits = int(ceil_div<int64_t>(D, p.d_per_split));
+  return p;
+}
+
+// ---- shared noise + permutations ---------------------------------------------------------
+
+// out-only: G[k, s] += w_d for s = pout[d,k] < out_sp;  in-only: H[j, pin[d,j]] += w_d
+__global__ void permutation_histogram_kernel(const int16_t* __restrict__ perm, const float* __restrict__ w,
+                                             float* __restrict__ hist, int64_t D, int cols, int hist_cols,
+                                             int limit) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= D * cols) return;
+  const int64_t d = e / cols;
+  const int c = int(e - d * cols);
+  const int s = perm[e];
+  if (s < limit) atomicAdd(hist + size_t(c) * hist_cols + s, __ldg(w + d));
+}
+
+// grad[k,m,t] = sum_s G[k,s] * eps[s,m,t]     (out-only; eps has `in` input channels)
+__global__ void grad_from_out_hist_kernel(const float* __restrict__ G, const float* __restrict__ eps,
+                                          float* __restrict__ grad, int out, int out_sp, int64_t inner) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;   // over inner = in*ksz
+  const int k = blockIdx.y;
+  if (e >= inner) return;
+  const float* g = G + size_t(k) * out_sp;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int s = 0;
+  for (; s + 4 <= out_sp; s += 4) {
+    a0 = fmaf(__ldg(g + s), __ldg(eps + (s + 0) * inner + e), a0);
+    a1 = fmaf(__ldg(g + s + 1), __ldg(eps + (s + 1) * inner + e), a1);
+    a2 = fmaf(__ldg(g + s + 2), __ldg(eps + (s + 2) * inner + e), a2);
+    a3 = fmaf(__ldg(g + s + 3), __ldg(eps + (s + 3) * inner + e), a3);
+  }
+  for (; s < out_sp; ++s) a0 = fmaf(__ldg(g + s), __ldg(eps + s * inner + e), a0);
+  grad[size_t(k) * inner + e] = (a0 + a1) + (a2 + a3);
+}
+
+// grad[k,m,t] = sum_j eps[k,j,t] * H[j,m]      (in-only)
+__global__ void grad_from_in_hist_kernel(const float* __restrict__ H, const float* __restrict__ eps,
+                                         float* __restrict__ grad, int in, int in_sp, int ksz) {
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y / ksz, t = blockIdx.y - k * ksz;
+  if (m >= in) return;
+  const float* er = eps + size_t(k) * in_sp * ksz + t;
+  float a0 = 0.f, a1 = 0.f;
+  int j = 0;
+  for (; j + 2 <= in_sp; j += 2) {
+    a0 = fmaf(__ldg(er + size_t(j) * ksz), __ldg(H + size_t(j) * in + m), a0);
+    a1 = fmaf(__ldg(er + size_t(j + 1) * ksz), __ldg(H + size_t(j + 1) * in + m), a1);
+  }
+  for (; j < in_sp; ++j) a0 = fmaf(__ldg(er + size_t(j) * ksz), __ldg(H + size_t(j) * in + m), a0);
+  grad[(size_t(k) * in + m) * ksz + t] = a0 + a1;
+}
+
+// both: grad[k, pin[d,j], t] += w_d * eps[pout[d,k], j, t]
+__global__ void grad_two_sided_kernel(const float* __restrict__ eps, const float* __restrict__ w,
+                                      const int16_t* __restrict__ pin, const int16_t* __restrict__ pout,
+                                      float* __restrict__ grad, int64_t D, int in, int out, int in_sp,
+                                      int out_sp, int ksz) {
+  const int64_t per_member = int64_t(out) * in_sp * ksz;
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= D * per_member) return;
+  const int64_t d = e / per_member;
+  int64_t r = e - d * per_member;
+  const int k = int(r / (int64_t(in_sp) * ksz));
+  r -= int64_t(k) * in_sp * ksz;
+  const int j = int(r / ksz), t = int(r - int64_t(j) * ksz);
+  const int so = pout[d * out + k];
+  if (so >= out_sp) return;
+  const int m = pin[d * in_sp + j];
+  atomicAdd(grad + (size_t(k) * in + m) * ksz + t, __ldg(w + d) * __ldg(eps + (size_t(so) * in_sp + j) * ksz + t));
+}
+
+// sparse: grad[o, idx[d,o,t]] += w_d * val[d,o,t]
+__global__ void grad_sparse_kernel(const int32_t* __restrict__ idx, const float* __restrict__ val,
+                                   const float* __restrict__ w, float* __restrict__ grad, int64_t D,
+                                   int64_t in, int64_t out, int k) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= D * out * k) return;
+  const int64_t d = e / (out * k);
+  const int64_t o = (e / k) % out;
+  atomicAdd(grad + o * in + idx[e], __ldg(w + d) * __ldg(val + e));
+}
+
+static int finish(const float* partial, int splits, const float* weight, float* grad, int64_t n, float l1,
+                  float l2, cudaStream_t st, const char* what) {
+  if (splits == 0 && (weight == nullptr || (l1 == 0.f && l2 == 0.f))) return NES_OK;
+  finish_update_kernel<<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, st>>>(partial, splits, weight, grad, n, l1, l2);
+  return check_launch(what);
+}
+
+}  // namespace nes
+
+using namespace nes;
+
+extern "C" int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n) {
+  if (D <= 0 || n <= 0) return 0;
+  const UpdatePlan p = plan_update(D, n, n % 4 == 0);
+  return (p.splits > 1 ? p.splits : 0) * n * (int64_t)sizeof(float);
+}
+
+extern "C" int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
+                                    int64_t D, int64_t n, float l1, float l2,
+                                    void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && n >= 0, NES_ERR_BAD_ARG, "perturbed_update: negative extent");
+  if (n == 0) return NES_OK;
+  NES_REQUIRE(grad && (D == 0 || (noise && w)), NES_ERR_BAD_ARG, "perturbed_update: null pointer");
+  NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "perturbed_update: l1/l2 given without weight");
+  cudaStream_t st = as_stream(stream);
+  if (D == 0) {
+    cudaMemsetAsync(grad, 0, n * sizeof(float), st);
+    return finish(nullptr, 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
+  }
+  const bool vec = (n % 4 == 0) && aligned16(noise) && aligned16(grad) && aligned16(scratch);
+  const UpdatePlan p = plan_update(D, n, vec);
+  NES_REQUIRE(p.bx <= INT32_MAX, NES_ERR_UNSUPPORTED, "perturbed_update: n too large");
+  float* dst = grad;
+  if (p.splits > 1) {
+    NES_REQUIRE(scratch && scratch_bytes >= int64_t(p.splits) * n * (int64_t)sizeof(float), NES_ERR_SCRATCH,
+                "perturbed_update: scratch needs %lld bytes", (long long)(int64_t(p.splits) * n * sizeof(float)));
+    dst = static_cast<float*>(scratch);
+  }
+  dim3 grid((unsigned)p.bx, (unsigned)p.splits);
+  if (vec) weighted_noise_sum_kernel<true><<<grid, UPD_THREADS, 0, st>>>(noise, w, dst, D, n, p.d_per_split);
+  else weighted_noise_sum_kernel<false><<<grid, UPD_THREADS, 0, st>>>(noise, w, dst, D, n, p.d_per_split);
+  int rc = check_launch("perturbed_update");
+  if (rc != NES_OK) return rc;
+  return finish(dst, p.splits > 1 ? p.splits : 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
+}
+
+extern "C" int64_t nes_permuted_update_scratch_bytes(int in, int out, int in_sp, int out_sp) {
+  const int64_t g = int64_t(out) * out_sp, h = int64_t(in_sp) * in;
+  return (g > h ? g : h) * (int64_t)sizeof(float);
+}
+
+extern "C" int nes_permuted_update(const float* eps, const float* w, const int16_t* pin, const int16_t* pout,
+                                   const float* weight, float* grad, float* perm_weights_out,
+                                   int64_t D, int in, int out, int in_sp, int out_sp, int ksize,
+                                   float l1, float l2, void* scratch, int64_t scratch_bytes,
+                                   nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && in > 0 && out > 0 && in_sp > 0 && out_sp > 0 && ksize > 0, NES_ERR_BAD_ARG,
+              "permuted_update: bad extent");
+  NES_REQUIRE(eps && grad && (D == 0 || w) && (pin || pout), NES_ERR_BAD_ARG, "permuted_update: null pointer");
+  NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "permuted_update: l1/l2 given without weight");
+  NES_REQUIRE(out_sp <= out && (pin || in_sp == in), NES_ERR_BAD_ARG, "permuted_update: sparsity exceeds degree");
+  NES_REQUIRE(out <= 65535 && int64_t(out) * ksize <= 65535, NES_ERR_UNSUPPORTED, "permuted_update: out*ksize > 65535");
+  cudaStream_t st = as_stream(stream);
+  const int64_t n = int64_t(out) * in * ksize;
+  int rc;
+  if (pin && pout) {
+    cudaMemsetAsync(grad, 0, n * sizeof(float), st);
+    const int64_t total = D * out * in_sp * ksize;
+    if (total > 0) {
+      NES_REQUIRE(ceil_div<int64_t>(total, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "permuted_update: two-sided problem too large");
+      grad_two_sided_kernel<<<(unsigned)ceil_div<int64_t>(total, 256), 256, 0, st>>>(eps, w, pin, pout, grad, D, in, out, in_sp, out_sp, ksize);
+      rc = check_launch("permuted_update(two-sided)");
+      if (rc != NES_OK) return rc;
+    }
+    return finish(nullptr, 0, weight, grad, n, l1, l2, st, "permuted_update(finish)");
+  }
+  NES_REQUIRE(scratch && scratch_bytes >= nes_permuted_update_scratch_bytes(in, out, in_sp, out_sp), NES_ERR_SCRATCH,
+              "permuted_update: scratch needs %lld bytes", (long long)nes_permuted_update_scratch_bytes(in, out, in_sp, out_sp));
+  float* hist = static_cast<float*>(scratch);
+  if (pout) {
+    const int64_t hn = int64_t(out) * out_sp;
+    cudaMemsetAsync(hist, 0, hn * sizeof(float), st);
+    if (D > 0) {
+      permutation_histogram_kernel<<<(unsigned)ceil_div<int64_t>(D * out, 256), 256, 0, st>>>(pout, w, hist, D, out, out_sp, out_sp);
+      rc = check_launch("permuted_update(histogram)");
+      if (rc != NES_OK) return rc;
+    }
+    const int64_t inner = int64_t(in) * ksize;
+    dim3 grid((unsigned)ceil_div<int64_t>(inner, 256), (unsigned)out);
+    grad_from_out_hist_kernel<<<grid, 256, 0, st>>>(hist, eps, grad, out, out_sp, inner);
+    rc = check_launch("permuted_update(grad)");
+    if (rc != NES_OK) return rc;
+    if (perm_weights_out) cudaMemcpyAsync(perm_weights_out, hist, hn * sizeof(float), cudaMemcpyDeviceToDevice, st);
+  } else {
+    const int64_t hn = int64_t(in_sp) * in;
+    cudaMemsetAsync(hist, 0, hn * sizeof(float), st);
+    if (D > 0) {
+      permutation_histogram_kernel<<<(unsigned)ceil_div<int64_t>(D * in_sp, 256), 256, 0, st>>>(pin, w, hist, D, in_sp, in, in);
+      rc = check_launch("permuted_update(histogram)");
+      if (rc != NES_OK) return rc;
+    }
+    dim3 grid((unsigned)ceil_div(in, 128), (unsigned)(out * ksize));
+    grad_from_in_hist_kernel<<<grid, 128, 0, st>>>(hist, eps, grad, in, in_sp, ksize);
+    rc = check_launch("permuted_update(grad)");
+    if (rc != NES_OK) return rc;
+    if (perm_weights_out) cudaMemcpyAsync(perm_weights_out, hist, hn * sizeof(float), cudaMemcpyDeviceToDevice, st);
+  }
+  return finish(nullptr, 0, weight, grad, n, l1, l2, st, "permuted_update(finish)");
+}
+
+extern "C" int nes_sparse_perturbed_update(const int32_t* idx, const float* val, const float* w,
+                                           const float* weight, float* grad, int64_t D, int64_t in,
+                                           int64_t out, int k, float l1, float l2, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && in > 0 && out > 0 && k >= 0, NES_ERR_BAD_ARG, "sparse_perturbed_update: bad extent");
+  NES_REQUIRE(grad && (D * k == 0 || (idx && val && w)), NES_ERR_BAD_ARG, "sparse_perturbed_update: null pointer");
+  NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "sparse_perturbed_update: l1/l2 given without weight");
+  cudaStream_t st = as_stream(stream);
+  cudaMemsetAsync(grad, 0, out * in * sizeof(float), st);
+  const int64_t total = D * out * k;
+  if (total > 0) {
+    NES_REQUIRE(ceil_div<int64_t>(total, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "sparse_perturbed_update: too large");
+    grad_sparse_kernel<<<(unsigned)ceil_div<int64_t>(total, 256), 256, 0, st>>>(idx, val, w, grad, D, in, out, k);
+    int rc = check_launch("sparse_perturbed_update");
+    if (rc != NES_OK) return rc;
+  }
+  return finish(nullptr, 0, weight, grad, out * in, l1, l2, st, "sparse_perturbed_update(finish)");
+}

@@ -1,0 +1,87 @@
+"""Sharding a population over the GPUs of one box: one process per GPU, members split in
+contiguous slices, no communication in the forward pass, one all-reduce of the concatenated
+update per step (and one all-gather of fitness values when the fitness shaping is global).
+
+The reference is single-GPU and has no counterpart; this is the data-parallel split its
+member-independent forward (``modules/base.py:355-381,487-508``) and member-summed update
+(``modules/base.py:110-138``) admit.  Works on any ``torch.distributed`` backend: NCCL over
+NVLink on GPUs, gloo on CPU for tests of the host logic.
+"""
+import torch
+import torch.distributed as dist
+
+
+def member_slice(directions, rank, world_size):
+    """Contiguous slice [lo, hi) of the member index owned by ``rank``; sizes differ by at most one."""
+    if world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError("bad rank/world_size")
+    base, extra = divmod(directions, world_size)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def local_rows(batch, directions, rank, world_size):
+    """Rows of a global batch (layout ``b = r * directions + d``) that belong to ``rank``'s
+    members, as a (R, local_D, ...) -> (R * local_D, ...) re-batched tensor with the same layout
+    for ``local_D`` directions."""
+    lo, hi = member_slice(directions, rank, world_size)
+    R = batch.shape[0] // directions
+    return batch.view(R, directions, *batch.shape[1:])[:, lo:hi].reshape(R * (hi - lo), *batch.shape[1:])
+
+
+def gather_fitness(local_fitness, group=None):
+    """All ranks' per-member fitness, concatenated in rank order (ranks may own unequal slices)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return local_fitness
+    world = dist.get_world_size(group)
+    sizes = [torch.zeros(1, dtype=torch.int64, device=local_fitness.device) for _ in range(world)]
+    dist.all_gather(sizes, torch.tensor([local_fitness.numel()], dtype=torch.int64, device=local_fitness.device),
+                    group=group)
+    n_max = int(max(s.item() for s in sizes))
+    padded = torch.zeros(n_max, dtype=local_fitness.dtype, device=local_fitness.device)
+    padded[:local_fitness.numel()] = local_fitness.flatten()
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p[:int(s.item())] for p, s in zip(parts, sizes)])
+
+
+class UpdateBucket:
+    """One flat fp32 buffer that holds every partial gradient of a step, so that a step costs a
+    single all-reduce whatever the number of layers."""
+
+    def __init__(self, tensors):
+        self.shapes = [tuple(t.shape) for t in tensors]
+        self.sizes = [t.numel() for t in tensors]
+        ref = tensors[0]
+        self.flat = torch.empty(sum(self.sizes), dtype=torch.float32, device=ref.device)
+
+    def views(self):
+        out, off = [], 0
+        for shape, n in zip(self.shapes, self.sizes):
+            out.append(self.flat[off:off + n].view(shape))
+            off += n
+        return out
+
+    def pack(self, tensors):
+        for v, t in zip(self.views(), tensors):
+            v.copy_(t)
+
+    def all_reduce(self, group=None):
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group)
+        return self.views()
+
+
+def all_reduce_grads(parameters, bucket=None, group=None):
+    """Sum ``.grad`` of the given parameters over the ranks through one bucket; every rank ends
+    with the full-population update and applies the same optimiser step."""
+    params = [p for p in parameters if p.grad is not None]
+    if not params:
+        return bucket
+    grads = [p.grad for p in params]
+    if bucket is None or bucket.sizes != [g.numel() for g in grads]:
+        bucket = UpdateBucket(grads)
+    bucket.pack(grads)
+    for p, v in zip(params, bucket.all_reduce(group)):
+        p.grad.copy_(v)
+    return bucket
