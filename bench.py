@@ -53,7 +53,8 @@ class ClockSampler:
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
-        self.lines = []
+        self.lines = []          # (host time when read, csv line)
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -67,7 +68,18 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def wait_first_sample(self, timeout=3.0):
+        t0 = time.time()
+        while self.proc is not None and not self.lines and time.time() - t0 < timeout:
+            time.sleep(0.02)
+
+    def begin(self):
+        self.t_begin = time.time()
+
+    def end(self):
+        self.t_end = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -79,7 +91,12 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = [l for t, l in self.lines if self.t_begin is not None and self.t_begin <= t <= (self.t_end or t) + 0.1]
+        window = "timed region"
+        if not inside:
+            inside = [l for _, l in self.lines]
+            window = "whole run (timed region shorter than the sampling period)"
+        for line in inside:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -91,7 +108,8 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "window": window,
+                "reasons": sorted(reasons)}
 
 
 # ---------------------------------------------------------------------------------- workloads
@@ -111,7 +129,9 @@ class PerturbedLinear1024(Workload):
     name = "perturbed_linear_1024"
     D, R, n = 1024, 2, 1024
 
-    def __init__(self):
+    def __init__(self, members=None):
+        if members:
+            self.D = members        # reduced member count: profiling captures only
         self.units_per_step = self.D * self.R
         self.resident_bytes = self.D * self.n * self.n * 4
 
@@ -553,7 +573,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload](args.members) if args.members else WORKLOADS[args.workload]()
     wl.setup(dev, rank, world)
     peaks = measured_peaks()
     flush = None
@@ -567,20 +587,24 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         wl.step(null_mark)
         if flush is not None:
             flush.fill_(1.0)
     barrier()
+    if sampler:
+        sampler.wait_first_sample()
 
     # ---- timed region: exactly K steps, CUDA events on the launching stream
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
     names = []
     events = []
     launches0 = _cabi.lib.nes_launch_count()
     barrier()
+    if sampler:
+        sampler.begin()
     t_wall0 = time.perf_counter()
     for i in range(args.steps):
         ev = [torch.cuda.Event(enable_timing=True)]
@@ -598,6 +622,8 @@ def run_ours(args, rank, world, local_rank):
             flush.fill_(1.0)
     barrier()
     wall = time.perf_counter() - t_wall0
+    if sampler:
+        sampler.end()
     launches = _cabi.lib.nes_launch_count() - launches0
     clocks = sampler.stop() if sampler else None
     step_ms = [ev[0].elapsed_time(ev[-1]) for ev in events]
@@ -652,11 +678,13 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="perturbed_linear_1024", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--members", type=int, default=0,
+                    help="perturbed_linear_1024 only: members per GPU instead of 1024 (small case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
