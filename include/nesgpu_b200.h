@@ -94,6 +94,32 @@ int nes_perturbed_update(const float* noise, const float* w, const float* weight
                          int64_t D, int64_t n, float l1, float l2,
                          void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
+/* nes_perturbed_update for callers that have no workspace to give.  (No counterpart in the
+ * reference: there the reduction is one library GEMV that allocates whatever it likes.)
+ *
+ * Some hosts of this library own no device allocator of their own: a plug-in that is handed
+ * input and output buffers by a runtime with a fixed memory budget, or a step that runs at a
+ * point where the process must not create device memory.  They cannot size and provide the
+ * `scratch` buffer of nes_perturbed_update, so this variant keeps the split partial sums in a
+ * workspace built into the library: NES_NOALLOC_SCRATCH_FLOATS fp32 values (16 MiB) of device
+ * memory that every GPU which loads the library holds until the process exits.  It performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.
+ *
+ *  - Limit: the call fails with NES_ERR_UNSUPPORTED (and says so in nes_last_error) when the
+ *    member split needs more than the built-in workspace, i.e. when
+ *    nes_perturbed_update_scratch_bytes(D, n) > 4 * NES_NOALLOC_SCRATCH_FLOATS
+ *    (D = 1024, n = 1024*1024 is the largest benchmark shape that fits).
+ *  - The first call on each device looks up the workspace address (with that device current);
+ *    make that first call before any stream capture starts.
+ *  - All calls on a device share the one workspace and it keeps the previous call's partial
+ *    sums; every element that is read is rewritten first, so nothing has to start at zero --
+ *    but two calls that overlap on the GPU (different streams, no ordering) race on it.
+ *    Order them, or use nes_perturbed_update with separate buffers.
+ * Arguments and result are those of nes_perturbed_update. */
+#define NES_NOALLOC_SCRATCH_FLOATS 4194304
+int nes_perturbed_update_noalloc(const float* noise, const float* w, const float* weight, float* grad,
+                                 int64_t D, int64_t n, float l1, float l2, nes_stream_t stream);
+
 /* Sparse Gaussian noise ("SparsePerturbedLinear", README.md:12,29-30; the layer has no
  * source in the reference snapshot): k (index,value) pairs per member and output row,
  *   y[b,o] = x[b].weight[o] + bias[o] + s(r) * (sum_t x[b, idx[d,o,t]] * val[d,o,t] + bias_noise[d,o]),

@@ -226,6 +226,53 @@ extern "C" int nes_perturbed_update(const float* noise, const float* w, const fl
   return finish(dst, p.splits > 1 ? p.splits : 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
 }
 
+// ---- the same reduction for callers that cannot supply a workspace -------------------------
+//
+// Built-in workspace for nes_perturbed_update_noalloc: NES_NOALLOC_SCRATCH_FLOATS fp32 values
+// (16 MiB) that every GPU which loads this library keeps until the process exits.  In host code
+// the array's name is only a stand-in for the symbol; the device address is looked up once per
+// device and handed to the kernels as an ordinary pointer.
+static __device__ __align__(256) float g_builtin_update_scratch[NES_NOALLOC_SCRATCH_FLOATS];
+
+static int builtin_update_scratch(float** out) {
+  static float* address_on_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "perturbed_update_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  NES_REQUIRE(dev >= 0 && dev < 64, NES_ERR_UNSUPPORTED, "perturbed_update_noalloc: device index %d out of range", dev);
+  if (address_on_device[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_builtin_update_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(NES_ERR_LAUNCH, "perturbed_update_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    address_on_device[dev] = p;
+  }
+  *out = address_on_device[dev];
+  return NES_OK;
+}
+
+extern "C" int nes_perturbed_update_noalloc(const float* noise, const float* w, const float* weight, float* grad,
+                                            int64_t D, int64_t n, float l1, float l2, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && n >= 0, NES_ERR_BAD_ARG, "perturbed_update_noalloc: negative extent");
+  if (n == 0) return NES_OK;
+  int64_t need_floats = 0;
+  if (D > 0) {
+    const UpdatePlan p = plan_update(D, n, n % 4 == 0);
+    if (p.splits > 1) need_floats = int64_t(p.splits) * n;
+  }
+  NES_REQUIRE(need_floats <= (int64_t)NES_NOALLOC_SCRATCH_FLOATS, NES_ERR_UNSUPPORTED,
+              "perturbed_update_noalloc: D=%lld, n=%lld needs %lld floats of workspace but the built-in one holds %lld; "
+              "use nes_perturbed_update with a caller-owned scratch buffer",
+              (long long)D, (long long)n, (long long)need_floats, (long long)NES_NOALLOC_SCRATCH_FLOATS);
+  float* ws = nullptr;
+  if (need_floats > 0) {
+    int rc = builtin_update_scratch(&ws);
+    if (rc != NES_OK) return rc;
+  }
+  return nes_perturbed_update(noise, w, weight, grad, D, n, l1, l2, ws,
+                              (int64_t)NES_NOALLOC_SCRATCH_FLOATS * (int64_t)sizeof(float), stream);
+}
+
 extern "C" int64_t nes_permuted_update_scratch_bytes(int in, int out, int in_sp, int out_sp) {
   const int64_t g = int64_t(out) * out_sp, h = int64_t(in_sp) * in;
   return (g > h ? g : h) * (int64_t)sizeof(float);
