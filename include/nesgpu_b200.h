@@ -57,6 +57,20 @@ int64_t nes_launch_count(void);
 int nes_linear_fwd(const float* x, const float* weight, const float* bias, float* y,
                    int64_t M, int64_t N, int64_t K, nes_stream_t stream);
 
+/* The same product on the tensor cores (TMA-fed tcgen05.mma, kind::tf32, fp32 accumulation in tensor
+ * memory).  mode 1: operands rounded to TF32 (relative error ~1e-3; for callers that state it);
+ * mode 3: error-compensated 3xTF32 (operands split into tf32 hi + lo parts, three products), fp32-level
+ * accuracy.  K must be a multiple of 4.  `scratch` holds the rounded / split operand copies.
+ * Replaces F.linear at modules/base.py:366,381,488. */
+int64_t nes_linear_fwd_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int mode);
+int nes_linear_fwd_tc(const float* x, const float* weight, const float* bias, float* y,
+                      int64_t M, int64_t N, int64_t K, int mode,
+                      void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+/* Reads (synchronously) the device word in which a tensor-core kernel records that one of its bounded
+ * waits ran out: 0 = none, 1 = producer, 2 = MMA issuer, 3 = epilogue.  Diagnostic; no counterpart in
+ * the reference. */
+int nes_tc_error_flag(int* flag);
+
 /* NCHW convolution, groups == 1, zero padding.  x (B,Cin,H,W), weight (Cout,Cin,kh,kw),
  * y (B,Cout,Ho,Wo).  Replaces F.conv2d at modules/base.py:411,558. */
 int nes_conv2d_fwd(const float* x, const float* weight, const float* bias, float* y,
@@ -68,8 +82,9 @@ int nes_conv2d_fwd(const float* x, const float* weight, const float* bias, float
 /* PerturbedLinear.forward with the perturbed flag set (modules/base.py:355-381):
  *   y[b,o] = x[b].weight[o] + bias[o] + s(r) * (x[b].noise[d,o] + bias_noise[d,o]).
  * x (R*D,in), weight (out,in), noise (D,out,in), bias_noise (D,out) or NULL, y (R*D,out).
- * direct != 0 follows modules/base.py:356-364: noise holds W+E, bias_noise holds b+beta,
- * weight/bias are ignored and no sign is applied. */
+ * direct == 1 follows modules/base.py:356-364: noise holds W+E, bias_noise holds b+beta,
+ * weight/bias are ignored and no sign is applied.  direct == 2: y already holds x.weight^T + bias
+ * (for instance from nes_linear_fwd_tc) and only the per-member term is added to it. */
 int nes_perturbed_linear_fwd(const float* x, const float* weight, const float* bias,
                              const float* noise, const float* bias_noise, float* y,
                              int64_t D, int64_t R, int64_t in, int64_t out,

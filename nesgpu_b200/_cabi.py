@@ -21,6 +21,9 @@ SIGNATURES = {
     "nes_last_error": [],
     "nes_launch_count": [],
     "nes_linear_fwd": [c_ptr] * 4 + [c_i64] * 3 + [c_ptr],
+    "nes_linear_fwd_tc_scratch_bytes": [c_i64, c_i64, c_i64, c_int],
+    "nes_linear_fwd_tc": [c_ptr] * 4 + [c_i64] * 3 + [c_int, c_ptr, c_i64, c_ptr],
+    "nes_tc_error_flag": [c_ptr],
     "nes_conv2d_fwd": [c_ptr] * 4 + [c_i64] + [c_int] * 12 + [c_ptr],
     "nes_perturbed_linear_fwd": [c_ptr] * 6 + [c_i64] * 4 + [c_int] * 2 + [c_ptr],
     "nes_perturbed_conv2d_fwd": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr],
@@ -57,6 +60,7 @@ _RETURNS = {
     "nes_last_error": ctypes.c_char_p,
     "nes_launch_count": c_i64,
     "nes_perturbed_update_scratch_bytes": c_i64,
+    "nes_linear_fwd_tc_scratch_bytes": c_i64,
     "nes_permuted_linear_fwd_scratch_bytes": c_i64,
     "nes_permuted_conv2d_fwd_scratch_bytes": c_i64,
     "nes_permuted_update_scratch_bytes": c_i64,

@@ -229,14 +229,16 @@ extern "C" int nes_perturbed_linear_fwd(const float* x, const float* weight, con
                                         int antithetic, int direct, nes_stream_t stream) {
   NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0, NES_ERR_BAD_ARG, "perturbed_linear_fwd: negative extent");
   if (D == 0 || R == 0 || out == 0) return NES_OK;
-  NES_REQUIRE(x && noise && y && (direct || weight), NES_ERR_BAD_ARG, "perturbed_linear_fwd: null pointer");
+  NES_REQUIRE(x && noise && y && (direct != 0 || weight), NES_ERR_BAD_ARG, "perturbed_linear_fwd: null pointer");
   NES_REQUIRE(D <= 65535, NES_ERR_UNSUPPORTED, "perturbed_linear_fwd: D=%lld > 65535", (long long)D);
   NES_REQUIRE(in <= 48000, NES_ERR_UNSUPPORTED, "perturbed_linear_fwd: in=%lld > 48000", (long long)in);
   cudaStream_t st = as_stream(stream);
-  if (!direct) {
+  NES_REQUIRE(direct >= 0 && direct <= 2, NES_ERR_BAD_ARG, "perturbed_linear_fwd: direct must be 0, 1 or 2");
+  if (direct == 0) {
     int rc = nes_linear_fwd(x, weight, bias, y, D * R, out, in, stream);
     if (rc != NES_OK) return rc;
   }
+  if (direct == 2) direct = 0;   // y already holds x.W^T + bias: only the per-member term is added
   int64_t r0 = 0;
   while (r0 < R) {
     const int64_t left = R - r0;
