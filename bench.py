@@ -117,6 +117,7 @@ class ClockSampler:
 class Workload:
     name = ""
     dtype = "f32"
+    tc = None                   # tensor-core mode override (--tc)
     units_per_step = 0          # member-samples one rank processes per step
     resident_bytes = 0          # working set touched per step (decides whether L2 must be flushed)
 
@@ -145,7 +146,8 @@ class PerturbedLinear1024(Workload):
         from nesgpu_b200 import base, dist as ndist
         self.ndist, self.world = ndist, world
         g = torch.Generator().manual_seed(1002 + rank)
-        self.layer = base.PerturbedLinear(self.n, self.n, self.D, antithetic=True).to(dev)
+        self.layer = base.PerturbedLinear(self.n, self.n, self.D, antithetic=True,
+                                          options={"tc": self.tc or "3xtf32"}).to(dev)
         with torch.no_grad():
             self.layer.weight.copy_(torch.randn(self.n, self.n, generator=g) / self.n ** .5)
             self.layer.bias.zero_()
@@ -343,7 +345,8 @@ class PermutedConv64(Workload):
         from nesgpu_b200 import base, dist as ndist
         self.ndist, self.world = ndist, world
         g = torch.Generator().manual_seed(1003 + rank)
-        self.layer = base.PermutedConv2d(self.c, self.c, 3, self.D, padding=1, out_sparsity=.5).to(dev)
+        self.layer = base.PermutedConv2d(self.c, self.c, 3, self.D, padding=1, out_sparsity=.5,
+                                         options={"tc": self.tc or "fp32"}).to(dev)
         with torch.no_grad():
             self.layer.weight.copy_(torch.randn(self.c, self.c, 3, 3, generator=g) * (2 / 576) ** .5)
             self.layer.bias.zero_()
@@ -574,6 +577,7 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     wl = WORKLOADS[args.workload](args.members) if args.members else WORKLOADS[args.workload]()
+    wl.tc = args.tc
     wl.setup(dev, rank, world)
     peaks = measured_peaks()
     flush = None
@@ -659,7 +663,7 @@ def run_ours(args, rank, world, local_rank):
         line = {"metric": "perturbed-member samples/sec per layer (forward + update)", "value": round(value, 1),
                 "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(world),
+                "dtype": wl.dtype, "data": "synthetic", "config": dict(wl.describe(world), tc=getattr(wl.layer, "options", {}).get("tc") if hasattr(wl, "layer") else None),
                 "e2e": {"value": round(wl.units_per_step * world / (e2e_ms * 1e-3), 1), "unit": unit,
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(e2e_ms, 4),
                         "steps": e2e_steps},
@@ -683,6 +687,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="perturbed_linear_1024", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32"],
+                    help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
     ap.add_argument("--members", type=int, default=0,
                     help="perturbed_linear_1024 only: members per GPU instead of 1024 (small case for ncu captures)")
     args = ap.parse_args()

@@ -318,7 +318,29 @@ class Permuted(Perturbed):
         return self._permuted_update(weights, l1, l2)[0]
 
 
+_TC_MODES = {"3xtf32": 3, "tf32": 1}
+
+
 class _LinearMixin:
+    def _tensor_core_base(self, x, y):
+        """y = x W^T + b on the tensor cores when the layer's ``options["tc"]`` allows it.
+
+        ``"3xtf32"`` (default; error-compensated, fp32-level accuracy), ``"tf32"`` (plain TF32,
+        relative error ~1e-3: a stated reduced-precision mode) or ``"fp32"`` (CUDA cores).
+        Returns False when the CUDA-core kernel has to be used (mode "fp32" or a row length that is
+        not a multiple of 4, which the TMA descriptors cannot express)."""
+        mode = self.options.get("tc", "3xtf32")
+        if mode == "fp32" or self.in_features % 4 or x.shape[0] == 0:
+            return False
+        if mode not in _TC_MODES:
+            raise NotImplementedError('options["tc"] must be "3xtf32", "tf32" or "fp32"')
+        M, N, K = x.shape[0], self.out_features, self.in_features
+        nbytes = C.call("nes_linear_fwd_tc_scratch_bytes", M, N, K, _TC_MODES[mode])
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_linear_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(y),
+               M, N, K, _TC_MODES[mode], C.ptr(buf), nbytes, C.stream())
+        return True
+
     def _flatten_rows(self, input):
         x = C.require_cuda(input, "input", _F32)
         if x.shape[-1] != self.in_features:
@@ -350,10 +372,12 @@ class PerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
         noise = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        if not direct and self._tensor_core_base(x, y):
+            direct = 2          # y now holds x W^T + b; the streaming kernel adds the per-member term
         C.call("nes_perturbed_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, self.in_features, self.out_features,
                1 if self.antithetic else 0, direct, C.stream())
-        if direct:
+        if direct == 1:
             return y.view(R, self.directions, self.out_features)
         return y.view(*lead, self.out_features)
 
@@ -479,10 +503,29 @@ class _ConvMixin:
                x.shape[0], *geom, C.stream())
         return y
 
+    def _use_tensor_cores(self):
+        """``options["tc"] == "tf32"`` selects the tcgen05 path (operands rounded to TF32: a stated
+        reduced-precision mode, relative error ~1e-3); the default ``"fp32"`` is exact fp32 on CUDA cores."""
+        mode = self.options.get("tc", "fp32")
+        if mode not in ("fp32", "tf32"):
+            raise NotImplementedError('options["tc"] for convolutions must be "fp32" or "tf32"')
+        return mode == "tf32"
+
+    def _tc_scratch(self, x, R):
+        nbytes = C.call("nes_conv2d_fwd_tc_scratch_bytes", self.directions, R, self.in_channels,
+                        x.shape[-2], x.shape[-1], self.out_channels)
+        return C.scratch(nbytes, x.device), nbytes
+
     def _dense_forward(self, x, geom, out_hw, noise):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
+        if self._use_tensor_cores() and x.shape[0]:
+            buf, nbytes = self._tc_scratch(x, R)
+            C.call("nes_perturbed_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+                   C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, *geom,
+                   1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+            return y
         C.call("nes_perturbed_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, *geom,
                1 if self.antithetic else 0, C.stream())
@@ -545,6 +588,12 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
+        if self._use_tensor_cores() and x.shape[0]:
+            buf, nbytes = self._tc_scratch(x, R)
+            C.call("nes_permuted_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+                   C.ptr(eps), C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, *geom,
+                   self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+            return y
         nbytes = C.call("nes_permuted_conv2d_fwd_scratch_bytes", self.directions, self.in_channels, self.out_channels)
         buf = C.scratch(nbytes, x.device)
         C.call("nes_permuted_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),

@@ -226,6 +226,14 @@ __global__ void permuted_dense_noise_kernel(const float* __restrict__ eps, const
   }
 }
 
+// host-side launcher shared with the tensor-core path (conv_tc.cu)
+int launch_permuted_maps(const int16_t* pin, const int16_t* pout, int16_t* omap, int16_t* imap, int64_t D,
+                         int Cin, int Cout, int in_sp, int out_sp, cudaStream_t st) {
+  NES_REQUIRE(Cin <= 32767 && Cout <= 32767 && D <= INT32_MAX, NES_ERR_UNSUPPORTED, "permuted maps: degree > 32767");
+  permuted_maps_kernel<<<(unsigned)D, 128, 0, st>>>(pin, pout, omap, imap, D, Cin, Cout, in_sp, out_sp);
+  return check_launch("permuted_conv2d_fwd(maps)");
+}
+
 }  // namespace nes
 
 using namespace nes;
@@ -283,8 +291,7 @@ extern "C" int nes_permuted_conv2d_fwd(const float* x, const float* weight, cons
   cudaStream_t st = as_stream(stream);
   int16_t* omap = static_cast<int16_t*>(scratch);
   int16_t* imap = omap + D * Cout;
-  permuted_maps_kernel<<<(unsigned)D, 128, 0, st>>>(pin, pout, omap, imap, D, Cin, Cout, in_sp, out_sp);
-  rc = check_launch("permuted_conv2d_fwd(maps)");
+  rc = launch_permuted_maps(pin, pout, omap, imap, D, Cin, Cout, in_sp, out_sp, st);
   if (rc != NES_OK) return rc;
   PermutedNoise n; n.eps = eps; n.omap = omap; n.imap = imap; n.Cout = Cout; n.Cin = Cin; n.in_sp = in_sp; n.ksz = g.ksz;
   return launch_conv(g, n, x, weight, bias, bias_noise, y, D, R, antithetic, st, "permuted_conv2d_fwd");

@@ -17,8 +17,7 @@
 // Every wait on an mbarrier is bounded: when the limit is hit the thread records an error code
 // in a device word (read by nes_tc_error_flag), stops issuing work and falls through to the
 // common exit, where tensor memory is released.
-#include <cuda.h>
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace nes {
 namespace tc {
@@ -26,104 +25,6 @@ namespace tc {
 constexpr int BM = 128, BN = 128, BKE = 32;          // tile, K elements (fp32) per stage = one 128-byte swizzle row
 constexpr int TILE_BYTES = BM * BKE * 4;             // 16 KiB per operand tile
 constexpr int NTHREADS = 192;                        // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second at B200 clocks
-
-__device__ int g_tc_error = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false = gave up (error recorded).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  const long long t0 = clock64();
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
-  }
-  atomicCAS(&g_tc_error, 0, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are one 128-byte swizzle span:
-// start address (>>4), leading byte offset 16 B (unused for this layout), stride byte offset
-// 1024 B between 8-row groups, descriptor version 1, layout type 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= uint64_t((saddr & 0x3FFFFu) >> 4);
-  d |= uint64_t(1) << 16;
-  d |= uint64_t(1024 >> 4) << 32;
-  d |= uint64_t(1) << 46;
-  d |= uint64_t(2) << 61;
-  return d;
-}
-
-// Instruction descriptor: D = fp32, A = B = tf32, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
-}
 
 struct Maps { CUtensorMap a_hi, b_hi, a_lo, b_lo; };
 
@@ -254,27 +155,9 @@ __global__ void split_tf32_kernel(const float* __restrict__ src, float* __restri
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float a = src[i];
-  uint32_t u = __float_as_uint(a);
-  if ((u & 0x7F800000u) != 0x7F800000u) u = (u + 0x0FFFu + ((u >> 13) & 1u)) & 0xFFFFE000u;
-  const float h = __uint_as_float(u);
+  const float h = round_tf32(a);
   hi[i] = h;
   if (lo) lo[i] = a - h;
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 // 2-D fp32 row-major [rows][cols] tensor, box = 32 columns x box_rows rows, 128-byte swizzle, zero fill
@@ -361,11 +244,15 @@ extern "C" int nes_linear_fwd_tc(const float* x, const float* weight, const floa
   return check_launch("linear_fwd_tc");
 }
 
+namespace nes { namespace tc { int conv_tc_error_word(int* v); } }
+
 extern "C" int nes_tc_error_flag(int* flag) {
   NES_REQUIRE(flag != nullptr, NES_ERR_BAD_ARG, "tc_error_flag: null pointer");
-  int v = 0;
+  int v = 0, vc = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
-  *flag = v;
+  int rc = nes::tc::conv_tc_error_word(&vc);
+  if (rc != NES_OK) return rc;
+  *flag = v ? v : vc;
   return NES_OK;
 }
