@@ -207,8 +207,10 @@ class PerturbedLinear1024(Workload):
                           " and the 1024-element bias update" + ("; all-reduce included" if self.world > 1 else "") + ")",
                 "bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm"], 4), "peak_source": peaks["source"],
-                "algorithmic_bytes_per_launch": upd_bytes, "ms_per_launch": round(upd_ms, 4), "traffic": None,
-                "forward_phase": {"kernels": "gemm_kernel (base x.W^T) + perturbed_linear_stream_kernel",
+                "algorithmic_bytes_per_launch": upd_bytes, "ms_per_launch": round(upd_ms, 4),
+                # ncu dram__bytes_read+write of this kernel at 128 members (544.1 MB), scaled by members (profiles/)
+                "traffic": int(544.12e6 * D / 128), "traffic_source": "ncu capture at 128 members, scaled by member count",
+                "forward_phase": {"kernels": "base x.W^T (tcgen05 3xTF32 gemm_tf32_kernel + operand split, or fp32 gemm_kernel with --tc fp32) + perturbed_linear_stream_kernel",
                                   "algorithmic_bytes": fwd_bytes, "ms": round(phase_ms["forward"], 4),
                                   "achieved_GBps": round(fwd_bytes / (phase_ms["forward"] * 1e-3) / 1e9, 1),
                                   "frac": round(fwd_bytes / (phase_ms["forward"] * 1e-3) / 1e9 / peaks["hbm"], 4)}}
@@ -331,7 +333,9 @@ class PermutedConv64(Workload):
     name = "permuted_conv_64"
     D, c, hw = 1024, 64, 32
 
-    def __init__(self):
+    def __init__(self, members=None):
+        if members:
+            self.D = members        # reduced member count: profiling captures only
         self.units_per_step = self.D
         self.resident_bytes = 2 * self.D * self.c * self.hw * self.hw * 4
 
@@ -394,11 +398,14 @@ class PermutedConv64(Workload):
         flops = 2.0 * self.D * self.hw * self.hw * self.c * 9 * self.c
         ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
         peak = peaks["bf16_sustained"] / 2
-        return {"kernel": "gemm_kernel<ConvProb<PermutedNoise>> (implicit-GEMM conv, forward phase)",
+        tf32 = self.layer.options.get("tc") == "tf32"
+        return {"kernel": ("conv_tf32_kernel (tcgen05) + stage_input_tf32_kernel, forward phase" if tf32 else
+                           "gemm_kernel<ConvProb<PermutedNoise>> (implicit-GEMM conv, forward phase)"),
                 "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(ach / peak, 4), "peak_source": peaks["source"] + " bf16 sustained / 2 taken as TF32",
                 "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 4), "traffic": None,
-                "note": "fp32 CUDA-core path (exact-fp32 parity); flops counted for the minimal form N=64"}
+                "note": ("TF32 tensor-core mode (stated reduced precision, bar 2e-2)" if tf32 else
+                         "fp32 CUDA-core path (exact-fp32 parity)") + "; flops counted for the minimal form N=64"}
 
     def cpu_sample(self, reps):
         from oracle import perturbed_ref as O
@@ -690,7 +697,7 @@ def main():
     ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32"],
                     help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
     ap.add_argument("--members", type=int, default=0,
-                    help="perturbed_linear_1024 only: members per GPU instead of 1024 (small case for ncu captures)")
+                    help="perturbed_linear_1024 / permuted_conv_64: members per GPU instead of 1024 (small case for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

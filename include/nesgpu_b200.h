@@ -187,11 +187,12 @@ int nes_permuted_conv2d_fwd(const float* x, const float* weight, const float* bi
 /* Tensor-core (TF32) versions of the two per-member convolutions: same arguments and meaning as
  * nes_perturbed_conv2d_fwd / nes_permuted_conv2d_fwd (modules/base.py:410-425, 557-588), evaluated by a
  * persistent tcgen05 kernel that builds each member's effective filter in shared memory and reads the
- * input through TMA from a channels-last TF32-rounded copy kept in `scratch`.  Reduced precision
+ * input through TMA from a zero-padded channels-last TF32-rounded copy kept in `scratch`.  Reduced precision
  * (operands rounded to TF32, relative error ~1e-3): for callers that state it.  Supported: stride 1,
  * Cin % 32 == 0, Cout % 32 == 0 and <= 256, member filter <= ~200 KB, D*R <= 65535 images per call;
  * anything else returns NES_ERR_UNSUPPORTED. */
-int64_t nes_conv2d_fwd_tc_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout);
+int64_t nes_conv2d_fwd_tc_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                        int ph, int pw);
 int nes_perturbed_conv2d_fwd_tc(const float* x, const float* weight, const float* bias,
                                 const float* noise, const float* bias_noise, float* y,
                                 int64_t D, int64_t R, int Cin, int H, int W, int Cout,

@@ -36,7 +36,7 @@ SIGNATURES = {
     "nes_permuted_linear_fwd": [c_ptr] * 8 + [c_i64] * 6 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_scratch_bytes": [c_i64, c_int, c_int],
     "nes_permuted_conv2d_fwd": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
-    "nes_conv2d_fwd_tc_scratch_bytes": [c_i64, c_i64, c_int, c_int, c_int, c_int],
+    "nes_conv2d_fwd_tc_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
     "nes_perturbed_conv2d_fwd_tc": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_tc": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_dense_noise": [c_ptr] * 4 + [c_i64] + [c_int] * 5 + [c_ptr],

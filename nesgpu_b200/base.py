@@ -511,9 +511,10 @@ class _ConvMixin:
             raise NotImplementedError('options["tc"] for convolutions must be "fp32" or "tf32"')
         return mode == "tf32"
 
-    def _tc_scratch(self, x, R):
+    def _tc_scratch(self, x, R, geom):
         nbytes = C.call("nes_conv2d_fwd_tc_scratch_bytes", self.directions, R, self.in_channels,
-                        x.shape[-2], x.shape[-1], self.out_channels)
+                        x.shape[-2], x.shape[-1], self.out_channels, self.kernel_size[0], self.kernel_size[1],
+                        geom[8], geom[9])
         return C.scratch(nbytes, x.device), nbytes
 
     def _dense_forward(self, x, geom, out_hw, noise):
@@ -521,7 +522,7 @@ class _ConvMixin:
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
         if self._use_tensor_cores() and x.shape[0]:
-            buf, nbytes = self._tc_scratch(x, R)
+            buf, nbytes = self._tc_scratch(x, R, geom)
             C.call("nes_perturbed_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, *geom,
                    1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
@@ -589,7 +590,7 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
         if self._use_tensor_cores() and x.shape[0]:
-            buf, nbytes = self._tc_scratch(x, R)
+            buf, nbytes = self._tc_scratch(x, R, geom)
             C.call("nes_permuted_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(eps), C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, *geom,
                    self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())

@@ -36,7 +36,8 @@ def _deps_mtime():
 
 def _compile(src, verbose):
     obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    extra = os.environ.get("NES_NVCC_EXTRA", "").split()      # e.g. -DNAME for an instrumented build
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, res.stdout, res.stderr))

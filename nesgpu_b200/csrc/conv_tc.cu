@@ -6,14 +6,21 @@
 //      member's channel maps, or from the member's dense noise -- already rounded to TF32, reordered to
 //      k = tap * Cin + c and laid out as the 128-byte-swizzled K-major tiles tcgen05.mma reads
 //      (never materialised in HBM);
-//   2. a producer thread streams the member's input as im2col tiles straight out of a channels-last
-//      copy of x: one 4-D TMA box {32 channels, BW, BH, 1 image} per (tile, tap, channel chunk),
-//      shifted by the tap, with the zero padding supplied by TMA's out-of-bounds fill;
-//   3. one thread issues tcgen05.mma (kind::tf32, M = 128 pixels, N = Cout, K = 8) into one of two
-//      accumulator tiles in tensor memory, so that
+//   2. a producer thread streams the member's input out of a zero-padded channels-last copy of x viewed
+//      as a 1-D sequence of pixels (pitch Wp = W + 2*pad): an output tile is 128 consecutive positions
+//      q = y*Wp + x of that sequence, and filter tap (i,j) needs the same sequence shifted by
+//      i*dil*Wp + j*dil.  So ONE staged run of 128 + max-shift pixels per (tile, 32-channel chunk) serves
+//      all taps: the im2col expansion happens in shared memory, not in L2 traffic.  The copy is stored
+//      chunk-major and already in the 128-byte-swizzled byte order of the shared-memory tile, so a run
+//      is one contiguous range fetched by a single bulk async copy (cp.async.bulk + mbarrier);
+//   3. one thread issues tcgen05.mma (kind::tf32, M = 128 positions, N = Cout, K = 8): per tap the A
+//      descriptor simply starts (shift * 128 bytes) further into the same staged box (the box itself
+//      starts on a 1024-byte boundary, so the swizzle pattern stays aligned and the descriptor's base
+//      offset is 0); accumulators alternate between two tiles in tensor memory, so that
 //   4. the builder warps, now epilogue warps, read the other accumulator with tcgen05.ld (one pixel per
 //      thread), add bias + s * bias_noise and store NCHW rows while the next tile is multiplied.
-// A pre-pass writes the channels-last, TF32-rounded copy of x (the only extra HBM traffic).
+// A pre-pass writes that padded, swizzled, TF32-rounded copy of x (the only extra HBM traffic).
+// Positions that fall on padding columns (x >= Wo) are computed and dropped (2*pad/Wp of the work).
 // All mbarrier waits are bounded (see tc_ptx.cuh); an error code is left in the device error word.
 #include "tc_ptx.cuh"
 
@@ -25,18 +32,19 @@ int launch_permuted_maps(const int16_t* pin, const int16_t* pout, int16_t* omap,
 
 namespace tc {
 
-constexpr int CONV_THREADS = 192;
-constexpr int A_TILE_BYTES = 128 * 128;   // 128 pixels x 32 fp32 channels
+constexpr int CONV_THREADS = 320;        // producer, MMA issuer, 4 epilogue + builder warps, 4 builder warps
 
 struct ConvTcParams {
   int Cin, H, W, Cout, kh, kw, ph, pw, dh, dw, Ho, Wo;
-  int BW, BH, tiles_w, tiles_h;
+  int Hp, Wp, tiles_img, img_rows, load_bytes, stage_bytes;
   long long D, R;
   int antithetic, sign_groups, units;
   int stages, kchunks, cchunks, tmem_cols;
   const float* weight; const float* bias; const float* bias_noise; float* y;
   int noise_kind;               // 0 none, 1 dense (D,Cout,Cin,ksz), 2 permuted (out_sp,in_sp,ksz) through omap / imap
   const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
+  const float* weight_t; const float* noise_t;   // (n, tap, c) re-ordered copies for noise_kind 2
+  int identity_in;                                // no input permutation: imap is the identity
 };
 
 // repeats [r0, r1) that belong to sign group sg, and the sign
@@ -46,20 +54,25 @@ __device__ __forceinline__ void unit_range(const ConvTcParams& p, int sg, long l
   if (sg == 0) { r0 = 0; r1 = half; s = 1.f; } else { r0 = half; r1 = p.R; s = -1.f; }
 }
 
-__global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid_constant__ CUtensorMap xmap, const ConvTcParams p) {
+__global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float* __restrict__ xs, const ConvTcParams p) {
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw = smem_u32(dyn_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
   unsigned char* wd = dyn_raw + pad;                                   // [kchunks][Cout][128 B]
   const int wd_chunk_bytes = p.Cout * 128;
-  unsigned char* atiles = wd + size_t(p.kchunks) * wd_chunk_bytes;     // [stages][16 KiB]
-  uint64_t* full = reinterpret_cast<uint64_t*>(atiles + size_t(p.stages) * A_TILE_BYTES);
+  unsigned char* atiles = wd + size_t(p.kchunks) * wd_chunk_bytes;     // [stages][stage_bytes]: one staged pixel box each
+  uint64_t* full = reinterpret_cast<uint64_t*>(atiles + size_t(p.stages) * p.stage_bytes);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;     // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2]
   uint64_t* wd_ready = acc_empty + 2;
   uint64_t* wd_free = wd_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wd_free + 1);
+  uint64_t* tbl_ready = wd_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_ready + 1);
+  const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
+  const int table_bytes = table_maps_bytes + 4 * p.Cout;
+  unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;    // two parities
+  uint32_t* tap_off = reinterpret_cast<uint32_t*>(tables + 2 * size_t(table_bytes));   // [ksz][2] descriptor offsets
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksz = p.kh * p.kw;
@@ -68,8 +81,9 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
-    mbar_init(wd_ready, 4);
+    mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
+    mbar_init(tbl_ready, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols);
@@ -88,21 +102,17 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
         long long r0, r1; float s;
         unit_range(p, u % p.sign_groups, r0, r1, s);
         for (long long r = r0; r < r1 && ok; ++r) {
-          const int b = int(r * p.D + d);
-          for (int th = 0; th < p.tiles_h && ok; ++th)
-            for (int tw = 0; tw < p.tiles_w && ok; ++tw)
-              for (int tap = 0; tap < ksz && ok; ++tap) {
-                const int i = tap / p.kw, j = tap - i * p.kw;
-                const int x0 = tw * p.BW + j * p.dw - p.pw;
-                const int y0 = th * p.BH + i * p.dh - p.ph;
-                for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
-                  const int st = g % p.stages;
-                  const uint32_t phs = (g / p.stages) & 1;
-                  if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
-                  mbar_expect_tx(&full[st], A_TILE_BYTES);
-                  tma_load_4d(atiles + size_t(st) * A_TILE_BYTES, &xmap, &full[st], cc * 32, x0, y0, b);
-                }
-              }
+          const long long b = r * p.D + d;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti) {
+            for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+              const int st = g % p.stages;
+              const uint32_t phs = (g / p.stages) & 1;
+              if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
+              const long long row0 = (b * p.cchunks + cc) * (long long)p.img_rows + (long long)ti * 128;
+              mbar_expect_tx(&full[st], uint32_t(p.load_bytes));
+              bulk_load_1d(atiles + size_t(st) * p.stage_bytes, xs + row0 * 32, uint32_t(p.load_bytes), &full[st]);
+            }
+          }
         }
       }
     }
@@ -110,6 +120,19 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
     if (lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(p.Cout >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+      // Descriptor arithmetic is hoisted out of the issue loop (a single thread issues every MMA, so each
+      // instruction saved there is on the critical path): per tap the A operand starts (shift * 128) bytes
+      // into the staged box and the B operand is filter chunk (tap, cc); both are offsets in 16-byte units
+      // on the low descriptor word.
+      const uint32_t desc_hi = uint32_t(smem_desc_sw128(0) >> 32);
+      const uint32_t desc_lo0 = uint32_t(smem_desc_sw128(0));
+      for (int tap = 0; tap < ksz; ++tap) {
+        const int i = tap / p.kw, j = tap - i * p.kw;
+        tap_off[2 * tap] = uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u;
+        tap_off[2 * tap + 1] = uint32_t(tap * p.cchunks) * uint32_t(wd_chunk_bytes >> 4);
+      }
+      const uint32_t wd_lo = desc_lo0 + (smem_u32(wd) >> 4);
+      const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
       uint32_t g = 0, t = 0, ul = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
@@ -118,22 +141,28 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
         if (r1 <= r0) continue;
         if (!mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
         tc_fence_after();
-        const long long ntiles = (r1 - r0) * p.tiles_h * p.tiles_w;
+        const long long ntiles = (r1 - r0) * p.tiles_img;
         for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
           const uint32_t buf = t & 1;
           if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + buf * uint32_t(p.Cout);
-          for (int jc = 0; jc < p.kchunks; ++jc, ++g) {
+          for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
             const int st = g % p.stages;
             const uint32_t phs = (g / p.stages) & 1;
             if (!mbar_wait(&full[st], phs, 2)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t adesc = smem_desc_sw128(smem_u32(atiles + size_t(st) * A_TILE_BYTES));
-            const uint64_t bdesc = smem_desc_sw128(smem_u32(wd + size_t(jc) * wd_chunk_bytes));
+            const uint32_t a_lo = desc_lo0 + (smem_u32(atiles + size_t(st) * p.stage_bytes) >> 4);
+            const uint32_t b_lo = wd_lo + uint32_t(cc) * cc_step;
+            uint32_t accumulate = (cc > 0) ? 1u : 0u;
+            for (int tap = 0; tap < ksz; ++tap) {
+              const uint32_t al = a_lo + tap_off[2 * tap], bl = b_lo + tap_off[2 * tap + 1];
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_tf32(tmem_d, adesc + uint64_t(2 * k), bdesc + uint64_t(2 * k), idesc, (jc > 0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < 4; ++k) {
+                mma_tf32_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
+                accumulate = 1u;
+              }
+            }
             mma_commit(&empty[st]);
           }
           mma_commit(&acc_full[buf]);
@@ -144,10 +173,13 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
     }
   } else {
     // ---------------------------------------------------------------------- filter builders / epilogue
-    const int te = threadIdx.x - 64;            // 0..127
-    const int q = warp & 3;                     // TMEM lane quadrant this warp may read
-    const int pix = q * 32 + lane;              // pixel of the tile = accumulator row
-    const int ty = pix / p.BW, tx = pix - ty * p.BW;
+    // warps 2-5 build the member filter and then drain accumulators; warps 6-9 only build
+    const int bt = threadIdx.x - 64;            // builder thread 0..255
+    const bool drains = warp < 6;
+    const int q = warp & 3;                     // TMEM lane quadrant an epilogue warp may read
+    const int pix = q * 32 + lane;              // position of the tile = accumulator row
+    const int HoWo = p.Ho * p.Wo;
+    const int k4 = K / 4, c4n = p.Cin / 4;
     uint32_t t = 0, ul = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
@@ -155,58 +187,127 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
       long long r0, r1; float s;
       unit_range(p, u % p.sign_groups, r0, r1, s);
       if (r1 <= r0) continue;
-      if (!mbar_wait(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
-      // W_d[n][tap*Cin + c] = tf32(W[n][c][tap] + s * noise_d[n][c][tap])
-      const int total = p.Cout * K;
-      for (int idx = te; idx < total; idx += 128) {
-        const int n = idx / K;
-        const int rem = idx - n * K;
-        const int c = rem / ksz, tap = rem - c * ksz;
-        float v = __ldg(p.weight + idx);
-        if (p.noise_kind == 1) {
-          v += s * __ldg(p.noise + size_t(d) * total + idx);
-        } else if (p.noise_kind == 2) {
-          const int so = p.omap[d * p.Cout + n];
-          const int ci = p.imap[d * p.Cin + c];
-          if (so >= 0 && ci >= 0) v += s * __ldg(p.noise + (size_t(so) * p.in_sp + ci) * ksz + tap);
+      // per-unit tables (double-buffered by unit parity): channel maps and bias + s * bias_noise
+      unsigned char* tb = tables + size_t(ul & 1) * table_bytes;
+      int16_t* omap_s = reinterpret_cast<int16_t*>(tb);
+      int16_t* imap_s = omap_s + p.Cout;
+      float* add_s = reinterpret_cast<float*>(tb + table_maps_bytes);
+      for (int n = bt; n < p.Cout; n += 256) {
+        omap_s[n] = (p.noise_kind == 2) ? p.omap[d * p.Cout + n] : int16_t(n);
+        float a = p.bias ? __ldg(p.bias + n) : 0.f;
+        if (p.bias_noise) a += s * __ldg(p.bias_noise + d * p.Cout + n);
+        add_s[n] = a;
+      }
+      for (int c = bt; c < p.Cin; c += 256) imap_s[c] = (p.noise_kind == 2) ? p.imap[d * p.Cin + c] : int16_t(c);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tbl_ready);          // all eight builder warps have written their table entries
+      if (!mbar_wait_relaxed(tbl_ready, ul & 1, 4)) { ok = false; break; }
+      if (!mbar_wait_relaxed(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
+
+      if (p.noise_kind == 1) {
+        // dense member noise in its native (n, c, tap) order: coalesced reads, scattered 4-byte writes
+        const int total = p.Cout * K;
+        const float* E = p.noise + size_t(d) * total;
+        for (int base = bt; base < total; base += 256 * 8) {
+          float wv[8], ev[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 256;
+            wv[i] = idx < total ? __ldg(p.weight + idx) : 0.f;
+            ev[i] = idx < total ? __ldcs(E + idx) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 256;
+            if (idx >= total) break;
+            const int n = idx / K;
+            const int rem = idx - n * K;
+            const int c = rem / ksz, tap = rem - c * ksz;
+            const int kk = tap * p.Cin + c;
+            const int jc = kk >> 5, w32 = kk & 31;
+            unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
+                                 ((((w32 >> 2) ^ (n & 7))) << 4) + (w32 & 3) * 4;
+            *reinterpret_cast<float*>(dst) = round_tf32(fmaf(s, ev[i], wv[i]));
+          }
         }
-        const int kk = tap * p.Cin + c;
-        const int jc = kk >> 5, w32 = kk & 31;
-        unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
-                             ((((w32 >> 2) ^ (n & 7))) << 4) + (w32 & 3) * 4;
-        *reinterpret_cast<float*>(dst) = round_tf32(v);
+      } else {
+        // W and eps were re-ordered to (n, tap, c): 128-bit reads along c, 128-bit swizzled writes
+        const float4* Wt = reinterpret_cast<const float4*>(p.weight_t);
+        const bool identity_in = p.identity_in != 0;
+        const int groups = p.Cout * k4;
+        // group index -> (n, rem) is carried incrementally (no division in the loop): +256 per step
+        const int step_n = 256 / k4, step_r = 256 - step_n * k4;
+        int n_cur = bt / k4, r_cur = bt - n_cur * k4;
+        constexpr int BATCH = 6;
+        for (int g0 = bt; g0 < groups; g0 += 256 * BATCH) {
+          float4 wv[BATCH], ev[BATCH];
+          int nn[BATCH], kk[BATCH];
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            const int gidx = g0 + i * 256;
+            wv[i] = make_float4(0.f, 0.f, 0.f, 0.f); ev[i] = wv[i]; nn[i] = -1; kk[i] = 0;
+            if (gidx < groups) {
+              const int n = n_cur, rem = r_cur;
+              const int tap = rem / c4n, c = (rem - tap * c4n) * 4;
+              nn[i] = n; kk[i] = tap * p.Cin + c;
+              wv[i] = __ldg(Wt + gidx);
+              const int so = (p.noise_kind == 2) ? int(omap_s[n]) : -1;
+              if (so >= 0) {
+                const float* er = p.noise_t + (size_t(so) * ksz + tap) * p.in_sp;
+                if (identity_in) {
+                  ev[i] = __ldg(reinterpret_cast<const float4*>(er + c));
+                } else {
+                  const int c0 = imap_s[c], c1 = imap_s[c + 1], c2 = imap_s[c + 2], c3 = imap_s[c + 3];
+                  if (c0 >= 0) ev[i].x = __ldg(er + c0);
+                  if (c1 >= 0) ev[i].y = __ldg(er + c1);
+                  if (c2 >= 0) ev[i].z = __ldg(er + c2);
+                  if (c3 >= 0) ev[i].w = __ldg(er + c3);
+                }
+              }
+            }
+            n_cur += step_n; r_cur += step_r;
+            if (r_cur >= k4) { r_cur -= k4; ++n_cur; }
+          }
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            if (nn[i] < 0) continue;
+            const int n = nn[i];
+            const int jc = kk[i] >> 5, w32 = kk[i] & 31;
+            unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
+                                 ((((w32 >> 2) ^ (n & 7))) << 4);
+            *reinterpret_cast<float4*>(dst) = make_float4(round_tf32(fmaf(s, ev[i].x, wv[i].x)), round_tf32(fmaf(s, ev[i].y, wv[i].y)),
+                                                          round_tf32(fmaf(s, ev[i].z, wv[i].z)), round_tf32(fmaf(s, ev[i].w, wv[i].w)));
+          }
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(wd_ready);
 
-      for (long long r = r0; r < r1 && ok; ++r) {
-        const long long b = r * p.D + d;
-        for (int th = 0; th < p.tiles_h && ok; ++th)
-          for (int tw = 0; tw < p.tiles_w && ok; ++tw, ++t) {
-            const uint32_t buf = t & 1;
-            if (!mbar_wait(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
-            tc_fence_after();
-            const int oy = th * p.BH + ty, ox = tw * p.BW + tx;
-            const bool valid = (oy < p.Ho) && (ox < p.Wo) && (g_tc_error == 0);
-            for (int c0 = 0; c0 < p.Cout; c0 += 32) {
-              uint32_t acc[32];
-              tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(p.Cout) + uint32_t(c0), acc);
-              if (valid) {
+      if (drains) {
+        for (long long r = r0; r < r1 && ok; ++r) {
+          const long long b = r * p.D + d;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++t) {
+              const uint32_t buf = t & 1;
+              if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
+              tc_fence_after();
+              const int qpos = ti * 128 + pix;
+              const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
+              const bool valid = (oy < p.Ho) && (ox < p.Wo) && (g_tc_error == 0);
+              float* yb = p.y + size_t(b) * p.Cout * HoWo + size_t(oy) * p.Wo + ox;
+              for (int c0 = 0; c0 < p.Cout; c0 += 32) {
+                uint32_t acc[32];
+                tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(p.Cout) + uint32_t(c0), acc);
+                if (valid) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  const int n = c0 + j;
-                  float v = __uint_as_float(acc[j]);
-                  if (p.bias) v += __ldg(p.bias + n);
-                  if (p.bias_noise) v += s * __ldg(p.bias_noise + d * p.Cout + n);
-                  p.y[((size_t(b) * p.Cout + n) * p.Ho + oy) * p.Wo + ox] = v;
+                  for (int j = 0; j < 32; ++j) yb[size_t(c0 + j) * HoWo] = __uint_as_float(acc[j]) + add_s[c0 + j];
                 }
               }
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          }
+        }
       }
       ++ul;
     }
@@ -219,23 +320,69 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const __grid
   }
 }
 
-// x (B,C,H,W) -> channels-last (B,H,W,C), rounded to TF32.  32x32 tiles through shared memory so that both
-// the reads (along HW) and the writes (along C) are coalesced.
-__global__ void nchw_to_nhwc_tf32_kernel(const float* __restrict__ x, float* __restrict__ out, int C, int HW) {
-  __shared__ float tile[32][33];
-  const size_t b = blockIdx.z;
-  const int hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
-  const float* src = x + b * size_t(C) * HW;
-  float* dst = out + b * size_t(C) * HW;
-  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-    const int c = c0 + i, hw = hw0 + threadIdx.x;
-    tile[i][threadIdx.x] = (c < C && hw < HW) ? src[size_t(c) * HW + hw] : 0.f;
+// x (B,C,H,W) -> the staged layout the kernel above copies from: for every image and 32-channel chunk a
+// run of img_rows pixel rows (zero-padded image, pitch Wp, 128 bytes = 32 channels per row), values rounded
+// to TF32, 16-byte groups of each row permuted by (row mod 8) exactly as the 128-byte shared-memory swizzle
+// does.  One block per (image, channel chunk) walks the image in strips of STRIP padded rows: each warp
+// reads whole image rows of one channel with 128-bit loads (contiguous in NCHW), the strip is transposed in
+// shared memory, and every warp store writes one 128-byte pixel row of a contiguous run.
+constexpr int STRIP = 4;
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) stage_input_tf32_kernel(const float* __restrict__ x, float* __restrict__ out,
+                                                               int C, int H, int W, int Hp, int Wp, int ph, int pw,
+                                                               int img_rows) {
+  extern __shared__ float tile[];                 // [32][pitch], pitch odd: conflict-free transposed reads
+  const int pitch = (STRIP * Wp) | 1;
+  const size_t b = blockIdx.y;
+  const int cc = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* src = x + (b * size_t(C) + size_t(cc) * 32) * H * W;
+  float* dst = out + (b * gridDim.x + cc) * size_t(img_rows) * 32;
+  for (int y0 = 0; y0 < Hp; y0 += STRIP) {
+    const int rows = (Hp - y0 < STRIP) ? (Hp - y0) : STRIP;
+    // zero the strip (padding), then drop the interior values in
+    for (int e = threadIdx.x; e < 32 * pitch; e += 256) tile[e] = 0.f;
+    __syncthreads();
+    for (int ch = warp; ch < 32; ch += 8) {
+      const float* plane = src + size_t(ch) * H * W;
+      if (VEC) {
+        const int w4 = W >> 2;
+        for (int g = lane; g < rows * w4; g += 32) {
+          const int rr = g / w4, x4 = (g - rr * w4) * 4;
+          const int yy = y0 + rr - ph;
+          if (yy >= 0 && yy < H) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(plane + size_t(yy) * W + x4));
+            float* t = tile + ch * pitch + rr * Wp + pw + x4;
+            t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
+          }
+        }
+      } else {
+        for (int g = lane; g < rows * W; g += 32) {
+          const int rr = g / W, xx = g - rr * W;
+          const int yy = y0 + rr - ph;
+          if (yy >= 0 && yy < H) tile[ch * pitch + rr * Wp + pw + xx] = __ldcs(plane + size_t(yy) * W + xx);
+        }
+      }
+    }
+    __syncthreads();
+    const int first = y0 * Wp;
+    for (int r = warp; r < rows * Wp; r += 8) {
+      const int row = first + r;                       // row inside this image/chunk run (run starts at a multiple of 8)
+      dst[size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3))] = round_tf32(tile[lane * pitch + r]);
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
-    const int hw = hw0 + i, c = c0 + threadIdx.x;
-    if (hw < HW && c < C) dst[size_t(hw) * C + c] = round_tf32(tile[threadIdx.x][i]);
-  }
+}
+
+// (N, C, ksz) -> (N, ksz, C): the K order the tensor-core kernel uses (k = tap * C + c)
+__global__ void reorder_filter_kernel(const float* __restrict__ src, float* __restrict__ dst, int N, int C, int ksz) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= N * C * ksz) return;
+  const int n = idx / (C * ksz);
+  const int rem = idx - n * C * ksz;
+  const int tap = rem / C, c = rem - tap * C;
+  dst[idx] = src[(size_t(n) * C + c) * ksz + tap];
 }
 
 int conv_tc_error_word(int* v) {
@@ -246,7 +393,7 @@ int conv_tc_error_word(int* v) {
 
 static int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
-struct ConvTcPlan { ConvTcParams p; size_t smem; int64_t x_bytes, map_bytes; };
+struct ConvTcPlan { ConvTcParams p; size_t smem; int64_t x_bytes, map_bytes, filt_bytes; };
 
 static int plan_conv_tc(ConvTcPlan& pl, int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
                         int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what) {
@@ -260,10 +407,13 @@ static int plan_conv_tc(ConvTcPlan& pl, int64_t D, int64_t R, int Cin, int H, in
   p.Ho = H + 2 * ph - dh * (kh - 1);
   p.Wo = W + 2 * pw - dw * (kw - 1);
   NES_REQUIRE(p.Ho > 0 && p.Wo > 0, NES_ERR_BAD_ARG, "%s: empty output", what);
-  int bw = 8;
-  while (bw < p.Wo && bw < 128) bw <<= 1;
-  p.BW = bw; p.BH = 128 / bw;
-  p.tiles_w = ceil_div(p.Wo, p.BW); p.tiles_h = ceil_div(p.Ho, p.BH);
+  p.Hp = H + 2 * ph; p.Wp = W + 2 * pw;
+  p.tiles_img = ceil_div(p.Ho * p.Wp, 128);
+  const int max_shift = (kh - 1) * dh * p.Wp + (kw - 1) * dw;
+  const int rows_needed = 128 + max_shift;
+  p.img_rows = (p.Hp * p.Wp + 7) & ~7;            // image stride in rows: keeps (row mod 8) aligned with the tiles
+  p.load_bytes = rows_needed * 128;
+  p.stage_bytes = (p.load_bytes + 1023) & ~1023;
   p.D = D; p.R = R; p.antithetic = antithetic;
   p.sign_groups = antithetic ? 2 : 1;
   NES_REQUIRE(D * p.sign_groups <= INT32_MAX && D * R <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: population too large", what);
@@ -274,46 +424,41 @@ static int plan_conv_tc(ConvTcPlan& pl, int64_t D, int64_t R, int Cin, int H, in
   while (cols < 2 * Cout) cols <<= 1;
   p.tmem_cols = cols;
   const size_t wd_bytes = size_t(p.kchunks) * Cout * 128;
-  const size_t fixed = 1024 + wd_bytes + 64 /* barriers */ + 16;
+  const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
+  const size_t fixed = 1024 + wd_bytes + 64 /* barriers */ + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw;
   const size_t limit = 227 * 1024;
-  NES_REQUIRE(fixed + 2 * (A_TILE_BYTES + 16) <= limit, NES_ERR_UNSUPPORTED,
-              "%s: the member filter (%zu bytes) does not fit in shared memory on the tensor-core path", what, wd_bytes);
-  int stages = int((limit - fixed) / (A_TILE_BYTES + 16));
+  NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
+              "%s: the member filter (%zu bytes) plus two input stages (%d bytes each) do not fit in shared memory on the "
+              "tensor-core path", what, wd_bytes, p.stage_bytes);
+  int stages = int((limit - fixed) / (size_t(p.stage_bytes) + 16));
   if (stages > 8) stages = 8;
   p.stages = stages;
-  pl.smem = 1024 + wd_bytes + size_t(stages) * A_TILE_BYTES + (2 * stages + 6) * sizeof(uint64_t) + 16;
-  pl.x_bytes = align256(D * R * int64_t(Cin) * H * W * 4);
+  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 7) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw;
+  pl.x_bytes = align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
   pl.map_bytes = align256(D * (int64_t(Cin) + Cout) * 2);
+  pl.filt_bytes = align256(int64_t(Cout) * Cin * kh * kw * 4);
   return NES_OK;
 }
 
 static int run_conv_tc(ConvTcPlan& pl, const float* x, float* x_nhwc, cudaStream_t st, const char* what) {
   ConvTcParams& p = pl.p;
   const int64_t B = p.D * p.R;
-  const int HW = p.H * p.W;
   NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
-  dim3 tgrid((unsigned)ceil_div(HW, 32), (unsigned)ceil_div(p.Cin, 32), (unsigned)B);
-  nchw_to_nhwc_tf32_kernel<<<tgrid, dim3(32, 8), 0, st>>>(x, x_nhwc, p.Cin, HW);
+  const size_t tsmem = size_t(32) * ((STRIP * p.Wp) | 1) * sizeof(float);
+  NES_REQUIRE(tsmem <= 48 * 1024, NES_ERR_UNSUPPORTED, "%s: image row too wide for the layout pre-pass (%zu bytes)", what, tsmem);
+  dim3 tgrid((unsigned)p.cchunks, (unsigned)B);
+  if (p.W % 4 == 0 && aligned16(x))
+    stage_input_tf32_kernel<true><<<tgrid, 256, tsmem, st>>>(x, x_nhwc, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
+  else
+    stage_input_tf32_kernel<false><<<tgrid, 256, tsmem, st>>>(x, x_nhwc, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
   int rc = check_launch(what);
   if (rc != NES_OK) return rc;
-
-  EncodeTiledFn fn = encode_fn();
-  NES_REQUIRE(fn != nullptr, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
-  CUtensorMap xmap;
-  cuuint64_t dims[4] = {(cuuint64_t)p.Cin, (cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)p.Cin * 4, (cuuint64_t)p.W * p.Cin * 4, (cuuint64_t)p.H * p.W * p.Cin * 4};
-  cuuint32_t box[4] = {32, (cuuint32_t)p.BW, (cuuint32_t)p.BH, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x_nhwc, dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  NES_REQUIRE(r == CUDA_SUCCESS, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
 
   cudaError_t e = cudaFuncSetAttribute(conv_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
   int grid = p.units < sm_count() ? p.units : sm_count();
   if (grid < 1) grid = 1;
-  conv_tf32_kernel<<<grid, CONV_THREADS, pl.smem, st>>>(xmap, p);
+  conv_tf32_kernel<<<grid, CONV_THREADS, pl.smem, st>>>(x_nhwc, p);
   return check_launch(what);
 }
 
@@ -323,9 +468,14 @@ static int run_conv_tc(ConvTcPlan& pl, const float* x, float* x_nhwc, cudaStream
 using namespace nes;
 using namespace nes::tc;
 
-extern "C" int64_t nes_conv2d_fwd_tc_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout) {
+extern "C" int64_t nes_conv2d_fwd_tc_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                   int ph, int pw) {
   if (D <= 0 || R <= 0) return 0;
-  return align256(D * R * int64_t(Cin) * H * W * 4) + align256(D * (int64_t(Cin) + Cout) * 2);
+  const int64_t hp = H + 2 * ph, wp = W + 2 * pw;
+  const int64_t img_rows = (hp * wp + 7) & ~int64_t(7);
+  const int64_t tail = ((128 + (kh - 1) * wp * 8 + (kw - 1) * 8) * 128 + 1023) & ~int64_t(1023);   // covers any dilation <= 8
+  return align256(D * R * int64_t(Cin / 32) * img_rows * 128 + tail) + align256(D * (int64_t(Cin) + Cout) * 2) +
+         2 * align256(int64_t(Cout) * Cin * kh * kw * 4);
 }
 
 extern "C" int nes_perturbed_conv2d_fwd_tc(const float* x, const float* weight, const float* bias,
@@ -342,6 +492,7 @@ extern "C" int nes_perturbed_conv2d_fwd_tc(const float* x, const float* weight, 
               "perturbed_conv2d_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)pl.x_bytes);
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 1; pl.p.noise = noise; pl.p.omap = nullptr; pl.p.imap = nullptr; pl.p.in_sp = Cin;
+  pl.p.weight_t = nullptr; pl.p.noise_t = nullptr; pl.p.identity_in = 1;
   return run_conv_tc(pl, x, static_cast<float*>(scratch), as_stream(stream), "perturbed_conv2d_fwd_tc");
 }
 
@@ -359,15 +510,27 @@ extern "C" int nes_permuted_conv2d_fwd_tc(const float* x, const float* weight, c
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_conv2d_fwd_tc: null pointer");
   NES_REQUIRE(out_sp >= 0 && out_sp <= Cout && in_sp >= 0 && in_sp <= Cin && (pin || in_sp == Cin), NES_ERR_BAD_ARG,
               "permuted_conv2d_fwd_tc: sparsity exceeds degree");
-  NES_REQUIRE(scratch && scratch_bytes >= pl.x_bytes + pl.map_bytes && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
-              NES_ERR_SCRATCH, "permuted_conv2d_fwd_tc: scratch needs %lld bytes, 256-byte aligned",
-              (long long)(pl.x_bytes + pl.map_bytes));
+  const int64_t need = pl.x_bytes + pl.map_bytes + 2 * pl.filt_bytes;
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
+              NES_ERR_SCRATCH, "permuted_conv2d_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)need);
   cudaStream_t st = as_stream(stream);
-  int16_t* omap = reinterpret_cast<int16_t*>(static_cast<unsigned char*>(scratch) + pl.x_bytes);
+  unsigned char* sp = static_cast<unsigned char*>(scratch);
+  int16_t* omap = reinterpret_cast<int16_t*>(sp + pl.x_bytes);
   int16_t* imap = omap + D * Cout;
+  float* weight_t = reinterpret_cast<float*>(sp + pl.x_bytes + pl.map_bytes);
+  float* eps_t = reinterpret_cast<float*>(sp + pl.x_bytes + pl.map_bytes + pl.filt_bytes);
   rc = launch_permuted_maps(pin, pout, omap, imap, D, Cin, Cout, in_sp, out_sp, st);
   if (rc != NES_OK) return rc;
+  const int ksz = kh * kw;
+  reorder_filter_kernel<<<ceil_div(Cout * Cin * ksz, 256), 256, 0, st>>>(weight, weight_t, Cout, Cin, ksz);
+  if ((rc = check_launch("permuted_conv2d_fwd_tc(reorder W)")) != NES_OK) return rc;
+  if (out_sp * in_sp > 0) {
+    reorder_filter_kernel<<<ceil_div(out_sp * in_sp * ksz, 256), 256, 0, st>>>(eps, eps_t, out_sp, in_sp, ksz);
+    if ((rc = check_launch("permuted_conv2d_fwd_tc(reorder eps)")) != NES_OK) return rc;
+  }
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 2; pl.p.noise = eps; pl.p.omap = omap; pl.p.imap = imap; pl.p.in_sp = in_sp;
+  pl.p.weight_t = weight_t; pl.p.noise_t = eps_t; pl.p.identity_in = (pin == nullptr) ? 1 : 0;
   return run_conv_tc(pl, x, static_cast<float*>(scratch), st, "permuted_conv2d_fwd_tc");
 }
+

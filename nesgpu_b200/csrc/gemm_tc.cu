@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
   } else {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
     const int q = warp & 3;
-    const bool ok = mbar_wait(accum, 0, 3);
+    const bool ok = mbar_wait_relaxed(accum, 0, 3);
     tc_fence_after();
     if (ok && g_tc_error == 0 && nk > 0) {
       const int64_t gm = int64_t(m0) + q * 32 + lane;

@@ -35,21 +35,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait; false = gave up (error recorded).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+// Bounded wait; false = gave up (error recorded).  The producer and the MMA issuer spin (they are single
+// threads on the critical path); everything else backs off with nanosleep so that the waiting warps do not
+// take issue slots away from them.
+template <bool BACKOFF>
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
+    if (BACKOFF) __nanosleep(128);
     if (mbar_try_wait(bar, parity)) return true;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
   }
   atomicCAS(&g_tc_error, 0, code);
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+  return mbar_wait_impl<false>(bar, parity, code);
+}
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int code) {
+  return mbar_wait_impl<true>(bar, parity, code);
+}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// contiguous global -> shared bulk copy (no tensor map); addresses and size are multiples of 16 bytes
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
 
@@ -71,6 +90,22 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
       "}\n"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same instruction with the two descriptors given as (low word, shared high word): the issuing thread
+// then only needs 32-bit adds per MMA.
+__device__ __forceinline__ void mma_tf32_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
