@@ -509,7 +509,135 @@ class Binary1024(Workload):
         return Ds, [once() for _ in range(max(1, min(reps, 2)))], "64 of 1024 members, uniforms pre-drawn: sample_bits + pack + bmm + weighted_sum (numpy port, single thread)"
 
 
-WORKLOADS = {w.name: w for w in (PerturbedLinear1024, PermutedLinear256, PermutedConv64, Binary1024)}
+
+class EsCnn(Workload):
+    """BASELINE configuration 5: one ES step of the small CNN, 1024 members per GPU (8192 over 8 GPUs)."""
+    name = "es_cnn_8192"
+    D, R = 1024, 256
+    FLOP_PER_PAIR = 5.262e6       # conv1 0.389 + conv2 4.461 + fc1 0.410 + fc2 0.003 MFLOP per (member, image), minimal form
+
+    def __init__(self, members=None):
+        if members:
+            self.D = members
+        self.units_per_step = self.D * self.R
+        self.resident_bytes = 1 << 40     # activations far exceed L2
+
+    def describe(self, world):
+        return {"workload": self.name, "net": "Conv(1,32,3)-ReLU-MaxPool2-Conv(32,64,3)-ReLU-MaxPool2-Linear(1600,128)-ReLU-Linear(128,10), Permuted layers",
+                "directions_per_gpu": self.D, "population": self.D * world, "images_per_member": self.R,
+                "step": "set_noise + chunked population forward + CE fitness + centred ranks + update (+ all-gather / all-reduce at N>1)",
+                "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02}
+
+    def setup(self, dev, rank, world):
+        from nesgpu_b200 import base, es
+        self.es, self.world, self.dev = es, world, dev
+        D = self.D
+        torch.manual_seed(1005)       # same initial weights on every rank
+        opts = {"tc": "tf32"} if self.tc == "tf32" else {}
+        self.net = torch.nn.Sequential(
+            base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
+            base.PermutedConv2d(32, 64, 3, D, options=opts), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Flatten(),
+            base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
+        self.layer = self.net[3]
+        self.pm = base.PerturbedModel(self.net, D)
+        self.pm.set_noise_scale(0.02)
+        self.pm.set_seed(9000 + rank)
+        g = torch.Generator().manual_seed(2005)
+        self.images_host = torch.rand(self.R, 1, 28, 28, generator=g).pin_memory()
+        self.labels_host = torch.randint(10, (self.R,), generator=g).pin_memory()
+        self.images, self.labels = self.images_host.to(dev), self.labels_host.to(dev)
+        self.fit_host = torch.empty(D).pin_memory()
+        self.nparams = sum(p.numel() for p in self.net.parameters())
+        self.grad_host = torch.empty(self.nparams).pin_memory()
+        self.bucket = None
+        self.h2d = self.images_host.numel() * 4 + self.labels_host.numel() * 8
+        self.d2h = (D + self.nparams) * 4
+
+    def step(self, mark):
+        pm, es = self.pm, self.es
+        pm.set_noise()
+        mark("set_noise")
+        fit = es.population_fitness(pm, self.images, self.labels, self.D, chunk=16)
+        mark("forward")
+        _, self.bucket = self._update(fit)
+        mark("update")
+        return fit
+
+    def _update(self, fit):
+        from nesgpu_b200 import dist as ndist
+        everyone = ndist.gather_fitness(fit)
+        w_all = self.es.centered_ranks(everyone)
+        rank = torch.distributed.get_rank() if self.world > 1 else 0
+        lo, hi = ndist.member_slice(everyone.numel(), rank, self.world)
+        for p in self.net.parameters():
+            p.grad = None
+        with torch.no_grad():
+            self.pm.update(w_all[lo:hi].contiguous())
+        return fit, ndist.all_reduce_grads(self.net.parameters(), self.bucket)
+
+    def step_e2e(self):
+        self.images.copy_(self.images_host, non_blocking=True)
+        self.labels.copy_(self.labels_host, non_blocking=True)
+        fit = self.step(lambda name: None)
+        self.fit_host.copy_(fit, non_blocking=True)
+        if self.bucket is not None:
+            self.grad_host.copy_(self.bucket.flat, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def roofline(self, phase_ms, peaks):
+        flops = self.FLOP_PER_PAIR * self.D * self.R
+        ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
+        peak = peaks["bf16_sustained"] / 2
+        return {"kernel": "population forward (conv1, conv2, fc1, fc2 kernels + torch ReLU / MaxPool / CE), forward phase",
+                "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
+                "peak_source": peaks["source"] + " bf16 sustained / 2 taken as TF32",
+                "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 3), "traffic": None,
+                "es_steps_per_s": round(1e3 / sum(phase_ms.values()), 3),
+                "note": "flops for the minimal one-product form; conv2 on tensor cores only with --tc tf32"}
+
+    def cpu_sample(self, reps):
+        """CPU oracle on 16 members x 32 images of the same net (forward + CE + ranks + update)."""
+        from oracle import perturbed_ref as O
+        import torch.nn.functional as F
+        Ds, Rs = 16, 32
+        g = torch.Generator().manual_seed(5)
+        shapes = [("conv", 1, 32), ("conv", 32, 64), ("lin", 1600, 128), ("lin", 128, 10)]
+        layers = []
+        for kind, cin, cout in shapes:
+            p_in, p_out, isp, osp = O.resolve_permutation(cin, cout)
+            tail = (3, 3) if kind == "conv" else ()
+            layers.append(dict(kind=kind, cin=cin, cout=cout,
+                               W=torch.randn(cout, cin, *tail, generator=g) * 0.05, b=torch.zeros(cout),
+                               eps=0.02 * torch.randn(osp, isp, *tail, generator=g), beta=0.02 * torch.randn(Ds, cout, generator=g),
+                               pin=torch.stack([torch.randperm(cin, generator=g) for _ in range(Ds)]).short() if p_in else None,
+                               pout=torch.stack([torch.randperm(cout, generator=g) for _ in range(Ds)]).short() if p_out else None))
+        images = torch.rand(Rs, 1, 28, 28, generator=g)
+        labels = torch.randint(10, (Rs,), generator=g)
+
+        def once():
+            t0 = time.perf_counter()
+            x = images.unsqueeze(1).expand(Rs, Ds, 1, 28, 28).reshape(Rs * Ds, 1, 28, 28)
+            for i, L in enumerate(layers):
+                if L["kind"] == "conv":
+                    x = O.permuted_conv2d_forward(x, L["W"], L["b"], L["eps"], L["beta"], L["pin"], L["pout"], Ds)
+                    x = F.max_pool2d(F.relu(x), 2)
+                else:
+                    x = O.permuted_linear_forward(x.reshape(Rs * Ds, -1), L["W"], L["b"], L["eps"], L["beta"], L["pin"], L["pout"], Ds)
+                    if i == 2:
+                        x = F.relu(x)
+            ce = F.cross_entropy(x, labels.repeat_interleave(Ds), reduction="none").view(Rs, Ds)
+            w = O.centered_ranks(-ce.mean(0))
+            for L in layers:
+                if L["kind"] == "conv":
+                    O.permuted_conv2d_weight_grad(L["eps"], w, L["pin"], L["pout"], L["cin"], L["cout"])
+                else:
+                    O.permuted_linear_weight_grad(L["eps"], w, L["pin"], L["pout"], L["cin"], L["cout"])
+            return time.perf_counter() - t0
+        once()
+        return Ds * Rs, [once() for _ in range(reps)], "16 members x 32 images of the same net: forward + CE + ranks + update per repetition"
+
+
+WORKLOADS = {w.name: w for w in (PerturbedLinear1024, PermutedLinear256, PermutedConv64, Binary1024, EsCnn)}
 
 
 # ---------------------------------------------------------------------------------- runs
@@ -697,7 +825,7 @@ def main():
     ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32"],
                     help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
     ap.add_argument("--members", type=int, default=0,
-                    help="perturbed_linear_1024 / permuted_conv_64: members per GPU instead of 1024 (small case for ncu captures)")
+                    help="members per GPU instead of 1024 (small case for ncu captures; not for binary_1024 / permuted_linear_256)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

@@ -1,0 +1,62 @@
+"""One evolution-strategies step over a population-batched model: the step sequence of the
+reference's trainers (``mnisttest.py:127-157``: set_noise -> perturbed forward -> per-member loss ->
+centring -> update), with the population sharded over ranks as in :mod:`nesgpu_b200.dist`.
+
+Every member sees the same minibatch of ``R`` examples; the batch handed to the model is laid out
+``b = r * directions + d`` (reference ``modules/base.py:357``).  The forward is run in chunks of
+examples so that activation memory stays bounded for large populations.
+"""
+import torch
+import torch.nn.functional as F
+
+from . import dist as ndist
+
+
+def centered_ranks(fitness):
+    """rank / (n - 1) - 1/2 with a stable sort (ties keep member order)."""
+    n = fitness.numel()
+    order = torch.argsort(fitness, stable=True)
+    ranks = torch.empty(n, dtype=torch.float32, device=fitness.device)
+    ranks[order] = torch.arange(n, dtype=torch.float32, device=fitness.device)
+    return ranks / max(n - 1, 1) - 0.5
+
+
+def population_fitness(perturbed_model, inputs, labels, directions, chunk=16):
+    """Negative mean cross-entropy of every member on the shared minibatch: (directions,) tensor."""
+    R = inputs.shape[0]
+    loss_sum = torch.zeros(directions, device=inputs.device, dtype=torch.float32)
+    with torch.no_grad():
+        for r0 in range(0, R, chunk):
+            r1 = min(R, r0 + chunk)
+            rc = r1 - r0
+            xb = inputs[r0:r1].unsqueeze(1).expand(rc, directions, *inputs.shape[1:]).reshape(
+                rc * directions, *inputs.shape[1:])
+            logits = perturbed_model.forward(xb)
+            target = labels[r0:r1].repeat_interleave(directions)
+            ce = F.cross_entropy(logits.view(rc * directions, -1), target, reduction="none")
+            loss_sum += ce.view(rc, directions).sum(dim=0)
+    return -(loss_sum / R)
+
+
+def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=16, bucket=None, group=None,
+            new_noise=True):
+    """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
+
+    ``directions`` is the number of members owned by this rank.  Returns (local fitness, bucket); the
+    full-population gradient is left in ``.grad`` of the model's parameters on every rank."""
+    if new_noise:
+        perturbed_model.set_noise(noise_scale)
+    fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk)
+    everyone = ndist.gather_fitness(fitness, group)
+    weights_all = centered_ranks(everyone)
+    rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
+    world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
+    # ranks own contiguous member slices in rank order (sizes may differ by one)
+    sizes = [ndist.member_slice(everyone.numel(), r, world) for r in range(world)]
+    lo, hi = sizes[rank]
+    for p in perturbed_model.model.parameters():
+        p.grad = None
+    with torch.no_grad():
+        perturbed_model.update(weights_all[lo:hi].contiguous())
+    bucket = ndist.all_reduce_grads(perturbed_model.model.parameters(), bucket, group)
+    return fitness, bucket

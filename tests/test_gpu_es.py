@@ -1,0 +1,84 @@
+"""The ES step on the small CNN of the last benchmark configuration (reduced population), against the
+CPU oracle evaluated layer by layer on the same injected noise."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gpu_util import DEV, assert_close, rel_err
+from oracle import perturbed_ref as O
+
+pytestmark = pytest.mark.gpu
+
+
+def build(base, D):
+    return torch.nn.Sequential(
+        base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
+        base.PermutedConv2d(32, 64, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Flatten(),
+        base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(DEV)
+
+
+def oracle_forward(layers, x, D):
+    c = lambda t: None if t is None else t.detach().cpu()
+    for layer in layers:
+        name = type(layer).__name__
+        if name == "PermutedConv2d":
+            x = O.permuted_conv2d_forward(x, c(layer.weight), c(layer.bias), c(layer.weight_noise), c(layer.bias_noise),
+                                          c(layer.input_permutations), c(layer.output_permutations), D, 1, 0, 1, False)
+        elif name == "PermutedLinear":
+            x = O.permuted_linear_forward(x, c(layer.weight), c(layer.bias), c(layer.weight_noise), c(layer.bias_noise),
+                                          c(layer.input_permutations), c(layer.output_permutations), D, False)
+        else:
+            x = layer(x)
+    return x
+
+
+def test_es_step_small_population():
+    from nesgpu_b200 import base, es
+    D, R = 6, 5
+    torch.manual_seed(0)
+    net = build(base, D)
+    pm = base.PerturbedModel(net, D)
+    modes = [(l.permute_inputs, l.permute_outputs) for l in pm.perturbed_layers]
+    assert modes == [(False, True), (False, True), (True, False), (True, False)]     # auto: out, out, in, in
+    pm.set_noise_scale(0.02)
+    pm.set_seed(11)
+    images = torch.rand(R, 1, 28, 28, device=DEV)
+    labels = torch.randint(10, (R,), device=DEV)
+    fitness, _ = es.es_step(pm, images, labels, D, chunk=2)
+    # oracle: same noise, whole batch at once
+    xb = images.cpu().unsqueeze(1).expand(R, D, 1, 28, 28).reshape(R * D, 1, 28, 28)
+    logits = oracle_forward(list(net), xb, D)
+    ce = F.cross_entropy(logits, labels.cpu().repeat_interleave(D), reduction="none").view(R, D)
+    want_fit = -ce.mean(dim=0)
+    assert_close(fitness, want_fit, tol=1e-4, what="fitness")
+    w = O.centered_ranks(want_fit)
+    assert torch.equal(es.centered_ranks(fitness).cpu(), w)
+    c = lambda t: None if t is None else t.detach().cpu()
+    for layer in pm.perturbed_layers:
+        if type(layer).__name__ == "PermutedConv2d":
+            g = O.permuted_conv2d_weight_grad(c(layer.weight_noise), w, c(layer.input_permutations),
+                                              c(layer.output_permutations), layer.in_channels, layer.out_channels)
+        else:
+            g = O.permuted_linear_weight_grad(c(layer.weight_noise), w, c(layer.input_permutations),
+                                              c(layer.output_permutations), layer.in_features, layer.out_features)
+        assert_close(layer.weight.grad, g, tol=1e-4, what=type(layer).__name__ + " grad")
+        assert_close(layer.bias.grad, w @ c(layer.bias_noise), tol=1e-4, what="bias grad")
+
+
+def test_es_step_tensor_core_conv_close_to_fp32():
+    """conv2 (32 -> 64 channels) on the TF32 tensor-core path: fitness within the stated reduced-precision bar."""
+    from nesgpu_b200 import base, es
+    D, R = 8, 4
+    torch.manual_seed(1)
+    net = build(base, D)
+    pm = base.PerturbedModel(net, D)
+    pm.set_noise_scale(0.02)
+    pm.set_seed(5)
+    pm.set_noise()
+    images = torch.rand(R, 1, 28, 28, device=DEV)
+    labels = torch.randint(10, (R,), device=DEV)
+    f32 = es.population_fitness(pm, images, labels, D, chunk=4)
+    net[3].options = {"tc": "tf32"}
+    tf32 = es.population_fitness(pm, images, labels, D, chunk=4)
+    assert rel_err(tf32, f32.cpu()) <= 2e-2
+    assert not torch.equal(tf32, f32)
