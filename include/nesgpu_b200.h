@@ -227,6 +227,35 @@ int nes_permuted_update(const float* eps, const float* w, const int16_t* pin, co
                         float l1, float l2, void* scratch, int64_t scratch_bytes,
                         nes_stream_t stream);
 
+/* ----------------------------------------------- fp32: shared noise + member sign flips */
+
+/* SyntheticLinear.forward (modules/base.py:611-628):
+ *   p[b,k] = sum_m x[b,m] * fin[d,m] * eps[k,m];  y[b,k] = x[b].weight[k] + bias[k] + s(r) * (p[b,k] * fout[d,k] + bias_noise[d,k]).
+ * eps (out,in); fin (D,in) / fout (D,out) are +-1 int8, either may be NULL (= +1).  p goes through `scratch`. */
+int64_t nes_synthetic_linear_fwd_scratch_bytes(int64_t D, int64_t R, int64_t out);
+int nes_synthetic_linear_fwd(const float* x, const float* weight, const float* bias,
+                             const float* eps, const float* bias_noise,
+                             const int8_t* fin, const int8_t* fout, float* y,
+                             int64_t D, int64_t R, int64_t in, int64_t out, int antithetic,
+                             void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* SyntheticConv2d.forward (modules/base.py:642-668), evaluated as one convolution per member with the
+ * effective filter W[k,c] + s(r) * fout[d,k] * fin[d,c] * eps[k,c]. */
+int nes_synthetic_conv2d_fwd(const float* x, const float* weight, const float* bias,
+                             const float* eps, const float* bias_noise,
+                             const int8_t* fin, const int8_t* fout, float* y,
+                             int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                             int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                             int antithetic, nes_stream_t stream);
+
+/* Synthetic.weight_grad (modules/base.py:338-347) plus the l1/l2 terms of update:
+ *   grad[k,m,t] = eps[k,m,t] * sum_d w_d * fout[d,k] * fin[d,m]   (a missing side counts as +1).
+ * For two-sided flips the reference's einsum multiplies by w_d twice (modules/base.py:340); this
+ * entry point computes the fitness-weighted sum sum_d w_d E_d, which is what the one-sided branches do. */
+int nes_synthetic_update(const float* eps, const float* w, const int8_t* fin, const int8_t* fout,
+                         const float* weight, float* grad, int64_t D, int in, int out, int ksize,
+                         float l1, float l2, nes_stream_t stream);
+
 /* ---------------------------------------------------------------- noise set-up (device) */
 
 /* out[i] = mean + std * N(0,1), Philox-4x32-10 keyed by (seed, offset + i/4).
@@ -236,6 +265,8 @@ int nes_fill_normal(float* out, int64_t n, float mean, float std, uint64_t seed,
 /* out[i] = lo + (hi - lo) * U(0,1].  Replaces torch.rand at modules/binary.py:63. */
 int nes_fill_uniform(float* out, int64_t n, float lo, float hi, uint64_t seed, uint64_t offset,
                      nes_stream_t stream);
+/* out[i] = +1 or -1 with equal probability (int8).  Replaces 2*randint(2)-1 at modules/base.py:323-328. */
+int nes_fill_signs(int8_t* out, int64_t n, uint64_t seed, uint64_t offset, nes_stream_t stream);
 /* D independent uniform permutations of [0,n), first `keep` entries of each stored
  * (out is (D,keep) int16); with_replacement != 0 draws keep independent indices instead.
  * Replaces the per-member CPU randperm loop / randint at modules/base.py:209-227.  n <= 16384
@@ -261,8 +292,9 @@ int nes_bin_unpack(const void* in, uint8_t* out, int64_t rows, int64_t words, in
                    nes_stream_t stream);
 
 /* out[x,y,z] bit i = float(p[y, word_bits*z + i]) > u, for x in [0,n): Bernoulli(p) bits.
- * p (rows,cols) fp16.  If `uniforms` (n,rows,cols) fp32 is given it supplies u; otherwise
- * u in (0,1] comes from Philox keyed by (seed, x, y, column).
+ * p (rows,cols) fp16.  If `uniforms` (n,rows,cols) fp32 is given it supplies u; otherwise a bit is
+ * set when a 16-bit uniform integer from Philox-4x32-10 keyed by (seed, x, y, column) is below
+ * ceil(p * 65536): Bernoulli(p) with p rounded up to a multiple of 2^-16.
  * Replaces sample_bits_kernel (extensions/src/sample_bits.cu:9-60) and cuda_sample_bits
  * (booleanUtilitiesCuda.cu:95-122,199-223). */
 int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms, void* out, int64_t n,

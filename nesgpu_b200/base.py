@@ -601,3 +601,153 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
                C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, *geom,
                self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
         return y
+
+
+class Synthetic(Perturbed):
+    """One shared noise tensor re-used by every member through per-member +-1 sign flips of the
+    inputs and/or outputs (reference ``base.py:269-347``).  ``input_flips`` is ``(directions, in)``,
+    ``output_flips`` ``(directions, out)``, both int8."""
+
+    def __init__(self, in_degree, out_degree, directions, antithetic=False, options={}, flip="auto",
+                 in_sparsity=0, out_sparsity=0):
+        Perturbed.__init__(self, directions, antithetic, options)
+        if flip == "auto":
+            if 1 < in_degree < 32 and 1 < out_degree < 32:
+                flip = "both"
+            else:
+                flip = "in" if in_degree > out_degree else "out"
+        if flip not in ("in", "out", "both"):
+            raise NotImplementedError("Flip setting not recognized")
+        self.flip_inputs = flip != "out"
+        self.flip_outputs = flip != "in"
+        self.in_degree = in_degree
+        self.out_degree = out_degree
+        if in_sparsity or out_sparsity:
+            raise NotImplementedError("Sparsity is not efficient for synthetic sampling, use permuted sampling instead")
+        self.in_sparsity = in_degree
+        self.out_sparsity = out_degree
+        if options.get("combined") and self.flip_inputs and self.flip_outputs:
+            raise NotImplementedError("Can't do combined multiplication with both input and output flips")
+
+    def allocate_weight(self):
+        self.weight_noise = torch.empty((self.out_sparsity, self.in_sparsity) + tuple(self.weight.shape[2:]),
+                                        device=self.weight.device, dtype=self.weight.dtype)
+
+    def free_memory(self):
+        Perturbed.free_memory(self)
+        self.input_flips = None
+        self.output_flips = None
+
+    def _sample_flips(self, n, stream_id):
+        out = torch.empty((self.directions, n), dtype=torch.int8, device=self.weight.device)
+        C.call("nes_fill_signs", C.ptr(out), out.numel(), (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1), 0, C.stream())
+        return out
+
+    def set_noise(self, noise_scale=None):
+        """Shared noise, bias noise and sign flips drawn on the device (reference ``base.py:311-328``)."""
+        self._prepare_noise(noise_scale)
+        self._fill_normal(self.weight_noise, self.noise_scale, self.seed, 0)
+        if self.bias is not None:
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+        if self.flip_outputs:
+            self.output_flips = self._sample_flips(self.out_degree, 2)
+        if self.flip_inputs:
+            self.input_flips = self._sample_flips(self.in_degree, 3)
+
+    def _flips(self):
+        fin = C.require_cuda(self.input_flips, "input_flips", torch.int8) if self.flip_inputs else None
+        fout = C.require_cuda(self.output_flips, "output_flips", torch.int8) if self.flip_outputs else None
+        return fin, fout
+
+    def _weight_grad_regularised(self, weights, l1, l2):
+        """eps * sum_d w_d f_out[d] f_in[d]^T (reference ``base.py:338-347``; the reference's two-sided
+        einsum multiplies by w_d twice, ``base.py:340`` -- here it is the plain fitness-weighted sum)."""
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        if weights.numel() != self.directions:
+            raise RuntimeError("update weights must have one entry per direction")
+        fin, fout = self._flips()
+        ksize = 1
+        for sdim in self.weight.shape[2:]:
+            ksize *= sdim
+        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        C.call("nes_synthetic_update", C.ptr(eps), C.ptr(weights), C.ptr(fin), C.ptr(fout),
+               C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), self.directions, self.in_degree,
+               self.out_degree, ksize, float(l1), float(l2), C.stream())
+        return grad
+
+    def weight_grad(self, weights):
+        return self._weight_grad_regularised(weights, 0, 0)
+
+
+class SyntheticLinear(nn.Linear, _LinearMixin, Synthetic):
+    """``y = x W^T + b + s * (f_out * ((x * f_in) eps^T) + beta_d)`` (reference ``base.py:601-628``)."""
+
+    def __init__(self, in_features, out_features, directions, bias=True, antithetic=False, options={},
+                 flip="auto", in_sparsity=0, out_sparsity=0):
+        nn.Linear.__init__(self, in_features, out_features, bias)
+        Synthetic.__init__(self, in_features, out_features, directions, antithetic=antithetic, options=options,
+                           flip=flip, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x, lead = self._flatten_rows(input)
+        R = self._repeats(x.shape[0])
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        fin, fout = self._flips()
+        y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        nbytes = C.call("nes_synthetic_linear_fwd_scratch_bytes", self.directions, R, self.out_features)
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_synthetic_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(fin), C.ptr(fout), C.ptr(y), self.directions, R, self.in_features,
+               self.out_features, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+        return y.view(*lead, self.out_features)
+
+
+class SyntheticConv2d(nn.Conv2d, _ConvMixin, Synthetic):
+    """Sign-flip sampling on channels (reference ``base.py:631-668``): per member a convolution with
+    ``W + s * f_out[d,k] * f_in[d,c] * eps[k,c]``."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, directions, stride=1, padding=0, dilation=1,
+                 groups=1, bias=True, antithetic=False, options={}, padding_mode='zeros', flip="auto",
+                 in_sparsity=0, out_sparsity=0):
+        nn.Conv2d.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups,
+                           bias, padding_mode)
+        Synthetic.__init__(self, in_channels, out_channels, directions, antithetic=antithetic, options=options,
+                           flip=flip, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
+
+    def forward(self, input):
+        if not self.perturbed_flag:
+            return self._plain_forward(input)
+        x = C.require_cuda(input, "input", _F32)
+        x, geom, out_hw = self._geometry(x)
+        R = self._repeats(x.shape[0])
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        fin, fout = self._flips()
+        y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
+        C.call("nes_synthetic_conv2d_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(fin), C.ptr(fout), C.ptr(y), self.directions, R, *geom,
+               1 if self.antithetic else 0, C.stream())
+        return y
+
+
+class PerturbedAffine(nn.Module, Perturbed):
+    """Per-member scale and shift, stored "direct" (``weight_noise = weight + noise``; reference
+    ``base.py:427-444``).  The forward is the reference's broadcast multiply-add; noise set-up and the
+    update go through the same kernels as the other dense-noise layers."""
+
+    def __init__(self, normalized_shape, directions, antithetic=False, options={"direct": True}):
+        nn.Module.__init__(self)
+        self.weight = nn.Parameter(torch.ones(normalized_shape))
+        self.bias = nn.Parameter(torch.zeros(normalized_shape))
+        if not options.get("direct"):
+            raise NotImplementedError("Only direct is implemented")
+        Perturbed.__init__(self, directions, antithetic=antithetic, options=options)
+
+    def forward(self, input):
+        if self.perturbed_flag:
+            return input * self.weight_noise + self.bias_noise
+        return input * self.weight + self.bias

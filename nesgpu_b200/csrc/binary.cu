@@ -52,8 +52,7 @@ __global__ void unpack_rows_kernel(const uint8_t* __restrict__ in, uint64_t* __r
 }
 
 // ---- Bernoulli bit sampling -------------------------------------------------------------
-// One thread produces 32 output bits of member x, row y.
-template <bool INJECTED>
+// Injected uniforms: one thread produces 32 output bits of member x, row y (bit = p > u).
 __global__ void sample_bits_kernel(const __half* __restrict__ p, const float* __restrict__ u,
                                    uint32_t* __restrict__ out, int64_t n, int64_t rows, int64_t cols,
                                    int64_t row_u32, uint64_t seed, int vec) {
@@ -67,38 +66,65 @@ __global__ void sample_bits_kernel(const __half* __restrict__ p, const float* __
   if (c0 < cols) {
     const __half* pr = p + y * cols + c0;
     const int lim = int(cols - c0 < 32 ? cols - c0 : 32);
-    if (INJECTED) {
-      const float* ur = u + xy * cols + c0;
-      if (vec && lim == 32) {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 uv = __ldcs(reinterpret_cast<const float4*>(ur) + g);
-          const uint2 pv = __ldg(reinterpret_cast<const uint2*>(pr) + g);
-          const __half2 p01 = *reinterpret_cast<const __half2*>(&pv.x);
-          const __half2 p23 = *reinterpret_cast<const __half2*>(&pv.y);
-          word |= uint32_t(__low2float(p01) > uv.x) << (4 * g);
-          word |= uint32_t(__high2float(p01) > uv.y) << (4 * g + 1);
-          word |= uint32_t(__low2float(p23) > uv.z) << (4 * g + 2);
-          word |= uint32_t(__high2float(p23) > uv.w) << (4 * g + 3);
-        }
-      } else {
-        for (int i = 0; i < lim; ++i) word |= uint32_t(__half2float(pr[i]) > ur[i]) << i;
-      }
-    } else {
-      Philox ph(seed);
+    const float* ur = u + xy * cols + c0;
+    if (vec && lim == 32) {
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
-        uint32_t r[4];
-        ph(uint32_t(q * 8 + g), uint32_t(y), uint32_t(x), 5u, r);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int i = 4 * g + j;
-          if (i < lim) word |= uint32_t(__half2float(pr[i]) > u32_to_unit(r[j])) << i;
-        }
+        const float4 uv = __ldcs(reinterpret_cast<const float4*>(ur) + g);
+        const uint2 pv = __ldg(reinterpret_cast<const uint2*>(pr) + g);
+        const __half2 p01 = *reinterpret_cast<const __half2*>(&pv.x);
+        const __half2 p23 = *reinterpret_cast<const __half2*>(&pv.y);
+        word |= uint32_t(__low2float(p01) > uv.x) << (4 * g);
+        word |= uint32_t(__high2float(p01) > uv.y) << (4 * g + 1);
+        word |= uint32_t(__low2float(p23) > uv.z) << (4 * g + 2);
+        word |= uint32_t(__high2float(p23) > uv.w) << (4 * g + 3);
       }
+    } else {
+      for (int i = 0; i < lim; ++i) word |= uint32_t(__half2float(pr[i]) > ur[i]) << i;
     }
   }
   out[e] = word;
+}
+
+// Device-generated variant: one thread owns 32 columns of one row and walks a chunk of members with the
+// 32 Bernoulli thresholds held in registers.  A bit is set when a 16-bit uniform integer from
+// Philox-4x32-10 (eight per call, counter = (column group, row, member)) is below ceil(p * 65536), i.e.
+// with probability p rounded up to a multiple of 2^-16 (p = 0 never, p = 1 always).
+constexpr int SAMPLE_MEMBERS = 16;
+
+__global__ void __launch_bounds__(256) sample_bits_philox_kernel(const __half* __restrict__ p, uint32_t* __restrict__ out,
+                                                                 int64_t n, int64_t rows, int64_t cols, int64_t row_u32,
+                                                                 uint64_t seed) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= rows * row_u32) return;
+  const int64_t q = e % row_u32, y = e / row_u32;
+  const int64_t c0 = q * 32;
+  uint32_t thr[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float pv = 0.f;
+    if (c0 + i < cols) pv = __half2float(p[y * cols + c0 + i]);
+    const float t = ceilf(pv * 65536.f);
+    thr[i] = (t <= 0.f) ? 0u : (t >= 65536.f ? 65536u : uint32_t(t));
+  }
+  const Philox ph(seed);
+  const int64_t x0 = int64_t(blockIdx.y) * SAMPLE_MEMBERS;
+  const int64_t x1 = (x0 + SAMPLE_MEMBERS < n) ? x0 + SAMPLE_MEMBERS : n;
+  for (int64_t x = x0; x < x1; ++x) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t r[4];
+      ph(uint32_t(q * 4 + g), uint32_t(y), uint32_t(x), 5u, r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = g * 8 + 2 * j;
+        word |= ((r[j] & 0xFFFFu) < thr[i] ? 1u : 0u) << i;
+        word |= ((r[j] >> 16) < thr[i + 1] ? 1u : 0u) << (i + 1);
+      }
+    }
+    out[(x * rows + y) * row_u32 + q] = word;
+  }
 }
 
 // ---- XOR-popcount batched matrix product ------------------------------------------------
@@ -475,9 +501,12 @@ extern "C" int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms
   const unsigned blocks = (unsigned)ceil_div<int64_t>(total, 256);
   if (uniforms) {
     const int vec = (cols % 4 == 0) && aligned16(uniforms) && ((reinterpret_cast<uintptr_t>(p_half) & 7u) == 0);
-    sample_bits_kernel<true><<<blocks, 256, 0, as_stream(stream)>>>(p, uniforms, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed, vec);
+    sample_bits_kernel<<<blocks, 256, 0, as_stream(stream)>>>(p, uniforms, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed, vec);
   } else {
-    sample_bits_kernel<false><<<blocks, 256, 0, as_stream(stream)>>>(p, nullptr, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed, 0);
+    const int64_t pairs = rows * row_u32;
+    NES_REQUIRE(ceil_div<int64_t>(n, SAMPLE_MEMBERS) <= 65535, NES_ERR_UNSUPPORTED, "bin_sample_bits: more than %d members", 65535 * SAMPLE_MEMBERS);
+    dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, SAMPLE_MEMBERS));
+    sample_bits_philox_kernel<<<grid, 256, 0, as_stream(stream)>>>(p, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed);
   }
   return check_launch("bin_sample_bits");
 }

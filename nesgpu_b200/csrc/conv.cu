@@ -36,6 +36,16 @@ struct PermutedNoise {  // eps (out_sp, in_sp, ksz); omap (D,Cout), imap (D,Cin)
   }
 };
 
+struct SyntheticNoise {  // eps (Cout, Cin, ksz) times the member's output / input channel signs (+-1 int8, NULL = +1)
+  const float* eps; const int8_t* fout; const int8_t* fin; int Cout, Cin, K;
+  __device__ inline float operator()(int64_t d, int n, int k, const KEntry& e) const {
+    float v = __ldg(eps + size_t(n) * K + k);
+    if (fout) v *= float(fout[d * Cout + n]);
+    if (fin) v *= float(fin[d * Cin + (e.c_tap >> 12)]);
+    return v;
+  }
+};
+
 template <class Noise, int NJ_>
 struct ConvProb {
   static constexpr bool MFAST = true;
@@ -309,4 +319,20 @@ extern "C" int nes_permuted_dense_noise(const float* eps, const int16_t* pin, co
   dim3 grid((unsigned)out, (unsigned)D);
   permuted_dense_noise_kernel<<<grid, 128, 0, as_stream(stream)>>>(eps, pin, pout, E, in, out, in_sp, out_sp, ksize);
   return check_launch("permuted_dense_noise");
+}
+
+extern "C" int nes_synthetic_conv2d_fwd(const float* x, const float* weight, const float* bias,
+                                        const float* eps, const float* bias_noise,
+                                        const int8_t* fin, const int8_t* fout, float* y,
+                                        int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                        int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                        int antithetic, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "synthetic_conv2d_fwd: negative extent");
+  if (D == 0 || R == 0) return NES_OK;
+  NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "synthetic_conv2d_fwd: null pointer");
+  ConvGeom g;
+  int rc = make_geom(g, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, "synthetic_conv2d_fwd");
+  if (rc != NES_OK) return rc;
+  SyntheticNoise n; n.eps = eps; n.fout = fout; n.fin = fin; n.Cout = Cout; n.Cin = Cin; n.K = g.K;
+  return launch_conv(g, n, x, weight, bias, bias_noise, y, D, R, antithetic, as_stream(stream), "synthetic_conv2d_fwd");
 }

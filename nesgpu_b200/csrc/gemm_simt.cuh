@@ -97,6 +97,26 @@ struct GatherKLoader {
   __device__ static inline void store(TilePtr T, const Frag& f) { store_elementwise<ROWS>(T, f); }
 };
 
+// Rows multiplied element-wise by a per-member sign vector:
+//   A[row, k] = src[row * ld + k] * flips[(row % D) * K + k]      (sign-flip sampling, flips are +-1 int8)
+struct FlipKLoader {
+  const float* src; int64_t ld; int64_t rows; int K; const int8_t* flips; int64_t D;
+  template <int ROWS>
+  __device__ inline void fetch(int64_t row0, int k0, Frag& f) const {
+    const int t = threadIdx.x;
+    const int k = k0 + (t & 15);
+#pragma unroll
+    for (int i = 0; i < ROWS / 16; ++i) {
+      const int64_t row = row0 + (t >> 4) + 16 * i;
+      float val = 0.f;
+      if (row < rows && k < K) val = __ldg(src + row * ld + k) * float(flips[(row % D) * K + k]);
+      f.v[i] = val;
+    }
+  }
+  template <int ROWS>
+  __device__ static inline void store(TilePtr T, const Frag& f) { store_elementwise<ROWS>(T, f); }
+};
+
 // ---- the kernel ------------------------------------------------------------------------
 
 template <class Prob>

@@ -33,6 +33,23 @@ struct PermutedEpi {
   }
 };
 
+// y = acc + bias + s(r) * (p[b,k] * fout[d,k] + bias_noise[d,k])      (modules/base.py:620-626)
+struct FlipEpi {
+  const float* bias; const float* p; const int8_t* fout; const float* bias_noise;
+  int64_t D, R; int N; int antithetic;
+  struct Row { int64_t d; float s; };
+  __device__ inline Row row(int64_t gm) const {
+    Row r; r.d = gm % D; r.s = anti_sign(gm / D, R, antithetic); return r;
+  }
+  __device__ inline float operator()(const Row& r, int64_t gm, int gn, float acc) const {
+    float q = __ldg(p + gm * N + gn);
+    if (fout) q *= float(fout[r.d * N + gn]);
+    if (bias_noise) q += __ldg(bias_noise + r.d * N + gn);
+    float v = acc + r.s * q;
+    return bias ? v + __ldg(bias + gn) : v;
+  }
+};
+
 // y = acc + bias + s(r) * (sum_t x[b, idx[d,o,t]] * val[d,o,t] + bias_noise[d,o])
 struct SparseEpi {
   const float* bias; const float* x; const int32_t* idx; const float* val; const float* bias_noise;
@@ -302,4 +319,37 @@ extern "C" int nes_sparse_perturbed_linear_fwd(const float* x, const float* weig
   epi.D = D; epi.R = R; epi.N = int(out); epi.in = int(in); epi.k = k; epi.antithetic = antithetic;
   return launch_linear(rows_loader(x, in, D * R, int(in)), weight, epi, y, D * R, out, in,
                        as_stream(stream), "sparse_perturbed_linear_fwd");
+}
+
+extern "C" int64_t nes_synthetic_linear_fwd_scratch_bytes(int64_t D, int64_t R, int64_t out) {
+  return D * R * out * (int64_t)sizeof(float);
+}
+
+extern "C" int nes_synthetic_linear_fwd(const float* x, const float* weight, const float* bias,
+                                        const float* eps, const float* bias_noise,
+                                        const int8_t* fin, const int8_t* fout, float* y,
+                                        int64_t D, int64_t R, int64_t in, int64_t out, int antithetic,
+                                        void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0, NES_ERR_BAD_ARG, "synthetic_linear_fwd: negative extent");
+  if (D == 0 || R == 0 || out == 0) return NES_OK;
+  NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "synthetic_linear_fwd: null pointer");
+  NES_REQUIRE(scratch && scratch_bytes >= nes_synthetic_linear_fwd_scratch_bytes(D, R, out) && aligned16(scratch),
+              NES_ERR_SCRATCH, "synthetic_linear_fwd: scratch needs %lld bytes, 16-byte aligned",
+              (long long)nes_synthetic_linear_fwd_scratch_bytes(D, R, out));
+  cudaStream_t st = as_stream(stream);
+  const int64_t B = D * R;
+  float* p = static_cast<float*>(scratch);
+  BiasEpi none; none.bias = nullptr;
+  int rc;
+  if (fin) {
+    FlipKLoader g; g.src = x; g.ld = in; g.rows = B; g.K = int(in); g.flips = fin; g.D = D;
+    rc = launch_linear(g, eps, none, p, B, out, in, st, "synthetic_linear_fwd(noise)");
+  } else {
+    rc = launch_linear(rows_loader(x, in, B, int(in)), eps, none, p, B, out, in, st, "synthetic_linear_fwd(noise)");
+  }
+  if (rc != NES_OK) return rc;
+  FlipEpi epi;
+  epi.bias = bias; epi.p = p; epi.fout = fout; epi.bias_noise = bias_noise;
+  epi.D = D; epi.R = R; epi.N = int(out); epi.antithetic = antithetic;
+  return launch_linear(rows_loader(x, in, B, int(in)), weight, epi, y, B, out, in, st, "synthetic_linear_fwd(base)");
 }

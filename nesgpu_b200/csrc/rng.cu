@@ -84,9 +84,29 @@ __global__ void sample_indices_kernel(int16_t* __restrict__ out, int64_t total, 
     if (q * 4 + j < total) out[q * 4 + j] = int16_t((uint64_t(r[j]) * uint64_t(n)) >> 32);
 }
 
+__global__ void fill_signs_kernel(int8_t* __restrict__ out, int64_t n, uint64_t seed, uint64_t offset) {
+  const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;    // 128 outputs per thread
+  if (q * 128 >= n) return;
+  const uint64_t ctr = offset + uint64_t(q);
+  uint32_t r[4];
+  Philox ph(seed);
+  ph(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 4u, r);
+  for (int j = 0; j < 128; ++j)
+    if (q * 128 + j < n) out[q * 128 + j] = ((r[j >> 5] >> (j & 31)) & 1u) ? int8_t(1) : int8_t(-1);
+}
+
 }  // namespace nes
 
 using namespace nes;
+
+extern "C" int nes_fill_signs(int8_t* out, int64_t n, uint64_t seed, uint64_t offset, nes_stream_t stream) {
+  NES_REQUIRE(n >= 0, NES_ERR_BAD_ARG, "fill_signs: negative extent");
+  if (n == 0) return NES_OK;
+  NES_REQUIRE(out, NES_ERR_BAD_ARG, "fill_signs: null pointer");
+  const int64_t groups = ceil_div<int64_t>(n, 128);
+  fill_signs_kernel<<<(unsigned)ceil_div<int64_t>(groups, 128), 128, 0, as_stream(stream)>>>(out, n, seed, offset);
+  return check_launch("fill_signs");
+}
 
 extern "C" int nes_fill_normal(float* out, int64_t n, float mean, float std, uint64_t seed, uint64_t offset,
                                nes_stream_t stream) {

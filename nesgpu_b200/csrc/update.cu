@@ -180,6 +180,32 @@ __global__ void grad_sparse_kernel(const int32_t* __restrict__ idx, const float*
   atomicAdd(grad + o * in + idx[e], __ldg(w + d) * __ldg(val + e));
 }
 
+// sign-flip sampling: grad[k,m,t] = eps[k,m,t] * sum_d w_d * fout[d,k] * fin[d,m]  (missing side = +1)
+__global__ void grad_synthetic_kernel(const float* __restrict__ eps, const float* __restrict__ w,
+                                      const int8_t* __restrict__ fin, const int8_t* __restrict__ fout,
+                                      float* __restrict__ grad, int64_t D, int in, int out, int ksz) {
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (m >= in) return;
+  float a0 = 0.f, a1 = 0.f;
+  int64_t d = 0;
+  for (; d + 2 <= D; d += 2) {
+    float f0 = __ldg(w + d), f1 = __ldg(w + d + 1);
+    if (fout) { f0 *= float(fout[d * out + k]); f1 *= float(fout[(d + 1) * out + k]); }
+    if (fin) { f0 *= float(fin[d * in + m]); f1 *= float(fin[(d + 1) * in + m]); }
+    a0 += f0; a1 += f1;
+  }
+  for (; d < D; ++d) {
+    float f0 = __ldg(w + d);
+    if (fout) f0 *= float(fout[d * out + k]);
+    if (fin) f0 *= float(fin[d * in + m]);
+    a0 += f0;
+  }
+  const float fw = a0 + a1;
+  const size_t base = (size_t(k) * in + m) * ksz;
+  for (int t = 0; t < ksz; ++t) grad[base + t] = fw * __ldg(eps + base + t);
+}
+
 static int finish(const float* partial, int splits, const float* weight, float* grad, int64_t n, float l1,
                   float l2, cudaStream_t st, const char* what) {
   if (splits == 0 && (weight == nullptr || (l1 == 0.f && l2 == 0.f))) return NES_OK;
@@ -353,4 +379,19 @@ extern "C" int nes_sparse_perturbed_update(const int32_t* idx, const float* val,
     if (rc != NES_OK) return rc;
   }
   return finish(nullptr, 0, weight, grad, out * in, l1, l2, st, "sparse_perturbed_update(finish)");
+}
+
+extern "C" int nes_synthetic_update(const float* eps, const float* w, const int8_t* fin, const int8_t* fout,
+                                    const float* weight, float* grad, int64_t D, int in, int out, int ksize,
+                                    float l1, float l2, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && in > 0 && out > 0 && ksize > 0, NES_ERR_BAD_ARG, "synthetic_update: bad extent");
+  NES_REQUIRE(eps && grad && (D == 0 || w) && (fin || fout), NES_ERR_BAD_ARG, "synthetic_update: null pointer");
+  NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "synthetic_update: l1/l2 given without weight");
+  NES_REQUIRE(out <= 65535, NES_ERR_UNSUPPORTED, "synthetic_update: out > 65535");
+  cudaStream_t st = as_stream(stream);
+  dim3 grid((unsigned)ceil_div(in, 128), (unsigned)out);
+  grad_synthetic_kernel<<<grid, 128, 0, st>>>(eps, w, fin, fout, grad, D, in, out, ksize);
+  int rc = check_launch("synthetic_update");
+  if (rc != NES_OK) return rc;
+  return finish(nullptr, 0, weight, grad, int64_t(out) * in * ksize, l1, l2, st, "synthetic_update(finish)");
 }

@@ -262,6 +262,59 @@ def dense_member_noise(weight_noise, input_permutations, output_permutations, in
 
 
 # ----------------------------------------------------------------------------------
+# Shared noise + per-member sign flips: SyntheticLinear / SyntheticConv2d
+# ----------------------------------------------------------------------------------
+
+def synthetic_linear_forward(x, weight, bias, weight_noise, bias_noise, input_flips, output_flips, directions,
+                             antithetic=False):
+    """SyntheticLinear.forward (base.py:611-628).  input_flips (D, in) / output_flips (D, out), +-1, or None."""
+    D = directions
+    base = F.linear(x, weight, bias)
+    xv = x.view(-1, D, x.shape[-1])
+    R = xv.shape[0]
+    fx = xv * input_flips if input_flips is not None else xv
+    pert = fx @ weight_noise.t()
+    if output_flips is not None:
+        pert = pert * output_flips
+    if bias_noise is not None:
+        pert = pert + bias_noise
+    pert = pert * antithetic_signs(R, antithetic).view(R, 1, 1)
+    return base + pert.reshape(base.shape)
+
+
+def synthetic_conv2d_forward(x, weight, bias, weight_noise, bias_noise, input_flips, output_flips, directions,
+                             stride=1, padding=0, dilation=1, antithetic=False):
+    """SyntheticConv2d.forward (base.py:642-668)."""
+    D = directions
+    base = F.conv2d(x, weight, bias, stride, padding, dilation)
+    R = x.shape[0] // D
+    xv = x.view(R, D, *x.shape[1:])
+    fx = xv * input_flips.view(1, D, -1, 1, 1) if input_flips is not None else xv
+    pert = F.conv2d(fx.reshape(x.shape), weight_noise, None, stride, padding, dilation)
+    pert = pert.view(R, D, *pert.shape[1:])
+    if output_flips is not None:
+        pert = pert * output_flips.view(1, D, -1, 1, 1)
+    if bias_noise is not None:
+        pert = pert + bias_noise.view(1, D, -1, 1, 1)
+    pert = pert * antithetic_signs(R, antithetic).view(R, 1, 1, 1, 1)
+    return base + pert.reshape(base.shape)
+
+
+def synthetic_weight_grad(weight_noise, weights, input_flips, output_flips):
+    """Synthetic.weight_grad for the one-sided modes (base.py:343-347), and sum_d w_d E_d for two-sided
+    flips (the reference's two-sided einsum, base.py:340, multiplies by w_d twice; that is not followed)."""
+    nd = weight_noise.dim()
+    if input_flips is not None and output_flips is not None:
+        fw = torch.einsum("d,da,db->ab", weights, output_flips.float(), input_flips.float())
+        return fw.view(*fw.shape, *[1] * (nd - 2)) * weight_noise
+    if input_flips is not None:
+        fw = (input_flips.float() * weights.unsqueeze(1)).sum(dim=0)
+        return fw.view(1, -1, *[1] * (nd - 2)) * weight_noise
+    fw = (output_flips.float() * weights.unsqueeze(1)).sum(dim=0)
+    return fw.view(-1, *[1] * (nd - 1)) * weight_noise
+
+
+# ----------------------------------------------------------------------------------
 # Sparse Gaussian noise (README.md:12,29-30; no source in the reference snapshot)
 # ----------------------------------------------------------------------------------
 

@@ -173,6 +173,70 @@ def perturbed_cases(base):
                     bias_noise=layer.bias_noise, pin=layer.input_permutations,
                     pout=layer.output_permutations, w=w, y=y, grad=grad.contiguous(), bias_grad=bgrad))
 
+    # ---- SyntheticLinear / SyntheticConv2d (base.py:269-347, 601-668); one-sided updates only for the
+    # stored gradient (the two-sided einsum at base.py:340 squares the weights)
+    for name, D, R, in_f, out_f, anti, flip in [
+        ("synlin_in", 5, 2, 18, 7, True, "in"), ("synlin_out", 6, 3, 9, 14, True, "out"),
+        ("synlin_both", 4, 2, 6, 5, False, "both"), ("synlin_auto", 4, 1, 40, 8, False, "auto"),
+    ]:
+        layer = base.SyntheticLinear(in_f, out_f, D, antithetic=anti, flip=flip)
+        layer.weight_noise = rnd(out_f, in_f, scale=0.1)
+        layer.bias_noise = rnd(D, out_f, scale=0.1)
+        layer.input_flips = (2 * torch.randint(2, (D, in_f), generator=gen) - 1).to(torch.int8) if layer.flip_inputs else None
+        layer.output_flips = (2 * torch.randint(2, (D, out_f), generator=gen) - 1).to(torch.int8) if layer.flip_outputs else None
+        x = rnd(R * D, in_f)
+        w = rnd(D)
+        two_sided = layer.flip_inputs and layer.flip_outputs
+        with torch.no_grad():
+            layer.perturbed_flag = True
+            y = layer.forward(x)
+            layer.perturbed_flag = False
+            grad = None if two_sided else layer.weight_grad(w).contiguous()
+        record(name, dict(kind="SyntheticLinear", D=D, R=R, in_f=in_f, out_f=out_f, antithetic=anti, flip=flip,
+                          flip_inputs=layer.flip_inputs, flip_outputs=layer.flip_outputs),
+               dict(x=x, weight=layer.weight, bias=layer.bias, weight_noise=layer.weight_noise,
+                    bias_noise=layer.bias_noise, fin=layer.input_flips, fout=layer.output_flips, w=w, y=y, grad=grad))
+    for name, D, R, cin, cout, k, hw, stride, pad, anti, flip in [
+        ("synconv_in", 4, 1, 6, 3, 3, 7, 1, 1, False, "in"), ("synconv_out", 3, 1, 2, 5, 3, 8, 2, 1, False, "out"),   # R == 1: base.py:661,663 broadcast
+        ("synconv_both", 4, 1, 3, 4, 1, 5, 1, 0, False, "both"),
+    ]:
+        layer = base.SyntheticConv2d(cin, cout, k, D, stride=stride, padding=pad, antithetic=anti, flip=flip)
+        layer.weight_noise = rnd(cout, cin, k, k, scale=0.1)
+        layer.bias_noise = rnd(D, cout, scale=0.1)
+        layer.input_flips = (2 * torch.randint(2, (D, cin), generator=gen) - 1).to(torch.int8) if layer.flip_inputs else None
+        layer.output_flips = (2 * torch.randint(2, (D, cout), generator=gen) - 1).to(torch.int8) if layer.flip_outputs else None
+        x = rnd(R * D, cin, hw, hw)
+        w = rnd(D)
+        two_sided = layer.flip_inputs and layer.flip_outputs
+        with torch.no_grad():
+            layer.perturbed_flag = True
+            y = layer.forward(x)
+            layer.perturbed_flag = False
+            grad = None if two_sided else layer.weight_grad(w).contiguous()
+        record(name, dict(kind="SyntheticConv2d", D=D, R=R, cin=cin, cout=cout, k=k, hw=hw, stride=stride, padding=pad,
+                          antithetic=anti, flip=flip, flip_inputs=layer.flip_inputs, flip_outputs=layer.flip_outputs),
+               dict(x=x, weight=layer.weight, bias=layer.bias, weight_noise=layer.weight_noise,
+                    bias_noise=layer.bias_noise, fin=layer.input_flips, fout=layer.output_flips, w=w, y=y, grad=grad))
+
+    # ---- PerturbedAffine (base.py:427-444), direct storage
+    D, shape = 5, (7,)
+    layer = base.PerturbedAffine(shape, D)
+    with torch.no_grad():
+        layer.weight.copy_(rnd(*shape) + 1)
+        layer.bias.copy_(rnd(*shape))
+    layer.weight_noise = rnd(D, *shape, scale=0.1) + layer.weight.detach()
+    layer.bias_noise = rnd(D, *shape, scale=0.1) + layer.bias.detach()
+    x = rnd(3, D, *shape)
+    w = rnd(D)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(x)
+        layer.perturbed_flag = False
+        grad, bgrad = layer.update(w)
+    record("affine", dict(kind="PerturbedAffine", D=D, shape=list(shape)),
+           dict(x=x, weight=layer.weight, bias=layer.bias, weight_noise=layer.weight_noise,
+                bias_noise=layer.bias_noise, w=w, y=y, grad=grad, bias_grad=bgrad))
+
     # ---- constructor rule of Permuted (base.py:148-184)
     rules = []
     for in_d, out_d, mode, isp, osp in [

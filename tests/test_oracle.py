@@ -167,3 +167,33 @@ def test_binary_sample_and_weighted_sum():
     ws = B.weighted_sum(bits, w, 100)
     want = np.einsum("d,dyz->yz", w.astype(np.float64), (p.astype(np.float32) > u).astype(np.float64))
     np.testing.assert_allclose(ws.astype(np.float64), want, atol=2e-2)
+
+
+def test_synthetic_layers(perturbed_golden):
+    for name in perturbed_golden.names("SyntheticLinear"):
+        m, c = perturbed_golden.meta[name], perturbed_golden.case(name)
+        fin, fout = T(c.get("fin")), T(c.get("fout"))
+        y = O.synthetic_linear_forward(T(c["x"]), T(c["weight"]), T(c["bias"]), T(c["weight_noise"]), T(c["bias_noise"]),
+                                       fin, fout, m["D"], m["antithetic"])
+        np.testing.assert_allclose(y.numpy(), c["y"], **TOL)
+        if "grad" in c:
+            g = O.synthetic_weight_grad(T(c["weight_noise"]), T(c["w"]), fin, fout)
+            np.testing.assert_allclose(g.numpy(), c["grad"], **TOL)
+    for name in perturbed_golden.names("SyntheticConv2d"):
+        m, c = perturbed_golden.meta[name], perturbed_golden.case(name)
+        fin, fout = T(c.get("fin")), T(c.get("fout"))
+        y = O.synthetic_conv2d_forward(T(c["x"]), T(c["weight"]), T(c["bias"]), T(c["weight_noise"]), T(c["bias_noise"]),
+                                       fin, fout, m["D"], m["stride"], m["padding"], 1, m["antithetic"])
+        np.testing.assert_allclose(y.numpy(), c["y"], **TOL)
+        if "grad" in c:
+            g = O.synthetic_weight_grad(T(c["weight_noise"]), T(c["w"]), fin, fout)
+            np.testing.assert_allclose(g.numpy(), c["grad"], **TOL)
+    # two-sided gradient equals sum_d w_d E_d with E_d = f_out f_in^T * eps
+    g = torch.Generator().manual_seed(2)
+    D, out_f, in_f = 5, 4, 6
+    eps = torch.randn(out_f, in_f, generator=g)
+    fo = (2 * torch.randint(2, (D, out_f), generator=g) - 1).to(torch.int8)
+    fi = (2 * torch.randint(2, (D, in_f), generator=g) - 1).to(torch.int8)
+    w = torch.randn(D, generator=g)
+    E = fo.float().unsqueeze(2) * fi.float().unsqueeze(1) * eps
+    np.testing.assert_allclose(O.synthetic_weight_grad(eps, w, fi, fo).numpy(), torch.einsum("d,dkm->km", w, E).numpy(), **TOL)
