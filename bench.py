@@ -184,17 +184,26 @@ class PerturbedLinear1024(Workload):
         return y, out
 
     def step_e2e(self):
+        """Host buffers in, host buffers out.  The read-back of y runs on a copy stream while the update
+        computes; everything has landed on the host when the step returns."""
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "copy_stream"):
+            self.copy_stream = torch.cuda.Stream()
         with torch.no_grad():
             self.x.copy_(self.x_host, non_blocking=True)
+            self.w.copy_(self.w_host, non_blocking=True)
             self.layer.perturbed_flag = True
             y = self.layer.forward(self.x)
             self.layer.perturbed_flag = False
-            self.y_host.copy_(y, non_blocking=True)
-            self.w.copy_(self.w_host, non_blocking=True)
+            self.copy_stream.wait_stream(main)
+            with torch.cuda.stream(self.copy_stream):
+                self.y_host.copy_(y, non_blocking=True)
+                y.record_stream(self.copy_stream)
             grad, bgrad = self._update(self.w)
             self.grad_host.copy_(grad, non_blocking=True)
             self.bgrad_host.copy_(bgrad, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        main.synchronize()
+        self.copy_stream.synchronize()
 
     def roofline(self, phase_ms, peaks):
         n, D, R = self.n, self.D, self.R
@@ -403,13 +412,16 @@ class PermutedConv64(Workload):
         flops = 2.0 * self.D * self.hw * self.hw * self.c * 9 * self.c
         ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
         peak = peaks["bf16_sustained"] / 2
-        tf32 = self.layer.options.get("tc") == "tf32"
-        return {"kernel": ("conv_tf32_kernel (tcgen05) + stage_input_tf32_kernel, forward phase" if tf32 else
+        mode = self.layer.options.get("tc")
+        tf32 = mode in ("tf32", "bf16")
+        if mode == "bf16":
+            peak = peaks["bf16_sustained"]
+        return {"kernel": ("conv_%s_kernel (tcgen05) + stage_input_%s_kernel, forward phase" % (mode, mode) if tf32 else
                            "gemm_kernel<ConvProb<PermutedNoise>> (implicit-GEMM conv, forward phase)"),
                 "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s",
-                "frac": round(ach / peak, 4), "peak_source": peaks["source"] + " bf16 sustained / 2 taken as TF32",
+                "frac": round(ach / peak, 4), "peak_source": peaks["source"] + (" bf16 sustained" if mode == "bf16" else " bf16 sustained / 2 taken as TF32"),
                 "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 4), "traffic": None,
-                "note": ("TF32 tensor-core mode (stated reduced precision, bar 2e-2)" if tf32 else
+                "note": ("%s tensor-core mode (stated reduced precision, bar 2e-2)" % mode if tf32 else
                          "fp32 CUDA-core path (exact-fp32 parity)") + "; flops counted for the minimal form N=64"}
 
     def cpu_sample(self, reps):
@@ -538,7 +550,7 @@ class EsCnn(Workload):
         self.es, self.world, self.dev = es, world, dev
         D = self.D
         torch.manual_seed(1005)       # same initial weights on every rank
-        opts = {"tc": "tf32"} if self.tc == "tf32" else {}
+        opts = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}
         self.net = torch.nn.Sequential(
             base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
             base.PermutedConv2d(32, 64, 3, D, options=opts), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Flatten(),
@@ -848,7 +860,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="permuted_linear_256: launch every step from Python instead of replaying a captured CUDA graph")
-    ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32"],
+    ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32", "bf16"],
                     help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
     ap.add_argument("--members", type=int, default=0,
                     help="members per GPU instead of 1024 (small case for ncu captures; not for binary_1024 / permuted_linear_256)")

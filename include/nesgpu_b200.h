@@ -206,6 +206,25 @@ int nes_permuted_conv2d_fwd_tc(const float* x, const float* weight, const float*
                                int in_sp, int out_sp, int antithetic,
                                void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
+/* BF16 tensor-core versions (same arguments again): operands rounded to bf16, fp32 accumulation, the member
+ * filter as the M operand (M = 64 / 128) and 256 output positions as N, so one tcgen05.mma does four times
+ * the work of the TF32 path.  Reduced precision (relative error ~3e-3): for callers that state it.
+ * Supported: stride 1, Cin % 64 == 0, Cout % 8 == 0 and <= 128, D*R <= 65535 images per call. */
+int64_t nes_conv2d_fwd_bf16_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                          int ph, int pw);
+int nes_perturbed_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                  const float* noise, const float* bias_noise, float* y,
+                                  int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                  int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                  int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                 const float* eps, const float* bias_noise,
+                                 const int16_t* pin, const int16_t* pout, float* y,
+                                 int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                 int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                 int in_sp, int out_sp, int antithetic,
+                                 void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
 /* The dense noise a Permuted layer is equal to (derived from modules/base.py:487-508):
  *   E[d,k,m,t] = sum_j [pin[d,j] == m] * eps[pout[d,k], j, t]   (0 where pout[d,k] >= out_sp).
  * E (D,out,in,ksize) is fully overwritten.  Repeated pin entries add. */

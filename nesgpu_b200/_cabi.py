@@ -39,6 +39,9 @@ SIGNATURES = {
     "nes_conv2d_fwd_tc_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
     "nes_perturbed_conv2d_fwd_tc": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_tc": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
+    "nes_conv2d_fwd_bf16_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
+    "nes_perturbed_conv2d_fwd_bf16": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
+    "nes_permuted_conv2d_fwd_bf16": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_dense_noise": [c_ptr] * 4 + [c_i64] + [c_int] * 5 + [c_ptr],
     "nes_permuted_update_scratch_bytes": [c_int] * 4,
     "nes_permuted_update": [c_ptr] * 7 + [c_i64] + [c_int] * 5 + [c_f32, c_f32, c_ptr, c_i64, c_ptr],
@@ -71,6 +74,7 @@ _RETURNS = {
     "nes_linear_fwd_tc_scratch_bytes": c_i64,
     "nes_synthetic_linear_fwd_scratch_bytes": c_i64,
     "nes_conv2d_fwd_tc_scratch_bytes": c_i64,
+    "nes_conv2d_fwd_bf16_scratch_bytes": c_i64,
     "nes_permuted_linear_fwd_scratch_bytes": c_i64,
     "nes_permuted_conv2d_fwd_scratch_bytes": c_i64,
     "nes_permuted_update_scratch_bytes": c_i64,

@@ -503,16 +503,17 @@ class _ConvMixin:
                x.shape[0], *geom, C.stream())
         return y
 
-    def _use_tensor_cores(self):
-        """``options["tc"] == "tf32"`` selects the tcgen05 path (operands rounded to TF32: a stated
-        reduced-precision mode, relative error ~1e-3); the default ``"fp32"`` is exact fp32 on CUDA cores."""
+    def _tensor_core_mode(self):
+        """``options["tc"]``: ``"fp32"`` (default) is exact fp32 on CUDA cores; ``"tf32"`` and ``"bf16"`` select the
+        tcgen05 paths (operands rounded to TF32 / bf16, fp32 accumulation): stated reduced-precision modes with
+        relative error ~1e-3 / ~3e-3.  Returns the entry-point suffix or None."""
         mode = self.options.get("tc", "fp32")
-        if mode not in ("fp32", "tf32"):
-            raise NotImplementedError('options["tc"] for convolutions must be "fp32" or "tf32"')
-        return mode == "tf32"
+        if mode not in ("fp32", "tf32", "bf16"):
+            raise NotImplementedError('options["tc"] for convolutions must be "fp32", "tf32" or "bf16"')
+        return {"fp32": None, "tf32": "tc", "bf16": "bf16"}[mode]
 
-    def _tc_scratch(self, x, R, geom):
-        nbytes = C.call("nes_conv2d_fwd_tc_scratch_bytes", self.directions, R, self.in_channels,
+    def _tc_scratch(self, x, R, geom, suffix):
+        nbytes = C.call("nes_conv2d_fwd_%s_scratch_bytes" % suffix, self.directions, R, self.in_channels,
                         x.shape[-2], x.shape[-1], self.out_channels, self.kernel_size[0], self.kernel_size[1],
                         geom[8], geom[9])
         return C.scratch(nbytes, x.device), nbytes
@@ -521,9 +522,10 @@ class _ConvMixin:
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        if self._use_tensor_cores() and x.shape[0]:
-            buf, nbytes = self._tc_scratch(x, R, geom)
-            C.call("nes_perturbed_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+        suffix = self._tensor_core_mode()
+        if suffix and x.shape[0]:
+            buf, nbytes = self._tc_scratch(x, R, geom, suffix)
+            C.call("nes_perturbed_conv2d_fwd_" + suffix, C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, *geom,
                    1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
             return y
@@ -589,9 +591,10 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        if self._use_tensor_cores() and x.shape[0]:
-            buf, nbytes = self._tc_scratch(x, R, geom)
-            C.call("nes_permuted_conv2d_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+        suffix = self._tensor_core_mode()
+        if suffix and x.shape[0]:
+            buf, nbytes = self._tc_scratch(x, R, geom, suffix)
+            C.call("nes_permuted_conv2d_fwd_" + suffix, C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(eps), C.ptr(beta), C.ptr(pin), C.ptr(pout), C.ptr(y), self.directions, R, *geom,
                    self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
             return y

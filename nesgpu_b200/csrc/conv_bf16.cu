@@ -1,0 +1,570 @@
+// Tensor-core convolution for the per-member layers, BF16 mode, with the filter as the M operand.
+//
+// Same decomposition as the TF32 kernel in conv_tc.cu -- persistent thread blocks over (member, sign)
+// units, the member's effective filter W_d = W + s * E_d built in shared memory, the input read from a
+// zero-padded, channel-chunked, pre-swizzled copy by one bulk async copy per (tile, chunk), filter taps
+// realised as row offsets into the staged run -- but arranged so that one tcgen05.mma does four times
+// the work, because with N = Cout = 64 the TF32 kernel is bound by the number of MMA instructions:
+//   * operands are bf16: one 128-byte swizzle row holds 64 channels and one instruction covers K = 16;
+//   * the product is transposed: D[Cout x pixels] = W_d[Cout x K] . X[pixels x K]^T, i.e. the filter is
+//     the A operand (M = 64 or 128 rows) and the staged pixel run is the B operand with N = 256 pixels.
+// An accumulator tile is M TMEM lanes x 256 fp32 columns; two of them (all 512 columns) alternate
+// between the MMA issuer and the epilogue.  With M = 64 the accumulator occupies lanes 0-15 of each
+// 32-lane quadrant, so each epilogue warp reads its quadrant with tcgen05.ld.32x32b and its first 16
+// threads own one output channel each, writing runs of consecutive pixels of that channel's plane.
+// Reduced precision (bf16 operands, fp32 accumulation): a stated mode, relative error ~3e-3.
+#include <cuda_bf16.h>
+#include "tc_ptx.cuh"
+
+namespace nes {
+
+int launch_permuted_maps(const int16_t* pin, const int16_t* pout, int16_t* omap, int16_t* imap, int64_t D,
+                         int Cin, int Cout, int in_sp, int out_sp, cudaStream_t st);
+
+namespace tc {
+
+constexpr int BF_THREADS = 320;     // producer, MMA issuer, 4 epilogue + builder warps, 4 builder warps
+constexpr int BF_NT = 256;          // pixels (positions) per tile = MMA N
+
+struct ConvBfParams {
+  int Cin, H, W, Cout, kh, kw, ph, pw, dh, dw, Ho, Wo;
+  int Hp, Wp, tiles_img, img_rows, load_bytes, stage_bytes;
+  int M;                         // 64 or 128 filter rows in the MMA (rows >= Cout are zero)
+  long long D, R;
+  int antithetic, sign_groups, units;
+  int stages, kchunks, cchunks;
+  const float* weight; const float* bias; const float* bias_noise; float* y;
+  int noise_kind;                // 1 dense (D,Cout,Cin,ksz), 2 permuted (out_sp,in_sp,ksz) through omap / imap
+  const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
+  const float* weight_t; const float* noise_t;    // (n, tap, c) re-ordered fp32 copies for noise_kind 2
+  int identity_in;
+};
+
+__device__ __forceinline__ void bf_unit_range(const ConvBfParams& p, int sg, long long& r0, long long& r1, float& s) {
+  if (!p.antithetic) { r0 = 0; r1 = p.R; s = 1.f; return; }
+  const long long half = (p.R + 1) / 2;
+  if (sg == 0) { r0 = 0; r1 = half; s = 1.f; } else { r0 = half; r1 = p.R; s = -1.f; }
+}
+
+__device__ __forceinline__ void mma_bf16_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfloat16* __restrict__ xs, const ConvBfParams p) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw = smem_u32(dyn_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B]
+  const int wd_chunk_bytes = p.M * 128;
+  unsigned char* stages_base = wd + size_t(p.kchunks) * wd_chunk_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(stages_base + size_t(p.stages) * p.stage_bytes);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint64_t* wd_ready = acc_empty + 2;
+  uint64_t* wd_free = wd_ready + 1;
+  uint64_t* tbl_ready = wd_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_ready + 1);
+  const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
+  const int table_bytes = table_maps_bytes + 4 * p.Cout;
+  unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
+  uint32_t* tap_off = reinterpret_cast<uint32_t*>(tables + 2 * size_t(table_bytes));
+  float* xpose = reinterpret_cast<float*>(tap_off + 2 * p.kh * p.kw);     // [4 warps][32][33] epilogue transpose
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksz = p.kh * p.kw;
+  const int K = p.Cin * ksz;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    mbar_init(wd_ready, 8);
+    mbar_init(wd_free, 1);
+    mbar_init(tbl_ready, 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // filter rows beyond Cout (padding up to M) stay zero for the whole kernel
+  if (p.M > p.Cout) {
+    for (int e = threadIdx.x; e < p.kchunks * (p.M - p.Cout) * 8; e += BF_THREADS) {
+      const int jc = e / ((p.M - p.Cout) * 8);
+      const int r = e - jc * (p.M - p.Cout) * 8;
+      const int n = p.Cout + r / 8, g16 = r & 7;
+      *reinterpret_cast<uint4*>(wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 + (g16 << 4)) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ producer: one bulk copy per (tile, chunk)
+      uint32_t g = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        const long long d = u / p.sign_groups;
+        long long r0, r1; float s;
+        bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+        for (long long r = r0; r < r1 && ok; ++r) {
+          const long long b = r * p.D + d;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti)
+            for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+              const int st = g % p.stages;
+              const uint32_t phs = (g / p.stages) & 1;
+              if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
+              const long long row0 = (b * p.cchunks + cc) * (long long)p.img_rows + (long long)ti * BF_NT;
+              mbar_expect_tx(&full[st], uint32_t(p.load_bytes));
+              bulk_load_1d(stages_base + size_t(st) * p.stage_bytes, xs + row0 * 64, uint32_t(p.load_bytes), &full[st]);
+            }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      // D = fp32, A = B = bf16, both K-major, N = 256 pixels, M = filter rows
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BF_NT >> 3) << 17) | (uint32_t(p.M >> 4) << 24);
+      const uint32_t desc_hi = uint32_t(smem_desc_sw128(0) >> 32);
+      const uint32_t desc_lo0 = uint32_t(smem_desc_sw128(0));
+      for (int tap = 0; tap < ksz; ++tap) {
+        const int i = tap / p.kw, j = tap - i * p.kw;
+        tap_off[2 * tap] = uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u;                  // pixel-row shift, in 16-byte units
+        tap_off[2 * tap + 1] = uint32_t(tap * p.cchunks) * uint32_t(wd_chunk_bytes >> 4);
+      }
+      const uint32_t wd_lo = desc_lo0 + (smem_u32(wd) >> 4);
+      const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
+      uint32_t g = 0, t = 0, ul = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        long long r0, r1; float s;
+        bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+        if (r1 <= r0) continue;
+        if (!mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+        tc_fence_after();
+        const long long ntiles = (r1 - r0) * p.tiles_img;
+        for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
+          const uint32_t buf = t & 1;
+          if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * uint32_t(BF_NT);
+          for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+            const int st = g % p.stages;
+            const uint32_t phs = (g / p.stages) & 1;
+            if (!mbar_wait(&full[st], phs, 2)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t x_lo = desc_lo0 + (smem_u32(stages_base + size_t(st) * p.stage_bytes) >> 4);
+            const uint32_t w_lo = wd_lo + uint32_t(cc) * cc_step;
+            uint32_t accumulate = (cc > 0) ? 1u : 0u;
+            for (int tap = 0; tap < ksz; ++tap) {
+              const uint32_t bl = x_lo + tap_off[2 * tap], al = w_lo + tap_off[2 * tap + 1];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
+                accumulate = 1u;
+              }
+            }
+            mma_commit(&empty[st]);
+          }
+          mma_commit(&acc_full[buf]);
+        }
+        mma_commit(wd_free);
+        ++ul;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------------- filter builders / epilogue
+    const int bt = threadIdx.x - 64;            // builder thread 0..255
+    const bool drains = warp < 6;
+    const int q = warp & 3;
+    // accumulator row (= output channel) this thread reads: with M = 128 lane i of quadrant q is row 32q+i;
+    // with M = 64 rows 16q .. 16q+15 sit in the first 16 lanes of quadrant q
+    const int chan = (p.M == 128) ? (q * 32 + lane) : (q * 16 + lane);
+    const bool lane_has_row = (p.M == 128) || (lane < 16);
+    const int HoWo = p.Ho * p.Wo;
+    const int k8 = K / 8, c8n = p.Cin / 8;
+    uint32_t t = 0, ul = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      const long long d = u / p.sign_groups;
+      long long r0, r1; float s;
+      bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 <= r0) continue;
+      unsigned char* tb = tables + size_t(ul & 1) * table_bytes;
+      int16_t* omap_s = reinterpret_cast<int16_t*>(tb);
+      int16_t* imap_s = omap_s + p.Cout;
+      float* add_s = reinterpret_cast<float*>(tb + table_maps_bytes);
+      for (int n = bt; n < p.Cout; n += 256) {
+        omap_s[n] = (p.noise_kind == 2) ? p.omap[d * p.Cout + n] : int16_t(n);
+        float a = p.bias ? __ldg(p.bias + n) : 0.f;
+        if (p.bias_noise) a += s * __ldg(p.bias_noise + d * p.Cout + n);
+        add_s[n] = a;
+      }
+      for (int c = bt; c < p.Cin; c += 256) imap_s[c] = (p.noise_kind == 2) ? p.imap[d * p.Cin + c] : int16_t(c);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tbl_ready);
+      if (!mbar_wait_relaxed(tbl_ready, ul & 1, 4)) { ok = false; break; }
+      if (!mbar_wait_relaxed(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
+
+      if (p.noise_kind == 1) {
+        // dense member noise in its native (n, c, tap) order: coalesced reads, scattered 2-byte writes
+        const int total = p.Cout * K;
+        const float* E = p.noise + size_t(d) * total;
+        for (int base = bt; base < total; base += 256 * 8) {
+          float wv[8], ev[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 256;
+            wv[i] = idx < total ? __ldg(p.weight + idx) : 0.f;
+            ev[i] = idx < total ? __ldcs(E + idx) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int idx = base + i * 256;
+            if (idx >= total) break;
+            const int n = idx / K;
+            const int rem = idx - n * K;
+            const int c = rem / ksz, tap = rem - c * ksz;
+            const int kk = tap * p.Cin + c;
+            const int jc = kk >> 6, col = kk & 63;
+            unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
+                                 ((((col >> 3) ^ (n & 7))) << 4) + (col & 7) * 2;
+            *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(fmaf(s, ev[i], wv[i]));
+          }
+        }
+      } else {
+        // W and eps re-ordered to (n, tap, c): eight consecutive channels = one 16-byte bf16 group
+        const float4* Wt = reinterpret_cast<const float4*>(p.weight_t);
+        const bool identity_in = p.identity_in != 0;
+        const int groups = p.Cout * k8;
+        const int step_n = 256 / k8, step_r = 256 - step_n * k8;
+        int n_cur = bt / k8, r_cur = bt - n_cur * k8;
+        constexpr int BATCH = 3;
+        for (int g0 = bt; g0 < groups; g0 += 256 * BATCH) {
+          float4 wa[BATCH], wb[BATCH], ea[BATCH], eb[BATCH];
+          int nn[BATCH], kk[BATCH];
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            const int gidx = g0 + i * 256;
+            wa[i] = make_float4(0.f, 0.f, 0.f, 0.f); wb[i] = wa[i]; ea[i] = wa[i]; eb[i] = wa[i]; nn[i] = -1; kk[i] = 0;
+            if (gidx < groups) {
+              const int n = n_cur, rem = r_cur;
+              const int tap = rem / c8n, c = (rem - tap * c8n) * 8;
+              nn[i] = n; kk[i] = tap * p.Cin + c;
+              wa[i] = __ldg(Wt + 2 * size_t(gidx));
+              wb[i] = __ldg(Wt + 2 * size_t(gidx) + 1);
+              const int so = (p.noise_kind == 2) ? int(omap_s[n]) : -1;
+              if (so >= 0) {
+                const float* er = p.noise_t + (size_t(so) * ksz + tap) * p.in_sp;
+                if (identity_in) {
+                  ea[i] = __ldg(reinterpret_cast<const float4*>(er + c));
+                  eb[i] = __ldg(reinterpret_cast<const float4*>(er + c) + 1);
+                } else {
+                  float e8[8];
+#pragma unroll
+                  for (int z = 0; z < 8; ++z) { const int ci = imap_s[c + z]; e8[z] = ci >= 0 ? __ldg(er + ci) : 0.f; }
+                  ea[i] = make_float4(e8[0], e8[1], e8[2], e8[3]);
+                  eb[i] = make_float4(e8[4], e8[5], e8[6], e8[7]);
+                }
+              }
+            }
+            n_cur += step_n; r_cur += step_r;
+            if (r_cur >= k8) { r_cur -= k8; ++n_cur; }
+          }
+#pragma unroll
+          for (int i = 0; i < BATCH; ++i) {
+            if (nn[i] < 0) continue;
+            const int n = nn[i];
+            const int jc = kk[i] >> 6, col = kk[i] & 63;
+            unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
+                                 ((((col >> 3) ^ (n & 7))) << 4);
+            uint4 v;
+            v.x = pack_bf16(fmaf(s, ea[i].x, wa[i].x), fmaf(s, ea[i].y, wa[i].y));
+            v.y = pack_bf16(fmaf(s, ea[i].z, wa[i].z), fmaf(s, ea[i].w, wa[i].w));
+            v.z = pack_bf16(fmaf(s, eb[i].x, wb[i].x), fmaf(s, eb[i].y, wb[i].y));
+            v.w = pack_bf16(fmaf(s, eb[i].z, wb[i].z), fmaf(s, eb[i].w, wb[i].w));
+            *reinterpret_cast<uint4*>(dst) = v;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wd_ready);
+
+      if (drains) {
+        // Epilogue: a thread holds one output channel (accumulator row) and 32 consecutive positions per
+        // tcgen05.ld; the warp transposes that 32-position chunk through shared memory so that each store
+        // instruction writes 32 consecutive positions of ONE channel plane (full 128-byte lines).
+        const bool owns = lane_has_row && chan < p.Cout;
+        const float add = owns ? add_s[chan] : 0.f;
+        const int rows_per_warp = (p.M == 128) ? 32 : 16;
+        const int chan0 = (p.M == 128) ? q * 32 : q * 16;
+        float* xp = xpose + size_t(warp - 2) * 32 * 33;
+        for (long long r = r0; r < r1 && ok; ++r) {
+          const long long b = r * p.D + d;
+          float* img = p.y + size_t(b) * p.Cout * HoWo;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++t) {
+            const uint32_t buf = t & 1;
+            if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
+            tc_fence_after();
+            const bool live = (g_tc_error == 0);
+            for (int c0 = 0; c0 < BF_NT; c0 += 32) {
+              uint32_t acc[32];
+              tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(BF_NT) + uint32_t(c0), acc);
+              if (lane_has_row) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]) + add;
+              }
+              __syncwarp();
+              const int qpos = ti * BF_NT + c0 + lane;
+              const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
+              if (live && oy < p.Ho && ox < p.Wo) {
+                float* dst = img + size_t(chan0) * HoWo + oy * p.Wo + ox;
+                for (int rl = 0; rl < rows_per_warp && chan0 + rl < p.Cout; ++rl) dst[size_t(rl) * HoWo] = xp[rl * 33 + lane];
+              }
+              __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+        }
+      }
+      ++ul;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512u);
+  }
+}
+
+// x (B,C,H,W) fp32 -> staged bf16 layout: for every image and 64-channel chunk a run of img_rows pixel rows
+// (zero-padded image, pitch Wp, 128 bytes = 64 bf16 channels per row), 16-byte groups permuted by (row mod 8)
+// as the 128-byte shared-memory swizzle does.  One block per (image, chunk), strips of 4 padded rows.
+constexpr int BF_STRIP = 4;
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) stage_input_bf16_kernel(const float* __restrict__ x, uint32_t* __restrict__ out,
+                                                               int C, int H, int W, int Hp, int Wp, int ph, int pw,
+                                                               int img_rows) {
+  extern __shared__ float tile[];                 // [64][pitch]
+  const int pitch = (BF_STRIP * Wp) | 1;
+  const size_t b = blockIdx.y;
+  const int cc = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* src = x + (b * size_t(C) + size_t(cc) * 64) * H * W;
+  uint32_t* dst = out + (b * gridDim.x + cc) * size_t(img_rows) * 32;      // 32 packed pairs per row
+  for (int y0 = 0; y0 < Hp; y0 += BF_STRIP) {
+    const int rows = (Hp - y0 < BF_STRIP) ? (Hp - y0) : BF_STRIP;
+    for (int e = threadIdx.x; e < 64 * pitch; e += 256) tile[e] = 0.f;
+    __syncthreads();
+    for (int ch = warp; ch < 64; ch += 8) {
+      const float* plane = src + size_t(ch) * H * W;
+      if (VEC) {
+        const int w4 = W >> 2;
+        for (int g = lane; g < rows * w4; g += 32) {
+          const int rr = g / w4, x4 = (g - rr * w4) * 4;
+          const int yy = y0 + rr - ph;
+          if (yy >= 0 && yy < H) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(plane + size_t(yy) * W + x4));
+            float* tp = tile + ch * pitch + rr * Wp + pw + x4;
+            tp[0] = v.x; tp[1] = v.y; tp[2] = v.z; tp[3] = v.w;
+          }
+        }
+      } else {
+        for (int g = lane; g < rows * W; g += 32) {
+          const int rr = g / W, xx = g - rr * W;
+          const int yy = y0 + rr - ph;
+          if (yy >= 0 && yy < H) tile[ch * pitch + rr * Wp + pw + xx] = __ldcs(plane + size_t(yy) * W + xx);
+        }
+      }
+    }
+    __syncthreads();
+    const int first = y0 * Wp;
+    for (int r = warp; r < rows * Wp; r += 8) {
+      const int row = first + r;
+      // lane holds channels 2*lane, 2*lane+1 -> 4-byte unit `lane` of the row; units 4g..4g+3 form 16-byte group g
+      dst[size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3))] =
+          pack_bf16(tile[(2 * lane) * pitch + r], tile[(2 * lane + 1) * pitch + r]);
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void reorder_filter_bf_kernel(const float* __restrict__ src, float* __restrict__ dst, int N, int C, int ksz) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= N * C * ksz) return;
+  const int n = idx / (C * ksz);
+  const int rem = idx - n * C * ksz;
+  const int tap = rem / C, c = rem - tap * C;
+  dst[idx] = src[(size_t(n) * C + c) * ksz + tap];
+}
+
+int conv_bf16_error_word(int* v) {
+  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
+  return NES_OK;
+}
+
+static int64_t bf_align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+struct ConvBfPlan { ConvBfParams p; size_t smem; int64_t x_bytes, map_bytes, filt_bytes; };
+
+static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                          int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what) {
+  NES_REQUIRE(D >= 0 && R >= 0 && Cin > 0 && H > 0 && W > 0 && Cout > 0 && kh > 0 && kw > 0 && ph >= 0 && pw >= 0 &&
+              dh > 0 && dw > 0, NES_ERR_BAD_ARG, "%s: bad geometry", what);
+  NES_REQUIRE(sh == 1 && sw == 1, NES_ERR_UNSUPPORTED, "%s: the bf16 tensor-core path needs stride 1", what);
+  NES_REQUIRE(Cin % 64 == 0, NES_ERR_UNSUPPORTED, "%s: the bf16 tensor-core path needs Cin %% 64 == 0 (got %d)", what, Cin);
+  NES_REQUIRE(Cout % 8 == 0 && Cout <= 128, NES_ERR_UNSUPPORTED, "%s: the bf16 tensor-core path needs Cout %% 8 == 0 and <= 128 (got %d)", what, Cout);
+  ConvBfParams& p = pl.p;
+  p.Cin = Cin; p.H = H; p.W = W; p.Cout = Cout; p.kh = kh; p.kw = kw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
+  p.Ho = H + 2 * ph - dh * (kh - 1);
+  p.Wo = W + 2 * pw - dw * (kw - 1);
+  NES_REQUIRE(p.Ho > 0 && p.Wo > 0, NES_ERR_BAD_ARG, "%s: empty output", what);
+  p.Hp = H + 2 * ph; p.Wp = W + 2 * pw;
+  p.M = Cout <= 64 ? 64 : 128;
+  p.tiles_img = ceil_div(p.Ho * p.Wp, BF_NT);
+  const int max_shift = (kh - 1) * dh * p.Wp + (kw - 1) * dw;
+  p.img_rows = (p.Hp * p.Wp + 7) & ~7;
+  p.load_bytes = (BF_NT + max_shift) * 128;
+  p.stage_bytes = (p.load_bytes + 1023) & ~1023;
+  p.D = D; p.R = R; p.antithetic = antithetic;
+  p.sign_groups = antithetic ? 2 : 1;
+  NES_REQUIRE(D * p.sign_groups <= INT32_MAX && D * R <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: population too large", what);
+  p.units = int(D * p.sign_groups);
+  p.cchunks = Cin / 64;
+  p.kchunks = kh * kw * p.cchunks;
+  const size_t wd_bytes = size_t(p.kchunks) * p.M * 128;
+  const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
+  const size_t xpose_bytes = 4 * 32 * 33 * sizeof(float);
+  const size_t fixed = 1024 + wd_bytes + 64 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
+  const size_t limit = 227 * 1024;
+  NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
+              "%s: the member filter (%zu bytes) plus two input stages (%d bytes each) do not fit in shared memory on the "
+              "bf16 tensor-core path", what, wd_bytes, p.stage_bytes);
+  int stages = int((limit - fixed) / (size_t(p.stage_bytes) + 16));
+  if (stages > 6) stages = 6;
+  p.stages = stages;
+  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 7) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
+            8 * size_t(kh) * kw + xpose_bytes;
+  pl.x_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
+  pl.map_bytes = bf_align256(D * (int64_t(Cin) + Cout) * 2);
+  pl.filt_bytes = bf_align256(int64_t(Cout) * Cin * kh * kw * 4);
+  return NES_OK;
+}
+
+static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStream_t st, const char* what) {
+  ConvBfParams& p = pl.p;
+  const int64_t B = p.D * p.R;
+  NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
+  const size_t tsmem = size_t(64) * ((BF_STRIP * p.Wp) | 1) * sizeof(float);
+  NES_REQUIRE(tsmem <= 48 * 1024, NES_ERR_UNSUPPORTED, "%s: image row too wide for the layout pre-pass (%zu bytes)", what, tsmem);
+  dim3 tgrid((unsigned)p.cchunks, (unsigned)B);
+  if (p.W % 4 == 0 && aligned16(x))
+    stage_input_bf16_kernel<true><<<tgrid, 256, tsmem, st>>>(x, static_cast<uint32_t*>(x_staged), p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
+  else
+    stage_input_bf16_kernel<false><<<tgrid, 256, tsmem, st>>>(x, static_cast<uint32_t*>(x_staged), p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
+  int rc = check_launch(what);
+  if (rc != NES_OK) return rc;
+  cudaError_t e = cudaFuncSetAttribute(conv_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+  int grid = p.units < sm_count() ? p.units : sm_count();
+  if (grid < 1) grid = 1;
+  conv_bf16_kernel<<<grid, BF_THREADS, pl.smem, st>>>(static_cast<const __nv_bfloat16*>(x_staged), p);
+  return check_launch(what);
+}
+
+}  // namespace tc
+}  // namespace nes
+
+using namespace nes;
+using namespace nes::tc;
+
+extern "C" int64_t nes_conv2d_fwd_bf16_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                     int ph, int pw) {
+  if (D <= 0 || R <= 0) return 0;
+  const int64_t hp = H + 2 * ph, wp = W + 2 * pw;
+  const int64_t img_rows = (hp * wp + 7) & ~int64_t(7);
+  const int64_t tail = ((BF_NT + (kh - 1) * wp * 8 + (kw - 1) * 8) * 128 + 1023) & ~int64_t(1023);   // covers any dilation <= 8
+  return bf_align256(D * R * int64_t((Cin + 63) / 64) * img_rows * 128 + tail) + bf_align256(D * (int64_t(Cin) + Cout) * 2) +
+         2 * bf_align256(int64_t(Cout) * Cin * kh * kw * 4);
+}
+
+extern "C" int nes_perturbed_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                             const float* noise, const float* bias_noise, float* y,
+                                             int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                             int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                             int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  ConvBfPlan pl;
+  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "perturbed_conv2d_fwd_bf16");
+  if (rc != NES_OK) return rc;
+  if (D == 0 || R == 0) return NES_OK;
+  NES_REQUIRE(x && weight && noise && y, NES_ERR_BAD_ARG, "perturbed_conv2d_fwd_bf16: null pointer");
+  NES_REQUIRE(scratch && scratch_bytes >= pl.x_bytes && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "perturbed_conv2d_fwd_bf16: scratch needs %lld bytes, 256-byte aligned", (long long)pl.x_bytes);
+  pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
+  pl.p.noise_kind = 1; pl.p.noise = noise; pl.p.omap = nullptr; pl.p.imap = nullptr; pl.p.in_sp = Cin;
+  pl.p.weight_t = nullptr; pl.p.noise_t = nullptr; pl.p.identity_in = 1;
+  return run_conv_bf16(pl, x, scratch, as_stream(stream), "perturbed_conv2d_fwd_bf16");
+}
+
+extern "C" int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                            const float* eps, const float* bias_noise,
+                                            const int16_t* pin, const int16_t* pout, float* y,
+                                            int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                            int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                            int in_sp, int out_sp, int antithetic,
+                                            void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  ConvBfPlan pl;
+  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16");
+  if (rc != NES_OK) return rc;
+  if (D == 0 || R == 0) return NES_OK;
+  NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_conv2d_fwd_bf16: null pointer");
+  NES_REQUIRE(out_sp >= 0 && out_sp <= Cout && in_sp >= 0 && in_sp <= Cin && (pin || in_sp == Cin), NES_ERR_BAD_ARG,
+              "permuted_conv2d_fwd_bf16: sparsity exceeds degree");
+  NES_REQUIRE(pin || in_sp % 8 == 0, NES_ERR_UNSUPPORTED, "permuted_conv2d_fwd_bf16: in_sp must be a multiple of 8");
+  const int64_t need = pl.x_bytes + pl.map_bytes + 2 * pl.filt_bytes;
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0,
+              NES_ERR_SCRATCH, "permuted_conv2d_fwd_bf16: scratch needs %lld bytes, 256-byte aligned", (long long)need);
+  cudaStream_t st = as_stream(stream);
+  unsigned char* sp = static_cast<unsigned char*>(scratch);
+  int16_t* omap = reinterpret_cast<int16_t*>(sp + pl.x_bytes);
+  int16_t* imap = omap + D * Cout;
+  float* weight_t = reinterpret_cast<float*>(sp + pl.x_bytes + pl.map_bytes);
+  float* eps_t = reinterpret_cast<float*>(sp + pl.x_bytes + pl.map_bytes + pl.filt_bytes);
+  rc = launch_permuted_maps(pin, pout, omap, imap, D, Cin, Cout, in_sp, out_sp, st);
+  if (rc != NES_OK) return rc;
+  const int ksz = kh * kw;
+  reorder_filter_bf_kernel<<<ceil_div(Cout * Cin * ksz, 256), 256, 0, st>>>(weight, weight_t, Cout, Cin, ksz);
+  if ((rc = check_launch("permuted_conv2d_fwd_bf16(reorder W)")) != NES_OK) return rc;
+  if (out_sp * in_sp > 0) {
+    reorder_filter_bf_kernel<<<ceil_div(out_sp * in_sp * ksz, 256), 256, 0, st>>>(eps, eps_t, out_sp, in_sp, ksz);
+    if ((rc = check_launch("permuted_conv2d_fwd_bf16(reorder eps)")) != NES_OK) return rc;
+  }
+  pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
+  pl.p.noise_kind = 2; pl.p.noise = eps; pl.p.omap = omap; pl.p.imap = imap; pl.p.in_sp = in_sp;
+  pl.p.weight_t = weight_t; pl.p.noise_t = eps_t; pl.p.identity_in = (pin == nullptr) ? 1 : 0;
+  return run_conv_bf16(pl, x, scratch, st, "permuted_conv2d_fwd_bf16");
+}

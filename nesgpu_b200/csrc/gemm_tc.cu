@@ -244,15 +244,18 @@ extern "C" int nes_linear_fwd_tc(const float* x, const float* weight, const floa
   return check_launch("linear_fwd_tc");
 }
 
-namespace nes { namespace tc { int conv_tc_error_word(int* v); } }
+namespace nes { namespace tc { int conv_tc_error_word(int* v); int conv_bf16_error_word(int* v); } }
 
 extern "C" int nes_tc_error_flag(int* flag) {
   NES_REQUIRE(flag != nullptr, NES_ERR_BAD_ARG, "tc_error_flag: null pointer");
   int v = 0, vc = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
+  int vb = 0;
   int rc = nes::tc::conv_tc_error_word(&vc);
   if (rc != NES_OK) return rc;
-  *flag = v ? v : vc;
+  rc = nes::tc::conv_bf16_error_word(&vb);
+  if (rc != NES_OK) return rc;
+  *flag = v ? v : (vc ? vc : vb);
   return NES_OK;
 }

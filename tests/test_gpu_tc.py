@@ -161,3 +161,88 @@ def test_conv_tc_rejects_unsupported_shapes():
     layer.perturbed_flag = True
     with pytest.raises(NotImplementedError):
         layer.forward(torch.zeros(4, 3, 8, 8, device=DEV))
+
+
+# ------------------------------------------------------------------ bf16 tensor-core convolutions
+# Stated reduced-precision mode: operands rounded to bf16 (8 mantissa bits), fp32 accumulation.  Bar 2e-2.
+BF16_CONV_TOL = 1e-2
+
+
+@pytest.mark.parametrize("mode,in_sp,out_sp,R,anti,hw,k,pad,cout", [
+    ("out", 0, 0.5, 1, False, 13, 3, 1, 64), ("in", 0, 0, 2, True, 9, 3, 1, 32), ("both", 0, 0, 3, True, 8, 3, 0, 64),
+    ("out", 0, 0, 2, True, 33, 1, 0, 128), ("auto", 0.5, 0, 1, False, 20, 3, 2, 24),
+])
+def test_permuted_conv_bf16(mode, in_sp, out_sp, R, anti, hw, k, pad, cout):
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    D, cin = 5, 64
+    g = torch.Generator().manual_seed(hw + k)
+    layer = base.PermutedConv2d(cin, cout, k, D, padding=pad, antithetic=anti, permutation=mode, in_sparsity=in_sp,
+                                out_sparsity=out_sp, options={"tc": "bf16"}).to(DEV)
+    isp, osp = layer.in_sparsity, layer.out_sparsity
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g)
+    eps = 0.05 * torch.randn(osp, isp, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    pin = _perms(g, D, cin, isp) if layer.permute_inputs else None
+    pout = _perms(g, D, cout) if layer.permute_outputs else None
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(eps), G(beta)
+    layer.input_permutations, layer.output_permutations = G(pin), G(pout)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert _flag(C) == 0
+    e = rel_err(y, O.permuted_conv2d_forward(x, W, b, eps, beta, pin, pout, D, 1, pad, 1, anti))
+    assert e <= BF16_CONV_TOL, "bf16 conv rel err %g" % e
+
+
+def test_perturbed_conv_bf16():
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    D, R, cin, cout, hw, k = 4, 2, 64, 64, 12, 3
+    g = torch.Generator().manual_seed(29)
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g)
+    E = 0.05 * torch.randn(D, cout, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    layer = base.PerturbedConv2d(cin, cout, k, D, padding=1, antithetic=True, options={"tc": "bf16"}).to(DEV)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(E), G(beta)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert _flag(C) == 0
+    e = rel_err(y, O.perturbed_conv2d_forward(x, W, b, E, beta, D, 1, 1, 1, True))
+    assert e <= BF16_CONV_TOL, "bf16 conv rel err %g" % e
+
+
+def test_config3_permuted_conv_bf16_full_size():
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    D, c, hw = 1024, 64, 32
+    g = torch.Generator().manual_seed(1003)
+    layer = base.PermutedConv2d(c, c, 3, D, padding=1, out_sparsity=.5, options={"tc": "bf16"}).to(DEV)
+    x = torch.randn(D, c, hw, hw, generator=g)
+    W = torch.randn(c, c, 3, 3, generator=g) * (2 / 576) ** .5
+    b = torch.zeros(c)
+    eps = 0.02 * 2 ** .5 * torch.randn(32, c, 3, 3, generator=g)
+    beta = 0.02 * torch.randn(D, c, generator=g)
+    pout = _perms(g, D, c)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.output_permutations = G(eps), G(beta), G(pout)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert _flag(C) == 0
+    want = O.permuted_conv2d_forward(x, W, b, eps, beta, None, pout, D, 1, 1, 1, False)
+    e = rel_err(y, want)
+    assert e <= BF16_CONV_TOL, "bf16 conv rel err %g" % e
