@@ -10,8 +10,9 @@
 //     the A operand (M = 64 or 128 rows) and the staged pixel run is the B operand with N = 256 pixels.
 // An accumulator tile is M TMEM lanes x 256 fp32 columns; two of them (all 512 columns) alternate
 // between the MMA issuer and the epilogue.  With M = 64 the accumulator occupies lanes 0-15 of each
-// 32-lane quadrant, so each epilogue warp reads its quadrant with tcgen05.ld.32x32b and its first 16
-// threads own one output channel each, writing runs of consecutive pixels of that channel's plane.
+// 32-lane quadrant, so each epilogue warp reads its quadrant with tcgen05.ld.32x32b, its first 16 threads
+// own one output channel each, and a per-warp shared-memory transpose turns that into stores of 32
+// consecutive positions of one channel plane.  All eight builder warps drain (two per lane quadrant).
 // Reduced precision (bf16 operands, fp32 accumulation): a stated mode, relative error ~3e-3.
 #include <cuda_bf16.h>
 #include "tc_ptx.cuh"
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
   uint32_t* tap_off = reinterpret_cast<uint32_t*>(tables + 2 * size_t(table_bytes));
-  float* xpose = reinterpret_cast<float*>(tap_off + 2 * p.kh * p.kw);     // [4 warps][32][33] epilogue transpose
+  float* xpose = reinterpret_cast<float*>(tap_off + 2 * p.kh * p.kw);     // [8 warps][rows per warp][33] epilogue transpose
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksz = p.kh * p.kw;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
     mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
     mbar_init(tbl_ready, 8);
@@ -193,7 +194,6 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   } else {
     // ---------------------------------------------------------------------- filter builders / epilogue
     const int bt = threadIdx.x - 64;            // builder thread 0..255
-    const bool drains = warp < 6;
     const int q = warp & 3;
     // accumulator row (= output channel) this thread reads: with M = 128 lane i of quadrant q is row 32q+i;
     // with M = 64 rows 16q .. 16q+15 sit in the first 16 lanes of quadrant q
@@ -309,15 +309,17 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       __syncwarp();
       if (lane == 0) mbar_arrive(wd_ready);
 
-      if (drains) {
-        // Epilogue: a thread holds one output channel (accumulator row) and 32 consecutive positions per
+      {
+        // Epilogue (all eight builder warps; two warps share a TMEM lane quadrant and split the tile's columns
+        // between them): a thread holds one output channel (accumulator row) and 32 consecutive positions per
         // tcgen05.ld; the warp transposes that 32-position chunk through shared memory so that each store
         // instruction writes 32 consecutive positions of ONE channel plane (full 128-byte lines).
         const bool owns = lane_has_row && chan < p.Cout;
         const float add = owns ? add_s[chan] : 0.f;
         const int rows_per_warp = (p.M == 128) ? 32 : 16;
         const int chan0 = (p.M == 128) ? q * 32 : q * 16;
-        float* xp = xpose + size_t(warp - 2) * 32 * 33;
+        float* xp = xpose + size_t(warp - 2) * rows_per_warp * 33;
+        const int col_lo = (warp < 6) ? 0 : BF_NT / 2, col_hi = col_lo + BF_NT / 2;
         for (long long r = r0; r < r1 && ok; ++r) {
           const long long b = r * p.D + d;
           float* img = p.y + size_t(b) * p.Cout * HoWo;
@@ -326,7 +328,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
             tc_fence_after();
             const bool live = (g_tc_error == 0);
-            for (int c0 = 0; c0 < BF_NT; c0 += 32) {
+            for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               uint32_t acc[32];
               tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(BF_NT) + uint32_t(c0), acc);
               if (lane_has_row) {
@@ -458,7 +460,7 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   p.kchunks = kh * kw * p.cchunks;
   const size_t wd_bytes = size_t(p.kchunks) * p.M * 128;
   const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
-  const size_t xpose_bytes = 4 * 32 * 33 * sizeof(float);
+  const size_t xpose_bytes = 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
   const size_t fixed = 1024 + wd_bytes + 64 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
   const size_t limit = 227 * 1024;
   NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
