@@ -320,6 +320,13 @@ int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms, void* out
                         int64_t rows, int64_t cols, int word_bits, uint64_t seed,
                         nes_stream_t stream);
 
+/* Fused Bernoulli sampling + product: C[x,y] = sum_z popcount(bits(x,y,z) ^ B[x,z]) where bits(x,y,z) are
+ * exactly the words nes_bin_sample_bits (device generator, same seed) would store -- the (n,rows,words) weight
+ * bits are never materialised.  p (rows,cols) fp16, B (n, words) packed inputs, C (n, rows) int32.
+ * Replaces cuda_binary_seeded_bmv (extensions/booleanOperationsCuda.cu:172-202,301-322). */
+int nes_bin_seeded_bmv(const uint16_t* p_half, const void* B, int32_t* C, int64_t n, int64_t rows,
+                       int64_t cols, int word_bits, uint64_t seed, nes_stream_t stream);
+
 /* C[z,x,y] = sum_k popcount(A[z,x,k] ^ B[z,k,y]) as int32.  A (P,M,K), B (P,K,N), C (P,M,N).
  * Replaces bmm_kernel (extensions/src/bmm.cu:5-58) and cuda_binary_bmm (booleanOperationsCuda.cu:33-100,206-238). */
 int nes_bin_bmm(const void* A, const void* B, int32_t* C, int64_t P, int64_t M, int64_t K,

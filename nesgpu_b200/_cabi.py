@@ -58,6 +58,7 @@ SIGNATURES = {
     "nes_bin_pack8": [c_ptr, c_ptr, c_i64, c_i64, c_ptr],
     "nes_bin_unpack": [c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr],
     "nes_bin_sample_bits": [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_int, c_u64, c_ptr],
+    "nes_bin_seeded_bmv": [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_i64, c_int, c_u64, c_ptr],
     "nes_bin_bmm": [c_ptr] * 3 + [c_i64] * 4 + [c_int, c_ptr],
     "nes_bin_bmm_act": [c_ptr] * 4 + [c_i64] * 4 + [c_int, c_ptr],
     "nes_bin_im2col": [c_ptr, c_ptr, c_i64] + [c_int] * 10 + [c_ptr],

@@ -82,6 +82,22 @@ def sample_bits(p, n, dtype, seed, uniforms=None):
     return ret
 
 
+def binary_seeded_bmv(A, B, seed):
+    """Fused Bernoulli sampling + XOR-popcount product (reference pybind name ``boolop_cuda.binary_seeded_bmv``,
+    booleanOperations.cpp:58-63): ``A`` (out, in) fp16 probabilities, ``B`` (batch, words) packed inputs ->
+    (batch, out) int32, equal to ``bmm(sample_bits(A, batch, B.dtype, seed), B.view(batch, -1, 1))`` without
+    storing the sampled bits."""
+    assert len(A.shape) == 2 and len(B.shape) == 2
+    A = C.require_cuda(A, "A", torch.float16)
+    B = C.require_cuda(B, "B")
+    bits = _bits(B.dtype)
+    assert B.size(1) == ceil_div(A.size(1), bits)
+    ret = torch.empty((B.size(0), A.size(0)), dtype=torch.int32, device=A.device)
+    C.call("nes_bin_seeded_bmv", C.ptr(A), C.ptr(B), C.ptr(ret), B.size(0), A.size(0), A.size(1), bits,
+           int(seed) & (2 ** 64 - 1), C.stream())
+    return ret
+
+
 def _bmm_args(A, B):
     assert len(A.shape) == 3
     assert len(B.shape) == 3

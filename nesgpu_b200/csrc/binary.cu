@@ -127,6 +127,54 @@ __global__ void __launch_bounds__(256) sample_bits_philox_kernel(const __half* _
   }
 }
 
+// Fused sampling + product: the weight bits of member x are drawn exactly as sample_bits_philox_kernel draws
+// them (same counters, same thresholds) and consumed on the spot,
+//   C[x, y] = sum_z popcount(bits(x, y, z) ^ B[x, z]),
+// so the (n, rows, words) bit tensor is never stored.  Integer atomics make the sum order-independent.
+__global__ void __launch_bounds__(256) seeded_bmv_kernel(const __half* __restrict__ p, const uint32_t* __restrict__ B,
+                                                         int32_t* __restrict__ C, int64_t n, int64_t rows, int64_t cols,
+                                                         int64_t row_u32, uint64_t seed) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= rows * row_u32) return;
+  const int64_t q = e % row_u32, y = e / row_u32;
+  const int64_t c0 = q * 32;
+  uint32_t thr[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float pv = 0.f;
+    if (c0 + i < cols) pv = __half2float(p[y * cols + c0 + i]);
+    const float t = ceilf(pv * 65536.f);
+    thr[i] = (t <= 0.f) ? 0u : (t >= 65536.f ? 65536u : uint32_t(t));
+  }
+  const Philox ph(seed);
+  const int64_t x0 = int64_t(blockIdx.y) * SAMPLE_MEMBERS;
+  const int64_t x1 = (x0 + SAMPLE_MEMBERS < n) ? x0 + SAMPLE_MEMBERS : n;
+  for (int64_t x = x0; x < x1; ++x) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t r[4];
+      ph(uint32_t(q * 4 + g), uint32_t(y), uint32_t(x), 5u, r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = g * 8 + 2 * j;
+        word |= ((r[j] & 0xFFFFu) < thr[i] ? 1u : 0u) << i;
+        word |= ((r[j] >> 16) < thr[i + 1] ? 1u : 0u) << (i + 1);
+      }
+    }
+    int cnt = __popc(word ^ __ldg(B + x * row_u32 + q));
+    // lanes of a warp hold consecutive 32-bit columns; when a row is a whole number of warps wide the
+    // warp reduces first and issues one atomic
+    if ((row_u32 & 31) == 0) {
+#pragma unroll
+      for (int sh = 16; sh > 0; sh >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, sh);
+      if ((threadIdx.x & 31) == 0) atomicAdd(C + x * rows + y, cnt);
+    } else {
+      atomicAdd(C + x * rows + y, cnt);
+    }
+  }
+}
+
 // ---- XOR-popcount batched matrix product ------------------------------------------------
 
 struct DirectA {   // A (P, M, K) words
@@ -603,4 +651,23 @@ extern "C" int nes_bin_maxpool2d(const void* in, void* out, int64_t P, int H, in
   else
     maxpool_kernel<uint32_t><<<blocks, 256, 0, as_stream(stream)>>>(static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), total, H, W, Cw, ho, wo, px, py, sx, sy);
   return check_launch("bin_maxpool2d");
+}
+
+extern "C" int nes_bin_seeded_bmv(const uint16_t* p_half, const void* B, int32_t* C, int64_t n, int64_t rows,
+                                  int64_t cols, int word_bits, uint64_t seed, nes_stream_t stream) {
+  NES_REQUIRE(n >= 0 && rows >= 0 && cols >= 0, NES_ERR_BAD_ARG, "bin_seeded_bmv: negative extent");
+  NES_REQUIRE(word_bits == 32 || word_bits == 64, NES_ERR_BAD_ARG, "bin_seeded_bmv: word_bits must be 32 or 64");
+  if (n == 0 || rows == 0) return NES_OK;
+  NES_REQUIRE(p_half && B && C, NES_ERR_BAD_ARG, "bin_seeded_bmv: null pointer");
+  const int64_t row_u32 = ceil_div<int64_t>(cols, word_bits) * (word_bits / 32);
+  cudaStream_t st = as_stream(stream);
+  cudaMemsetAsync(C, 0, n * rows * sizeof(int32_t), st);
+  if (row_u32 == 0) return NES_OK;
+  const int64_t pairs = rows * row_u32;
+  NES_REQUIRE(ceil_div<int64_t>(n, SAMPLE_MEMBERS) <= 65535 && ceil_div<int64_t>(pairs, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED,
+              "bin_seeded_bmv: too large");
+  NES_REQUIRE(rows <= UINT32_MAX && n <= UINT32_MAX, NES_ERR_UNSUPPORTED, "bin_seeded_bmv: too large");
+  dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, SAMPLE_MEMBERS));
+  seeded_bmv_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(p_half), static_cast<const uint32_t*>(B), C, n, rows, cols, row_u32, seed);
+  return check_launch("bin_seeded_bmv");
 }

@@ -196,3 +196,16 @@ def test_config4_binary_layer_full_size(ops):
     mp_in = torch.randint(-2 ** 62, 2 ** 62, (D, 32, 32, 1), generator=g)
     np.testing.assert_array_equal(npy(ops.max_pool2d(mp_in.to(DEV), 2, 2, 0, 0, 2, 2)),
                                   B.max_pool2d(mp_in.numpy(), 2, 2, 0, 0, 2, 2))
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("n,rows,cols", [(40, 33, 1024), (5, 7, 100), (17, 3, 2048), (1, 1, 1)])
+def test_seeded_bmv_equals_sample_then_bmm(ops, bits, n, rows, cols):
+    g = torch.Generator().manual_seed(n + rows + cols)
+    p = torch.rand(rows, cols, generator=g).half().to(DEV)
+    x = torch.randint(2, (n, cols), generator=g).bool().to(DEV)
+    xb = ops.pack(x, DT[bits])
+    fused = ops.binary_seeded_bmv(p, xb, 1234)
+    stored = ops.bmm(ops.sample_bits(p, n, DT[bits], 1234), xb.view(n, -1, 1)).squeeze(2)
+    assert torch.equal(fused, stored)
+    assert not torch.equal(fused, ops.binary_seeded_bmv(p, xb, 1235)) or n * rows * cols < 64
