@@ -343,8 +343,16 @@ __global__ void maxpool_kernel(const T* __restrict__ in, T* __restrict__ out, in
 // are (member slot, column) pairs, each keeping 32 fp32 accumulators and walking its members
 // with four loads in flight.  Slots are combined through shared memory 16 bits at a time;
 // blockIdx.z splits the members, with fp32 partial rows in scratch summed by a last kernel.
+//
+// When every warp holds one member slot (column count per block a multiple of 32) members are
+// taken four at a time: the four words are bit-transposed so that each nibble holds the four
+// members' bits of one position, and the nibble selects one of the 16 subset sums of the four
+// weights, which the lanes of the warp hold (lane & 15) and hand out by shuffle.  One shift,
+// one shuffle and one add then cover four member-bits.  (A 16-entry shared-memory table in
+// place of the shuffle measured slower: 102 us against 81 us at 1024 members of 1024x1024 bits.)
 constexpr int WS_THREADS = 256;
 
+template <bool QUAD>
 __global__ void __launch_bounds__(WS_THREADS) weighted_sum_kernel(
     const uint32_t* __restrict__ in, const __half* __restrict__ w, float* __restrict__ partial,
     int64_t D, int64_t rows, int row_u32, int64_t zbits, int64_t d_per_split, int cols_per_block, int slots) {
@@ -363,6 +371,45 @@ __global__ void __launch_bounds__(WS_THREADS) weighted_sum_kernel(
     const uint32_t* src = in + y * row_u32 + col;
     const int64_t stride = rows * row_u32;
     int64_t d = d0 + slot;
+    if (QUAD) {
+      const int e = t & 15;
+      const int64_t quads = (d1 - d0) / 4;
+      uint32_t n0 = 0, n1 = 0, n2 = 0, n3 = 0;
+      if (slot < quads) {
+        const int64_t db = d0 + 4 * int64_t(slot);
+        n0 = __ldcs(src + db * stride); n1 = __ldcs(src + (db + 1) * stride);
+        n2 = __ldcs(src + (db + 2) * stride); n3 = __ldcs(src + (db + 3) * stride);
+      }
+      for (int64_t g = slot; g < quads; g += slots) {
+        const int64_t db = d0 + 4 * g;
+        const uint32_t a0 = n0, a1 = n1, a2 = n2, a3 = n3;
+        if (g + slots < quads) {            // next group's words fly while this one is summed
+          const int64_t dn = db + 4 * int64_t(slots);
+          n0 = __ldcs(src + dn * stride); n1 = __ldcs(src + (dn + 1) * stride);
+          n2 = __ldcs(src + (dn + 2) * stride); n3 = __ldcs(src + (dn + 3) * stride);
+        }
+        float lut = (e & 1) ? __half2float(w[db]) : 0.f;
+        lut += (e & 2) ? __half2float(w[db + 1]) : 0.f;
+        lut += (e & 4) ? __half2float(w[db + 2]) : 0.f;
+        lut += (e & 8) ? __half2float(w[db + 3]) : 0.f;
+        // 4x4 bit transposes: nibble k of u[tt] = members' bits (m3 m2 m1 m0) of position 4k + tt
+        const uint32_t b0 = (a0 & 0x55555555u) | ((a1 & 0x55555555u) << 1);
+        const uint32_t b1 = ((a0 >> 1) & 0x55555555u) | (a1 & 0xAAAAAAAAu);
+        const uint32_t b2 = (a2 & 0x55555555u) | ((a3 & 0x55555555u) << 1);
+        const uint32_t b3 = ((a2 >> 1) & 0x55555555u) | (a3 & 0xAAAAAAAAu);
+        uint32_t u[4];
+        u[0] = (b0 & 0x33333333u) | ((b2 & 0x33333333u) << 2);
+        u[2] = ((b0 >> 2) & 0x33333333u) | (b2 & 0xCCCCCCCCu);
+        u[1] = (b1 & 0x33333333u) | ((b3 & 0x33333333u) << 2);
+        u[3] = ((b1 >> 2) & 0x33333333u) | (b3 & 0xCCCCCCCCu);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt)
+            acc[4 * k + tt] += __shfl_sync(0xffffffffu, lut, int(u[tt] >> (4 * k)), 16);
+      }
+      d = d0 + 4 * quads + slot;
+    }
     for (; d + 3 * slots < d1; d += 4 * slots) {
       uint32_t v[4]; float wd[4];
 #pragma unroll
@@ -624,9 +671,15 @@ extern "C" int nes_bin_weighted_sum(const void* in, const uint16_t* w_half, uint
   NES_REQUIRE(scratch && scratch_bytes >= need, NES_ERR_SCRATCH, "bin_weighted_sum: scratch needs %lld bytes", (long long)need);
   NES_REQUIRE(rows <= 65535 && p.splits <= 65535, NES_ERR_UNSUPPORTED, "bin_weighted_sum: rows > 65535");
   dim3 grid((unsigned)p.bx, (unsigned)rows, (unsigned)p.splits);
-  weighted_sum_kernel<<<grid, WS_THREADS, 0, st>>>(static_cast<const uint32_t*>(in), reinterpret_cast<const __half*>(w_half),
-                                                    static_cast<float*>(scratch), D, rows, int(row_u32), zbits,
-                                                    p.d_per_split, p.cols_per_block, p.slots);
+  // the four-member path needs whole warps per member slot (and so per active column range)
+  if (p.cols_per_block % 32 == 0 && row_u32 % 32 == 0)
+    weighted_sum_kernel<true><<<grid, WS_THREADS, 0, st>>>(static_cast<const uint32_t*>(in), reinterpret_cast<const __half*>(w_half),
+                                                           static_cast<float*>(scratch), D, rows, int(row_u32), zbits,
+                                                           p.d_per_split, p.cols_per_block, p.slots);
+  else
+    weighted_sum_kernel<false><<<grid, WS_THREADS, 0, st>>>(static_cast<const uint32_t*>(in), reinterpret_cast<const __half*>(w_half),
+                                                            static_cast<float*>(scratch), D, rows, int(row_u32), zbits,
+                                                            p.d_per_split, p.cols_per_block, p.slots);
   int rc = check_launch("bin_weighted_sum");
   if (rc != NES_OK) return rc;
   const int64_t n = rows * zbits;

@@ -101,7 +101,8 @@ def test_sample_bits_philox(ops):
 
 
 @pytest.mark.parametrize("bits", [32, 64])
-@pytest.mark.parametrize("D,rows,cols", [(64, 5, 100), (200, 3, 64), (33, 2, 700), (1, 1, 1)])
+@pytest.mark.parametrize("D,rows,cols", [(64, 5, 100), (200, 3, 64), (33, 2, 700), (1, 1, 1),
+                                         (203, 3, 1024), (37, 2, 3072), (70, 1, 9216), (3, 2, 2048)])
 def test_weighted_sum(ops, bits, D, rows, cols):
     rng = np.random.default_rng(D + rows + cols)
     b = rng.integers(0, 2, (D, rows, cols)).astype(bool)
