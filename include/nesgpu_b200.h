@@ -313,7 +313,10 @@ int nes_bin_unpack(const void* in, uint8_t* out, int64_t rows, int64_t words, in
 /* out[x,y,z] bit i = float(p[y, word_bits*z + i]) > u, for x in [0,n): Bernoulli(p) bits.
  * p (rows,cols) fp16.  If `uniforms` (n,rows,cols) fp32 is given it supplies u; otherwise a bit is
  * set when a 16-bit uniform integer from Philox-4x32-10 keyed by (seed, x, y, column) is below
- * ceil(p * 65536): Bernoulli(p) with p rounded up to a multiple of 2^-16.
+ * ceil(p * 65536): Bernoulli(p) with p rounded up to a multiple of 2^-16.  The compare runs
+ * bit-sliced over the 32 columns of a word (threshold bit-planes against random words, eight
+ * random words per output word; a uniform's low byte reuses, rotated, bits that are high-byte
+ * bits of other columns, so each uniform is sixteen independent bits).
  * Replaces sample_bits_kernel (extensions/src/sample_bits.cu:9-60) and cuda_sample_bits
  * (booleanUtilitiesCuda.cu:95-122,199-223). */
 int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms, void* out, int64_t n,

@@ -86,45 +86,70 @@ __global__ void sample_bits_kernel(const __half* __restrict__ p, const float* __
   out[e] = word;
 }
 
-// Device-generated variant: one thread owns 32 columns of one row and walks a chunk of members with the
-// 32 Bernoulli thresholds held in registers.  A bit is set when a 16-bit uniform integer from
-// Philox-4x32-10 (eight per call, counter = (column group, row, member)) is below ceil(p * 65536), i.e.
-// with probability p rounded up to a multiple of 2^-16 (p = 0 never, p = 1 always).
-constexpr int SAMPLE_MEMBERS = 16;
+// Device-generated variant: one thread owns 32 columns of one row and walks a chunk of members.  A bit
+// is set when a 16-bit uniform integer U is below T = ceil(p * 65536), i.e. with probability p rounded
+// up to a multiple of 2^-16 (p = 0 never, p = 1 always).  The comparison runs on all 32 columns at once,
+// bit-sliced: the thresholds are held as 16 bit-planes (plane j, bit i = bit j of T_i), a random word
+// supplies bit j of all 32 uniforms, and from the top plane down a column is decided at the first plane
+// where its uniform and its threshold differ.  Two Philox-4x32-10 calls per word (counter = (column
+// group, row, member)) give eight words: word k is bit 15-k of the uniforms, and the same word rotated
+// by k+1 columns is bit 7-k, so each U is sixteen independent random bits (its low byte is made of bits
+// that serve as high-byte bits of other columns; it only matters when the high bytes of U and T agree).
+struct BitDrawer {
+  uint32_t plane[16];
+  uint32_t always;
+
+  __device__ inline void init(const __half* __restrict__ p, int64_t y, int64_t c0, int64_t cols) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) plane[j] = 0u;
+    always = 0u;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float pv = 0.f;
+      if (c0 + i < cols) pv = __half2float(p[y * cols + c0 + i]);
+      const float t = ceilf(pv * 65536.f);
+      const uint32_t T = (t <= 0.f) ? 0u : (t >= 65536.f ? 65536u : uint32_t(t));
+      always |= (T >> 16) << i;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) plane[j] |= ((T >> j) & 1u) << i;
+    }
+  }
+
+  __device__ inline uint32_t draw(const Philox& ph, int64_t q, int64_t y, int64_t x) const {
+    uint32_t r[8];
+    ph(uint32_t(q * 2), uint32_t(y), uint32_t(x), 5u, r);
+    ph(uint32_t(q * 2 + 1), uint32_t(y), uint32_t(x), 5u, r + 4);
+    uint32_t und = ~0u, res = always;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t P = plane[15 - k];
+      const uint32_t diff = r[k] ^ P;
+      res |= und & diff & P;
+      und &= ~diff;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t P = plane[7 - k];
+      const uint32_t diff = __funnelshift_r(r[k], r[k], k + 1) ^ P;
+      res |= und & diff & P;
+      und &= ~diff;
+    }
+    return res;
+  }
+};
 
 __global__ void __launch_bounds__(256) sample_bits_philox_kernel(const __half* __restrict__ p, uint32_t* __restrict__ out,
                                                                  int64_t n, int64_t rows, int64_t cols, int64_t row_u32,
-                                                                 uint64_t seed) {
+                                                                 uint64_t seed, int members) {
   const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (e >= rows * row_u32) return;
   const int64_t q = e % row_u32, y = e / row_u32;
-  const int64_t c0 = q * 32;
-  uint32_t thr[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float pv = 0.f;
-    if (c0 + i < cols) pv = __half2float(p[y * cols + c0 + i]);
-    const float t = ceilf(pv * 65536.f);
-    thr[i] = (t <= 0.f) ? 0u : (t >= 65536.f ? 65536u : uint32_t(t));
-  }
+  BitDrawer bd;
+  bd.init(p, y, q * 32, cols);
   const Philox ph(seed);
-  const int64_t x0 = int64_t(blockIdx.y) * SAMPLE_MEMBERS;
-  const int64_t x1 = (x0 + SAMPLE_MEMBERS < n) ? x0 + SAMPLE_MEMBERS : n;
-  for (int64_t x = x0; x < x1; ++x) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint32_t r[4];
-      ph(uint32_t(q * 4 + g), uint32_t(y), uint32_t(x), 5u, r);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = g * 8 + 2 * j;
-        word |= ((r[j] & 0xFFFFu) < thr[i] ? 1u : 0u) << i;
-        word |= ((r[j] >> 16) < thr[i + 1] ? 1u : 0u) << (i + 1);
-      }
-    }
-    out[(x * rows + y) * row_u32 + q] = word;
-  }
+  const int64_t x0 = int64_t(blockIdx.y) * members;
+  const int64_t x1 = (x0 + members < n) ? x0 + members : n;
+  for (int64_t x = x0; x < x1; ++x) out[(x * rows + y) * row_u32 + q] = bd.draw(ph, q, y, x);
 }
 
 // Fused sampling + product: the weight bits of member x are drawn exactly as sample_bits_philox_kernel draws
@@ -133,35 +158,17 @@ __global__ void __launch_bounds__(256) sample_bits_philox_kernel(const __half* _
 // so the (n, rows, words) bit tensor is never stored.  Integer atomics make the sum order-independent.
 __global__ void __launch_bounds__(256) seeded_bmv_kernel(const __half* __restrict__ p, const uint32_t* __restrict__ B,
                                                          int32_t* __restrict__ C, int64_t n, int64_t rows, int64_t cols,
-                                                         int64_t row_u32, uint64_t seed) {
+                                                         int64_t row_u32, uint64_t seed, int members) {
   const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (e >= rows * row_u32) return;
   const int64_t q = e % row_u32, y = e / row_u32;
-  const int64_t c0 = q * 32;
-  uint32_t thr[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    float pv = 0.f;
-    if (c0 + i < cols) pv = __half2float(p[y * cols + c0 + i]);
-    const float t = ceilf(pv * 65536.f);
-    thr[i] = (t <= 0.f) ? 0u : (t >= 65536.f ? 65536u : uint32_t(t));
-  }
+  BitDrawer bd;
+  bd.init(p, y, q * 32, cols);
   const Philox ph(seed);
-  const int64_t x0 = int64_t(blockIdx.y) * SAMPLE_MEMBERS;
-  const int64_t x1 = (x0 + SAMPLE_MEMBERS < n) ? x0 + SAMPLE_MEMBERS : n;
+  const int64_t x0 = int64_t(blockIdx.y) * members;
+  const int64_t x1 = (x0 + members < n) ? x0 + members : n;
   for (int64_t x = x0; x < x1; ++x) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint32_t r[4];
-      ph(uint32_t(q * 4 + g), uint32_t(y), uint32_t(x), 5u, r);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = g * 8 + 2 * j;
-        word |= ((r[j] & 0xFFFFu) < thr[i] ? 1u : 0u) << i;
-        word |= ((r[j] >> 16) < thr[i + 1] ? 1u : 0u) << (i + 1);
-      }
-    }
+    const uint32_t word = bd.draw(ph, q, y, x);
     int cnt = __popc(word ^ __ldg(B + x * row_u32 + q));
     // lanes of a warp hold consecutive 32-bit columns; when a row is a whole number of warps wide the
     // warp reduces first and issues one atomic
@@ -173,6 +180,14 @@ __global__ void __launch_bounds__(256) seeded_bmv_kernel(const __half* __restric
       atomicAdd(C + x * rows + y, cnt);
     }
   }
+}
+
+// Members per block for the two kernels above: the threshold planes cost about a thousand instructions
+// to set up, so a block keeps them for as many members as still leaves the grid a few waves deep.
+static int sample_members_per_block(int64_t n, int64_t column_blocks) {
+  int m = 64;
+  while (m > 8 && column_blocks * ceil_div<int64_t>(n, m) < int64_t(sm_count()) * 8) m >>= 1;
+  return m;
 }
 
 // ---- XOR-popcount batched matrix product ------------------------------------------------
@@ -599,9 +614,10 @@ extern "C" int nes_bin_sample_bits(const uint16_t* p_half, const float* uniforms
     sample_bits_kernel<<<blocks, 256, 0, as_stream(stream)>>>(p, uniforms, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed, vec);
   } else {
     const int64_t pairs = rows * row_u32;
-    NES_REQUIRE(ceil_div<int64_t>(n, SAMPLE_MEMBERS) <= 65535, NES_ERR_UNSUPPORTED, "bin_sample_bits: more than %d members", 65535 * SAMPLE_MEMBERS);
-    dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, SAMPLE_MEMBERS));
-    sample_bits_philox_kernel<<<grid, 256, 0, as_stream(stream)>>>(p, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed);
+    const int members = sample_members_per_block(n, ceil_div<int64_t>(pairs, 256));
+    NES_REQUIRE(ceil_div<int64_t>(n, members) <= 65535, NES_ERR_UNSUPPORTED, "bin_sample_bits: more than %d members", 65535 * members);
+    dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, members));
+    sample_bits_philox_kernel<<<grid, 256, 0, as_stream(stream)>>>(p, static_cast<uint32_t*>(out), n, rows, cols, row_u32, seed, members);
   }
   return check_launch("bin_sample_bits");
 }
@@ -717,10 +733,11 @@ extern "C" int nes_bin_seeded_bmv(const uint16_t* p_half, const void* B, int32_t
   cudaMemsetAsync(C, 0, n * rows * sizeof(int32_t), st);
   if (row_u32 == 0) return NES_OK;
   const int64_t pairs = rows * row_u32;
-  NES_REQUIRE(ceil_div<int64_t>(n, SAMPLE_MEMBERS) <= 65535 && ceil_div<int64_t>(pairs, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED,
+  const int members = sample_members_per_block(n, ceil_div<int64_t>(pairs, 256));
+  NES_REQUIRE(ceil_div<int64_t>(n, members) <= 65535 && ceil_div<int64_t>(pairs, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED,
               "bin_seeded_bmv: too large");
   NES_REQUIRE(rows <= UINT32_MAX && n <= UINT32_MAX, NES_ERR_UNSUPPORTED, "bin_seeded_bmv: too large");
-  dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, SAMPLE_MEMBERS));
-  seeded_bmv_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(p_half), static_cast<const uint32_t*>(B), C, n, rows, cols, row_u32, seed);
+  dim3 grid((unsigned)ceil_div<int64_t>(pairs, 256), (unsigned)ceil_div<int64_t>(n, members));
+  seeded_bmv_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(p_half), static_cast<const uint32_t*>(B), C, n, rows, cols, row_u32, seed, members);
   return check_launch("bin_seeded_bmv");
 }

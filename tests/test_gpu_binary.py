@@ -100,6 +100,25 @@ def test_sample_bits_philox(ops):
     assert not torch.equal(a[0], a[1])
 
 
+def test_sample_bits_philox_statistics(ops):
+    """Per-column frequencies over 16384 members match thresholds that need the low planes
+    (p = k / 65536), the ends are exact, and neighbouring columns are uncorrelated."""
+    n = 16384
+    pv = torch.tensor([0.0, 1.0, 0.5, 0.25, 2.0 ** -9, 0.5 + 2.0 ** -9, 0.75, 2.0 ** -12,
+                       1.0 - 2.0 ** -10, 0.3, 0.5, 0.5, 0.1, 0.9, 2.0 ** -8 + 2.0 ** -9, 0.6])
+    p = pv.repeat(2, 4).half().to(DEV)                     # (2 rows, 64 columns)
+    a = ops.sample_bits(p, n, torch.int32, 7)
+    bits = ops.unpack(a.view(-1, a.shape[-1])).view(n, 2, 64).float()
+    freq = bits.mean(dim=0).cpu()
+    want = p.float().cpu()
+    sd = (want * (1 - want) / n).sqrt()
+    assert torch.all((freq - want).abs() <= 5 * sd + 1e-9), (freq - want).abs().max()
+    assert torch.all(freq[want == 0] == 0) and torch.all(freq[want == 1] == 1)
+    x = bits[:, 0, 10].cpu() - 0.5                          # p = .5 at columns 10 and 11
+    y = bits[:, 0, 11].cpu() - 0.5
+    assert abs(float((x * y).mean()) / 0.25) < 5 / n ** 0.5
+
+
 @pytest.mark.parametrize("bits", [32, 64])
 @pytest.mark.parametrize("D,rows,cols", [(64, 5, 100), (200, 3, 64), (33, 2, 700), (1, 1, 1),
                                          (203, 3, 1024), (37, 2, 3072), (70, 1, 9216), (3, 2, 2048)])
