@@ -531,6 +531,7 @@ class EsCnn(Workload):
     """BASELINE configuration 5: one ES step of the small CNN, 1024 members per GPU (8192 over 8 GPUs)."""
     name = "es_cnn_8192"
     D, R = 1024, 256
+    fused = True                  # --unfused: module-by-module Conv / ReLU / MaxPool2d, per-member input copies
     FLOP_PER_PAIR = 5.262e6       # conv1 0.389 + conv2 4.461 + fc1 0.410 + fc2 0.003 MFLOP per (member, image), minimal form
 
     def __init__(self, members=None):
@@ -543,7 +544,7 @@ class EsCnn(Workload):
         return {"workload": self.name, "net": "Conv(1,32,3)-ReLU-MaxPool2-Conv(32,64,3)-ReLU-MaxPool2-Linear(1600,128)-ReLU-Linear(128,10), Permuted layers",
                 "directions_per_gpu": self.D, "population": self.D * world, "images_per_member": self.R,
                 "step": "set_noise + chunked population forward + CE fitness + centred ranks + update (+ all-gather / all-reduce at N>1)",
-                "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02}
+                "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02, "fused_layers": self.fused}
 
     def setup(self, dev, rank, world):
         from nesgpu_b200 import base, es
@@ -551,11 +552,18 @@ class EsCnn(Workload):
         D = self.D
         torch.manual_seed(1005)       # same initial weights on every rank
         opts = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}
-        self.net = torch.nn.Sequential(
-            base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
-            base.PermutedConv2d(32, 64, 3, D, options=opts), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Flatten(),
-            base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
-        self.layer = self.net[3]
+        if self.fused:
+            # Conv -> ReLU -> MaxPool2 blocks as fused layers; the first one is told that the images are shared
+            o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_tf32": bool(opts)}
+            self.net = torch.nn.Sequential(
+                base.PermutedConv2d(1, 32, 3, D, options=o1),
+                base.PermutedConv2d(32, 64, 3, D, options=dict(opts, fuse="relu_maxpool2")), torch.nn.Flatten(),
+                base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
+        else:
+            self.net = torch.nn.Sequential(
+                base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
+                base.PermutedConv2d(32, 64, 3, D, options=opts), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Flatten(),
+                base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
         self.pm = base.PerturbedModel(self.net, D)
         self.pm.set_noise_scale(0.02)
         self.pm.set_seed(9000 + rank)
@@ -730,6 +738,8 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
     wl = WORKLOADS[args.workload](args.members) if args.members else WORKLOADS[args.workload]()
     wl.tc = args.tc
+    if args.unfused:
+        wl.fused = False
     wl.setup(dev, rank, world)
     peaks = measured_peaks()
     flush = None
@@ -862,6 +872,8 @@ def main():
                     help="permuted_linear_256: launch every step from Python instead of replaying a captured CUDA graph")
     ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32", "bf16"],
                     help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
+    ap.add_argument("--unfused", action="store_true",
+                    help="es_cnn_8192: separate Conv / ReLU / MaxPool2d modules and per-member input copies instead of the fused layers")
     ap.add_argument("--members", type=int, default=0,
                     help="members per GPU instead of 1024 (small case for ncu captures; not for binary_1024 / permuted_linear_256)")
     args = ap.parse_args()

@@ -168,6 +168,32 @@ int nes_permuted_linear_fwd(const float* x, const float* weight, const float* bi
                             int64_t in_sp, int64_t out_sp, int antithetic,
                             void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
+/* The same layer without output permutations (pout == NULL) as ONE tensor-core product
+ *   y = [ x | s(r) * xg ] . [ weight | eps ]^T + bias + s(r) * bias_noise[d]
+ * (K = in + in_sp): a pre-pass writes the concatenated, TF32-rounded (mode 1) or hi/lo-split (mode 3,
+ * fp32-level accuracy) operand into `scratch`, then the tcgen05 tile kernel of nes_linear_fwd_tc runs
+ * on it with the per-member bias term in its epilogue.  Rows of eps at or above out_sp count as zero.
+ * Replaces the same reference lines (modules/base.py:487-508) for input-permuted layers. */
+int64_t nes_permuted_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out,
+                                                 int64_t in_sp, int mode);
+int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float* bias,
+                               const float* eps, const float* bias_noise, const int16_t* pin,
+                               float* y, int64_t D, int64_t R, int64_t in, int64_t out,
+                               int64_t in_sp, int64_t out_sp, int antithetic, int mode,
+                               void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* Out-permuted convolution of an input shared by all members, fused with ReLU and 2x2/2 max-pooling
+ * (floor mode).  z (R, Cout + out_sp, Ho, Wo) is the plain convolution of the R shared images with
+ * the stacked filter [weight; eps] and no bias (for instance from nes_conv2d_fwd); for b = r*D + d
+ *   y[b, py, px, c] = relu(max_{2x2}( z[r, c] + s(r) * z[r, Cout + pout[d,c]] ) + bias[c] + s(r) * bias_noise[d,c])
+ * with the noise term dropped where pout[d,c] >= out_sp (pout == NULL: identity).  y is channels-last,
+ * (R*D, Ho/2, Wo/2, Cout); round_tf32 != 0 rounds the stored values to TF32 (for a tensor-core consumer).
+ * Replaces, for this case, PermutedConv2d.forward (modules/base.py:557-588) followed by the ReLU and
+ * MaxPool2d modules of the reference's models (models/mnistmodels.py:35-57). */
+int nes_shared_conv_pool_fwd(const float* z, const float* bias, const float* bias_noise,
+                             const int16_t* pout, float* y, int64_t R, int64_t D, int Cout, int out_sp,
+                             int Ho, int Wo, int antithetic, int round_tf32, nes_stream_t stream);
+
 /* PermutedConv2d.forward, default branch (modules/base.py:557-588), evaluated as one
  * convolution per member with the effective filter
  *   W_d[k,c,:,:] = weight[k,c] + s(r) * eps[pout[d,k], j]  for the j with pin[d,j] == c

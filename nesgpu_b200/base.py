@@ -457,6 +457,24 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         Permuted.__init__(self, in_features, out_features, directions, antithetic=antithetic, options=options,
                           permutation=permutation, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
 
+    # rows x outputs from which the one-product tensor-core form is chosen by default (64 tiles of 128 x 128)
+    SINGLE_PRODUCT_MIN = 64 * 128 * 128
+
+    def _single_product_mode(self, rows, pout):
+        """Mode (1 = TF32, 3 = 3xTF32) of the one-product tensor-core forward, or 0 for the CUDA-core kernels.
+
+        ``options["tc"]``: ``"3xtf32"`` / ``"tf32"`` force it, ``"fp32"`` forbids it; by default ("auto") the
+        error-compensated 3xTF32 form (fp32-level accuracy) is taken for batches of at least
+        ``SINGLE_PRODUCT_MIN`` outputs.  It needs a layer without output permutations."""
+        mode = self.options.get("tc", "auto")
+        if mode not in ("auto", "fp32", "3xtf32", "tf32"):
+            raise NotImplementedError('options["tc"] must be "auto", "3xtf32", "tf32" or "fp32"')
+        if mode == "fp32" or pout is not None or rows == 0:
+            return 0
+        if mode == "auto":
+            return 3 if rows * self.out_features >= self.SINGLE_PRODUCT_MIN else 0
+        return _TC_MODES[mode]
+
     def forward(self, input):
         if not self.perturbed_flag:
             return self._plain_forward(input)
@@ -466,6 +484,16 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         pin, pout = self._perms()
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        mode = self._single_product_mode(x.shape[0], pout)
+        if mode:
+            nbytes = C.call("nes_permuted_linear_fwd_tc_scratch_bytes", self.directions, R, self.in_features,
+                            self.out_features, self.in_sparsity, mode)
+            buf = C.scratch(nbytes, x.device)
+            C.call("nes_permuted_linear_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+                   C.ptr(eps), C.ptr(beta), C.ptr(pin), C.ptr(y), self.directions, R, self.in_features,
+                   self.out_features, self.in_sparsity, self.out_sparsity, 1 if self.antithetic else 0, mode,
+                   C.ptr(buf), nbytes, C.stream())
+            return y.view(*lead, self.out_features)
         nbytes = C.call("nes_permuted_linear_fwd_scratch_bytes", self.directions, R, self.out_sparsity)
         buf = C.scratch(nbytes, x.device)
         C.call("nes_permuted_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
@@ -579,8 +607,62 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         return E
 
     def forward(self, input):
+        """Two options beyond the reference's, both off by default:
+
+        ``options["fuse"] = "relu_maxpool2"`` makes the layer return ``max_pool2d(relu(conv), 2)`` (the
+        Conv -> ReLU -> MaxPool2d(2) block of the reference's models, ``models/mnistmodels.py:35-57``) so
+        that the full-resolution activations never reach memory where a fused kernel exists;
+        ``options["shared_input"] = True`` declares that every member sees the same images: the layer then
+        takes ``(R, C, H, W)`` and returns the ``(R * directions, ...)`` population batch.  With both set and
+        output permutations only, the two convolutions ``conv(x, W)`` and ``conv(x, eps)`` are computed once
+        per image and the per-member work is a fused gather + add + ReLU + pool; the result is a
+        channels-last tensor (``options["out_tf32"]`` rounds it to TF32 for a tensor-core consumer)."""
+        fuse = self.options.get("fuse")
+        if fuse not in (None, "relu_maxpool2"):
+            raise NotImplementedError('options["fuse"] must be "relu_maxpool2"')
+        shared = bool(self.options.get("shared_input"))
         if not self.perturbed_flag:
-            return self._plain_forward(input)
+            y = self._plain_forward(input)
+            return F.max_pool2d(F.relu(y), 2) if fuse else y
+        if shared:
+            y = self._shared_fused_forward(input) if fuse else None
+            if y is not None:
+                return y
+            input = input.unsqueeze(1).expand(input.shape[0], self.directions, *input.shape[1:]).reshape(
+                input.shape[0] * self.directions, *input.shape[1:])
+        y = self._fused_tc_forward(input) if fuse else None
+        if y is not None:
+            return y
+        y = self._perturbed_forward(input)
+        return F.max_pool2d(F.relu(y), 2) if fuse else y
+
+    def _shared_fused_forward(self, input):
+        """Shared images, output permutations only: one stacked convolution per image, then the fused
+        per-member kernel.  Returns None when the case is not covered."""
+        pin, pout = self._perms()
+        if pin is not None or self.options.get("allow_repeats"):
+            return None
+        x = C.require_cuda(input, "input", _F32)
+        x, geom, (Ho, Wo) = self._geometry(x)
+        osp, cout = self.out_sparsity, self.out_channels
+        if (cout + osp) * ((Ho * Wo) | 1) * 4 > 220 * 1024 or Ho < 2 or Wo < 2:
+            return None
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        R, D = x.shape[0], self.directions
+        stacked = torch.cat([self.weight.detach(), eps.view(osp, *self.weight.shape[1:])], dim=0).contiguous()
+        z = torch.empty((R, cout + osp, Ho, Wo), device=x.device, dtype=_F32)
+        C.call("nes_conv2d_fwd", C.ptr(x), C.ptr(stacked), None, C.ptr(z), R, geom[0], geom[1], geom[2], cout + osp,
+               *geom[4:], C.stream())
+        y = torch.empty((R * D, Ho // 2, Wo // 2, cout), device=x.device, dtype=_F32)
+        C.call("nes_shared_conv_pool_fwd", C.ptr(z), C.ptr(_opt(self.bias)), C.ptr(beta), C.ptr(pout), C.ptr(y),
+               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, 1 if self.options.get("out_tf32") else 0, C.stream())
+        return y.permute(0, 3, 1, 2)
+
+    def _fused_tc_forward(self, input):
+        return None
+
+    def _perturbed_forward(self, input):
         x = C.require_cuda(input, "input", _F32)
         x, geom, out_hw = self._geometry(x)
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)

@@ -28,9 +28,13 @@ constexpr int NTHREADS = 192;                        // warp 0: TMA, warp 1: MMA
 
 struct Maps { CUtensorMap a_hi, b_hi, a_lo, b_lo; };
 
+// Optional per-row epilogue term of the population-batched layers: row gm belongs to member gm % D and
+// repeat gm / D, and receives sign(repeat) * bias_noise[member, column].
+struct RowTerm { const float* bias_noise; int64_t D, R; int antithetic; };
+
 template <int TERMS>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_constant__ Maps maps, const float* __restrict__ bias,
-                                                                 float* __restrict__ C, int M, int N, int K, int stages) {
+                                                                 const RowTerm rt, float* __restrict__ C, int M, int N, int K, int stages) {
   extern __shared__ unsigned char dyn_raw[];
   constexpr int OPERANDS = (TERMS == 3) ? 4 : 2;
   constexpr int STAGE_BYTES = OPERANDS * TILE_BYTES;
@@ -111,6 +115,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
     tc_fence_after();
     if (ok && g_tc_error == 0 && nk > 0) {
       const int64_t gm = int64_t(m0) + q * 32 + lane;
+      const float* bn_row = nullptr;
+      float bn_sign = 1.f;
+      if (rt.bias_noise && gm < M) {
+        bn_row = rt.bias_noise + (gm % rt.D) * N;
+        bn_sign = anti_sign(gm / rt.D, rt.R, rt.antithetic);
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -126,6 +136,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
             for (int u = 0; u < 4; ++u) {
               v[u] = __uint_as_float(r[j + u]);
               if (bias && gn + u < N) v[u] += __ldg(bias + gn + u);
+              if (bn_row && gn + u < N) v[u] += bn_sign * __ldg(bn_row + gn + u);
             }
             if (vec && gn + 3 < N) {
               *reinterpret_cast<float4*>(dst + j) = make_float4(v[0], v[1], v[2], v[3]);
@@ -139,7 +150,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
     } else if (ok && nk == 0) {
       const int64_t gm = int64_t(m0) + q * 32 + lane;
       if (gm < M)
-        for (int j = 0; j < BN; ++j) if (n0 + j < N) C[gm * N + n0 + j] = bias ? bias[n0 + j] : 0.f;
+        for (int j = 0; j < BN; ++j)
+          if (n0 + j < N) {
+            float v = bias ? bias[n0 + j] : 0.f;
+            if (rt.bias_noise) v += anti_sign(gm / rt.D, rt.R, rt.antithetic) * rt.bias_noise[(gm % rt.D) * N + n0 + j];
+            C[gm * N + n0 + j] = v;
+          }
     }
   }
   tc_fence_before();
@@ -155,6 +171,45 @@ __global__ void split_tf32_kernel(const float* __restrict__ src, float* __restri
   const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float a = src[i];
+  const float h = round_tf32(a);
+  hi[i] = h;
+  if (lo) lo[i] = a - h;
+}
+
+// Operand of the permuted layer's single product: row b of A2 is [ x[b, :] | s(b) * x[b, pin[d, :]] | 0.. ],
+// rounded to tf32 (hi) with the residual kept (lo) for the 3-term scheme.  One block per row; the row is
+// read once coalesced, the gather then hits it in L1/L2.
+__global__ void __launch_bounds__(256) permuted_operand_kernel(const float* __restrict__ x, const int16_t* __restrict__ pin,
+                                                               float* __restrict__ hi, float* __restrict__ lo,
+                                                               int64_t B, int64_t D, int64_t R, int in, int in_sp, int K2,
+                                                               int antithetic) {
+  for (int64_t b = blockIdx.x; b < B; b += gridDim.x) {
+    const int64_t d = b % D;
+    const float sgn = anti_sign(b / D, R, antithetic);
+    const float* xr = x + b * in;
+    const int16_t* pr = pin ? pin + d * in_sp : nullptr;
+    for (int k = threadIdx.x; k < K2; k += blockDim.x) {
+      float a = 0.f;
+      if (k < in) a = xr[k];
+      else if (k < in + in_sp) a = sgn * xr[pr ? int(pr[k - in]) : k - in];
+      const float h = round_tf32(a);
+      hi[b * K2 + k] = h;
+      if (lo) lo[b * K2 + k] = a - h;
+    }
+  }
+}
+
+// B2[o, :] = [ weight[o, :] | eps[o, :] (rows below out_sp, else 0) | 0.. ]
+__global__ void permuted_filter_kernel(const float* __restrict__ w, const float* __restrict__ eps,
+                                       float* __restrict__ hi, float* __restrict__ lo, int64_t out, int64_t out_sp,
+                                       int in, int in_sp, int K2) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= out * K2) return;
+  const int64_t o = i / K2;
+  const int k = int(i - o * K2);
+  float a = 0.f;
+  if (k < in) a = w[o * in + k];
+  else if (k < in + in_sp && o < out_sp) a = eps[o * in_sp + (k - in)];
   const float h = round_tf32(a);
   hi[i] = h;
   if (lo) lo[i] = a - h;
@@ -176,6 +231,37 @@ static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t c
 }
 
 static int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+// Launches the tile kernel on prepared (rounded / split) operands.
+static int run_gemm(const float* a_hi, const float* a_lo, const float* b_hi, const float* b_lo, const float* bias,
+                    const RowTerm& rt, float* y, int64_t M, int64_t N, int64_t K, int mode, cudaStream_t st, const char* what) {
+  int rc;
+  Maps maps;
+  if ((rc = make_map(&maps.a_hi, a_hi, M, K, BM, what)) != NES_OK) return rc;
+  if ((rc = make_map(&maps.b_hi, b_hi, N, K, BN, what)) != NES_OK) return rc;
+  if (mode == 3) {
+    if ((rc = make_map(&maps.a_lo, a_lo, M, K, BM, what)) != NES_OK) return rc;
+    if ((rc = make_map(&maps.b_lo, b_lo, N, K, BN, what)) != NES_OK) return rc;
+  } else {
+    maps.a_lo = maps.a_hi;
+    maps.b_lo = maps.b_hi;
+  }
+  const int stages = (mode == 3) ? 3 : 4;
+  const int stage_bytes = (mode == 3 ? 4 : 2) * TILE_BYTES;
+  const size_t smem = 1024 + size_t(stages) * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
+  dim3 grid((unsigned)ceil_div<int64_t>(M, BM), (unsigned)ceil_div<int64_t>(N, BN));
+  cudaError_t e;
+  if (mode == 3) {
+    e = cudaFuncSetAttribute(gemm_tf32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+    gemm_tf32_kernel<3><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
+  } else {
+    e = cudaFuncSetAttribute(gemm_tf32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+    gemm_tf32_kernel<1><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
+  }
+  return check_launch(what);
+}
 
 }  // namespace tc
 }  // namespace nes
@@ -217,31 +303,53 @@ extern "C" int nes_linear_fwd_tc(const float* x, const float* weight, const floa
   rc = check_launch("linear_fwd_tc(split w)");
   if (rc != NES_OK) return rc;
 
-  Maps maps;
-  if ((rc = make_map(&maps.a_hi, a_hi, M, K, BM, "linear_fwd_tc")) != NES_OK) return rc;
-  if ((rc = make_map(&maps.b_hi, b_hi, N, K, BN, "linear_fwd_tc")) != NES_OK) return rc;
-  if (mode == 3) {
-    if ((rc = make_map(&maps.a_lo, a_lo, M, K, BM, "linear_fwd_tc")) != NES_OK) return rc;
-    if ((rc = make_map(&maps.b_lo, b_lo, N, K, BN, "linear_fwd_tc")) != NES_OK) return rc;
-  } else {
-    maps.a_lo = maps.a_hi;
-    maps.b_lo = maps.b_hi;
-  }
-  const int stages = (mode == 3) ? 3 : 4;
-  const int stage_bytes = (mode == 3 ? 4 : 2) * TILE_BYTES;
-  const size_t smem = 1024 + size_t(stages) * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
-  dim3 grid((unsigned)ceil_div<int64_t>(M, BM), (unsigned)ceil_div<int64_t>(N, BN));
-  cudaError_t e;
-  if (mode == 3) {
-    e = cudaFuncSetAttribute(gemm_tf32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "linear_fwd_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
-    gemm_tf32_kernel<3><<<grid, NTHREADS, smem, st>>>(maps, bias, y, int(M), int(N), int(K), stages);
-  } else {
-    e = cudaFuncSetAttribute(gemm_tf32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "linear_fwd_tc: shared memory opt-in failed: %s", cudaGetErrorString(e));
-    gemm_tf32_kernel<1><<<grid, NTHREADS, smem, st>>>(maps, bias, y, int(M), int(N), int(K), stages);
-  }
-  return check_launch("linear_fwd_tc");
+  const RowTerm none = {nullptr, 1, 1, 0};
+  return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, none, y, M, N, K, mode, st, "linear_fwd_tc");
+}
+
+static int64_t permuted_k2(int64_t in, int64_t in_sp) { return (in + in_sp + 3) & ~int64_t(3); }
+
+extern "C" int64_t nes_permuted_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out, int64_t in_sp, int mode) {
+  if (D <= 0 || R <= 0 || out <= 0 || in < 0 || in_sp < 0) return 0;
+  const int64_t K2 = permuted_k2(in, in_sp);
+  const int64_t a = align256(D * R * K2 * 4), b = align256(out * K2 * 4);
+  return mode == 3 ? 2 * (a + b) : (a + b);
+}
+
+extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float* bias, const float* eps,
+                                          const float* bias_noise, const int16_t* pin, float* y,
+                                          int64_t D, int64_t R, int64_t in, int64_t out, int64_t in_sp, int64_t out_sp,
+                                          int antithetic, int mode, void* scratch, int64_t scratch_bytes,
+                                          nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0 && in_sp >= 0 && out_sp >= 0 && out_sp <= out, NES_ERR_BAD_ARG,
+              "permuted_linear_fwd_tc: bad extent");
+  NES_REQUIRE(mode == 1 || mode == 3, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: mode must be 1 (TF32) or 3 (3xTF32)");
+  if (D == 0 || R == 0 || out == 0) return NES_OK;
+  NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: null pointer");
+  NES_REQUIRE(pin || in_sp == in, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: in_sp != in without input permutations");
+  NES_REQUIRE(in > 0 && in <= 32767 && in_sp <= INT32_MAX - in, NES_ERR_UNSUPPORTED, "permuted_linear_fwd_tc: in=%lld out of range", (long long)in);
+  const int64_t B = D * R, K2 = permuted_k2(in, in_sp);
+  NES_REQUIRE(B <= INT32_MAX && out <= INT32_MAX && K2 <= INT32_MAX && ceil_div<int64_t>(out, BN) <= 65535, NES_ERR_UNSUPPORTED,
+              "permuted_linear_fwd_tc: extent too large");
+  const int64_t need = nes_permuted_linear_fwd_tc_scratch_bytes(D, R, in, out, in_sp, mode);
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "permuted_linear_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)need);
+  cudaStream_t st = as_stream(stream);
+  unsigned char* sp = static_cast<unsigned char*>(scratch);
+  const int64_t a_bytes = align256(B * K2 * 4), b_bytes = align256(out * K2 * 4);
+  float* a_hi = reinterpret_cast<float*>(sp);
+  float* b_hi = reinterpret_cast<float*>(sp + a_bytes);
+  float* a_lo = mode == 3 ? reinterpret_cast<float*>(sp + a_bytes + b_bytes) : nullptr;
+  float* b_lo = mode == 3 ? reinterpret_cast<float*>(sp + 2 * a_bytes + b_bytes) : nullptr;
+  const unsigned blocks = (unsigned)(B < int64_t(sm_count()) * 16 ? B : int64_t(sm_count()) * 16);
+  permuted_operand_kernel<<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
+  int rc = check_launch("permuted_linear_fwd_tc(operand)");
+  if (rc != NES_OK) return rc;
+  permuted_filter_kernel<<<(unsigned)ceil_div<int64_t>(out * K2, 256), 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
+  rc = check_launch("permuted_linear_fwd_tc(filter)");
+  if (rc != NES_OK) return rc;
+  const RowTerm rt = {bias_noise, D, R, antithetic};
+  return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, rt, y, B, out, K2, mode, st, "permuted_linear_fwd_tc");
 }
 
 namespace nes { namespace tc { int conv_tc_error_word(int* v); int conv_bf16_error_word(int* v); } }

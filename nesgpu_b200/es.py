@@ -21,16 +21,29 @@ def centered_ranks(fitness):
     return ranks / max(n - 1, 1) - 0.5
 
 
+def takes_shared_input(perturbed_model):
+    """True when the model's first perturbed layer declares ``options["shared_input"]``: it then receives the
+    minibatch itself instead of its copy per member."""
+    for m in perturbed_model.model.modules():
+        if hasattr(m, "perturbed_flag") and hasattr(m, "options"):
+            return bool(m.options.get("shared_input"))
+    return False
+
+
 def population_fitness(perturbed_model, inputs, labels, directions, chunk=16):
     """Negative mean cross-entropy of every member on the shared minibatch: (directions,) tensor."""
     R = inputs.shape[0]
     loss_sum = torch.zeros(directions, device=inputs.device, dtype=torch.float32)
+    shared = takes_shared_input(perturbed_model)
     with torch.no_grad():
         for r0 in range(0, R, chunk):
             r1 = min(R, r0 + chunk)
             rc = r1 - r0
-            xb = inputs[r0:r1].unsqueeze(1).expand(rc, directions, *inputs.shape[1:]).reshape(
-                rc * directions, *inputs.shape[1:])
+            if shared:
+                xb = inputs[r0:r1].contiguous()
+            else:
+                xb = inputs[r0:r1].unsqueeze(1).expand(rc, directions, *inputs.shape[1:]).reshape(
+                    rc * directions, *inputs.shape[1:])
             logits = perturbed_model.forward(xb)
             target = labels[r0:r1].repeat_interleave(directions)
             ce = F.cross_entropy(logits.view(rc * directions, -1), target, reduction="none")

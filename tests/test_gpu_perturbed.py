@@ -441,3 +441,59 @@ def test_population_model_end_to_end(base):
     assert all(p.grad is not None for p in net.parameters())
     pm.free_memory()
     assert net[0].weight_noise is None and net[3].input_permutations is None
+
+
+@pytest.mark.parametrize("cin,cout,out_sp,hw,k,pad,R,anti,bias", [
+    (1, 32, 0, 28, 3, 0, 3, False, True),      # first layer of the small CNN
+    (3, 40, 0.5, 15, 3, 1, 4, True, True),     # odd output size (floor pooling), sparsity, antithetic halves
+    (2, 8, 0, 9, 2, 0, 1, True, False),
+])
+def test_shared_input_conv_relu_pool(base, cin, cout, out_sp, hw, k, pad, R, anti, bias):
+    """options shared_input + fuse: every member sees the same images; result equals the oracle's layer on the
+    expanded batch followed by ReLU and MaxPool2d(2), returned as a channels-last tensor."""
+    D = 12
+    g = gen(31 + cout)
+    layer = base.PermutedConv2d(cin, cout, k, D, padding=pad, bias=bias, antithetic=anti, permutation="out",
+                                out_sparsity=out_sp, options={"shared_input": True, "fuse": "relu_maxpool2"}).to(DEV)
+    osp = layer.out_sparsity
+    x = torch.rand(R, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g) * .1 if bias else None
+    eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g) if bias else None
+    pout = perms(g, D, cout)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.output_permutations = G(eps), (G(beta) if bias else None), G(pout)
+    xb = x.unsqueeze(1).expand(R, D, cin, hw, hw).reshape(R * D, cin, hw, hw).contiguous()
+    want = O.permuted_conv2d_forward(xb, W, b if bias else torch.zeros(cout), eps,
+                                     beta if bias else torch.zeros(D, cout), None, pout, D, 1, pad, 1, anti)
+    want = torch.nn.functional.max_pool2d(torch.relu(want), 2)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+        layer.perturbed_flag = False
+        y_off = layer.forward(G(x))
+    assert y.shape == want.shape and y.is_contiguous(memory_format=torch.channels_last)
+    assert_close(y, want, what="fused forward")
+    plain = torch.nn.functional.conv2d(x, W, b, 1, pad)
+    assert_close(y_off, torch.nn.functional.max_pool2d(torch.relu(plain), 2), what="inference")
+
+
+def test_fuse_option_falls_back_to_separate_kernels(base):
+    """fuse without a fused kernel for the case (input permutations): same numbers through conv + torch ops."""
+    D, R, cin, cout, hw = 6, 2, 10, 12, 11
+    g = gen(41)
+    layer = base.PermutedConv2d(cin, cout, 3, D, permutation="in", options={"fuse": "relu_maxpool2"}).to(DEV)
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, 3, 3, generator=g) * .1
+    b = torch.randn(cout, generator=g) * .1
+    eps = 0.05 * torch.randn(cout, cin, 3, 3, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    pin = perms(g, D, cin)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.input_permutations = G(eps), G(beta), G(pin)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    want = O.permuted_conv2d_forward(x, W, b, eps, beta, pin, None, D, 1, 0, 1, False)
+    assert_close(y, torch.nn.functional.max_pool2d(torch.relu(want), 2), what="forward")

@@ -246,3 +246,72 @@ def test_config3_permuted_conv_bf16_full_size():
     want = O.permuted_conv2d_forward(x, W, b, eps, beta, None, pout, D, 1, 1, 1, False)
     e = rel_err(y, want)
     assert e <= BF16_CONV_TOL, "bf16 conv rel err %g" % e
+
+
+# ---- PermutedLinear as one tensor-core product ----------------------------------------------------
+
+@pytest.mark.parametrize("tc,tol", [("3xtf32", 1e-4), ("tf32", 2e-2)])
+@pytest.mark.parametrize("mode,in_sp,out_sp,R,anti,in_f,out_f,bias", [
+    ("in", 0, 0, 2, True, 200, 136, True), ("in", 0.1, 0, 3, True, 203, 70, True),
+    ("in", 0, 0, 1, False, 64, 10, False), ("in", 0.5, 0, 4, True, 1600, 128, True),
+])
+def test_permuted_linear_single_product(tc, tol, mode, in_sp, out_sp, R, anti, in_f, out_f, bias):
+    """options["tc"] forces the one-product form; 3xTF32 holds the fp32 bar, TF32 is the stated 2e-2 mode."""
+    from nesgpu_b200 import base
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    D = 48
+    g = torch.Generator().manual_seed(in_f + out_f + R)
+    layer = base.PermutedLinear(in_f, out_f, D, bias=bias, antithetic=anti, permutation=mode, in_sparsity=in_sp,
+                                out_sparsity=out_sp, options={"tc": tc}).to(DEV)
+    isp, osp = layer.in_sparsity, layer.out_sparsity
+    assert layer.permute_inputs and not layer.permute_outputs
+    x = torch.randn(R * D, in_f, generator=g)
+    W = torch.randn(out_f, in_f, generator=g) / in_f ** .5
+    b = torch.randn(out_f, generator=g) if bias else None
+    eps = 0.05 * torch.randn(osp, isp, generator=g)
+    beta = 0.02 * torch.randn(D, out_f, generator=g) if bias else None
+    pin = torch.stack([torch.randperm(in_f, generator=g)[:isp] for _ in range(D)]).short()
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(eps), (G(beta) if bias else None)
+    layer.input_permutations = G(pin)
+    before = C_launches()
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    assert C_launches() - before == 3                       # operand pre-pass, filter pre-pass, tile kernel
+    want = O.permuted_linear_forward(x, W, b if bias else torch.zeros(out_f), eps,
+                                     beta if bias else torch.zeros(D, out_f), pin, None, D, anti)
+    assert rel_err(y, want) <= tol
+    assert _flag(_C()) == 0
+
+
+def test_permuted_linear_auto_takes_single_product_for_large_batches():
+    from nesgpu_b200 import base
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    D, R, in_f, out_f = 512, 16, 96, 128
+    g = torch.Generator().manual_seed(3)
+    layer = base.PermutedLinear(in_f, out_f, D, antithetic=True, permutation="in").to(DEV)
+    x = torch.randn(R * D, in_f, generator=g)
+    W = torch.randn(out_f, in_f, generator=g) / in_f ** .5
+    b = torch.randn(out_f, generator=g)
+    eps = 0.05 * torch.randn(out_f, in_f, generator=g)
+    beta = 0.02 * torch.randn(D, out_f, generator=g)
+    pin = torch.stack([torch.randperm(in_f, generator=g) for _ in range(D)]).short()
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.input_permutations = G(eps), G(beta), G(pin)
+    assert layer._single_product_mode(R * D, None) == 3 and layer._single_product_mode(64, None) == 0
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    assert rel_err(y, O.permuted_linear_forward(x, W, b, eps, beta, pin, None, D, True)) <= 1e-4
+
+
+def _C():
+    from nesgpu_b200 import _cabi
+    return _cabi
+
+
+def C_launches():
+    return _C().call("nes_launch_count")
