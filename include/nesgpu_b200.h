@@ -194,6 +194,23 @@ int nes_shared_conv_pool_fwd(const float* z, const float* bias, const float* bia
                              const int16_t* pout, float* y, int64_t R, int64_t D, int Cout, int out_sp,
                              int Ho, int Wo, int antithetic, int round_tf32, nes_stream_t stream);
 
+/* Out-permuted convolution (no input permutations; stride 1, no padding, no dilation) fused with ReLU
+ * and 2x2/2 max-pooling on the tensor cores (tcgen05, kind::tf32: operands rounded / truncated to
+ * TF32, fp32 accumulation; a stated reduced-precision mode, relative error ~1e-3).
+ * x_nhwc (R*D, H, W, 32) channels-last fp32; weight (Cout,32,kh,kw); eps (out_sp,32,kh,kw);
+ * pout (D,Cout) or NULL; y (R*D, Cout, Ho/2, Wo/2) NCHW:
+ *   y[b,c] = relu(maxpool2(conv(x[b], weight)[c] + s(r) * conv(x[b], eps)[pout[d,c]]) + bias[c] + s(r) * bias_noise[d,c]).
+ * Covered: Cin == 32, Cout <= 64, out_sp <= 64, kh*kw <= 9, (2*(Ho/2)-1)*W + 2*(Wo/2) <= 128;
+ * anything else returns NES_ERR_UNSUPPORTED.  `scratch` holds the stacked TF32 filter [W; eps].
+ * Replaces, for this case, PermutedConv2d.forward (modules/base.py:557-588) followed by the ReLU and
+ * MaxPool2d modules of the reference's models (models/mnistmodels.py:35-57). */
+int64_t nes_permuted_conv_pool_fwd_tc_scratch_bytes(int kh, int kw);
+int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* weight, const float* bias,
+                                  const float* eps, const float* bias_noise, const int16_t* pout,
+                                  float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                  int kh, int kw, int out_sp, int antithetic,
+                                  void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
 /* PermutedConv2d.forward, default branch (modules/base.py:557-588), evaluated as one
  * convolution per member with the effective filter
  *   W_d[k,c,:,:] = weight[k,c] + s(r) * eps[pout[d,k], j]  for the j with pin[d,j] == c

@@ -660,7 +660,38 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         return y.permute(0, 3, 1, 2)
 
     def _fused_tc_forward(self, input):
-        return None
+        """Conv + ReLU + MaxPool2d(2) in one tensor-core kernel (``options["tc"] = "tf32"``, output permutations
+        only, 32 input channels, stride 1 / no padding, one image per 128-column accumulator).  Takes the
+        input channels-last without a copy.  Returns None when the case is not covered."""
+        if self.options.get("tc") != "tf32" or self.options.get("allow_repeats") or self.groups != 1:
+            return None
+        pin, pout = self._perms()
+        kh, kw = self.kernel_size
+        if (pin is not None or self.in_channels != 32 or self.out_channels > 64 or self.out_sparsity > 64
+                or kh * kw > 9 or _pair(self.stride) != (1, 1) or _pair(self.dilation) != (1, 1)
+                or self.padding_mode != "zeros" or _pair(self.padding) != (0, 0)):
+            return None
+        if not isinstance(input, torch.Tensor) or not input.is_cuda or input.dtype != _F32 or input.dim() != 4:
+            return None
+        B, _, H, W = input.shape
+        if H < kh or W < kw or B == 0:
+            return None
+        Hp, Wp = (H - kh + 1) // 2, (W - kw + 1) // 2
+        if Hp < 1 or Wp < 1 or (2 * Hp - 1) * W + 2 * Wp > 128 or 128 + (kh - 1) * W + kw - 1 > 256:
+            return None
+        x = input.permute(0, 2, 3, 1)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        R = self._repeats(B)
+        y = torch.empty((B, self.out_channels, Hp, Wp), device=x.device, dtype=_F32)
+        nbytes = C.call("nes_permuted_conv_pool_fwd_tc_scratch_bytes", kh, kw)
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_permuted_conv_pool_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, H, W, self.out_channels, kh, kw,
+               self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+        return y
 
     def _perturbed_forward(self, input):
         x = C.require_cuda(input, "input", _F32)

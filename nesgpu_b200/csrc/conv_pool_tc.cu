@@ -1,0 +1,301 @@
+// Out-permuted convolution + ReLU + 2x2 max-pooling on the tensor cores (sm_100a), one image per tile.
+//
+// With output permutations only, member d's convolution is
+//   conv(x, W)[c] + s * conv(x, eps)[pout[d, c]] + bias[c] + s * bias_noise[d, c],
+// so every image of the population batch meets the SAME stacked filter [W; eps]: the kernel keeps that
+// filter resident in shared memory as the M operand (lanes 0-63 = W channels, 64-127 = eps channels) and
+// streams images through it.  The input is channels-last with 32 channels, so a pixel is one 128-byte
+// row; the B operand of tap (i, j) is the staged image shifted by i*W + j rows, and the accumulator
+// column m = oy*W + ox is output pixel (oy, ox) (columns with ox >= Wo are never read).  One TMA load
+// per image, kh*kw*4 tcgen05.mma (kind::tf32, M = N = 128, K = 8) per image into one of two TMEM
+// accumulators, and an epilogue that overlaps the next image's MMAs:
+//   warps of lane quadrants 2-3 (eps channels) copy their rows to shared memory, [position][channel];
+//   warps of quadrants 0-1 (W channels) read the four positions of each pooling window straight from
+//   tensor memory (runtime column addresses), add the permuted eps value from shared memory, take the
+//   maximum, add the bias terms, apply the ReLU and store NCHW.
+// Every mbarrier wait is bounded; on a time-out the role stops, the error word is set and all roles
+// fall through to the common exit that frees tensor memory.
+#include "tc_ptx.cuh"
+
+namespace nes {
+namespace tc {
+
+constexpr int CP_CIN = 32;                 // channels per pixel row (128 bytes of fp32)
+constexpr int CP_M = 128, CP_N = 128;      // stacked channels x positions per image
+constexpr int CP_HALF = 64;                // W channels in lanes [0, 64), eps channels in [64, 128)
+constexpr int CP_TAP_BYTES = CP_M * CP_CIN * 4;        // 16 KiB of filter per tap
+constexpr int CP_THREADS = 192;            // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+
+struct ConvPoolParams {
+  const float* bias; const float* bias_noise; const int16_t* pout; float* y;
+  int64_t B, D, R;
+  int Cout, osp, W, kh, kw, Hp, Wp, rows_per_image, stage_rows, antithetic;
+};
+
+__device__ __forceinline__ void tmem_ld_x2(uint32_t taddr, uint32_t& a, uint32_t& b) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                        const __grid_constant__ CUtensorMap map_f,
+                                                                        const ConvPoolParams p) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw = smem_u32(dyn_raw);
+  unsigned char* base = dyn_raw + (((raw + 1023u) & ~1023u) - raw);
+  const int taps = p.kh * p.kw;
+  const int stage_bytes = p.stage_rows * 128;
+  unsigned char* filt = base;
+  unsigned char* stage0 = filt + size_t(taps) * CP_TAP_BYTES;
+  float* zeps = reinterpret_cast<float*>(stage0 + 2 * size_t(stage_bytes));       // [CP_N][CP_HALF]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps + CP_N * CP_HALF);
+  uint64_t* full = bars;            // [2] image staged
+  uint64_t* empty = bars + 2;       // [2] stage consumed by the MMAs
+  uint64_t* acc_full = bars + 4;    // [2] accumulator complete
+  uint64_t* acc_empty = bars + 6;   // [2] accumulator drained (128 epilogue threads)
+  uint64_t* zeps_full = bars + 8;   // eps rows in shared memory (64 threads)
+  uint64_t* zeps_empty = bars + 9;  // ... and consumed (64 threads)
+  uint64_t* filt_full = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&full[s], 1); mbar_init(&empty[s], 1);
+      mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128);
+    }
+    mbar_init(zeps_full, 64); mbar_init(zeps_empty, 64); mbar_init(filt_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * CP_N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: the stacked filter once, then one load per image
+      mbar_expect_tx(filt_full, uint32_t(taps) * CP_TAP_BYTES);
+      for (int t = 0; t < taps; ++t) tma_load_2d(filt + size_t(t) * CP_TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
+      int i = 0;
+      for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(&empty[s], ((i >> 1) & 1) ^ 1, 1)) break;
+        mbar_expect_tx(&full[s], uint32_t(stage_bytes));
+        tma_load_2d(stage0 + size_t(s) * stage_bytes, &map_x, &full[s], 0, int(b * p.rows_per_image));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer
+      constexpr uint32_t idesc = idesc_tf32(CP_M, CP_N);
+      bool ok = mbar_wait(filt_full, 0, 2);
+      const uint32_t filt_addr = smem_u32(filt);
+      int i = 0;
+      for (int64_t b = blockIdx.x; b < p.B && ok; b += gridDim.x, ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        ok = mbar_wait(&acc_empty[s], ph ^ 1, 2) && mbar_wait(&full[s], ph, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
+        const uint32_t acc = tmem_base + uint32_t(s * CP_N);
+        for (int t = 0; t < taps; ++t) {
+          const int ti = t / p.kw, tj = t - ti * p.kw;
+          const uint64_t a = smem_desc_sw128(filt_addr + uint32_t(t) * CP_TAP_BYTES);
+          const uint64_t bd = smem_desc_sw128(st + uint32_t(ti * p.W + tj) * 128u);
+#pragma unroll
+          for (int k = 0; k < CP_CIN / 8; ++k)
+            mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&empty[s]);
+        mma_commit(&acc_full[s]);
+      }
+    }
+  } else {
+    const int q = warp & 3;                        // TMEM lane quadrant of this warp
+    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    if (q >= 2) {
+      // ---- eps channels: accumulator rows -> shared memory [position][channel]
+      const int ch = (q - 2) * 32 + lane;
+      int i = 0;
+      for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
+        const int s = i & 1;
+        if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < CP_N; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(lane_addr + uint32_t(s * CP_N + c0), r);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) zeps[(c0 + j) * CP_HALF + ch] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[s]);
+        mbar_arrive(zeps_full);
+      }
+    } else {
+      // ---- W channels: pooling windows from tensor memory + permuted eps values from shared memory
+      const int c = q * 32 + lane;
+      const bool live = c < p.Cout;
+      const float bc = (live && p.bias) ? p.bias[c] : 0.f;
+      const int pooled = p.Hp * p.Wp;
+      int i = 0;
+      for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
+        const int s = i & 1;
+        const int64_t d = b % p.D;
+        const float sgn = anti_sign(b / p.D, p.R, p.antithetic);
+        int so = live ? (p.pout ? int(p.pout[d * p.Cout + c]) : c) : 0;
+        const bool noisy = live && so < p.osp;
+        if (!noisy) so = 0;
+        const float sn = noisy ? sgn : 0.f;
+        const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
+        if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
+        tc_fence_after();
+        float* out = p.y + (b * p.Cout + c) * pooled;
+        const uint32_t acc = lane_addr + uint32_t(s * CP_N);
+        for (int py = 0; py < p.Hp; ++py) {
+          for (int px0 = 0; px0 < p.Wp; px0 += 4) {
+            uint32_t top[4][2], bot[4][2];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int px = (px0 + u < p.Wp) ? px0 + u : px0;       // uniform across the warp
+              const uint32_t col = uint32_t(2 * py * p.W + 2 * px);
+              tmem_ld_x2(acc + col, top[u][0], top[u][1]);
+              tmem_ld_x2(acc + col + uint32_t(p.W), bot[u][0], bot[u][1]);
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (px0 + u < p.Wp) {
+                const int pos = 2 * py * p.W + 2 * (px0 + u);
+                const float* e = zeps + pos * CP_HALF + so;
+                const float v0 = __uint_as_float(top[u][0]) + sn * e[0];
+                const float v1 = __uint_as_float(top[u][1]) + sn * e[CP_HALF];
+                const float v2 = __uint_as_float(bot[u][0]) + sn * e[p.W * CP_HALF];
+                const float v3 = __uint_as_float(bot[u][1]) + sn * e[(p.W + 1) * CP_HALF];
+                const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
+                if (live) out[py * p.Wp + px0 + u] = v;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[s]);
+        mbar_arrive(zeps_empty);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * CP_N);
+  }
+}
+
+// stacked[tap][m][cin], tf32-rounded: m < Cout -> weight[m], 64 <= m < 64 + osp -> eps[m - 64], else 0
+__global__ void stack_filter_tf32_kernel(const float* __restrict__ w, const float* __restrict__ eps, float* __restrict__ out,
+                                         int Cout, int osp, int taps) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= taps * CP_M * CP_CIN) return;
+  const int cin = idx % CP_CIN, m = (idx / CP_CIN) % CP_M, t = idx / (CP_CIN * CP_M);
+  float v = 0.f;
+  if (m < Cout) v = w[(size_t(m) * CP_CIN + cin) * taps + t];
+  else if (m >= CP_HALF && m - CP_HALF < osp) v = eps[(size_t(m - CP_HALF) * CP_CIN + cin) * taps + t];
+  out[idx] = round_tf32(v);
+}
+
+int conv_pool_error_word(int* v) {
+  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
+  return NES_OK;
+}
+
+static int make_rows_map(CUtensorMap* map, const float* base, int64_t rows, int box_rows, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  NES_REQUIRE(fn != nullptr, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
+  cuuint64_t dims[2] = {(cuuint64_t)CP_CIN, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)CP_CIN * sizeof(float)};
+  cuuint32_t box[2] = {(cuuint32_t)CP_CIN, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NES_REQUIRE(r == CUDA_SUCCESS, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
+  return NES_OK;
+}
+
+struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows; size_t smem; };
+
+// Shapes the kernel covers; on failure the message says which rule was broken.
+static int plan_conv_pool(ConvPoolPlan& pl, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what) {
+  NES_REQUIRE(Cin == CP_CIN, NES_ERR_UNSUPPORTED, "%s: needs %d input channels (got %d)", what, CP_CIN, Cin);
+  NES_REQUIRE(Cout >= 1 && Cout <= CP_HALF && osp >= 0 && osp <= CP_HALF, NES_ERR_UNSUPPORTED,
+              "%s: needs at most %d output channels (got %d, %d noise rows)", what, CP_HALF, Cout, osp);
+  NES_REQUIRE(kh >= 1 && kw >= 1 && H >= kh && W >= kw, NES_ERR_BAD_ARG, "%s: bad geometry", what);
+  pl.taps = kh * kw;
+  pl.Ho = H - kh + 1; pl.Wo = W - kw + 1;
+  pl.Hp = pl.Ho / 2; pl.Wp = pl.Wo / 2;
+  NES_REQUIRE(pl.Hp >= 1 && pl.Wp >= 1, NES_ERR_UNSUPPORTED, "%s: output smaller than one pooling window", what);
+  NES_REQUIRE((2 * pl.Hp - 1) * W + 2 * pl.Wp - 1 < CP_N, NES_ERR_UNSUPPORTED,
+              "%s: the pooled part of a %dx%d image does not fit %d accumulator columns", what, H, W, CP_N);
+  pl.stage_rows = (CP_N + (kh - 1) * W + (kw - 1) + 7) & ~7;
+  NES_REQUIRE(pl.stage_rows <= 256, NES_ERR_UNSUPPORTED, "%s: filter reach too large for one staged image", what);
+  pl.smem = 1024 + size_t(pl.taps) * CP_TAP_BYTES + 2 * size_t(pl.stage_rows) * 128 + size_t(CP_N) * CP_HALF * 4 + 128;
+  NES_REQUIRE(pl.smem <= 227 * 1024, NES_ERR_UNSUPPORTED, "%s: %d filter taps need %zu B of shared memory", what, pl.taps, pl.smem);
+  return NES_OK;
+}
+
+}  // namespace tc
+}  // namespace nes
+
+using namespace nes;
+using namespace nes::tc;
+
+extern "C" int64_t nes_permuted_conv_pool_fwd_tc_scratch_bytes(int kh, int kw) {
+  if (kh <= 0 || kw <= 0) return 0;
+  return int64_t(kh) * kw * CP_TAP_BYTES;
+}
+
+extern "C" int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* weight, const float* bias, const float* eps,
+                                             const float* bias_noise, const int16_t* pout, float* y,
+                                             int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                             int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                                             nes_stream_t stream) {
+  const char* what = "permuted_conv_pool_fwd_tc";
+  NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "%s: negative extent", what);
+  ConvPoolPlan pl;
+  int rc = plan_conv_pool(pl, Cin, H, W, Cout, out_sp, kh, kw, what);
+  if (rc != NES_OK) return rc;
+  const int64_t B = D * R;
+  if (B == 0) return NES_OK;
+  NES_REQUIRE(x_nhwc && weight && eps && y, NES_ERR_BAD_ARG, "%s: null pointer", what);
+  NES_REQUIRE(aligned16(x_nhwc), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
+  NES_REQUIRE(B * H * W <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: batch too large", what);
+  const int64_t need = nes_permuted_conv_pool_fwd_tc_scratch_bytes(kh, kw);
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "%s: scratch needs %lld bytes, 256-byte aligned", what, (long long)need);
+  cudaStream_t st = as_stream(stream);
+  float* stacked = static_cast<float*>(scratch);
+  const int n = pl.taps * CP_M * CP_CIN;
+  stack_filter_tf32_kernel<<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, stacked, Cout, out_sp, pl.taps);
+  rc = check_launch("permuted_conv_pool_fwd_tc(filter)");
+  if (rc != NES_OK) return rc;
+  CUtensorMap map_x, map_f;
+  if ((rc = make_rows_map(&map_x, x_nhwc, B * H * W, pl.stage_rows, what)) != NES_OK) return rc;
+  if ((rc = make_rows_map(&map_f, stacked, int64_t(pl.taps) * CP_M, CP_M, what)) != NES_OK) return rc;
+  ConvPoolParams p;
+  p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
+  p.B = B; p.D = D; p.R = R;
+  p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = pl.Hp; p.Wp = pl.Wp;
+  p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.antithetic = antithetic;
+  cudaError_t e = cudaFuncSetAttribute(conv_pool_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+  const unsigned grid = (unsigned)(B < sm_count() ? B : sm_count());
+  conv_pool_tf32_kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
+  return check_launch(what);
+}

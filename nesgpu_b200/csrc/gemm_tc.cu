@@ -352,7 +352,7 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
   return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, rt, y, B, out, K2, mode, st, "permuted_linear_fwd_tc");
 }
 
-namespace nes { namespace tc { int conv_tc_error_word(int* v); int conv_bf16_error_word(int* v); } }
+namespace nes { namespace tc { int conv_tc_error_word(int* v); int conv_bf16_error_word(int* v); int conv_pool_error_word(int* v); } }
 
 extern "C" int nes_tc_error_flag(int* flag) {
   NES_REQUIRE(flag != nullptr, NES_ERR_BAD_ARG, "tc_error_flag: null pointer");
@@ -364,6 +364,10 @@ extern "C" int nes_tc_error_flag(int* flag) {
   if (rc != NES_OK) return rc;
   rc = nes::tc::conv_bf16_error_word(&vb);
   if (rc != NES_OK) return rc;
+  int vp = 0;
+  rc = nes::tc::conv_pool_error_word(&vp);
+  if (rc != NES_OK) return rc;
+  if (!vb) vb = vp;
   *flag = v ? v : (vc ? vc : vb);
   return NES_OK;
 }

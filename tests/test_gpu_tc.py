@@ -315,3 +315,65 @@ def _C():
 
 def C_launches():
     return _C().call("nes_launch_count")
+
+
+# ---- out-permuted conv + ReLU + MaxPool2d(2) in one tensor-core kernel ------------------------------
+
+@pytest.mark.parametrize("cout,out_sp,hw,k,R,anti,bias,D", [
+    (64, 0, 13, 3, 2, False, True, 5),        # second layer of the small CNN
+    (64, 0.5, 13, 3, 4, True, True, 3),       # half of the channels carry noise, antithetic halves
+    (40, 0, 12, 3, 1, False, False, 7),       # fewer channels, even output, no bias
+    (64, 0, 10, 2, 3, True, True, 150),       # more images than SMs: several images per block
+])
+def test_permuted_conv_pool_tf32(cout, out_sp, hw, k, R, anti, bias, D):
+    from nesgpu_b200 import base
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    cin = 32
+    g = torch.Generator().manual_seed(cout + hw + D)
+    layer = base.PermutedConv2d(cin, cout, k, D, bias=bias, antithetic=anti, permutation="out", out_sparsity=out_sp,
+                                options={"tc": "tf32", "fuse": "relu_maxpool2"}).to(DEV)
+    osp = layer.out_sparsity
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g) * .1 if bias else None
+    eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g) if bias else None
+    pout = torch.stack([torch.randperm(cout, generator=g) for _ in range(D)]).short()
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.output_permutations = G(eps), (G(beta) if bias else None), G(pout)
+    want = O.permuted_conv2d_forward(x, W, b if bias else torch.zeros(cout), eps,
+                                     beta if bias else torch.zeros(D, cout), None, pout, D, 1, 0, 1, anti)
+    want = torch.nn.functional.max_pool2d(torch.relu(want), 2)
+    before = C_launches()
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y_nchw = layer.forward(G(x))                                                  # copies to channels-last first
+        y_cl = layer.forward(G(x).contiguous(memory_format=torch.channels_last))      # taken as is
+    assert C_launches() - before == 4                                                 # 2 x (filter stack + fused kernel)
+    assert _flag(_C()) == 0
+    assert y_nchw.shape == want.shape and y_nchw.is_contiguous()
+    assert rel_err(y_nchw, want) <= 2e-2 and rel_err(y_cl, want) <= 2e-2
+    assert torch.equal(y_nchw, y_cl)
+    # the perturbation itself is resolved: remove the member-independent part and compare what is left
+    layer.weight_noise = G(torch.zeros_like(eps))
+    with torch.no_grad():
+        y0 = layer.forward(G(x))
+    want0 = torch.nn.functional.max_pool2d(torch.relu(O.permuted_conv2d_forward(
+        x, W, b if bias else torch.zeros(cout), torch.zeros_like(eps), beta if bias else torch.zeros(D, cout),
+        None, pout, D, 1, 0, 1, anti)), 2)
+    assert rel_err(y_nchw - y0, want - want0) <= 5e-2
+
+
+def test_conv_pool_tc_rejects_uncovered_shapes():
+    C = _C()
+    x = torch.zeros(2, 14, 14, 32, device=DEV)
+    w = torch.zeros(64, 32, 3, 3, device=DEV)
+    y = torch.zeros(2, 64, 6, 6, device=DEV)
+    buf = torch.zeros(1 << 18, dtype=torch.uint8, device=DEV)
+    with pytest.raises(NotImplementedError):       # 12x12 outputs: pooled part needs more than 128 columns
+        C.call("nes_permuted_conv_pool_fwd_tc", C.ptr(x), C.ptr(w), None, C.ptr(w), None, None, C.ptr(y), 2, 1,
+               32, 14, 14, 64, 3, 3, 64, 0, C.ptr(buf), buf.numel(), C.stream())
+    with pytest.raises(NotImplementedError):       # 16 input channels
+        C.call("nes_permuted_conv_pool_fwd_tc", C.ptr(x), C.ptr(w), None, C.ptr(w), None, None, C.ptr(y), 2, 1,
+               16, 13, 13, 64, 3, 3, 64, 0, C.ptr(buf), buf.numel(), C.stream())
