@@ -26,37 +26,40 @@ __global__ void __launch_bounds__(512) shared_conv_pool_kernel(
   const int Hp = Ho / 2, Wp = Wo / 2, pooled = Hp * Wp;
   const int64_t r = blockIdx.x;
   const float* zr = z + r * int64_t(Cout + osp) * hw;
-  for (int i = threadIdx.x; i < (Cout + osp) * hw; i += blockDim.x) {
-    const int c = i / hw, p = i - c * hw;
-    planes[c * pitch + p] = zr[i];
-  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int c = warp; c < Cout + osp; c += warps)
+    for (int p = lane; p < hw; p += 32) planes[c * pitch + p] = zr[c * hw + p];
   __syncthreads();
   const float sgn = anti_sign(r, R, antithetic);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int64_t d0 = int64_t(blockIdx.y) * members_per_block;
   const int64_t d1 = (d0 + members_per_block < D) ? d0 + members_per_block : D;
-  for (int c0 = 0; c0 < Cout; c0 += 32) {
-    const int c = c0 + lane;
-    const bool live = c < Cout;
-    const float* base = planes + (live ? c : 0) * pitch;
-    const float bc = (live && bias) ? bias[c] : 0.f;
-    for (int64_t d = d0; d < d1; ++d) {
+  // a warp owns whole members, so the latency of a member's permutation / bias loads is hidden by the
+  // other warps' arithmetic
+  for (int64_t d = d0 + warp; d < d1; d += warps) {
+    for (int c0 = 0; c0 < Cout; c0 += 32) {
+      const int c = c0 + lane;
+      const bool live = c < Cout;
+      const float* base = planes + (live ? c : 0) * pitch;
       int so = live ? (pout ? int(pout[d * Cout + c]) : c) : 0;
       const bool noisy = live && so < osp;
       const float* noise = planes + (Cout + (noisy ? so : 0)) * pitch;
       const float s = noisy ? sgn : 0.f;
-      const float add = bc + ((live && bias_noise) ? sgn * bias_noise[d * Cout + c] : 0.f);
+      float add = (live && bias) ? bias[c] : 0.f;
+      if (live && bias_noise) add += sgn * bias_noise[d * Cout + c];
       float* out = y + ((r * D + d) * pooled) * Cout + c;
-      for (int pp = warp; pp < pooled; pp += warps) {
-        const int py = pp / Wp, px = pp - py * Wp;
-        const int p00 = (2 * py) * Wo + 2 * px;
-        const float v0 = base[p00] + s * noise[p00];
-        const float v1 = base[p00 + 1] + s * noise[p00 + 1];
-        const float v2 = base[p00 + Wo] + s * noise[p00 + Wo];
-        const float v3 = base[p00 + Wo + 1] + s * noise[p00 + Wo + 1];
-        float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
-        if (round_tf32) v = round_to_tf32(v);
-        if (live) out[int64_t(pp) * Cout] = v;
+      for (int py = 0; py < Hp; ++py) {
+        const int row = (2 * py) * Wo;
+#pragma unroll 4
+        for (int px = 0; px < Wp; ++px) {
+          const int p00 = row + 2 * px;
+          const float v0 = base[p00] + s * noise[p00];
+          const float v1 = base[p00 + 1] + s * noise[p00 + 1];
+          const float v2 = base[p00 + Wo] + s * noise[p00 + Wo];
+          const float v3 = base[p00 + Wo + 1] + s * noise[p00 + Wo + 1];
+          float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
+          if (round_tf32) v = round_to_tf32(v);
+          if (live) out[int64_t(py * Wp + px) * Cout] = v;
+        }
       }
     }
   }
@@ -81,8 +84,10 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
               "shared_conv_pool_fwd: %zu B of feature maps per image do not fit in shared memory", smem);
   cudaError_t e = cudaFuncSetAttribute(shared_conv_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "shared_conv_pool_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e));
-  // enough member groups per image for two blocks per SM overall, at least 8 members per block
-  int64_t groups = ceil_div<int64_t>(int64_t(sm_count()) * 2, R);
+  // member groups per image so that the grid is just under a whole number of waves (one block per SM),
+  // at least 8 members per block
+  int64_t groups = (int64_t(sm_count()) * 2) / R;
+  if (groups < 1) groups = ceil_div<int64_t>(sm_count(), R);
   if (groups > ceil_div<int64_t>(D, 8)) groups = ceil_div<int64_t>(D, 8);
   if (groups < 1) groups = 1;
   if (groups > 65535) groups = 65535;

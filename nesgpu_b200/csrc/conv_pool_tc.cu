@@ -26,6 +26,20 @@ constexpr int CP_HALF = 64;                // W channels in lanes [0, 64), eps c
 constexpr int CP_TAP_BYTES = CP_M * CP_CIN * 4;        // 16 KiB of filter per tap
 constexpr int CP_THREADS = 192;            // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
 
+#ifdef NES_TRACE
+static __device__ unsigned long long g_trace[8][64];
+__device__ __forceinline__ void trace(int role, int i) {
+  if (blockIdx.x == 0 && i < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_trace[role][i] = t;
+  }
+}
+#define TRACE(role, i) trace(role, i)
+#else
+#define TRACE(role, i)
+#endif
+
 struct ConvPoolParams {
   const float* bias; const float* bias_noise; const int16_t* pout; float* y;
   int64_t B, D, R;
@@ -35,8 +49,27 @@ struct ConvPoolParams {
 __device__ __forceinline__ void tmem_ld_x2(uint32_t taddr, uint32_t& a, uint32_t& b) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// TW / THP / TWP: input width and pooled output size known at compile time (0 = taken from the parameters).
+// With them the W-channel warps read their whole accumulator row into registers with four wide loads
+// and index it statically; the runtime form reads each pooling window with two narrow loads.
+template <int TW, int THP, int TWP>
 __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                         const __grid_constant__ CUtensorMap map_f,
                                                                         const ConvPoolParams p) {
@@ -83,7 +116,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         const int s = i & 1;
         if (!mbar_wait(&empty[s], ((i >> 1) & 1) ^ 1, 1)) break;
         mbar_expect_tx(&full[s], uint32_t(stage_bytes));
+        TRACE(0, i);
         tma_load_2d(stage0 + size_t(s) * stage_bytes, &map_x, &full[s], 0, int(b * p.rows_per_image));
+        // two stages cannot cover the HBM latency of the next load: pull the image after next into L2 now
+        const int64_t ahead = b + 2 * int64_t(gridDim.x);
+        if (ahead < p.B) tma_prefetch_2d(&map_x, 0, int(ahead * p.rows_per_image));
       }
     }
   } else if (warp == 1) {
@@ -99,6 +136,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         ok = mbar_wait(&acc_empty[s], ph ^ 1, 2) && mbar_wait(&full[s], ph, 2);
         if (!ok) break;
         tc_fence_after();
+        TRACE(1, i);
         const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
         const uint32_t acc = tmem_base + uint32_t(s * CP_N);
         for (int t = 0; t < taps; ++t) {
@@ -111,6 +149,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         }
         mma_commit(&empty[s]);
         mma_commit(&acc_full[s]);
+        TRACE(2, i);
       }
     }
   } else {
@@ -123,18 +162,19 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
       for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
         const int s = i & 1;
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (lane == 0 && q == 2) TRACE(3, i);
         if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
         tc_fence_after();
-#pragma unroll 1
-        for (int c0 = 0; c0 < CP_N; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(lane_addr + uint32_t(s * CP_N + c0), r);
+        uint32_t r[CP_N];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) zeps[(c0 + j) * CP_HALF + ch] = __uint_as_float(r[j]);
-        }
+        for (int c0 = 0; c0 < CP_N; c0 += 32) tmem_ld32_nowait(lane_addr + uint32_t(s * CP_N + c0), r + c0);
+        tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
+#pragma unroll
+        for (int j = 0; j < CP_N; ++j) zeps[j * CP_HALF + ch] = __uint_as_float(r[j]);
         mbar_arrive(zeps_full);
+        if (lane == 0 && q == 2) TRACE(4, i);
       }
     } else {
       // ---- W channels: pooling windows from tensor memory + permuted eps values from shared memory
@@ -153,10 +193,37 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         const float sn = noisy ? sgn : 0.f;
         const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (lane == 0 && q == 0) TRACE(5, i);
         if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
         tc_fence_after();
+        if (lane == 0 && q == 0) TRACE(6, i);
         float* out = p.y + (b * p.Cout + c) * pooled;
         const uint32_t acc = lane_addr + uint32_t(s * CP_N);
+        if (TW > 0) {
+          uint32_t r[CP_N];
+#pragma unroll
+          for (int c0 = 0; c0 < CP_N; c0 += 32) tmem_ld32_nowait(acc + uint32_t(c0), r + c0);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(&acc_empty[s]);              // accumulator is in registers: the next image may overwrite it
+          const float* e = zeps + so;
+#pragma unroll
+          for (int py = 0; py < THP; ++py)
+#pragma unroll
+            for (int px = 0; px < TWP; ++px) {
+              constexpr int W_ = TW > 0 ? TW : 1;
+              const int pos = 2 * py * W_ + 2 * px;
+              const float v0 = __uint_as_float(r[pos]) + sn * e[pos * CP_HALF];
+              const float v1 = __uint_as_float(r[pos + 1]) + sn * e[(pos + 1) * CP_HALF];
+              const float v2 = __uint_as_float(r[pos + W_]) + sn * e[(pos + W_) * CP_HALF];
+              const float v3 = __uint_as_float(r[pos + W_ + 1]) + sn * e[(pos + W_ + 1) * CP_HALF];
+              const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
+              if (live) out[py * TWP + px] = v;
+            }
+          mbar_arrive(zeps_empty);
+          if (lane == 0 && q == 0) TRACE(7, i);
+          continue;
+        }
         for (int py = 0; py < p.Hp; ++py) {
           for (int px0 = 0; px0 < p.Wp; px0 += 4) {
             uint32_t top[4][2], bot[4][2];
@@ -208,6 +275,14 @@ __global__ void stack_filter_tf32_kernel(const float* __restrict__ w, const floa
   else if (m >= CP_HALF && m - CP_HALF < osp) v = eps[(size_t(m - CP_HALF) * CP_CIN + cin) * taps + t];
   out[idx] = round_tf32(v);
 }
+
+#ifdef NES_TRACE
+}}
+extern "C" int nes_debug_conv_pool_trace(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, nes::tc::g_trace, sizeof(unsigned long long) * 8 * 64) == cudaSuccess ? 0 : -1;
+}
+namespace nes { namespace tc {
+#endif
 
 int conv_pool_error_word(int* v) {
   cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
@@ -293,9 +368,13 @@ extern "C" int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* w
   p.B = B; p.D = D; p.R = R;
   p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = pl.Hp; p.Wp = pl.Wp;
   p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.antithetic = antithetic;
-  cudaError_t e = cudaFuncSetAttribute(conv_pool_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  // compile-time geometry for 13x13 inputs pooled to 5x5 (3x3 filters on the 13x13 maps of the small MNIST
+  // network); every other covered shape takes the runtime-indexed form
+  const bool fixed = (W == 13 && pl.Hp == 5 && pl.Wp == 5);
+  auto kernel = fixed ? conv_pool_tf32_kernel<13, 5, 5> : conv_pool_tf32_kernel<0, 0, 0>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
   const unsigned grid = (unsigned)(B < sm_count() ? B : sm_count());
-  conv_pool_tf32_kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
+  kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
   return check_launch(what);
 }

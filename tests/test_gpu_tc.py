@@ -324,6 +324,7 @@ def C_launches():
     (64, 0.5, 13, 3, 4, True, True, 3),       # half of the channels carry noise, antithetic halves
     (40, 0, 12, 3, 1, False, False, 7),       # fewer channels, even output, no bias
     (64, 0, 10, 2, 3, True, True, 150),       # more images than SMs: several images per block
+    (64, 0, 13, 3, 3, True, True, 210),       # the same for the compile-time 13x13 -> 5x5 geometry
 ])
 def test_permuted_conv_pool_tf32(cout, out_sp, hw, k, R, anti, bias, D):
     from nesgpu_b200 import base
