@@ -544,21 +544,27 @@ class EsCnn(Workload):
         return {"workload": self.name, "net": "Conv(1,32,3)-ReLU-MaxPool2-Conv(32,64,3)-ReLU-MaxPool2-Linear(1600,128)-ReLU-Linear(128,10), Permuted layers",
                 "directions_per_gpu": self.D, "population": self.D * world, "images_per_member": self.R,
                 "step": "set_noise + chunked population forward + CE fitness + centred ranks + update (+ all-gather / all-reduce at N>1)",
-                "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02, "fused_layers": self.fused}
+                "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02, "fused_layers": self.fused,
+                "precision": "tf32 operands, fp32 accumulation (stated mode, rel err ~1e-3 per layer)" if self.tc in (None, "tf32") else self.tc}
 
     def setup(self, dev, rank, world):
         from nesgpu_b200 import base, es
         self.es, self.world, self.dev = es, world, dev
         D = self.D
         torch.manual_seed(1005)       # same initial weights on every rank
+        if self.tc is None:
+            self.tc = "tf32"       # default for this workload: the stated TF32 tensor-core mode (--tc fp32 for CUDA cores)
+        self.dtype = "tf32" if self.tc == "tf32" else "f32"
         opts = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}
+        lin = {"tc": "tf32"} if self.tc == "tf32" else {}       # the stated TF32 mode covers the linear layers too
         if self.fused:
             # Conv -> ReLU -> MaxPool2 blocks as fused layers; the first one is told that the images are shared
             o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_tf32": bool(opts)}
             self.net = torch.nn.Sequential(
                 base.PermutedConv2d(1, 32, 3, D, options=o1),
                 base.PermutedConv2d(32, 64, 3, D, options=dict(opts, fuse="relu_maxpool2")), torch.nn.Flatten(),
-                base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
+                base.PermutedLinear(1600, 128, D, options=lin), torch.nn.ReLU(),
+                base.PermutedLinear(128, 10, D, options=lin)).to(dev)
         else:
             self.net = torch.nn.Sequential(
                 base.PermutedConv2d(1, 32, 3, D), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
@@ -613,12 +619,15 @@ class EsCnn(Workload):
         flops = self.FLOP_PER_PAIR * self.D * self.R
         ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
         peak = peaks["bf16_sustained"] / 2
-        return {"kernel": "population forward (conv1, conv2, fc1, fc2 kernels + torch ReLU / MaxPool / CE), forward phase",
+        kernels = ("shared_conv_pool_kernel, conv_pool_tf32_kernel, permuted_operand_kernel + gemm_tf32_kernel, fc2, CE"
+                   if self.fused else "conv1, conv2, fc1, fc2 kernels + torch ReLU / MaxPool / CE")
+        return {"kernel": "population forward (%s), forward phase" % kernels,
                 "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
                 "peak_source": peaks["source"] + " bf16 sustained / 2 taken as TF32",
                 "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 3), "traffic": None,
                 "es_steps_per_s": round(1e3 / sum(phase_ms.values()), 3),
-                "note": "flops for the minimal one-product form; conv2 on tensor cores only with --tc tf32"}
+                "note": "flops for the minimal one-product form (5.262 MFLOP per member-image pair); the fused conv2 kernel "
+                        "evaluates the two-product form (stacked filter [W; eps]), i.e. about twice these flops on the tensor pipe"}
 
     def cpu_sample(self, reps):
         """CPU oracle on 16 members x 32 images of the same net (forward + CE + ranks + update)."""
@@ -843,7 +852,7 @@ def run_ours(args, rank, world, local_rank):
         line = {"metric": "perturbed-member samples/sec per layer (forward + update)", "value": round(value, 1),
                 "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": wl.dtype, "data": "synthetic", "config": dict(wl.describe(world), tc=getattr(wl.layer, "options", {}).get("tc") if hasattr(wl, "layer") else None),
+                "dtype": wl.dtype, "data": "synthetic", "config": dict(wl.describe(world), tc=getattr(wl.layer, "options", {}).get("tc") if hasattr(wl, "layer") else wl.tc),
                 "e2e": {"value": round(wl.units_per_step * world / (e2e_ms * 1e-3), 1), "unit": unit,
                         "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(e2e_ms, 4),
                         "steps": e2e_steps},

@@ -457,22 +457,22 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         Permuted.__init__(self, in_features, out_features, directions, antithetic=antithetic, options=options,
                           permutation=permutation, in_sparsity=in_sparsity, out_sparsity=out_sparsity)
 
-    # rows x outputs from which the one-product tensor-core form is chosen by default (64 tiles of 128 x 128)
-    SINGLE_PRODUCT_MIN = 64 * 128 * 128
+    # batch rows from which the one-product tensor-core form is chosen by default (64 row tiles of 128)
+    SINGLE_PRODUCT_MIN_ROWS = 64 * 128
 
     def _single_product_mode(self, rows, pout):
         """Mode (1 = TF32, 3 = 3xTF32) of the one-product tensor-core forward, or 0 for the CUDA-core kernels.
 
         ``options["tc"]``: ``"3xtf32"`` / ``"tf32"`` force it, ``"fp32"`` forbids it; by default ("auto") the
         error-compensated 3xTF32 form (fp32-level accuracy) is taken for batches of at least
-        ``SINGLE_PRODUCT_MIN`` outputs.  It needs a layer without output permutations."""
+        ``SINGLE_PRODUCT_MIN_ROWS`` rows.  It needs a layer without output permutations."""
         mode = self.options.get("tc", "auto")
         if mode not in ("auto", "fp32", "3xtf32", "tf32"):
             raise NotImplementedError('options["tc"] must be "auto", "3xtf32", "tf32" or "fp32"')
         if mode == "fp32" or pout is not None or rows == 0:
             return 0
         if mode == "auto":
-            return 3 if rows * self.out_features >= self.SINGLE_PRODUCT_MIN else 0
+            return 3 if rows >= self.SINGLE_PRODUCT_MIN_ROWS else 0
         return _TC_MODES[mode]
 
     def forward(self, input):
