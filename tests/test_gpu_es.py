@@ -82,3 +82,49 @@ def test_es_step_tensor_core_conv_close_to_fp32():
     tf32 = es.population_fitness(pm, images, labels, D, chunk=4)
     assert rel_err(tf32, f32.cpu()) <= 2e-2
     assert not torch.equal(tf32, f32)
+
+
+def build_fused(base, D, tc):
+    o2 = {"fuse": "relu_maxpool2"}
+    lin = {}
+    if tc:
+        o2["tc"] = "tf32"
+        lin = {"tc": "tf32"}
+    return torch.nn.Sequential(
+        base.PermutedConv2d(1, 32, 3, D, options={"shared_input": True, "fuse": "relu_maxpool2", "out_tf32": tc}),
+        base.PermutedConv2d(32, 64, 3, D, options=o2), torch.nn.Flatten(),
+        base.PermutedLinear(1600, 128, D, options=lin), torch.nn.ReLU(), base.PermutedLinear(128, 10, D, options=lin)).to(DEV)
+
+
+@pytest.mark.parametrize("tc,tol", [(False, 1e-4), (True, 2e-2)])
+def test_es_step_fused_layers_match_the_module_by_module_network(tc, tol):
+    """Same weights, noise and permutations in both networks: the fused Conv-ReLU-Pool layers (layer 1 fed with the
+    shared minibatch) give the fitness of the Conv / ReLU / MaxPool2d network; exact-fp32 kernels hold 1e-4, the TF32
+    mode its stated 2e-2."""
+    from nesgpu_b200 import base, es
+    D, R = 24, 6
+    torch.manual_seed(2)
+    plain = build(base, D)
+    fused = build_fused(base, D, tc)
+    pm_plain, pm_fused = base.PerturbedModel(plain, D), base.PerturbedModel(fused, D)
+    pm_plain.set_noise_scale(0.02)
+    pm_plain.set_seed(7)
+    pm_plain.set_noise()
+    pm_fused.set_noise_scale(0.02)
+    pm_fused.set_seed(8)
+    pm_fused.set_noise()
+    for a, b in zip(pm_plain.perturbed_layers, pm_fused.perturbed_layers):
+        with torch.no_grad():
+            b.weight.copy_(a.weight)
+            b.bias.copy_(a.bias)
+        b.weight_noise, b.bias_noise = a.weight_noise, a.bias_noise
+        b.input_permutations, b.output_permutations = a.input_permutations, a.output_permutations
+    assert es.takes_shared_input(pm_fused) and not es.takes_shared_input(pm_plain)
+    images = torch.rand(R, 1, 28, 28, device=DEV)
+    labels = torch.randint(10, (R,), device=DEV)
+    want = es.population_fitness(pm_plain, images, labels, D, chunk=4)
+    got = es.population_fitness(pm_fused, images, labels, D, chunk=4)
+    assert rel_err(got, want.cpu()) <= tol
+    # inference (perturbed flag off): both networks are the plain CNN
+    with torch.no_grad():
+        assert_close(fused(images), plain(images).cpu(), tol=1e-4, what="inference")
