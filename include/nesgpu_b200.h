@@ -187,12 +187,13 @@ int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float*
  * the stacked filter [weight; eps] and no bias (for instance from nes_conv2d_fwd); for b = r*D + d
  *   y[b, py, px, c] = relu(max_{2x2}( z[r, c] + s(r) * z[r, Cout + pout[d,c]] ) + bias[c] + s(r) * bias_noise[d,c])
  * with the noise term dropped where pout[d,c] >= out_sp (pout == NULL: identity).  y is channels-last,
- * (R*D, Ho/2, Wo/2, Cout); round_tf32 != 0 rounds the stored values to TF32 (for a tensor-core consumer).
+ * (R*D, Ho/2, Wo/2, Cout); out_mode 0 stores fp32, 1 fp32 rounded to TF32, 2 bf16 (for a tensor-core
+ * consumer).
  * Replaces, for this case, PermutedConv2d.forward (modules/base.py:557-588) followed by the ReLU and
  * MaxPool2d modules of the reference's models (models/mnistmodels.py:35-57). */
 int nes_shared_conv_pool_fwd(const float* z, const float* bias, const float* bias_noise,
-                             const int16_t* pout, float* y, int64_t R, int64_t D, int Cout, int out_sp,
-                             int Ho, int Wo, int antithetic, int round_tf32, nes_stream_t stream);
+                             const int16_t* pout, void* y, int64_t R, int64_t D, int Cout, int out_sp,
+                             int Ho, int Wo, int antithetic, int out_mode, nes_stream_t stream);
 
 /* Out-permuted convolution (no input permutations; stride 1, no padding, no dilation) fused with ReLU
  * and 2x2/2 max-pooling on the tensor cores (tcgen05, kind::tf32: operands rounded / truncated to
@@ -210,6 +211,14 @@ int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* weight, cons
                                   float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,
                                   int kh, int kw, int out_sp, int antithetic,
                                   void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+/* The same kernel with bf16 operands (x_nhwc_bf16 (R*D, H, W, 32) bf16; the filter is rounded to bf16;
+ * fp32 accumulation and fp32 y; relative error ~3e-3, the other stated reduced-precision mode): half the
+ * MMA instructions and half the input bytes.  Scratch as for the TF32 form. */
+int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const float* weight, const float* bias,
+                                    const float* eps, const float* bias_noise, const int16_t* pout,
+                                    float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                    int kh, int kw, int out_sp, int antithetic,
+                                    void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
 /* PermutedConv2d.forward, default branch (modules/base.py:557-588), evaluated as one
  * convolution per member with the effective filter

@@ -616,7 +616,8 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         takes ``(R, C, H, W)`` and returns the ``(R * directions, ...)`` population batch.  With both set and
         output permutations only, the two convolutions ``conv(x, W)`` and ``conv(x, eps)`` are computed once
         per image and the per-member work is a fused gather + add + ReLU + pool; the result is a
-        channels-last tensor (``options["out_tf32"]`` rounds it to TF32 for a tensor-core consumer)."""
+        channels-last tensor (``options["out_dtype"]`` = ``"tf32"`` rounds it to TF32, ``"bf16"`` stores bf16, for a
+        tensor-core consumer)."""
         fuse = self.options.get("fuse")
         if fuse not in (None, "relu_maxpool2"):
             raise NotImplementedError('options["fuse"] must be "relu_maxpool2"')
@@ -645,7 +646,7 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         x = C.require_cuda(input, "input", _F32)
         x, geom, (Ho, Wo) = self._geometry(x)
         osp, cout = self.out_sparsity, self.out_channels
-        if (cout + osp) * ((Ho * Wo) | 1) * 4 > 220 * 1024 or Ho < 2 or Wo < 2:
+        if (cout + osp) * (Ho * Wo + 7) * 4 > 220 * 1024 or Ho < 2 or Wo < 2:
             return None
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
@@ -654,16 +655,23 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         z = torch.empty((R, cout + osp, Ho, Wo), device=x.device, dtype=_F32)
         C.call("nes_conv2d_fwd", C.ptr(x), C.ptr(stacked), None, C.ptr(z), R, geom[0], geom[1], geom[2], cout + osp,
                *geom[4:], C.stream())
-        y = torch.empty((R * D, Ho // 2, Wo // 2, cout), device=x.device, dtype=_F32)
+        out = self.options.get("out_dtype", "fp32")
+        if self.options.get("out_tf32"):
+            out = "tf32"
+        if out not in ("fp32", "tf32", "bf16"):
+            raise NotImplementedError('options["out_dtype"] must be "fp32", "tf32" or "bf16"')
+        y = torch.empty((R * D, Ho // 2, Wo // 2, cout), device=x.device,
+                        dtype=torch.bfloat16 if out == "bf16" else _F32)
         C.call("nes_shared_conv_pool_fwd", C.ptr(z), C.ptr(_opt(self.bias)), C.ptr(beta), C.ptr(pout), C.ptr(y),
-               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, 1 if self.options.get("out_tf32") else 0, C.stream())
+               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, {"fp32": 0, "tf32": 1, "bf16": 2}[out], C.stream())
         return y.permute(0, 3, 1, 2)
 
     def _fused_tc_forward(self, input):
-        """Conv + ReLU + MaxPool2d(2) in one tensor-core kernel (``options["tc"] = "tf32"``, output permutations
+        """Conv + ReLU + MaxPool2d(2) in one tensor-core kernel (``options["tc"]`` = ``"tf32"`` or ``"bf16"``, output permutations
         only, 32 input channels, stride 1 / no padding, one image per 128-column accumulator).  Takes the
         input channels-last without a copy.  Returns None when the case is not covered."""
-        if self.options.get("tc") != "tf32" or self.options.get("allow_repeats") or self.groups != 1:
+        mode = self.options.get("tc")
+        if mode not in ("tf32", "bf16") or self.options.get("allow_repeats") or self.groups != 1:
             return None
         pin, pout = self._perms()
         kh, kw = self.kernel_size
@@ -671,7 +679,9 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
                 or kh * kw > 9 or _pair(self.stride) != (1, 1) or _pair(self.dilation) != (1, 1)
                 or self.padding_mode != "zeros" or _pair(self.padding) != (0, 0)):
             return None
-        if not isinstance(input, torch.Tensor) or not input.is_cuda or input.dtype != _F32 or input.dim() != 4:
+        if not isinstance(input, torch.Tensor) or not input.is_cuda or input.dim() != 4:
+            return None
+        if input.dtype not in (_F32, torch.bfloat16):
             return None
         B, _, H, W = input.shape
         if H < kh or W < kw or B == 0:
@@ -680,6 +690,9 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         if Hp < 1 or Wp < 1 or (2 * Hp - 1) * W + 2 * Wp > 128 or 128 + (kh - 1) * W + kw - 1 > 256:
             return None
         x = input.permute(0, 2, 3, 1)
+        want = torch.bfloat16 if mode == "bf16" else _F32
+        if x.dtype != want:
+            x = x.to(want)
         if not x.is_contiguous():
             x = x.contiguous()
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
@@ -688,7 +701,8 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         y = torch.empty((B, self.out_channels, Hp, Wp), device=x.device, dtype=_F32)
         nbytes = C.call("nes_permuted_conv_pool_fwd_tc_scratch_bytes", kh, kw)
         buf = C.scratch(nbytes, x.device)
-        C.call("nes_permuted_conv_pool_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+        C.call("nes_permuted_conv_pool_fwd_" + ("bf16" if mode == "bf16" else "tc"), C.ptr(x), C.ptr(_opt(self.weight)),
+               C.ptr(_opt(self.bias)), C.ptr(eps),
                C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, H, W, self.out_channels, kh, kw,
                self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
         return y

@@ -13,8 +13,11 @@
 //   warps of quadrants 0-1 (W channels) read the four positions of each pooling window straight from
 //   tensor memory (runtime column addresses), add the permuted eps value from shared memory, take the
 //   maximum, add the bias terms, apply the ReLU and store NCHW.
+// The same kernel runs with bf16 operands (template flag): a pixel is then a 64-byte row, tiles use the
+// 64-byte swizzle, a tap takes two kind::f16 MMAs with K = 16, and four images are staged ahead.
 // Every mbarrier wait is bounded; on a time-out the role stops, the error word is set and all roles
 // fall through to the common exit that frees tensor memory.
+#include <cuda_bf16.h>
 #include "tc_ptx.cuh"
 
 namespace nes {
@@ -23,28 +26,39 @@ namespace tc {
 constexpr int CP_CIN = 32;                 // channels per pixel row (128 bytes of fp32)
 constexpr int CP_M = 128, CP_N = 128;      // stacked channels x positions per image
 constexpr int CP_HALF = 64;                // W channels in lanes [0, 64), eps channels in [64, 128)
-constexpr int CP_TAP_BYTES = CP_M * CP_CIN * 4;        // 16 KiB of filter per tap
+constexpr int CP_MAX_STAGES = 4;
 constexpr int CP_THREADS = 192;            // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
-
-#ifdef NES_TRACE
-static __device__ unsigned long long g_trace[8][64];
-__device__ __forceinline__ void trace(int role, int i) {
-  if (blockIdx.x == 0 && i < 64) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    g_trace[role][i] = t;
-  }
-}
-#define TRACE(role, i) trace(role, i)
-#else
-#define TRACE(role, i)
-#endif
 
 struct ConvPoolParams {
   const float* bias; const float* bias_noise; const int16_t* pout; float* y;
   int64_t B, D, R;
-  int Cout, osp, W, kh, kw, Hp, Wp, rows_per_image, stage_rows, antithetic;
+  int Cout, osp, W, kh, kw, Hp, Wp, rows_per_image, stage_rows, stages, antithetic;
 };
+
+// K-major tile descriptors: rows of one swizzle span (128 or 64 bytes), 8-row groups 8 spans apart.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);
+  d |= uint64_t(1) << 16;
+  d |= uint64_t(512 >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(4) << 61;
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D = fp32, A = B = bf16, both K-major
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
 
 __device__ __forceinline__ void tmem_ld_x2(uint32_t taddr, uint32_t& a, uint32_t& b) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(taddr) : "memory");
@@ -69,34 +83,36 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // TW / THP / TWP: input width and pooled output size known at compile time (0 = taken from the parameters).
 // With them the W-channel warps read their whole accumulator row into registers with four wide loads
 // and index it statically; the runtime form reads each pooling window with two narrow loads.
-template <int TW, int THP, int TWP>
-__global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __grid_constant__ CUtensorMap map_x,
+template <int TW, int THP, int TWP, bool BF16>
+__global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                         const __grid_constant__ CUtensorMap map_f,
                                                                         const ConvPoolParams p) {
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw = smem_u32(dyn_raw);
   unsigned char* base = dyn_raw + (((raw + 1023u) & ~1023u) - raw);
+  constexpr int ROW_BYTES = BF16 ? 64 : 128;            // one pixel: 32 channels
+  constexpr int TAP_BYTES = CP_M * ROW_BYTES;           // filter rows of one tap
+  constexpr int KSTEPS = BF16 ? 2 : 4;                  // MMAs per tap (K = 16 bf16 / 8 tf32 = 32 bytes each)
   const int taps = p.kh * p.kw;
-  const int stage_bytes = p.stage_rows * 128;
+  const int stages = p.stages;
+  const int stage_bytes = p.stage_rows * ROW_BYTES;
   unsigned char* filt = base;
-  unsigned char* stage0 = filt + size_t(taps) * CP_TAP_BYTES;
-  float* zeps = reinterpret_cast<float*>(stage0 + 2 * size_t(stage_bytes));       // [CP_N][CP_HALF]
+  unsigned char* stage0 = filt + size_t(taps) * TAP_BYTES;
+  float* zeps = reinterpret_cast<float*>(stage0 + size_t(stages) * stage_bytes);   // [CP_N][CP_HALF]
   uint64_t* bars = reinterpret_cast<uint64_t*>(zeps + CP_N * CP_HALF);
-  uint64_t* full = bars;            // [2] image staged
-  uint64_t* empty = bars + 2;       // [2] stage consumed by the MMAs
-  uint64_t* acc_full = bars + 4;    // [2] accumulator complete
-  uint64_t* acc_empty = bars + 6;   // [2] accumulator drained (128 epilogue threads)
-  uint64_t* zeps_full = bars + 8;   // eps rows in shared memory (64 threads)
-  uint64_t* zeps_empty = bars + 9;  // ... and consumed (64 threads)
-  uint64_t* filt_full = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* full = bars;                              // [stages] image staged
+  uint64_t* empty = bars + CP_MAX_STAGES;             // [stages] stage consumed by the MMAs
+  uint64_t* acc_full = bars + 2 * CP_MAX_STAGES;      // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + 2;                 // [2] accumulator drained (128 epilogue threads)
+  uint64_t* zeps_full = acc_full + 4;                 // eps rows in shared memory (64 threads)
+  uint64_t* zeps_empty = acc_full + 5;                // ... and consumed (64 threads)
+  uint64_t* filt_full = acc_full + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 7);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&full[s], 1); mbar_init(&empty[s], 1);
-      mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128);
-    }
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128); }
     mbar_init(zeps_full, 64); mbar_init(zeps_empty, 64); mbar_init(filt_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -109,47 +125,47 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: the stacked filter once, then one load per image
-      mbar_expect_tx(filt_full, uint32_t(taps) * CP_TAP_BYTES);
-      for (int t = 0; t < taps; ++t) tma_load_2d(filt + size_t(t) * CP_TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
+      mbar_expect_tx(filt_full, uint32_t(taps) * TAP_BYTES);
+      for (int t = 0; t < taps; ++t) tma_load_2d(filt + size_t(t) * TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
       int i = 0;
       for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
-        const int s = i & 1;
-        if (!mbar_wait(&empty[s], ((i >> 1) & 1) ^ 1, 1)) break;
+        const int s = i % stages;
+        if (!mbar_wait(&empty[s], ((i / stages) & 1) ^ 1, 1)) break;
         mbar_expect_tx(&full[s], uint32_t(stage_bytes));
-        TRACE(0, i);
         tma_load_2d(stage0 + size_t(s) * stage_bytes, &map_x, &full[s], 0, int(b * p.rows_per_image));
-        // two stages cannot cover the HBM latency of the next load: pull the image after next into L2 now
-        const int64_t ahead = b + 2 * int64_t(gridDim.x);
+        // the staged images alone may not cover the HBM latency: pull the first image not yet staged into L2
+        const int64_t ahead = b + int64_t(stages) * gridDim.x;
         if (ahead < p.B) tma_prefetch_2d(&map_x, 0, int(ahead * p.rows_per_image));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer
-      constexpr uint32_t idesc = idesc_tf32(CP_M, CP_N);
+      constexpr uint32_t idesc = BF16 ? idesc_bf16(CP_M, CP_N) : idesc_tf32(CP_M, CP_N);
       bool ok = mbar_wait(filt_full, 0, 2);
       const uint32_t filt_addr = smem_u32(filt);
       int i = 0;
       for (int64_t b = blockIdx.x; b < p.B && ok; b += gridDim.x, ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        ok = mbar_wait(&acc_empty[s], ph ^ 1, 2) && mbar_wait(&full[s], ph, 2);
+        const int s = i % stages, a2 = i & 1;
+        ok = mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && mbar_wait(&full[s], (i / stages) & 1, 2);
         if (!ok) break;
         tc_fence_after();
-        TRACE(1, i);
         const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
-        const uint32_t acc = tmem_base + uint32_t(s * CP_N);
+        const uint32_t acc = tmem_base + uint32_t(a2 * CP_N);
         for (int t = 0; t < taps; ++t) {
           const int ti = t / p.kw, tj = t - ti * p.kw;
-          const uint64_t a = smem_desc_sw128(filt_addr + uint32_t(t) * CP_TAP_BYTES);
-          const uint64_t bd = smem_desc_sw128(st + uint32_t(ti * p.W + tj) * 128u);
+          const uint32_t a_addr = filt_addr + uint32_t(t) * TAP_BYTES;
+          const uint32_t b_addr = st + uint32_t(ti * p.W + tj) * ROW_BYTES;
+          const uint64_t a = BF16 ? smem_desc_sw64(a_addr) : smem_desc_sw128(a_addr);
+          const uint64_t bd = BF16 ? smem_desc_sw64(b_addr) : smem_desc_sw128(b_addr);
 #pragma unroll
-          for (int k = 0; k < CP_CIN / 8; ++k)
-            mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < KSTEPS; ++k) {
+            if (BF16) mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+            else mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+          }
         }
         mma_commit(&empty[s]);
-        mma_commit(&acc_full[s]);
-        TRACE(2, i);
+        mma_commit(&acc_full[a2]);
       }
     }
   } else {
@@ -162,7 +178,6 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
       for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
         const int s = i & 1;
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (lane == 0 && q == 2) TRACE(3, i);
         if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
         tc_fence_after();
         uint32_t r[CP_N];
@@ -174,7 +189,6 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
 #pragma unroll
         for (int j = 0; j < CP_N; ++j) zeps[j * CP_HALF + ch] = __uint_as_float(r[j]);
         mbar_arrive(zeps_full);
-        if (lane == 0 && q == 2) TRACE(4, i);
       }
     } else {
       // ---- W channels: pooling windows from tensor memory + permuted eps values from shared memory
@@ -193,13 +207,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         const float sn = noisy ? sgn : 0.f;
         const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (lane == 0 && q == 0) TRACE(5, i);
         if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
         tc_fence_after();
-        if (lane == 0 && q == 0) TRACE(6, i);
         float* out = p.y + (b * p.Cout + c) * pooled;
         const uint32_t acc = lane_addr + uint32_t(s * CP_N);
-        if (TW > 0) {
+        if constexpr (TW > 0) {
           uint32_t r[CP_N];
 #pragma unroll
           for (int c0 = 0; c0 < CP_N; c0 += 32) tmem_ld32_nowait(acc + uint32_t(c0), r + c0);
@@ -221,9 +233,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
               if (live) out[py * TWP + px] = v;
             }
           mbar_arrive(zeps_empty);
-          if (lane == 0 && q == 0) TRACE(7, i);
-          continue;
-        }
+        } else {
         for (int py = 0; py < p.Hp; ++py) {
           for (int px0 = 0; px0 < p.Wp; px0 += 4) {
             uint32_t top[4][2], bot[4][2];
@@ -253,6 +263,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
         mbar_arrive(zeps_empty);
+        }
       }
     }
   }
@@ -264,25 +275,19 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tf32_kernel(const __g
   }
 }
 
-// stacked[tap][m][cin], tf32-rounded: m < Cout -> weight[m], 64 <= m < 64 + osp -> eps[m - 64], else 0
-__global__ void stack_filter_tf32_kernel(const float* __restrict__ w, const float* __restrict__ eps, float* __restrict__ out,
-                                         int Cout, int osp, int taps) {
+// stacked[tap][m][cin], rounded to the operand type: m < Cout -> weight[m], 64 <= m < 64 + osp -> eps[m - 64], else 0
+template <bool BF16>
+__global__ void stack_filter_kernel(const float* __restrict__ w, const float* __restrict__ eps, void* __restrict__ out,
+                                    int Cout, int osp, int taps) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= taps * CP_M * CP_CIN) return;
   const int cin = idx % CP_CIN, m = (idx / CP_CIN) % CP_M, t = idx / (CP_CIN * CP_M);
   float v = 0.f;
   if (m < Cout) v = w[(size_t(m) * CP_CIN + cin) * taps + t];
   else if (m >= CP_HALF && m - CP_HALF < osp) v = eps[(size_t(m - CP_HALF) * CP_CIN + cin) * taps + t];
-  out[idx] = round_tf32(v);
+  if (BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else static_cast<float*>(out)[idx] = round_tf32(v);
 }
-
-#ifdef NES_TRACE
-}}
-extern "C" int nes_debug_conv_pool_trace(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, nes::tc::g_trace, sizeof(unsigned long long) * 8 * 64) == cudaSuccess ? 0 : -1;
-}
-namespace nes { namespace tc {
-#endif
 
 int conv_pool_error_word(int* v) {
   cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
@@ -290,24 +295,27 @@ int conv_pool_error_word(int* v) {
   return NES_OK;
 }
 
-static int make_rows_map(CUtensorMap* map, const float* base, int64_t rows, int box_rows, const char* what) {
+// (rows, 32 channels) row-major tensor, box = box_rows whole rows, swizzle span = one row
+static int make_rows_map(CUtensorMap* map, const void* base, bool bf16, int64_t rows, int box_rows, const char* what) {
   EncodeTiledFn fn = encode_fn();
   NES_REQUIRE(fn != nullptr, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
+  const size_t esz = bf16 ? 2 : 4;
   cuuint64_t dims[2] = {(cuuint64_t)CP_CIN, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)CP_CIN * sizeof(float)};
+  cuuint64_t strides[1] = {(cuuint64_t)CP_CIN * esz};
   cuuint32_t box[2] = {(cuuint32_t)CP_CIN, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NES_REQUIRE(r == CUDA_SUCCESS, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
   return NES_OK;
 }
 
-struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows; size_t smem; };
+struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows, stages, row_bytes; size_t smem; };
 
 // Shapes the kernel covers; on failure the message says which rule was broken.
-static int plan_conv_pool(ConvPoolPlan& pl, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what) {
+static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what) {
   NES_REQUIRE(Cin == CP_CIN, NES_ERR_UNSUPPORTED, "%s: needs %d input channels (got %d)", what, CP_CIN, Cin);
   NES_REQUIRE(Cout >= 1 && Cout <= CP_HALF && osp >= 0 && osp <= CP_HALF, NES_ERR_UNSUPPORTED,
               "%s: needs at most %d output channels (got %d, %d noise rows)", what, CP_HALF, Cout, osp);
@@ -318,11 +326,56 @@ static int plan_conv_pool(ConvPoolPlan& pl, int Cin, int H, int W, int Cout, int
   NES_REQUIRE(pl.Hp >= 1 && pl.Wp >= 1, NES_ERR_UNSUPPORTED, "%s: output smaller than one pooling window", what);
   NES_REQUIRE((2 * pl.Hp - 1) * W + 2 * pl.Wp - 1 < CP_N, NES_ERR_UNSUPPORTED,
               "%s: the pooled part of a %dx%d image does not fit %d accumulator columns", what, H, W, CP_N);
-  pl.stage_rows = (CP_N + (kh - 1) * W + (kw - 1) + 7) & ~7;
+  pl.stage_rows = (CP_N + (kh - 1) * W + (kw - 1) + 15) & ~15;      // whole swizzle atoms (8 rows) at either row size
   NES_REQUIRE(pl.stage_rows <= 256, NES_ERR_UNSUPPORTED, "%s: filter reach too large for one staged image", what);
-  pl.smem = 1024 + size_t(pl.taps) * CP_TAP_BYTES + 2 * size_t(pl.stage_rows) * 128 + size_t(CP_N) * CP_HALF * 4 + 128;
-  NES_REQUIRE(pl.smem <= 227 * 1024, NES_ERR_UNSUPPORTED, "%s: %d filter taps need %zu B of shared memory", what, pl.taps, pl.smem);
+  pl.row_bytes = bf16 ? 64 : 128;
+  const size_t fixed = 1024 + size_t(pl.taps) * CP_M * pl.row_bytes + size_t(CP_N) * CP_HALF * 4 + 256;
+  const size_t stage = size_t(pl.stage_rows) * pl.row_bytes;
+  NES_REQUIRE(fixed + 2 * stage <= 227 * 1024, NES_ERR_UNSUPPORTED, "%s: %d filter taps do not fit shared memory", what, pl.taps);
+  pl.stages = int((227 * 1024 - fixed) / stage);
+  if (pl.stages > CP_MAX_STAGES) pl.stages = CP_MAX_STAGES;
+  pl.smem = fixed + size_t(pl.stages) * stage;
   return NES_OK;
+}
+
+template <bool BF16>
+static int run_conv_pool(const void* x_nhwc, const float* weight, const float* bias, const float* eps,
+                         const float* bias_noise, const int16_t* pout, float* y, int64_t D, int64_t R, int Cin, int H, int W,
+                         int Cout, int kh, int kw, int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                         cudaStream_t st, const char* what) {
+  NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "%s: negative extent", what);
+  ConvPoolPlan pl;
+  int rc = plan_conv_pool(pl, BF16, Cin, H, W, Cout, out_sp, kh, kw, what);
+  if (rc != NES_OK) return rc;
+  const int64_t B = D * R;
+  if (B == 0) return NES_OK;
+  NES_REQUIRE(x_nhwc && weight && eps && y, NES_ERR_BAD_ARG, "%s: null pointer", what);
+  NES_REQUIRE(aligned16(x_nhwc), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
+  NES_REQUIRE(B * H * W <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: batch too large", what);
+  const int64_t need = int64_t(pl.taps) * CP_M * pl.row_bytes;
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "%s: scratch needs %lld bytes, 256-byte aligned", what, (long long)need);
+  const int n = pl.taps * CP_M * CP_CIN;
+  stack_filter_kernel<BF16><<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, scratch, Cout, out_sp, pl.taps);
+  rc = check_launch(what);
+  if (rc != NES_OK) return rc;
+  CUtensorMap map_x, map_f;
+  if ((rc = make_rows_map(&map_x, x_nhwc, BF16, B * H * W, pl.stage_rows, what)) != NES_OK) return rc;
+  if ((rc = make_rows_map(&map_f, scratch, BF16, int64_t(pl.taps) * CP_M, CP_M, what)) != NES_OK) return rc;
+  ConvPoolParams p;
+  p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
+  p.B = B; p.D = D; p.R = R;
+  p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = pl.Hp; p.Wp = pl.Wp;
+  p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.stages = pl.stages; p.antithetic = antithetic;
+  // compile-time geometry for 13x13 inputs pooled to 5x5 (3x3 filters on the 13x13 maps of the small MNIST
+  // network); every other covered shape takes the runtime-indexed form
+  const bool fixed = (W == 13 && pl.Hp == 5 && pl.Wp == 5);
+  auto kernel = fixed ? conv_pool_tc_kernel<13, 5, 5, BF16> : conv_pool_tc_kernel<0, 0, 0, BF16>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+  const unsigned grid = (unsigned)(B < sm_count() ? B : sm_count());
+  kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
+  return check_launch(what);
 }
 
 }  // namespace tc
@@ -333,7 +386,7 @@ using namespace nes::tc;
 
 extern "C" int64_t nes_permuted_conv_pool_fwd_tc_scratch_bytes(int kh, int kw) {
   if (kh <= 0 || kw <= 0) return 0;
-  return int64_t(kh) * kw * CP_TAP_BYTES;
+  return int64_t(kh) * kw * CP_M * 128;
 }
 
 extern "C" int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* weight, const float* bias, const float* eps,
@@ -341,40 +394,15 @@ extern "C" int nes_permuted_conv_pool_fwd_tc(const float* x_nhwc, const float* w
                                              int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
                                              int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
                                              nes_stream_t stream) {
-  const char* what = "permuted_conv_pool_fwd_tc";
-  NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "%s: negative extent", what);
-  ConvPoolPlan pl;
-  int rc = plan_conv_pool(pl, Cin, H, W, Cout, out_sp, kh, kw, what);
-  if (rc != NES_OK) return rc;
-  const int64_t B = D * R;
-  if (B == 0) return NES_OK;
-  NES_REQUIRE(x_nhwc && weight && eps && y, NES_ERR_BAD_ARG, "%s: null pointer", what);
-  NES_REQUIRE(aligned16(x_nhwc), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
-  NES_REQUIRE(B * H * W <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: batch too large", what);
-  const int64_t need = nes_permuted_conv_pool_fwd_tc_scratch_bytes(kh, kw);
-  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
-              "%s: scratch needs %lld bytes, 256-byte aligned", what, (long long)need);
-  cudaStream_t st = as_stream(stream);
-  float* stacked = static_cast<float*>(scratch);
-  const int n = pl.taps * CP_M * CP_CIN;
-  stack_filter_tf32_kernel<<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, stacked, Cout, out_sp, pl.taps);
-  rc = check_launch("permuted_conv_pool_fwd_tc(filter)");
-  if (rc != NES_OK) return rc;
-  CUtensorMap map_x, map_f;
-  if ((rc = make_rows_map(&map_x, x_nhwc, B * H * W, pl.stage_rows, what)) != NES_OK) return rc;
-  if ((rc = make_rows_map(&map_f, stacked, int64_t(pl.taps) * CP_M, CP_M, what)) != NES_OK) return rc;
-  ConvPoolParams p;
-  p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
-  p.B = B; p.D = D; p.R = R;
-  p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = pl.Hp; p.Wp = pl.Wp;
-  p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.antithetic = antithetic;
-  // compile-time geometry for 13x13 inputs pooled to 5x5 (3x3 filters on the 13x13 maps of the small MNIST
-  // network); every other covered shape takes the runtime-indexed form
-  const bool fixed = (W == 13 && pl.Hp == 5 && pl.Wp == 5);
-  auto kernel = fixed ? conv_pool_tf32_kernel<13, 5, 5> : conv_pool_tf32_kernel<0, 0, 0>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
-  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
-  const unsigned grid = (unsigned)(B < sm_count() ? B : sm_count());
-  kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
-  return check_launch(what);
+  return run_conv_pool<false>(x_nhwc, weight, bias, eps, bias_noise, pout, y, D, R, Cin, H, W, Cout, kh, kw, out_sp,
+                              antithetic, scratch, scratch_bytes, as_stream(stream), "permuted_conv_pool_fwd_tc");
+}
+
+extern "C" int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const float* weight, const float* bias, const float* eps,
+                                               const float* bias_noise, const int16_t* pout, float* y,
+                                               int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                               int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                                               nes_stream_t stream) {
+  return run_conv_pool<true>(x_nhwc_bf16, weight, bias, eps, bias_noise, pout, y, D, R, Cin, H, W, Cout, kh, kw, out_sp,
+                             antithetic, scratch, scratch_bytes, as_stream(stream), "permuted_conv_pool_fwd_bf16");
 }

@@ -477,6 +477,15 @@ def test_shared_input_conv_relu_pool(base, cin, cout, out_sp, hw, k, pad, R, ant
     assert_close(y, want, what="fused forward")
     plain = torch.nn.functional.conv2d(x, W, b, 1, pad)
     assert_close(y_off, torch.nn.functional.max_pool2d(torch.relu(plain), 2), what="inference")
+    # reduced-precision stores for a tensor-core consumer: the same values rounded once
+    for out, step in (("tf32", 2.0 ** -11), ("bf16", 2.0 ** -8)):
+        layer.options = dict(layer.options, out_dtype=out)
+        with torch.no_grad():
+            layer.perturbed_flag = True
+            yr = layer.forward(G(x))
+            layer.perturbed_flag = False
+        assert yr.dtype == (torch.bfloat16 if out == "bf16" else torch.float32)
+        assert torch.all((yr.float() - y).abs() <= step * y.abs() + 1e-30)
 
 
 def test_fuse_option_falls_back_to_separate_kernels(base):

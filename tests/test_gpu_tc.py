@@ -326,16 +326,19 @@ def C_launches():
     (64, 0, 10, 2, 3, True, True, 150),       # more images than SMs: several images per block
     (64, 0, 13, 3, 3, True, True, 210),       # the same for the compile-time 13x13 -> 5x5 geometry
 ])
-def test_permuted_conv_pool_tf32(cout, out_sp, hw, k, R, anti, bias, D):
+@pytest.mark.parametrize("tc", ["tf32", "bf16"])
+def test_permuted_conv_pool_tensor_core(tc, cout, out_sp, hw, k, R, anti, bias, D):
     from nesgpu_b200 import base
     from oracle import perturbed_ref as O
     from gpu_util import G, set_params
     cin = 32
     g = torch.Generator().manual_seed(cout + hw + D)
     layer = base.PermutedConv2d(cin, cout, k, D, bias=bias, antithetic=anti, permutation="out", out_sparsity=out_sp,
-                                options={"tc": "tf32", "fuse": "relu_maxpool2"}).to(DEV)
+                                options={"tc": tc, "fuse": "relu_maxpool2"}).to(DEV)
     osp = layer.out_sparsity
     x = torch.randn(R * D, cin, hw, hw, generator=g)
+    if tc == "bf16":
+        x = x.bfloat16().float()          # the input arrives as bf16 in this mode: compare on representable values
     W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
     b = torch.randn(cout, generator=g) * .1 if bias else None
     eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
@@ -350,7 +353,8 @@ def test_permuted_conv_pool_tf32(cout, out_sp, hw, k, R, anti, bias, D):
     with torch.no_grad():
         layer.perturbed_flag = True
         y_nchw = layer.forward(G(x))                                                  # copies to channels-last first
-        y_cl = layer.forward(G(x).contiguous(memory_format=torch.channels_last))      # taken as is
+        x_cl = G(x).contiguous(memory_format=torch.channels_last)
+        y_cl = layer.forward(x_cl.bfloat16() if tc == "bf16" else x_cl)                # taken as is
     assert C_launches() - before == 4                                                 # 2 x (filter stack + fused kernel)
     assert _flag(_C()) == 0
     assert y_nchw.shape == want.shape and y_nchw.is_contiguous()
