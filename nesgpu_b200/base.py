@@ -646,7 +646,7 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         x = C.require_cuda(input, "input", _F32)
         x, geom, (Ho, Wo) = self._geometry(x)
         osp, cout = self.out_sparsity, self.out_channels
-        if (cout + osp) * (Ho * Wo + 7) * 4 > 220 * 1024 or Ho < 2 or Wo < 2:
+        if (cout + osp + 1) * (Ho * Wo + 1) * 4 + 80 * cout + 16 > 220 * 1024 or Ho < 2 or Wo < 2:
             return None
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None

@@ -4,9 +4,11 @@
 //   conv(x, W)[c] + s * conv(x, eps)[pout[d, c]] + bias[c] + s * bias_noise[d, c],
 // so the two convolutions are computed once per image (one plain convolution with the stacked filter
 // [W; eps]) and the per-member work is a gather, an add, the ReLU and the pooling.  A block keeps the
-// stacked feature maps of one image in shared memory and walks a group of members; lanes are channels, so
-// every store is a run of consecutive channels of one pooled pixel: the output is channels-last.  With an
-// even row length the rows of a pooling window are read as 8-byte pairs.
+// feature maps of one image in shared memory (conv(x, W) channel-major, conv(x, eps) position-major) plus
+// its members' noise-map indices, signs and bias terms.  A warp owns pooling windows, a lane a channel: the
+// four W values of a window stay in registers while the warp walks the members, and because the channels
+// of a member point at different noise maps, the four noise reads per stored value hit 32 different banks.
+// Every store is a run of consecutive channels of one pooled pixel: the output is channels-last.
 #include <cuda_bf16.h>
 #include "common.cuh"
 
@@ -16,14 +18,6 @@ __device__ inline float round_to_tf32(float a) {
   uint32_t u = __float_as_uint(a);
   u += 0x00000FFFu + ((u >> 13) & 1u);
   return __uint_as_float(u & 0xFFFFE000u);
-}
-
-// even pitch >= hw with pitch / 2 odd: planes start 8-byte aligned and the 16 lanes of a 64-bit
-// shared-memory phase (16 channels) fall on 16 different bank pairs
-__host__ __device__ inline int plane_pitch(int hw) {
-  int p = (hw + 1) & ~1;
-  if (((p >> 1) & 1) == 0) p += 2;
-  return p;
 }
 
 // MODE: 0 = fp32, 1 = fp32 rounded to TF32, 2 = bf16
@@ -46,62 +40,52 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
     const int16_t* __restrict__ pout, typename OutType<MODE>::type* __restrict__ y, int64_t R, int64_t D, int Cout, int osp,
     int Ho, int Wo, int antithetic, int members_per_block) {
   typedef typename OutType<MODE>::type out_t;
-  extern __shared__ __align__(16) float planes[];                 // (Cout + osp) planes of Ho*Wo (+1 pad) floats
-  const int hw = Ho * Wo, pitch = plane_pitch(hw);
+  extern __shared__ __align__(16) float smem[];
+  const int hw = Ho * Wo, pitch = hw | 1, npitch = osp | 1;
   const int Hp = Ho / 2, Wp = Wo / 2, pooled = Hp * Wp;
+  float* wmaps = smem;                                          // [Cout][pitch]      conv(x, W), channel-major
+  float* nmaps = wmaps + size_t(Cout) * pitch;                  // [hw][npitch]       conv(x, eps), position-major
+  float2* tab = reinterpret_cast<float2*>(smem + ((size_t(Cout) * pitch + size_t(hw) * npitch + 1) & ~size_t(1)));   // [members][Cout] (scale, add)
+  int16_t* so_tab = reinterpret_cast<int16_t*>(tab + size_t(members_per_block) * Cout);        // [members][Cout] noise map
   const int64_t r = blockIdx.x;
-  const float* zr = z + r * int64_t(Cout + osp) * hw;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  for (int c = warp; c < Cout + osp; c += warps)
-    for (int p = lane; p < hw; p += 32) planes[c * pitch + p] = zr[c * hw + p];
-  __syncthreads();
-  const float sgn = anti_sign(r, R, antithetic);
   const int64_t d0 = int64_t(blockIdx.y) * members_per_block;
-  const int64_t d1 = (d0 + members_per_block < D) ? d0 + members_per_block : D;
-  // a warp owns whole members, so the latency of a member's permutation / bias loads is hidden by the
-  // other warps' arithmetic
-  for (int64_t d = d0 + warp; d < d1; d += warps) {
-    for (int c0 = 0; c0 < Cout; c0 += 32) {
-      const int c = c0 + lane;
-      const bool live = c < Cout;
-      const float* base = planes + (live ? c : 0) * pitch;
-      int so = live ? (pout ? int(pout[d * Cout + c]) : c) : 0;
-      const bool noisy = live && so < osp;
-      const float* noise = planes + (Cout + (noisy ? so : 0)) * pitch;
-      const float s = noisy ? sgn : 0.f;
-      float add = (live && bias) ? bias[c] : 0.f;
-      if (live && bias_noise) add += sgn * bias_noise[d * Cout + c];
-      out_t* out = y + ((r * D + d) * pooled) * Cout + c;
-      if ((Wo & 1) == 0) {
-        // even row length: both rows of a window start on 8-byte boundaries
-        for (int py = 0; py < Hp; ++py) {
-          const float* b = base + (2 * py) * Wo;
-          const float* n = noise + (2 * py) * Wo;
-          out_t* o = out + int64_t(py) * Wp * Cout;
+  const int nm = int((d0 + members_per_block < D ? d0 + members_per_block : D) - d0);
+  const float sgn = anti_sign(r, R, antithetic);
+  const float* zr = z + r * int64_t(Cout + osp) * hw;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int c = warp; c < Cout + osp; c += CP_WARPS) {
+    if (c < Cout) for (int p = lane; p < hw; p += 32) wmaps[c * pitch + p] = zr[c * hw + p];
+    else for (int p = lane; p < hw; p += 32) nmaps[p * npitch + (c - Cout)] = zr[c * hw + p];     // odd npitch: no conflicts
+  }
+  for (int e = threadIdx.x; e < nm * Cout; e += blockDim.x) {
+    const int m = e / Cout, c = e - m * Cout;
+    const int so = pout ? int(pout[(d0 + m) * Cout + c]) : c;
+    so_tab[e] = int16_t(so < osp ? so : 0);
+    tab[e] = make_float2(so < osp ? sgn : 0.f,
+                         (bias ? bias[c] : 0.f) + (bias_noise ? sgn * bias_noise[(d0 + m) * Cout + c] : 0.f));
+  }
+  __syncthreads();
+  const int64_t member_stride = int64_t(pooled) * Cout;
+  const int row = Wo * npitch;
+  for (int c0 = 0; c0 < Cout; c0 += 32) {
+    const int c = c0 + lane;
+    const bool live = c < Cout;
+    const int cc = live ? c : 0;
+    const float* base = wmaps + cc * pitch;
+    for (int pp = warp; pp < pooled; pp += CP_WARPS) {
+      const int py = pp / Wp, px = pp - py * Wp;
+      const int p00 = (2 * py) * Wo + 2 * px;
+      const float b00 = base[p00], b01 = base[p00 + 1], b10 = base[p00 + Wo], b11 = base[p00 + Wo + 1];
+      out_t* o = y + ((r * D + d0) * pooled + pp) * Cout + c;
+      const float* np = nmaps + p00 * npitch;
 #pragma unroll 4
-          for (int px = 0; px < Wp; ++px, b += 2, n += 2, o += Cout) {
-            const float2 b0 = *reinterpret_cast<const float2*>(b);
-            const float2 b1 = *reinterpret_cast<const float2*>(b + Wo);
-            const float2 n0 = *reinterpret_cast<const float2*>(n);
-            const float2 n1 = *reinterpret_cast<const float2*>(n + Wo);
-            const out_t v = pool_value<MODE>(fmaf(s, n0.x, b0.x), fmaf(s, n0.y, b0.y), fmaf(s, n1.x, b1.x), fmaf(s, n1.y, b1.y), add);
-            if (live) o[0] = v;
-          }
-        }
-        continue;
-      }
-      for (int py = 0; py < Hp; ++py) {
-        const int row = (2 * py) * Wo;
-#pragma unroll 4
-        for (int px = 0; px < Wp; ++px) {
-          const int p00 = row + 2 * px;
-          const float v0 = base[p00] + s * noise[p00];
-          const float v1 = base[p00 + 1] + s * noise[p00 + 1];
-          const float v2 = base[p00 + Wo] + s * noise[p00 + Wo];
-          const float v3 = base[p00 + Wo + 1] + s * noise[p00 + Wo + 1];
-          const out_t v = pool_value<MODE>(v0, v1, v2, v3, add);
-          if (live) out[int64_t(py * Wp + px) * Cout] = v;
-        }
+      for (int m = 0; m < nm; ++m, o += member_stride) {
+        // the 32 channels of a member point at 32 different noise maps = 32 different banks
+        const float* n = np + int(so_tab[m * Cout + cc]);
+        const float2 t = tab[m * Cout + cc];
+        const out_t v = pool_value<MODE>(fmaf(t.x, n[0], b00), fmaf(t.x, n[npitch], b01), fmaf(t.x, n[row], b10),
+                                         fmaf(t.x, n[row + npitch], b11), t.y);
+        if (live) *o = v;
       }
     }
   }
@@ -120,24 +104,29 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   NES_REQUIRE(out_mode >= 0 && out_mode <= 2, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: out_mode must be 0 (fp32), 1 (tf32) or 2 (bf16)");
   if (R == 0 || D == 0 || Cout == 0 || Ho < 2 || Wo < 2) return NES_OK;
   NES_REQUIRE(z && y, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: null pointer");
-  NES_REQUIRE(R <= INT32_MAX, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: too many images");
+  NES_REQUIRE(R <= INT32_MAX && Cout <= 32767, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: extent too large");
   const int64_t hw = int64_t(Ho) * Wo;
-  const size_t smem = size_t(Cout + out_sp) * size_t(plane_pitch(int(hw))) * sizeof(float);
-  NES_REQUIRE(smem <= 220 * 1024, NES_ERR_UNSUPPORTED,
-              "shared_conv_pool_fwd: %zu B of feature maps per image do not fit in shared memory", smem);
-  // Member groups per image: a block costs one round for loading the image's maps plus one round per
-  // CP_WARPS members (a warp owns whole members); pick the split with the fewest rounds x waves.
+  const size_t limit = 220 * 1024;
+  const size_t plane_bytes = ((size_t(Cout) * size_t(hw | 1) + size_t(hw) * size_t(out_sp | 1) + 1) & ~size_t(1)) * sizeof(float);
+  const size_t member_bytes = size_t(Cout) * 10;                // one float2 and one int16 per channel
+  NES_REQUIRE(plane_bytes + 8 * member_bytes <= limit, NES_ERR_UNSUPPORTED,
+              "shared_conv_pool_fwd: %zu B of feature maps per image do not fit in shared memory", plane_bytes);
+  // Members per block: a block costs about one round for loading the image's maps plus one round per
+  // window pass over its members; pick the split with the fewest rounds x waves, within the table space.
   const int64_t sms = sm_count();
-  int64_t best_groups = 1, best_cost = INT64_MAX;
-  const int64_t max_groups = D < 65535 ? D : 65535;
-  for (int64_t g = 1; g <= max_groups; ++g) {
+  const int64_t max_per = int64_t((limit - plane_bytes) / member_bytes);
+  const int64_t pooled = int64_t(Ho / 2) * (Wo / 2);
+  const int64_t passes = ceil_div<int64_t>(pooled, CP_WARPS) * ceil_div<int64_t>(Cout, 32);
+  int64_t best_per = 1, best_cost = INT64_MAX;
+  for (int64_t g = ceil_div<int64_t>(D, max_per); g <= D && g <= 65535; ++g) {
     const int64_t per_g = ceil_div<int64_t>(D, g);
     const int64_t blocks = R * ceil_div<int64_t>(D, per_g);
-    const int64_t cost = ceil_div<int64_t>(blocks, sms) * (ceil_div<int64_t>(per_g, CP_WARPS) + 1);
-    if (cost < best_cost) { best_cost = cost; best_groups = g; }
-    if (per_g <= CP_WARPS) break;
+    const int64_t cost = ceil_div<int64_t>(blocks, sms) * (passes * per_g + 64);
+    if (cost < best_cost) { best_cost = cost; best_per = per_g; }
+    if (blocks >= 4 * sms) break;
   }
-  const int per = int(ceil_div<int64_t>(D, best_groups));
+  const int per = int(best_per);
+  const size_t smem = plane_bytes + size_t(per) * member_bytes + 16;
   dim3 grid((unsigned)R, (unsigned)ceil_div<int64_t>(D, per));
   cudaError_t e;
   cudaStream_t st = as_stream(stream);

@@ -10,9 +10,9 @@
 // per image, kh*kw*4 tcgen05.mma (kind::tf32, M = N = 128, K = 8) per image into one of two TMEM
 // accumulators, and an epilogue that overlaps the next image's MMAs:
 //   warps of lane quadrants 2-3 (eps channels) copy their rows to shared memory, [position][channel];
-//   warps of quadrants 0-1 (W channels) read the four positions of each pooling window straight from
-//   tensor memory (runtime column addresses), add the permuted eps value from shared memory, take the
-//   maximum, add the bias terms, apply the ReLU and store NCHW.
+//   warps of quadrants 0-1 (W channels; two warps per quadrant, each with half of the pooling windows)
+//   read their accumulator row from tensor memory, add the permuted eps value from shared memory, take
+//   the maximum, add the bias terms, apply the ReLU and store NCHW.
 // The same kernel runs with bf16 operands (template flag): a pixel is then a 64-byte row, tiles use the
 // 64-byte swizzle, a tap takes two kind::f16 MMAs with K = 16, and four images are staged ahead.
 // Every mbarrier wait is bounded; on a time-out the role stops, the error word is set and all roles
@@ -27,12 +27,12 @@ constexpr int CP_CIN = 32;                 // channels per pixel row (128 bytes 
 constexpr int CP_M = 128, CP_N = 128;      // stacked channels x positions per image
 constexpr int CP_HALF = 64;                // W channels in lanes [0, 64), eps channels in [64, 128)
 constexpr int CP_MAX_STAGES = 4;
-constexpr int CP_THREADS = 192;            // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+constexpr int CP_THREADS = 320;            // warp 0 TMA, warp 1 MMA + TMEM, warps 2-3 eps rows, warps 4-5 and 8-9 pooling
 
 struct ConvPoolParams {
   const float* bias; const float* bias_noise; const int16_t* pout; float* y;
   int64_t B, D, R;
-  int Cout, osp, W, kh, kw, Hp, Wp, rows_per_image, stage_rows, stages, antithetic;
+  int Cout, osp, W, kh, kw, Hp, Wp, rows_per_image, stage_rows, stages, zbufs, antithetic;
 };
 
 // K-major tile descriptors: rows of one swizzle span (128 or 64 bytes), 8-row groups 8 spans apart.
@@ -98,22 +98,24 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   const int stage_bytes = p.stage_rows * ROW_BYTES;
   unsigned char* filt = base;
   unsigned char* stage0 = filt + size_t(taps) * TAP_BYTES;
-  float* zeps = reinterpret_cast<float*>(stage0 + size_t(stages) * stage_bytes);   // [CP_N][CP_HALF]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps + CP_N * CP_HALF);
+  float* zeps0 = reinterpret_cast<float*>(stage0 + size_t(stages) * stage_bytes);  // [zbufs][CP_N][CP_HALF]
+  const int zbufs = p.zbufs;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps0 + size_t(zbufs) * CP_N * CP_HALF);
   uint64_t* full = bars;                              // [stages] image staged
   uint64_t* empty = bars + CP_MAX_STAGES;             // [stages] stage consumed by the MMAs
   uint64_t* acc_full = bars + 2 * CP_MAX_STAGES;      // [2] accumulator complete
-  uint64_t* acc_empty = acc_full + 2;                 // [2] accumulator drained (128 epilogue threads)
-  uint64_t* zeps_full = acc_full + 4;                 // eps rows in shared memory (64 threads)
-  uint64_t* zeps_empty = acc_full + 5;                // ... and consumed (64 threads)
-  uint64_t* filt_full = acc_full + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 7);
+  uint64_t* acc_empty = acc_full + 2;                 // [2] accumulator drained (192 epilogue threads)
+  uint64_t* zeps_full = acc_full + 4;                 // [zbufs] eps rows in shared memory (64 threads)
+  uint64_t* zeps_empty = acc_full + 6;                // [zbufs] ... and consumed (128 threads)
+  uint64_t* filt_full = acc_full + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 9);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 128); }
-    mbar_init(zeps_full, 64); mbar_init(zeps_empty, 64); mbar_init(filt_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 192); }
+    for (int s = 0; s < zbufs; ++s) { mbar_init(&zeps_full[s], 64); mbar_init(&zeps_empty[s], 128); }
+    mbar_init(filt_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, 2 * CP_N);
@@ -168,8 +170,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
         mma_commit(&acc_full[a2]);
       }
     }
-  } else {
+  } else if (warp != 6 && warp != 7) {
+    // Each W-channel quadrant is served by two warps (4 and 8 for lanes 0-31, 5 and 9 for lanes 32-63) that
+    // share an image's pooling windows: the pooling is the longest per-image chain outside the MMAs.
     const int q = warp & 3;                        // TMEM lane quadrant of this warp
+    const int half = warp >> 3;                    // 0: first share of the windows, 1: second share
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
     if (q >= 2) {
       // ---- eps channels: accumulator rows -> shared memory [position][channel]
@@ -178,7 +183,9 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
       for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
         const int s = i & 1;
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
+        const int zb = i % zbufs;
+        float* zeps = zeps0 + size_t(zb) * CP_N * CP_HALF;
+        if (!mbar_wait_relaxed(&zeps_empty[zb], ((i / zbufs) & 1) ^ 1, 3)) break;
         tc_fence_after();
         uint32_t r[CP_N];
 #pragma unroll
@@ -188,7 +195,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
         mbar_arrive(&acc_empty[s]);
 #pragma unroll
         for (int j = 0; j < CP_N; ++j) zeps[j * CP_HALF + ch] = __uint_as_float(r[j]);
-        mbar_arrive(zeps_full);
+        mbar_arrive(&zeps_full[zb]);
       }
     } else {
       // ---- W channels: pooling windows from tensor memory + permuted eps values from shared memory
@@ -207,7 +214,9 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
         const float sn = noisy ? sgn : 0.f;
         const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
+        const int zb = i % zbufs;
+        const float* zeps = zeps0 + size_t(zb) * CP_N * CP_HALF;
+        if (!mbar_wait_relaxed(&zeps_full[zb], (i / zbufs) & 1, 3)) break;
         tc_fence_after();
         float* out = p.y + (b * p.Cout + c) * pooled;
         const uint32_t acc = lane_addr + uint32_t(s * CP_N);
@@ -219,11 +228,13 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
           tc_fence_before();
           mbar_arrive(&acc_empty[s]);              // accumulator is in registers: the next image may overwrite it
           const float* e = zeps + so;
+          constexpr int SPLIT = (THP * TWP + 1) / 2;
 #pragma unroll
           for (int py = 0; py < THP; ++py)
 #pragma unroll
             for (int px = 0; px < TWP; ++px) {
               constexpr int W_ = TW > 0 ? TW : 1;
+              if ((py * TWP + px < SPLIT) != (half == 0)) continue;
               const int pos = 2 * py * W_ + 2 * px;
               const float v0 = __uint_as_float(r[pos]) + sn * e[pos * CP_HALF];
               const float v1 = __uint_as_float(r[pos + 1]) + sn * e[(pos + 1) * CP_HALF];
@@ -232,9 +243,9 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
               const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
               if (live) out[py * TWP + px] = v;
             }
-          mbar_arrive(zeps_empty);
+          mbar_arrive(&zeps_empty[zb]);
         } else {
-        for (int py = 0; py < p.Hp; ++py) {
+        for (int py = half; py < p.Hp; py += 2) {
           for (int px0 = 0; px0 < p.Wp; px0 += 4) {
             uint32_t top[4][2], bot[4][2];
 #pragma unroll
@@ -262,7 +273,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
         }
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
-        mbar_arrive(zeps_empty);
+        mbar_arrive(&zeps_empty[zb]);
         }
       }
     }
@@ -312,7 +323,7 @@ static int make_rows_map(CUtensorMap* map, const void* base, bool bf16, int64_t 
   return NES_OK;
 }
 
-struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows, stages, row_bytes; size_t smem; };
+struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows, stages, zbufs, row_bytes; size_t smem; };
 
 // Shapes the kernel covers; on failure the message says which rule was broken.
 static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what) {
@@ -329,12 +340,18 @@ static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, in
   pl.stage_rows = (CP_N + (kh - 1) * W + (kw - 1) + 15) & ~15;      // whole swizzle atoms (8 rows) at either row size
   NES_REQUIRE(pl.stage_rows <= 256, NES_ERR_UNSUPPORTED, "%s: filter reach too large for one staged image", what);
   pl.row_bytes = bf16 ? 64 : 128;
-  const size_t fixed = 1024 + size_t(pl.taps) * CP_M * pl.row_bytes + size_t(CP_N) * CP_HALF * 4 + 256;
+  const size_t zbytes = size_t(CP_N) * CP_HALF * 4;
+  const size_t fixed = 1024 + size_t(pl.taps) * CP_M * pl.row_bytes + zbytes + 256;
   const size_t stage = size_t(pl.stage_rows) * pl.row_bytes;
-  NES_REQUIRE(fixed + 2 * stage <= 227 * 1024, NES_ERR_UNSUPPORTED, "%s: %d filter taps do not fit shared memory", what, pl.taps);
-  pl.stages = int((227 * 1024 - fixed) / stage);
+  const size_t limit = 227 * 1024;
+  NES_REQUIRE(fixed + 2 * stage <= limit, NES_ERR_UNSUPPORTED, "%s: %d filter taps do not fit shared memory", what, pl.taps);
+  // a second buffer for the eps rows (lets their copy for the next image overlap this image's pooling) when
+  // it still leaves room for three staged images
+  pl.zbufs = (fixed + zbytes + 3 * stage <= limit) ? 2 : 1;
+  const size_t base = fixed + (pl.zbufs - 1) * zbytes;
+  pl.stages = int((limit - base) / stage);
   if (pl.stages > CP_MAX_STAGES) pl.stages = CP_MAX_STAGES;
-  pl.smem = fixed + size_t(pl.stages) * stage;
+  pl.smem = base + size_t(pl.stages) * stage;
   return NES_OK;
 }
 
@@ -366,7 +383,7 @@ static int run_conv_pool(const void* x_nhwc, const float* weight, const float* b
   p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
   p.B = B; p.D = D; p.R = R;
   p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = pl.Hp; p.Wp = pl.Wp;
-  p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.stages = pl.stages; p.antithetic = antithetic;
+  p.rows_per_image = H * W; p.stage_rows = pl.stage_rows; p.stages = pl.stages; p.zbufs = pl.zbufs; p.antithetic = antithetic;
   // compile-time geometry for 13x13 inputs pooled to 5x5 (3x3 filters on the 13x13 maps of the small MNIST
   // network); every other covered shape takes the runtime-indexed form
   const bool fixed = (W == 13 && pl.Hp == 5 && pl.Wp == 5);
