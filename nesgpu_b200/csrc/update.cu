@@ -134,20 +134,53 @@ __global__ void grad_from_out_hist_kernel(const float* __restrict__ G, const flo
 }
 
 // grad[k,m,t] = sum_j eps[k,j,t] * H[j,m]      (in-only)
-__global__ void grad_from_in_hist_kernel(const float* __restrict__ H, const float* __restrict__ eps,
-                                         float* __restrict__ grad, int in, int in_sp, int ksz) {
+// A block owns 128 columns m and HG_ROWS consecutive rows q = k*ksz + t; eps for those rows goes through
+// shared memory in chunks of HG_CHUNK values of j, so every H element loaded feeds HG_ROWS products.
+constexpr int HG_ROWS = 8, HG_CHUNK = 256;
+
+__global__ void __launch_bounds__(128) grad_from_in_hist_kernel(const float* __restrict__ H, const float* __restrict__ eps,
+                                                                float* __restrict__ grad, int in, int in_sp, int ksz, int rows) {
+  __shared__ __align__(16) float es[HG_CHUNK][HG_ROWS];
   const int m = blockIdx.x * blockDim.x + threadIdx.x;
-  const int k = blockIdx.y / ksz, t = blockIdx.y - k * ksz;
-  if (m >= in) return;
-  const float* er = eps + size_t(k) * in_sp * ksz + t;
-  float a0 = 0.f, a1 = 0.f;
-  int j = 0;
-  for (; j + 2 <= in_sp; j += 2) {
-    a0 = fmaf(__ldg(er + size_t(j) * ksz), __ldg(H + size_t(j) * in + m), a0);
-    a1 = fmaf(__ldg(er + size_t(j + 1) * ksz), __ldg(H + size_t(j + 1) * in + m), a1);
+  const int q0 = blockIdx.y * HG_ROWS;
+  float a[HG_ROWS];
+#pragma unroll
+  for (int u = 0; u < HG_ROWS; ++u) a[u] = 0.f;
+  for (int j0 = 0; j0 < in_sp; j0 += HG_CHUNK) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < HG_CHUNK * HG_ROWS; e += blockDim.x) {
+      const int jj = e / HG_ROWS, u = e - jj * HG_ROWS;
+      const int q = q0 + u, j = j0 + jj;
+      float v = 0.f;
+      if (q < rows && j < in_sp) {
+        const int k = q / ksz, t = q - k * ksz;
+        v = __ldg(eps + (size_t(k) * in_sp + j) * ksz + t);
+      }
+      es[jj][u] = v;
+    }
+    __syncthreads();
+    if (m < in) {
+      const int lim = (in_sp - j0 < HG_CHUNK) ? in_sp - j0 : HG_CHUNK;
+      const float* hp = H + size_t(j0) * in + m;
+#pragma unroll 4
+      for (int jj = 0; jj < lim; ++jj) {
+        const float h = __ldg(hp + size_t(jj) * in);
+        const float4 e0 = *reinterpret_cast<const float4*>(&es[jj][0]);
+        const float4 e1 = *reinterpret_cast<const float4*>(&es[jj][4]);
+        a[0] = fmaf(e0.x, h, a[0]); a[1] = fmaf(e0.y, h, a[1]); a[2] = fmaf(e0.z, h, a[2]); a[3] = fmaf(e0.w, h, a[3]);
+        a[4] = fmaf(e1.x, h, a[4]); a[5] = fmaf(e1.y, h, a[5]); a[6] = fmaf(e1.z, h, a[6]); a[7] = fmaf(e1.w, h, a[7]);
+      }
+    }
   }
-  for (; j < in_sp; ++j) a0 = fmaf(__ldg(er + size_t(j) * ksz), __ldg(H + size_t(j) * in + m), a0);
-  grad[(size_t(k) * in + m) * ksz + t] = a0 + a1;
+  if (m >= in) return;
+#pragma unroll
+  for (int u = 0; u < HG_ROWS; ++u) {
+    const int q = q0 + u;
+    if (q < rows) {
+      const int k = q / ksz, t = q - k * ksz;
+      grad[(size_t(k) * in + m) * ksz + t] = a[u];
+    }
+  }
 }
 
 // both: grad[k, pin[d,j], t] += w_d * eps[pout[d,k], j, t]
@@ -354,8 +387,8 @@ extern "C" int nes_permuted_update(const float* eps, const float* w, const int16
       rc = check_launch("permuted_update(histogram)");
       if (rc != NES_OK) return rc;
     }
-    dim3 grid((unsigned)ceil_div(in, 128), (unsigned)(out * ksize));
-    grad_from_in_hist_kernel<<<grid, 128, 0, st>>>(hist, eps, grad, in, in_sp, ksize);
+    dim3 grid((unsigned)ceil_div(in, 128), (unsigned)ceil_div(out * ksize, HG_ROWS));
+    grad_from_in_hist_kernel<<<grid, 128, 0, st>>>(hist, eps, grad, in, in_sp, ksize, out * ksize);
     rc = check_launch("permuted_update(grad)");
     if (rc != NES_OK) return rc;
     if (perm_weights_out) cudaMemcpyAsync(perm_weights_out, hist, hn * sizeof(float), cudaMemcpyDeviceToDevice, st);
