@@ -546,7 +546,7 @@ class EsCnn(Workload):
                 "step": "set_noise + chunked population forward + CE fitness + centred ranks + update (+ all-gather / all-reduce at N>1)",
                 "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02, "fused_layers": self.fused,
                 "precision": {None: "tf32", "tf32": "tf32 operands, fp32 accumulation (stated mode, rel err ~1e-3 per layer)",
-                              "bf16": "bf16 operands in conv2 (rel err ~3e-3), tf32 in the linear layers, fp32 accumulation (stated mode)"}.get(self.tc, self.tc)}
+                              "bf16": "bf16 operands in conv2 and the linear layers (rel err ~3e-3 per layer), fp32 accumulation (stated mode)"}.get(self.tc, self.tc)}
 
     def setup(self, dev, rank, world):
         from nesgpu_b200 import base, es
@@ -557,7 +557,7 @@ class EsCnn(Workload):
             self.tc = "tf32"       # default for this workload: the stated TF32 tensor-core mode (--tc fp32 for CUDA cores)
         self.dtype = {"tf32": "tf32", "bf16": "bf16"}.get(self.tc, "f32")
         opts = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}
-        lin = {"tc": "tf32"} if self.tc in ("tf32", "bf16") else {}   # the stated reduced-precision modes cover the linear layers (TF32)
+        lin = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}  # the stated reduced-precision modes cover the linear layers
         if self.fused:
             # Conv -> ReLU -> MaxPool2 blocks as fused layers; the first one is told that the images are shared
             o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": self.tc if opts else "fp32"}

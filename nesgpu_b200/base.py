@@ -461,19 +461,20 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
     SINGLE_PRODUCT_MIN_ROWS = 64 * 128
 
     def _single_product_mode(self, rows, pout):
-        """Mode (1 = TF32, 3 = 3xTF32) of the one-product tensor-core forward, or 0 for the CUDA-core kernels.
+        """Mode (1 = TF32, 2 = bf16, 3 = 3xTF32) of the one-product tensor-core forward, or 0 for the CUDA-core
+        kernels.
 
-        ``options["tc"]``: ``"3xtf32"`` / ``"tf32"`` force it, ``"fp32"`` forbids it; by default ("auto") the
+        ``options["tc"]``: ``"3xtf32"`` / ``"tf32"`` / ``"bf16"`` force it, ``"fp32"`` forbids it; by default ("auto") the
         error-compensated 3xTF32 form (fp32-level accuracy) is taken for batches of at least
         ``SINGLE_PRODUCT_MIN_ROWS`` rows.  It needs a layer without output permutations."""
         mode = self.options.get("tc", "auto")
-        if mode not in ("auto", "fp32", "3xtf32", "tf32"):
-            raise NotImplementedError('options["tc"] must be "auto", "3xtf32", "tf32" or "fp32"')
+        if mode not in ("auto", "fp32", "3xtf32", "tf32", "bf16"):
+            raise NotImplementedError('options["tc"] must be "auto", "3xtf32", "tf32", "bf16" or "fp32"')
         if mode == "fp32" or pout is not None or rows == 0:
             return 0
         if mode == "auto":
             return 3 if rows >= self.SINGLE_PRODUCT_MIN_ROWS else 0
-        return _TC_MODES[mode]
+        return {"3xtf32": 3, "tf32": 1, "bf16": 2}[mode]
 
     def forward(self, input):
         if not self.perturbed_flag:

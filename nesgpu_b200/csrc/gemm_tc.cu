@@ -9,6 +9,7 @@
 //   * tcgen05.commit hands shared-memory stages back to the producer and signals the epilogue;
 //   * four epilogue warps read the accumulator with tcgen05.ld (one TMEM lane = one output
 //     row per thread), add the bias and store.
+// With BF16 the operands are bf16 (64 elements per 128-byte row, kind::f16 with K = 16, TERMS = 1 only).
 // Precision modes: TERMS = 1 is plain TF32 (inputs rounded to 10 mantissa bits; relative error
 // ~1e-3, for callers that state it).  TERMS = 3 is the error-compensated 3xTF32 scheme: every
 // operand is split beforehand into hi = tf32(a) and lo = a - hi, and the kernel accumulates
@@ -17,6 +18,7 @@
 // Every wait on an mbarrier is bounded: when the limit is hit the thread records an error code
 // in a device word (read by nes_tc_error_flag), stops issuing work and falls through to the
 // common exit, where tensor memory is released.
+#include <cuda_bf16.h>
 #include "tc_ptx.cuh"
 
 namespace nes {
@@ -32,7 +34,7 @@ struct Maps { CUtensorMap a_hi, b_hi, a_lo, b_lo; };
 // repeat gm / D, and receives sign(repeat) * bias_noise[member, column].
 struct RowTerm { const float* bias_noise; int64_t D, R; int antithetic; };
 
-template <int TERMS>
+template <int TERMS, bool BF16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_constant__ Maps maps, const float* __restrict__ bias,
                                                                  const RowTerm rt, float* __restrict__ C, int M, int N, int K, int stages) {
   extern __shared__ unsigned char dyn_raw[];
@@ -49,7 +51,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int nk = (K + BKE - 1) / BKE;
+  constexpr int BKS = BF16 ? 2 * BKE : BKE;          // K elements per stage (one 128-byte row)
+  const int nk = (K + BKS - 1) / BKS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -71,18 +74,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
         if (!mbar_wait(&empty[s], ph ^ 1, 1)) break;
         unsigned char* st = tiles + size_t(s) * STAGE_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
-        tma_load_2d(st, &maps.a_hi, &full[s], kt * BKE, m0);
-        tma_load_2d(st + TILE_BYTES, &maps.b_hi, &full[s], kt * BKE, n0);
+        tma_load_2d(st, &maps.a_hi, &full[s], kt * BKS, m0);
+        tma_load_2d(st + TILE_BYTES, &maps.b_hi, &full[s], kt * BKS, n0);
         if (TERMS == 3) {
-          tma_load_2d(st + 2 * TILE_BYTES, &maps.a_lo, &full[s], kt * BKE, m0);
-          tma_load_2d(st + 3 * TILE_BYTES, &maps.b_lo, &full[s], kt * BKE, n0);
+          tma_load_2d(st + 2 * TILE_BYTES, &maps.a_lo, &full[s], kt * BKS, m0);
+          tma_load_2d(st + 3 * TILE_BYTES, &maps.b_lo, &full[s], kt * BKS, n0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer
-      constexpr uint32_t idesc = idesc_tf32(BM, BN);
+      constexpr uint32_t idesc = BF16 ? idesc_bf16(BM, BN) : idesc_tf32(BM, BN);
       bool ok = true;
       for (int kt = 0; kt < nk && ok; ++kt) {
         const int s = kt % stages;
@@ -100,6 +103,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
             mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
             mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
             mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+          } else if (BF16) {
+            mma_bf16(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           } else {
             mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           }
@@ -179,6 +184,7 @@ __global__ void split_tf32_kernel(const float* __restrict__ src, float* __restri
 // Operand of the permuted layer's single product: row b of A2 is [ x[b, :] | s(b) * x[b, pin[d, :]] | 0.. ],
 // rounded to tf32 (hi) with the residual kept (lo) for the 3-term scheme.  One block per row; the row is
 // read once coalesced, the gather then hits it in L1/L2.
+template <bool BF16>
 __global__ void __launch_bounds__(256) permuted_operand_kernel(const float* __restrict__ x, const int16_t* __restrict__ pin,
                                                                float* __restrict__ hi, float* __restrict__ lo,
                                                                int64_t B, int64_t D, int64_t R, int in, int in_sp, int K2,
@@ -192,14 +198,19 @@ __global__ void __launch_bounds__(256) permuted_operand_kernel(const float* __re
       float a = 0.f;
       if (k < in) a = xr[k];
       else if (k < in + in_sp) a = sgn * xr[pr ? int(pr[k - in]) : k - in];
-      const float h = round_tf32(a);
-      hi[b * K2 + k] = h;
-      if (lo) lo[b * K2 + k] = a - h;
+      if (BF16) {
+        reinterpret_cast<__nv_bfloat16*>(hi)[b * K2 + k] = __float2bfloat16_rn(a);
+      } else {
+        const float h = round_tf32(a);
+        hi[b * K2 + k] = h;
+        if (lo) lo[b * K2 + k] = a - h;
+      }
     }
   }
 }
 
 // B2[o, :] = [ weight[o, :] | eps[o, :] (rows below out_sp, else 0) | 0.. ]
+template <bool BF16>
 __global__ void permuted_filter_kernel(const float* __restrict__ w, const float* __restrict__ eps,
                                        float* __restrict__ hi, float* __restrict__ lo, int64_t out, int64_t out_sp,
                                        int in, int in_sp, int K2) {
@@ -210,20 +221,25 @@ __global__ void permuted_filter_kernel(const float* __restrict__ w, const float*
   float a = 0.f;
   if (k < in) a = w[o * in + k];
   else if (k < in + in_sp && o < out_sp) a = eps[o * in_sp + (k - in)];
-  const float h = round_tf32(a);
-  hi[i] = h;
-  if (lo) lo[i] = a - h;
+  if (BF16) {
+    reinterpret_cast<__nv_bfloat16*>(hi)[i] = __float2bfloat16_rn(a);
+  } else {
+    const float h = round_tf32(a);
+    hi[i] = h;
+    if (lo) lo[i] = a - h;
+  }
 }
 
 // 2-D fp32 row-major [rows][cols] tensor, box = 32 columns x box_rows rows, 128-byte swizzle, zero fill
-static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows, const char* what) {
+static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows, const char* what,
+                    bool bf16 = false) {
   EncodeTiledFn fn = encode_fn();
   NES_REQUIRE(fn != nullptr, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(float)};
-  cuuint32_t box[2] = {(cuuint32_t)BKE, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * (bf16 ? 2 : 4)};
+  cuuint32_t box[2] = {(cuuint32_t)(bf16 ? 2 * BKE : BKE), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NES_REQUIRE(r == CUDA_SUCCESS, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
@@ -237,8 +253,9 @@ static int run_gemm(const float* a_hi, const float* a_lo, const float* b_hi, con
                     const RowTerm& rt, float* y, int64_t M, int64_t N, int64_t K, int mode, cudaStream_t st, const char* what) {
   int rc;
   Maps maps;
-  if ((rc = make_map(&maps.a_hi, a_hi, M, K, BM, what)) != NES_OK) return rc;
-  if ((rc = make_map(&maps.b_hi, b_hi, N, K, BN, what)) != NES_OK) return rc;
+  const bool bf16 = (mode == 2);
+  if ((rc = make_map(&maps.a_hi, a_hi, M, K, BM, what, bf16)) != NES_OK) return rc;
+  if ((rc = make_map(&maps.b_hi, b_hi, N, K, BN, what, bf16)) != NES_OK) return rc;
   if (mode == 3) {
     if ((rc = make_map(&maps.a_lo, a_lo, M, K, BM, what)) != NES_OK) return rc;
     if ((rc = make_map(&maps.b_lo, b_lo, N, K, BN, what)) != NES_OK) return rc;
@@ -255,6 +272,10 @@ static int run_gemm(const float* a_hi, const float* a_lo, const float* b_hi, con
     e = cudaFuncSetAttribute(gemm_tf32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
     gemm_tf32_kernel<3><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
+  } else if (bf16) {
+    e = cudaFuncSetAttribute(gemm_tf32_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+    gemm_tf32_kernel<1, true><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
   } else {
     e = cudaFuncSetAttribute(gemm_tf32_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
@@ -307,12 +328,16 @@ extern "C" int nes_linear_fwd_tc(const float* x, const float* weight, const floa
   return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, none, y, M, N, K, mode, st, "linear_fwd_tc");
 }
 
-static int64_t permuted_k2(int64_t in, int64_t in_sp) { return (in + in_sp + 3) & ~int64_t(3); }
+// row length of the concatenated operand: a multiple of 16 bytes (4 fp32 / 8 bf16)
+static int64_t permuted_k2(int64_t in, int64_t in_sp, int mode) {
+  return mode == 2 ? ((in + in_sp + 7) & ~int64_t(7)) : ((in + in_sp + 3) & ~int64_t(3));
+}
 
 extern "C" int64_t nes_permuted_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out, int64_t in_sp, int mode) {
   if (D <= 0 || R <= 0 || out <= 0 || in < 0 || in_sp < 0) return 0;
-  const int64_t K2 = permuted_k2(in, in_sp);
-  const int64_t a = align256(D * R * K2 * 4), b = align256(out * K2 * 4);
+  const int64_t K2 = permuted_k2(in, in_sp, mode);
+  const int64_t esz = mode == 2 ? 2 : 4;
+  const int64_t a = align256(D * R * K2 * esz), b = align256(out * K2 * esz);
   return mode == 3 ? 2 * (a + b) : (a + b);
 }
 
@@ -323,12 +348,12 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
                                           nes_stream_t stream) {
   NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0 && in_sp >= 0 && out_sp >= 0 && out_sp <= out, NES_ERR_BAD_ARG,
               "permuted_linear_fwd_tc: bad extent");
-  NES_REQUIRE(mode == 1 || mode == 3, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: mode must be 1 (TF32) or 3 (3xTF32)");
+  NES_REQUIRE(mode == 1 || mode == 2 || mode == 3, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: mode must be 1 (TF32), 2 (bf16) or 3 (3xTF32)");
   if (D == 0 || R == 0 || out == 0) return NES_OK;
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: null pointer");
   NES_REQUIRE(pin || in_sp == in, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: in_sp != in without input permutations");
   NES_REQUIRE(in > 0 && in <= 32767 && in_sp <= INT32_MAX - in, NES_ERR_UNSUPPORTED, "permuted_linear_fwd_tc: in=%lld out of range", (long long)in);
-  const int64_t B = D * R, K2 = permuted_k2(in, in_sp);
+  const int64_t B = D * R, K2 = permuted_k2(in, in_sp, mode);
   NES_REQUIRE(B <= INT32_MAX && out <= INT32_MAX && K2 <= INT32_MAX && ceil_div<int64_t>(out, BN) <= 65535, NES_ERR_UNSUPPORTED,
               "permuted_linear_fwd_tc: extent too large");
   const int64_t need = nes_permuted_linear_fwd_tc_scratch_bytes(D, R, in, out, in_sp, mode);
@@ -336,16 +361,20 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
               "permuted_linear_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)need);
   cudaStream_t st = as_stream(stream);
   unsigned char* sp = static_cast<unsigned char*>(scratch);
-  const int64_t a_bytes = align256(B * K2 * 4), b_bytes = align256(out * K2 * 4);
+  const int64_t esz = mode == 2 ? 2 : 4;
+  const int64_t a_bytes = align256(B * K2 * esz), b_bytes = align256(out * K2 * esz);
   float* a_hi = reinterpret_cast<float*>(sp);
   float* b_hi = reinterpret_cast<float*>(sp + a_bytes);
   float* a_lo = mode == 3 ? reinterpret_cast<float*>(sp + a_bytes + b_bytes) : nullptr;
   float* b_lo = mode == 3 ? reinterpret_cast<float*>(sp + 2 * a_bytes + b_bytes) : nullptr;
   const unsigned blocks = (unsigned)(B < int64_t(sm_count()) * 16 ? B : int64_t(sm_count()) * 16);
-  permuted_operand_kernel<<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
+  const unsigned fblocks = (unsigned)ceil_div<int64_t>(out * K2, 256);
+  if (mode == 2) permuted_operand_kernel<true><<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
+  else permuted_operand_kernel<false><<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
   int rc = check_launch("permuted_linear_fwd_tc(operand)");
   if (rc != NES_OK) return rc;
-  permuted_filter_kernel<<<(unsigned)ceil_div<int64_t>(out * K2, 256), 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
+  if (mode == 2) permuted_filter_kernel<true><<<fblocks, 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
+  else permuted_filter_kernel<false><<<fblocks, 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
   rc = check_launch("permuted_linear_fwd_tc(filter)");
   if (rc != NES_OK) return rc;
   const RowTerm rt = {bias_noise, D, R, antithetic};
