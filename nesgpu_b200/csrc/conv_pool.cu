@@ -78,13 +78,16 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
       const float b00 = base[p00], b01 = base[p00 + 1], b10 = base[p00 + Wo], b11 = base[p00 + Wo + 1];
       out_t* o = y + ((r * D + d0) * pooled + pp) * Cout + c;
       const float* np = nmaps + p00 * npitch;
+      const int16_t* sp = so_tab + cc;               // this channel's column of the member tables
+      const float2* tp = tab + cc;
+      const int o1 = npitch, o2 = row, o3 = row + npitch;
 #pragma unroll 4
-      for (int m = 0; m < nm; ++m, o += member_stride) {
+      for (int m = 0; m < nm; ++m, o += member_stride, sp += Cout, tp += Cout) {
         // the 32 channels of a member point at 32 different noise maps = 32 different banks
-        const float* n = np + int(so_tab[m * Cout + cc]);
-        const float2 t = tab[m * Cout + cc];
-        const out_t v = pool_value<MODE>(fmaf(t.x, n[0], b00), fmaf(t.x, n[npitch], b01), fmaf(t.x, n[row], b10),
-                                         fmaf(t.x, n[row + npitch], b11), t.y);
+        const float* n = np + int(*sp);
+        const float2 t = *tp;
+        const out_t v = pool_value<MODE>(fmaf(t.x, n[0], b00), fmaf(t.x, n[o1], b01), fmaf(t.x, n[o2], b10),
+                                         fmaf(t.x, n[o3], b11), t.y);
         if (live) *o = v;
       }
     }
