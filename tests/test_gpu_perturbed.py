@@ -506,3 +506,27 @@ def test_fuse_option_falls_back_to_separate_kernels(base):
         y = layer.forward(G(x))
     want = O.permuted_conv2d_forward(x, W, b, eps, beta, pin, None, D, 1, 0, 1, False)
     assert_close(y, torch.nn.functional.max_pool2d(torch.relu(want), 2), what="forward")
+
+
+def test_fused_layer_edge_cases(base):
+    """Empty batches pass through the fused layers; an unknown fuse option is refused."""
+    D = 4
+    shared = base.PermutedConv2d(1, 8, 3, D, permutation="out", options={"shared_input": True, "fuse": "relu_maxpool2"}).to(DEV)
+    shared.allocate_memory()
+    shared.set_seed(3)
+    shared.set_noise(0.02)
+    shared.perturbed_flag = True
+    with torch.no_grad():
+        y = shared.forward(torch.zeros(0, 1, 10, 10, device=DEV))
+    assert tuple(y.shape) == (0, 8, 4, 4)
+    tc = base.PermutedConv2d(32, 16, 3, D, permutation="out", options={"tc": "tf32", "fuse": "relu_maxpool2"}).to(DEV)
+    tc.allocate_memory()
+    tc.set_seed(4)
+    tc.set_noise(0.02)
+    tc.perturbed_flag = True
+    with torch.no_grad():
+        y = tc.forward(torch.zeros(0, 32, 13, 13, device=DEV))
+    assert tuple(y.shape) == (0, 16, 5, 5)
+    bad = base.PermutedConv2d(1, 8, 3, D, options={"fuse": "relu"}).to(DEV)
+    with pytest.raises(NotImplementedError):
+        bad.forward(torch.zeros(D, 1, 10, 10, device=DEV))
