@@ -707,7 +707,7 @@ def run_reference(args, rank, world):
             "e2e": {"value": round(value, 2), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
             "note": "CPU restatement (oracle/) of the reference's algorithm on the host cores; the reference itself is "
-                    "Python over /root/reference, which does not exist on the GPU box; each step is the bounded sample"}
+                    "a Python tree without a package, and no checkout of it exists on the GPU box; each step is the bounded sample"}
     print(json.dumps(line), flush=True)
 
 

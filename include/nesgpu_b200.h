@@ -113,7 +113,7 @@ int nes_perturbed_update(const float* noise, const float* w, const float* weight
  * reference: there the reduction is one library GEMV that allocates whatever it likes.)
  *
  * Some hosts of this library own no device allocator of their own: a plug-in that is handed
- * input and output buffers by a runtime with a fixed memory budget, or a step that runs at a
+ * input and output buffers by a runtime that owns all device memory, or a step that runs at a
  * point where the process must not create device memory.  They cannot size and provide the
  * `scratch` buffer of nes_perturbed_update, so this variant keeps the split partial sums in a
  * workspace built into the library: NES_NOALLOC_SCRATCH_FLOATS fp32 values (16 MiB) of device

@@ -1,9 +1,9 @@
 """Generates the golden vectors under tests/golden/ from the reference itself.
 
-Run once, in a container where the reference checkout is mounted (pass its root as the
-first argument, default ``/root/reference``):
+Run once, where a checkout of the reference is available; pass its root as the first argument (or set
+``NES_REFERENCE_ROOT``):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <reference checkout>
 
 fp32 layers: the reference's own ``modules/base.py`` is imported on CPU, its layers are
 constructed at small shapes, the noise / permutation tensors are assigned (bypassing
@@ -283,7 +283,9 @@ def binary_cases():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NES_REFERENCE_ROOT")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("usage: make_golden.py <reference checkout>  (or set NES_REFERENCE_ROOT)")
     sys.path.insert(0, ref_root)
     import modules.base as base   # the reference's own file
     torch.manual_seed(0)

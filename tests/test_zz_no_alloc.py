@@ -1,7 +1,7 @@
 """The workspace-free variant of the fitness-weighted noise sum, called through the C ABI.
 
 ``nes_perturbed_update_noalloc`` is for hosts that can pass inputs and outputs but own no
-device allocator (a plug-in inside a runtime with a fixed memory budget, a step that runs
+device allocator (a plug-in inside a runtime that owns all device memory, a step that runs
 where device memory must not be created): its partial sums live in a 16 MiB workspace built
 into the library instead of a caller-provided ``scratch`` buffer.  The test calls it twice in
 a row with different inputs -- the workspace keeps the first call's contents, so a stale read
