@@ -560,7 +560,10 @@ class EsCnn(Workload):
         lin = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}  # the stated reduced-precision modes cover the linear layers
         if self.fused:
             # Conv -> ReLU -> MaxPool2 blocks as fused layers; the first one is told that the images are shared
-            o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": self.tc if opts else "fp32"}
+            pair = self.tc == "bf16" and D % 2 == 0          # two images per tensor-core instruction in layer 2
+            o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": "bf16x2" if pair else (self.tc if opts else "fp32")}
+            if pair:
+                opts = dict(opts, in_layout="bf16x2")
             self.net = torch.nn.Sequential(
                 base.PermutedConv2d(1, 32, 3, D, options=o1),
                 base.PermutedConv2d(32, 64, 3, D, options=dict(opts, fuse="relu_maxpool2")), torch.nn.Flatten(),

@@ -188,7 +188,8 @@ int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float*
  *   y[b, py, px, c] = relu(max_{2x2}( z[r, c] + s(r) * z[r, Cout + pout[d,c]] ) + bias[c] + s(r) * bias_noise[d,c])
  * with the noise term dropped where pout[d,c] >= out_sp (pout == NULL: identity).  y is channels-last,
  * (R*D, Ho/2, Wo/2, Cout); out_mode 0 stores fp32, 1 fp32 rounded to TF32, 2 bf16 (for a tensor-core
- * consumer).
+ * consumer), 3 bf16 with images 2q and 2q+1 interleaved by pixel, (R*D/2, Ho/2, Wo/2, 2, Cout), the input
+ * layout of nes_permuted_conv_pool_fwd_bf16x2 (D even).
  * Replaces, for this case, PermutedConv2d.forward (modules/base.py:557-588) followed by the ReLU and
  * MaxPool2d modules of the reference's models (models/mnistmodels.py:35-57). */
 int nes_shared_conv_pool_fwd(const float* z, const float* bias, const float* bias_noise,
@@ -219,6 +220,16 @@ int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const float* weight
                                     float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,
                                     int kh, int kw, int out_sp, int antithetic,
                                     void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* The bf16 form with TWO images per MMA (N = 256; such an MMA takes hardly longer than one with N = 128).
+ * x_pairs_bf16 (R*D/2, H, W, 2, 32) bf16: images 2q and 2q+1 interleaved by pixel (out_mode 3 of
+ * nes_shared_conv_pool_fwd).  Covered: Cin == 32, 13x13 images, 3x3 filters, Cout <= 64, R*D even.
+ * y, scratch and everything else as for nes_permuted_conv_pool_fwd_bf16. */
+int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const float* weight, const float* bias,
+                                      const float* eps, const float* bias_noise, const int16_t* pout,
+                                      float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                      int kh, int kw, int out_sp, int antithetic,
+                                      void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
 /* PermutedConv2d.forward, default branch (modules/base.py:557-588), evaluated as one
  * convolution per member with the effective filter

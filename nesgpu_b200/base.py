@@ -618,7 +618,9 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         output permutations only, the two convolutions ``conv(x, W)`` and ``conv(x, eps)`` are computed once
         per image and the per-member work is a fused gather + add + ReLU + pool; the result is a
         channels-last tensor (``options["out_dtype"]`` = ``"tf32"`` rounds it to TF32, ``"bf16"`` stores bf16, for a
-        tensor-core consumer)."""
+        tensor-core consumer; ``"bf16x2"`` stores bf16 with images 2q and 2q+1 interleaved by pixel, shape
+        ``(R * directions / 2, 2 * C, H, W)``, which a following layer takes with ``options["in_layout"] =
+        "bf16x2"`` to put two images into every tensor-core instruction)."""
         fuse = self.options.get("fuse")
         if fuse not in (None, "relu_maxpool2"):
             raise NotImplementedError('options["fuse"] must be "relu_maxpool2"')
@@ -659,12 +661,18 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         out = self.options.get("out_dtype", "fp32")
         if self.options.get("out_tf32"):
             out = "tf32"
-        if out not in ("fp32", "tf32", "bf16"):
-            raise NotImplementedError('options["out_dtype"] must be "fp32", "tf32" or "bf16"')
+        if out not in ("fp32", "tf32", "bf16", "bf16x2"):
+            raise NotImplementedError('options["out_dtype"] must be "fp32", "tf32", "bf16" or "bf16x2"')
+        if out == "bf16x2" and D % 2:
+            raise NotImplementedError('options["out_dtype"] = "bf16x2" needs an even number of directions')
         y = torch.empty((R * D, Ho // 2, Wo // 2, cout), device=x.device,
-                        dtype=torch.bfloat16 if out == "bf16" else _F32)
+                        dtype=_F32 if out in ("fp32", "tf32") else torch.bfloat16)
         C.call("nes_shared_conv_pool_fwd", C.ptr(z), C.ptr(_opt(self.bias)), C.ptr(beta), C.ptr(pout), C.ptr(y),
-               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, {"fp32": 0, "tf32": 1, "bf16": 2}[out], C.stream())
+               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, {"fp32": 0, "tf32": 1, "bf16": 2, "bf16x2": 3}[out],
+               C.stream())
+        if out == "bf16x2":
+            # images 2q and 2q+1 interleaved by pixel: a channels-last tensor of R*D/2 "double" images
+            return y.view(R * D // 2, Ho // 2, Wo // 2, 2 * cout).permute(0, 3, 1, 2)
         return y.permute(0, 3, 1, 2)
 
     def _fused_tc_forward(self, input):
@@ -672,6 +680,8 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         only, 32 input channels, stride 1 / no padding, one image per 128-column accumulator).  Takes the
         input channels-last without a copy.  Returns None when the case is not covered."""
         mode = self.options.get("tc")
+        if self.options.get("in_layout") == "bf16x2":
+            return self._fused_pair_forward(input)
         if mode not in ("tf32", "bf16") or self.options.get("allow_repeats") or self.groups != 1:
             return None
         pin, pout = self._perms()
@@ -705,6 +715,35 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         C.call("nes_permuted_conv_pool_fwd_" + ("bf16" if mode == "bf16" else "tc"), C.ptr(x), C.ptr(_opt(self.weight)),
                C.ptr(_opt(self.bias)), C.ptr(eps),
                C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, H, W, self.out_channels, kh, kw,
+               self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
+        return y
+
+    def _fused_pair_forward(self, input):
+        """The bf16 fused kernel with two images per tensor-core instruction: ``input`` is the ``"bf16x2"`` output of
+        a shared-input layer, ``(B / 2, 64, 13, 13)`` bf16 channels-last.  No other form of this layer can read that
+        layout, so an uncovered case is an error."""
+        pin, pout = self._perms()
+        ok = (self.options.get("tc") == "bf16" and pin is None and not self.options.get("allow_repeats")
+              and self.groups == 1 and self.in_channels == 32 and self.out_channels <= 64 and self.out_sparsity <= 64
+              and tuple(self.kernel_size) == (3, 3) and _pair(self.stride) == (1, 1) and _pair(self.dilation) == (1, 1)
+              and self.padding_mode == "zeros" and _pair(self.padding) == (0, 0)
+              and isinstance(input, torch.Tensor) and input.is_cuda and input.dtype == torch.bfloat16
+              and input.dim() == 4 and tuple(input.shape[1:]) == (64, 13, 13))
+        if not ok:
+            raise NotImplementedError('options["in_layout"] = "bf16x2" needs options["tc"] = "bf16", output permutations '
+                                      'only, 32 -> <= 64 channels, 3x3 filters and a (B/2, 64, 13, 13) bf16 input')
+        x = input.permute(0, 2, 3, 1)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        B = 2 * input.shape[0]
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        R = self._repeats(B)
+        y = torch.empty((B, self.out_channels, 5, 5), device=x.device, dtype=_F32)
+        nbytes = C.call("nes_permuted_conv_pool_fwd_tc_scratch_bytes", 3, 3)
+        buf = C.scratch(nbytes, x.device)
+        C.call("nes_permuted_conv_pool_fwd_bf16x2", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+               C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, 13, 13, self.out_channels, 3, 3,
                self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes, C.stream())
         return y
 

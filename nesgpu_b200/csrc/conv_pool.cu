@@ -20,14 +20,15 @@ __device__ inline float round_to_tf32(float a) {
   return __uint_as_float(u & 0xFFFFE000u);
 }
 
-// MODE: 0 = fp32, 1 = fp32 rounded to TF32, 2 = bf16
+// MODE: 0 = fp32, 1 = fp32 rounded to TF32, 2 = bf16, 3 = bf16 with image pairs interleaved by pixel
 template <int MODE> struct OutType { typedef float type; };
 template <> struct OutType<2> { typedef __nv_bfloat16 type; };
+template <> struct OutType<3> { typedef __nv_bfloat16 type; };
 
 template <int MODE>
 __device__ __forceinline__ typename OutType<MODE>::type pool_value(float a0, float a1, float a2, float a3, float add) {
   const float v = fmaxf(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) + add, 0.f);
-  if constexpr (MODE == 2) return __float2bfloat16_rn(v);
+  if constexpr (MODE >= 2) return __float2bfloat16_rn(v);
   else if constexpr (MODE == 1) return round_to_tf32(v);
   else return v;
 }
@@ -76,13 +77,16 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
       const int py = pp / Wp, px = pp - py * Wp;
       const int p00 = (2 * py) * Wo + 2 * px;
       const float b00 = base[p00], b01 = base[p00 + 1], b10 = base[p00 + Wo], b11 = base[p00 + Wo + 1];
-      out_t* o = y + ((r * D + d0) * pooled + pp) * Cout + c;
+      // MODE 3: images b = 2q and 2q + 1 share rows, [q][pooled pixel][image][channel]; d0 and D are even there
+      out_t* o = (MODE == 3) ? y + (((r * D + d0) / 2 * pooled + pp) * 2) * Cout + c
+                             : y + ((r * D + d0) * pooled + pp) * Cout + c;
       const float* np = nmaps + p00 * npitch;
       const int16_t* sp = so_tab + cc;               // this channel's column of the member tables
       const float2* tp = tab + cc;
       const int o1 = npitch, o2 = row, o3 = row + npitch;
 #pragma unroll 4
-      for (int m = 0; m < nm; ++m, o += member_stride, sp += Cout, tp += Cout) {
+      for (int m = 0; m < nm; ++m, o += ((MODE == 3) ? ((m & 1) ? int64_t(Cout) : 2 * member_stride - Cout) : member_stride),   // m: the member stepped to
+                                 sp += Cout, tp += Cout) {
         // the 32 channels of a member point at 32 different noise maps = 32 different banks
         const float* n = np + int(*sp);
         const float2 t = *tp;
@@ -104,7 +108,9 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   NES_REQUIRE(R >= 0 && D >= 0 && Cout >= 0 && out_sp >= 0 && Ho >= 0 && Wo >= 0, NES_ERR_BAD_ARG,
               "shared_conv_pool_fwd: negative extent");
   NES_REQUIRE(out_sp <= Cout, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: out_sp exceeds the channel count");
-  NES_REQUIRE(out_mode >= 0 && out_mode <= 2, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: out_mode must be 0 (fp32), 1 (tf32) or 2 (bf16)");
+  NES_REQUIRE(out_mode >= 0 && out_mode <= 3, NES_ERR_BAD_ARG,
+              "shared_conv_pool_fwd: out_mode must be 0 (fp32), 1 (tf32), 2 (bf16) or 3 (bf16, image pairs interleaved)");
+  NES_REQUIRE(out_mode != 3 || D % 2 == 0, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: the pair layout needs an even number of members");
   if (R == 0 || D == 0 || Cout == 0 || Ho < 2 || Wo < 2) return NES_OK;
   NES_REQUIRE(z && y, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: null pointer");
   NES_REQUIRE(R <= INT32_MAX && Cout <= 32767, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: extent too large");
@@ -128,7 +134,8 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
     if (cost < best_cost) { best_cost = cost; best_per = per_g; }
     if (blocks >= 4 * sms) break;
   }
-  const int per = int(best_per);
+  int per = int(best_per);
+  if (out_mode == 3 && (per & 1)) ++per;             // blocks start on even members
   const size_t smem = plane_bytes + size_t(per) * member_bytes + 16;
   dim3 grid((unsigned)R, (unsigned)ceil_div<int64_t>(D, per));
   cudaError_t e;
@@ -138,7 +145,8 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "shared_conv_pool_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); \
   shared_conv_pool_kernel<MODE><<<grid, CP_WARPS * 32, smem, st>>>(z, bias, bias_noise, pout, static_cast<T*>(y), R, D, Cout, out_sp, \
                                                                    Ho, Wo, antithetic, per)
-  if (out_mode == 2) { NES_LAUNCH_SHARED_CONV_POOL(2, __nv_bfloat16); }
+  if (out_mode == 3) { NES_LAUNCH_SHARED_CONV_POOL(3, __nv_bfloat16); }
+  else if (out_mode == 2) { NES_LAUNCH_SHARED_CONV_POOL(2, __nv_bfloat16); }
   else if (out_mode == 1) { NES_LAUNCH_SHARED_CONV_POOL(1, float); }
   else { NES_LAUNCH_SHARED_CONV_POOL(0, float); }
 #undef NES_LAUNCH_SHARED_CONV_POOL

@@ -271,6 +271,199 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   }
 }
 
+// ---- two images per MMA (bf16, 13x13 inputs pooled to 5x5) -----------------------------------------------------
+// A kind::f16 MMA with N = 256 takes hardly longer than one with N = 128, so the pair form puts TWO images into
+// every MMA.  The input holds image pairs interleaved by pixel, [pair][pixel][image 0 | image 1][32 channels]
+// (what the shared-input layer stores with out_mode 3), i.e. 64-byte rows in the order pixel-major,
+// image-minor: the B operand of tap (i, j) starts 2*(i*W + j) rows into the staged pair, and accumulator
+// column n is position n / 2 of image n % 2.  Two accumulators of 256 columns fill tensor memory.  The eps
+// warps copy all 256 columns to shared memory; of the two pooling warps of a lane quadrant each takes one
+// image: per pooled row it reads 48 columns (two wide loads) and picks its image's values by static index.
+constexpr int PAIR_N = 256;
+constexpr int PAIR_W = 13, PAIR_HP = 5, PAIR_WP = 5;
+constexpr int PAIR_STAGE_ROWS = 320;                 // 2 x 160 rows of 64 bytes
+
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                        const __grid_constant__ CUtensorMap map_f,
+                                                                        const ConvPoolParams p) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw = smem_u32(dyn_raw);
+  unsigned char* base = dyn_raw + (((raw + 1023u) & ~1023u) - raw);
+  constexpr int TAP_BYTES = CP_M * 64;
+  constexpr int STAGE_BYTES = PAIR_STAGE_ROWS * 64;
+  const int taps = p.kh * p.kw;
+  const int stages = p.stages;
+  const int64_t pairs = p.B / 2;
+  unsigned char* filt = base;
+  unsigned char* stage0 = filt + size_t(taps) * TAP_BYTES;
+  float* zeps = reinterpret_cast<float*>(stage0 + size_t(stages) * STAGE_BYTES);      // [PAIR_N][CP_HALF]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps + size_t(PAIR_N) * CP_HALF);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + CP_MAX_STAGES;
+  uint64_t* acc_full = bars + 2 * CP_MAX_STAGES;      // [2]
+  uint64_t* acc_empty = acc_full + 2;                 // [2] 192 epilogue threads
+  uint64_t* zeps_full = acc_full + 4;                 // 64 threads
+  uint64_t* zeps_empty = acc_full + 5;                // 128 threads
+  uint64_t* filt_full = acc_full + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 7);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 192); }
+    mbar_init(zeps_full, 64); mbar_init(zeps_empty, 128); mbar_init(filt_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * PAIR_N);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(filt_full, uint32_t(taps) * TAP_BYTES);
+      for (int t = 0; t < taps; ++t) tma_load_2d(filt + size_t(t) * TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
+      int i = 0;
+      for (int64_t pr = blockIdx.x; pr < pairs; pr += gridDim.x, ++i) {
+        const int s = i % stages;
+        if (!mbar_wait(&empty[s], ((i / stages) & 1) ^ 1, 1)) break;
+        unsigned char* dst = stage0 + size_t(s) * STAGE_BYTES;
+        const int row0 = int(pr * p.rows_per_image * 2);              // 64-byte rows of this pair
+        mbar_expect_tx(&full[s], uint32_t(STAGE_BYTES));
+        tma_load_2d(dst, &map_x, &full[s], 0, row0);                  // two boxes of 160 rows
+        tma_load_2d(dst + STAGE_BYTES / 2, &map_x, &full[s], 0, row0 + PAIR_STAGE_ROWS / 2);
+        const int64_t ahead = pr + int64_t(stages) * gridDim.x;
+        if (ahead < pairs) {
+          const int ra = int(ahead * p.rows_per_image * 2);
+          tma_prefetch_2d(&map_x, 0, ra);
+          tma_prefetch_2d(&map_x, 0, ra + PAIR_STAGE_ROWS / 2);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(CP_M, PAIR_N);
+      bool ok = mbar_wait(filt_full, 0, 2);
+      const uint32_t filt_addr = smem_u32(filt);
+      int i = 0;
+      for (int64_t pr = blockIdx.x; pr < pairs && ok; pr += gridDim.x, ++i) {
+        const int s = i % stages, a2 = i & 1;
+        ok = mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && mbar_wait(&full[s], (i / stages) & 1, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(stage0 + size_t(s) * STAGE_BYTES);
+        const uint32_t acc = tmem_base + uint32_t(a2 * PAIR_N);
+        for (int t = 0; t < taps; ++t) {
+          const int ti = t / p.kw, tj = t - ti * p.kw;
+          const uint64_t a = smem_desc_sw64(filt_addr + uint32_t(t) * TAP_BYTES);
+          const uint64_t bd = smem_desc_sw64(st + uint32_t(2 * (ti * PAIR_W + tj)) * 64u);
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+            mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&empty[s]);
+        mma_commit(&acc_full[a2]);
+      }
+    }
+  } else if (warp != 6 && warp != 7) {
+    const int q = warp & 3;
+    const int img = warp >> 3;                       // pooling warps: the image of the pair this warp serves
+    const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    if (q >= 2) {
+      // ---- eps channels: 256 accumulator columns -> shared memory [column][channel]
+      const int ch = (q - 2) * 32 + lane;
+      int i = 0;
+      for (int64_t pr = blockIdx.x; pr < pairs; pr += gridDim.x, ++i) {
+        const int s = i & 1;
+        if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[128];
+#pragma unroll
+          for (int c0 = 0; c0 < 128; c0 += 32) tmem_ld32_nowait(lane_addr + uint32_t(s * PAIR_N + h * 128 + c0), r + c0);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 128; ++j) zeps[(h * 128 + j) * CP_HALF + ch] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[s]);
+        mbar_arrive(zeps_full);
+      }
+    } else {
+      // ---- W channels: this warp pools image `img` of every pair
+      const int c = q * 32 + lane;
+      const bool live = c < p.Cout;
+      const float bc = (live && p.bias) ? p.bias[c] : 0.f;
+      constexpr int pooled = PAIR_HP * PAIR_WP;
+      int i = 0;
+      for (int64_t pr = blockIdx.x; pr < pairs; pr += gridDim.x, ++i) {
+        const int s = i & 1;
+        const int64_t b = 2 * pr + img;
+        const int64_t d = b % p.D;
+        const float sgn = anti_sign(b / p.D, p.R, p.antithetic);
+        int so = live ? (p.pout ? int(p.pout[d * p.Cout + c]) : c) : 0;
+        const bool noisy = live && so < p.osp;
+        if (!noisy) so = 0;
+        const float sn = noisy ? sgn : 0.f;
+        const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
+        if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
+        if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
+        tc_fence_after();
+        float* out = p.y + (b * p.Cout + c) * pooled;
+        const uint32_t acc = lane_addr + uint32_t(s * PAIR_N);
+        const float* e = zeps + so + img * CP_HALF;            // column 2*pos + img of the eps copy
+#pragma unroll
+        for (int py = 0; py < PAIR_HP; ++py) {
+          // windows of pooled row py use positions 26*py .. 26*py + 22: columns 52*py .. 52*py + 45 (+ image)
+          uint32_t r[48];
+          const uint32_t col0 = uint32_t(2 * (2 * py * PAIR_W));
+          tmem_ld32_nowait(acc + col0, r);
+          tmem_ld16_nowait(acc + col0 + 32u, r + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int px = 0; px < PAIR_WP; ++px) {
+            const int rel = 2 * px;                              // position relative to 26*py
+            const int pos = 2 * py * PAIR_W + rel;
+            // both images' candidate values are in registers; the image is uniform in the warp
+            const float t0 = __uint_as_float(img ? r[2 * rel + 1] : r[2 * rel]);
+            const float t1 = __uint_as_float(img ? r[2 * (rel + 1) + 1] : r[2 * (rel + 1)]);
+            const float t2 = __uint_as_float(img ? r[2 * (rel + PAIR_W) + 1] : r[2 * (rel + PAIR_W)]);
+            const float t3 = __uint_as_float(img ? r[2 * (rel + PAIR_W + 1) + 1] : r[2 * (rel + PAIR_W + 1)]);
+            const float v0 = t0 + sn * e[(2 * pos) * CP_HALF];
+            const float v1 = t1 + sn * e[(2 * (pos + 1)) * CP_HALF];
+            const float v2 = t2 + sn * e[(2 * (pos + PAIR_W)) * CP_HALF];
+            const float v3 = t3 + sn * e[(2 * (pos + PAIR_W + 1)) * CP_HALF];
+            const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
+            if (live) out[py * PAIR_WP + px] = v;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[s]);
+        mbar_arrive(zeps_empty);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * PAIR_N);
+  }
+}
+
 // stacked[tap][m][cin], rounded to the operand type: m < Cout -> weight[m], 64 <= m < 64 + osp -> eps[m - 64], else 0
 template <bool BF16>
 __global__ void stack_filter_kernel(const float* __restrict__ w, const float* __restrict__ eps, void* __restrict__ out,
@@ -407,4 +600,52 @@ extern "C" int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const fl
                                                nes_stream_t stream) {
   return run_conv_pool<true>(x_nhwc_bf16, weight, bias, eps, bias_noise, pout, y, D, R, Cin, H, W, Cout, kh, kw, out_sp,
                              antithetic, scratch, scratch_bytes, as_stream(stream), "permuted_conv_pool_fwd_bf16");
+}
+
+extern "C" int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const float* weight, const float* bias,
+                                                 const float* eps, const float* bias_noise, const int16_t* pout, float* y,
+                                                 int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                 int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                                                 nes_stream_t stream) {
+  const char* what = "permuted_conv_pool_fwd_bf16x2";
+  NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "%s: negative extent", what);
+  NES_REQUIRE(Cin == CP_CIN && H == PAIR_W && W == PAIR_W && kh == 3 && kw == 3, NES_ERR_UNSUPPORTED,
+              "%s: covers 32 input channels, 13x13 images and 3x3 filters (got %d, %dx%d, %dx%d)", what, Cin, H, W, kh, kw);
+  NES_REQUIRE(Cout >= 1 && Cout <= CP_HALF && out_sp >= 0 && out_sp <= CP_HALF, NES_ERR_UNSUPPORTED,
+              "%s: needs at most %d output channels (got %d, %d noise rows)", what, CP_HALF, Cout, out_sp);
+  const int64_t B = D * R;
+  if (B == 0) return NES_OK;
+  NES_REQUIRE(B % 2 == 0, NES_ERR_UNSUPPORTED, "%s: the pair layout needs an even number of images", what);
+  NES_REQUIRE(x_pairs_bf16 && weight && eps && y, NES_ERR_BAD_ARG, "%s: null pointer", what);
+  NES_REQUIRE(aligned16(x_pairs_bf16), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
+  NES_REQUIRE(B * H * W <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: batch too large", what);
+  const int taps = kh * kw;
+  const int64_t need = int64_t(taps) * CP_M * 64;
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "%s: scratch needs %lld bytes, 256-byte aligned", what, (long long)need);
+  cudaStream_t st = as_stream(stream);
+  const int n = taps * CP_M * CP_CIN;
+  stack_filter_kernel<true><<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, scratch, Cout, out_sp, taps);
+  int rc = check_launch(what);
+  if (rc != NES_OK) return rc;
+  CUtensorMap map_x, map_f;
+  if ((rc = make_rows_map(&map_x, x_pairs_bf16, true, B * H * W, PAIR_STAGE_ROWS / 2, what)) != NES_OK) return rc;
+  if ((rc = make_rows_map(&map_f, scratch, true, int64_t(taps) * CP_M, CP_M, what)) != NES_OK) return rc;
+  ConvPoolParams p;
+  p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
+  p.B = B; p.D = D; p.R = R;
+  p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = PAIR_HP; p.Wp = PAIR_WP;
+  p.rows_per_image = H * W; p.stage_rows = PAIR_STAGE_ROWS; p.zbufs = 1; p.antithetic = antithetic;
+  const size_t fixed = 1024 + size_t(taps) * CP_M * 64 + size_t(PAIR_N) * CP_HALF * 4 + 256;
+  const size_t stage = size_t(PAIR_STAGE_ROWS) * 64;
+  p.stages = int((227 * 1024 - fixed) / stage);
+  if (p.stages > CP_MAX_STAGES) p.stages = CP_MAX_STAGES;
+  NES_REQUIRE(p.stages >= 2, NES_ERR_UNSUPPORTED, "%s: not enough shared memory", what);
+  const size_t smem = fixed + size_t(p.stages) * stage;
+  cudaError_t e = cudaFuncSetAttribute(conv_pool_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+  const int64_t pairs = B / 2;
+  const unsigned grid = (unsigned)(pairs < sm_count() ? pairs : sm_count());
+  conv_pool_pair_kernel<<<grid, CP_THREADS, smem, st>>>(map_x, map_f, p);
+  return check_launch(what);
 }

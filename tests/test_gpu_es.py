@@ -86,19 +86,24 @@ def test_es_step_tensor_core_conv_close_to_fp32():
 
 def build_fused(base, D, tc):
     """tc: None (exact fp32 kernels), "tf32" or "bf16" (the stated reduced-precision modes, all layers)."""
-    o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": tc or "fp32"}
+    pair = tc == "bf16x2"                     # bf16 with two images per tensor-core instruction in layer 2
+    if pair:
+        tc = "bf16"
+    o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": "bf16x2" if pair else (tc or "fp32")}
     o2 = {"fuse": "relu_maxpool2"}
     lin = {}
     if tc:
         o2["tc"] = tc
         lin = {"tc": tc}
+    if pair:
+        o2["in_layout"] = "bf16x2"
     return torch.nn.Sequential(
         base.PermutedConv2d(1, 32, 3, D, options=o1),
         base.PermutedConv2d(32, 64, 3, D, options=o2), torch.nn.Flatten(),
         base.PermutedLinear(1600, 128, D, options=lin), torch.nn.ReLU(), base.PermutedLinear(128, 10, D, options=lin)).to(DEV)
 
 
-@pytest.mark.parametrize("tc,tol", [(None, 1e-4), ("tf32", 2e-2), ("bf16", 2e-2)])
+@pytest.mark.parametrize("tc,tol", [(None, 1e-4), ("tf32", 2e-2), ("bf16", 2e-2), ("bf16x2", 2e-2)])
 def test_es_step_fused_layers_match_the_module_by_module_network(tc, tol):
     """Same weights, noise and permutations in both networks: the fused Conv-ReLU-Pool layers (layer 1 fed with the
     shared minibatch) give the fitness of the Conv / ReLU / MaxPool2d network; exact-fp32 kernels hold 1e-4, the TF32

@@ -486,6 +486,16 @@ def test_shared_input_conv_relu_pool(base, cin, cout, out_sp, hw, k, pad, R, ant
             layer.perturbed_flag = False
         assert yr.dtype == (torch.bfloat16 if out == "bf16" else torch.float32)
         assert torch.all((yr.float() - y).abs() <= step * y.abs() + 1e-30)
+    # pair layout: images 2q and 2q+1 interleaved by pixel, presented as R*D/2 images of 2*C channels
+    layer.options = dict(layer.options, out_dtype="bf16x2")
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        yp = layer.forward(G(x))
+        layer.perturbed_flag = False
+    Hp, Wp = y.shape[2:]
+    assert yp.dtype == torch.bfloat16 and tuple(yp.shape) == (R * D // 2, 2 * cout, Hp, Wp)
+    pairs = yp.permute(0, 2, 3, 1).reshape(R * D // 2, Hp, Wp, 2, cout).permute(0, 3, 4, 1, 2).reshape(R * D, cout, Hp, Wp)
+    assert torch.all((pairs.float() - y).abs() <= 2.0 ** -8 * y.abs() + 1e-30)
 
 
 def test_fuse_option_falls_back_to_separate_kernels(base):

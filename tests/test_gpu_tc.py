@@ -382,3 +382,44 @@ def test_conv_pool_tc_rejects_uncovered_shapes():
     with pytest.raises(NotImplementedError):       # 16 input channels
         C.call("nes_permuted_conv_pool_fwd_tc", C.ptr(x), C.ptr(w), None, C.ptr(w), None, None, C.ptr(y), 2, 1,
                16, 13, 13, 64, 3, 3, 64, 0, C.ptr(buf), buf.numel(), C.stream())
+
+
+@pytest.mark.parametrize("cout,out_sp,R,anti,bias,D", [
+    (64, 0, 2, False, True, 6),
+    (64, 0.5, 3, True, True, 4),
+    (40, 0, 1, False, False, 2),
+    (64, 0, 3, True, True, 210),          # more pairs than SMs
+])
+def test_permuted_conv_pool_two_images_per_mma(cout, out_sp, R, anti, bias, D):
+    """bf16 fused kernel fed with the pair layout (images 2q and 2q+1 interleaved by pixel)."""
+    from nesgpu_b200 import base
+    from oracle import perturbed_ref as O
+    from gpu_util import G, set_params
+    cin, hw, k = 32, 13, 3
+    g = torch.Generator().manual_seed(cout + D + R)
+    layer = base.PermutedConv2d(cin, cout, k, D, bias=bias, antithetic=anti, permutation="out", out_sparsity=out_sp,
+                                options={"tc": "bf16", "fuse": "relu_maxpool2", "in_layout": "bf16x2"}).to(DEV)
+    osp = layer.out_sparsity
+    x = torch.randn(R * D, cin, hw, hw, generator=g).bfloat16().float()
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g) * .1 if bias else None
+    eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g) if bias else None
+    pout = torch.stack([torch.randperm(cout, generator=g) for _ in range(D)]).short()
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.output_permutations = G(eps), (G(beta) if bias else None), G(pout)
+    want = O.permuted_conv2d_forward(x, W, b if bias else torch.zeros(cout), eps,
+                                     beta if bias else torch.zeros(D, cout), None, pout, D, 1, 0, 1, anti)
+    want = torch.nn.functional.max_pool2d(torch.relu(want), 2)
+    B = R * D
+    xp = x.permute(0, 2, 3, 1).reshape(B // 2, 2, hw, hw, cin).permute(0, 2, 3, 1, 4).reshape(B // 2, hw, hw, 2 * cin)
+    xp = G(xp).bfloat16().contiguous().permute(0, 3, 1, 2)             # (B/2, 64, 13, 13), channels-last
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(xp)
+    assert _flag(_C()) == 0
+    assert y.shape == want.shape
+    assert rel_err(y, want) <= 2e-2
+    with pytest.raises(NotImplementedError):                            # the layout is only readable by this kernel
+        layer.options = dict(layer.options, tc="tf32")
+        layer.forward(xp)
