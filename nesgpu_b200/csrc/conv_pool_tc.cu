@@ -276,9 +276,10 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
 // every MMA.  The input holds image pairs interleaved by pixel, [pair][pixel][image 0 | image 1][32 channels]
 // (what the shared-input layer stores with out_mode 3), i.e. 64-byte rows in the order pixel-major,
 // image-minor: the B operand of tap (i, j) starts 2*(i*W + j) rows into the staged pair, and accumulator
-// column n is position n / 2 of image n % 2.  Two accumulators of 256 columns fill tensor memory.  The eps
-// warps copy all 256 columns to shared memory; of the two pooling warps of a lane quadrant each takes one
-// image: per pooled row it reads 48 columns (two wide loads) and picks its image's values by static index.
+// column n is position n / 2 of image n % 2.  Two accumulators of 256 columns fill tensor memory.  Four eps
+// warps (two per lane quadrant) copy the eps rows to shared memory as bf16 pairs (image 0, image 1) per
+// [position][channel], one buffer per accumulator; of the two pooling warps of a lane quadrant each takes
+// one image: per pooled row it reads 48 columns (two wide loads) and picks its image's values by static index.
 constexpr int PAIR_N = 256;
 constexpr int PAIR_W = 13, PAIR_HP = 5, PAIR_WP = 5;
 constexpr int PAIR_STAGE_ROWS = 320;                 // 2 x 160 rows of 64 bytes
@@ -306,22 +307,27 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
   const int64_t pairs = p.B / 2;
   unsigned char* filt = base;
   unsigned char* stage0 = filt + size_t(taps) * TAP_BYTES;
-  float* zeps = reinterpret_cast<float*>(stage0 + size_t(stages) * STAGE_BYTES);      // [PAIR_N][CP_HALF]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps + size_t(PAIR_N) * CP_HALF);
+  // eps rows as bf16 pairs (image 0, image 1) per [position][channel], two buffers
+  __nv_bfloat162* zeps0 = reinterpret_cast<__nv_bfloat162*>(stage0 + size_t(stages) * STAGE_BYTES);
+  constexpr int ZBUF = CP_N * CP_HALF;                 // elements per buffer
+  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps0 + 2 * size_t(ZBUF));
   uint64_t* full = bars;
   uint64_t* empty = bars + CP_MAX_STAGES;
   uint64_t* acc_full = bars + 2 * CP_MAX_STAGES;      // [2]
-  uint64_t* acc_empty = acc_full + 2;                 // [2] 192 epilogue threads
-  uint64_t* zeps_full = acc_full + 4;                 // 64 threads
-  uint64_t* zeps_empty = acc_full + 5;                // 128 threads
-  uint64_t* filt_full = acc_full + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 7);
+  uint64_t* acc_empty = acc_full + 2;                 // [2] 256 epilogue threads
+  uint64_t* zeps_full = acc_full + 4;                 // [2] 128 threads
+  uint64_t* zeps_empty = acc_full + 6;                // [2] 128 threads
+  uint64_t* filt_full = acc_full + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 9);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 192); }
-    mbar_init(zeps_full, 64); mbar_init(zeps_empty, 128); mbar_init(filt_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 256);
+      mbar_init(&zeps_full[s], 128); mbar_init(&zeps_empty[s], 128);
+    }
+    mbar_init(filt_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, 2 * PAIR_N);
@@ -376,31 +382,32 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
         mma_commit(&acc_full[a2]);
       }
     }
-  } else if (warp != 6 && warp != 7) {
+  } else {
     const int q = warp & 3;
     const int img = warp >> 3;                       // pooling warps: the image of the pair this warp serves
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
     if (q >= 2) {
-      // ---- eps channels: 256 accumulator columns -> shared memory [column][channel]
+      // ---- eps channels (warps 2, 3 and 6, 7: two warps per lane quadrant, half of the positions each):
+      //      accumulator columns (2*pos, 2*pos + 1) -> one bf16 pair at [position][channel]
       const int ch = (q - 2) * 32 + lane;
+      const int part = (warp >> 2) & 1;
       int i = 0;
       for (int64_t pr = blockIdx.x; pr < pairs; pr += gridDim.x, ++i) {
         const int s = i & 1;
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (!mbar_wait_relaxed(zeps_empty, (i & 1) ^ 1, 3)) break;
+        if (!mbar_wait_relaxed(&zeps_empty[s], ((i >> 1) & 1) ^ 1, 3)) break;
         tc_fence_after();
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[128];
+        uint32_t r[128];
 #pragma unroll
-          for (int c0 = 0; c0 < 128; c0 += 32) tmem_ld32_nowait(lane_addr + uint32_t(s * PAIR_N + h * 128 + c0), r + c0);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 128; ++j) zeps[(h * 128 + j) * CP_HALF + ch] = __uint_as_float(r[j]);
-        }
+        for (int c0 = 0; c0 < 128; c0 += 32) tmem_ld32_nowait(lane_addr + uint32_t(s * PAIR_N + part * 128 + c0), r + c0);
+        tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
-        mbar_arrive(zeps_full);
+        __nv_bfloat162* zeps = zeps0 + size_t(s) * ZBUF + (part * 64) * CP_HALF + ch;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          zeps[j * CP_HALF] = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        mbar_arrive(&zeps_full[s]);
       }
     } else {
       // ---- W channels: this warp pools image `img` of every pair
@@ -420,11 +427,12 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
         const float sn = noisy ? sgn : 0.f;
         const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (!mbar_wait_relaxed(zeps_full, i & 1, 3)) break;
+        if (!mbar_wait_relaxed(&zeps_full[s], (i >> 1) & 1, 3)) break;
         tc_fence_after();
         float* out = p.y + (b * p.Cout + c) * pooled;
         const uint32_t acc = lane_addr + uint32_t(s * PAIR_N);
-        const float* e = zeps + so + img * CP_HALF;            // column 2*pos + img of the eps copy
+        // this image's half of the bf16 pair at [position][permuted channel]
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(zeps0 + size_t(s) * ZBUF + so) + img;
 #pragma unroll
         for (int py = 0; py < PAIR_HP; ++py) {
           // windows of pooled row py use positions 26*py .. 26*py + 22: columns 52*py .. 52*py + 45 (+ image)
@@ -442,17 +450,17 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
             const float t1 = __uint_as_float(img ? r[2 * (rel + 1) + 1] : r[2 * (rel + 1)]);
             const float t2 = __uint_as_float(img ? r[2 * (rel + PAIR_W) + 1] : r[2 * (rel + PAIR_W)]);
             const float t3 = __uint_as_float(img ? r[2 * (rel + PAIR_W + 1) + 1] : r[2 * (rel + PAIR_W + 1)]);
-            const float v0 = t0 + sn * e[(2 * pos) * CP_HALF];
-            const float v1 = t1 + sn * e[(2 * (pos + 1)) * CP_HALF];
-            const float v2 = t2 + sn * e[(2 * (pos + PAIR_W)) * CP_HALF];
-            const float v3 = t3 + sn * e[(2 * (pos + PAIR_W + 1)) * CP_HALF];
+            const float v0 = t0 + sn * __bfloat162float(e[pos * (2 * CP_HALF)]);
+            const float v1 = t1 + sn * __bfloat162float(e[(pos + 1) * (2 * CP_HALF)]);
+            const float v2 = t2 + sn * __bfloat162float(e[(pos + PAIR_W) * (2 * CP_HALF)]);
+            const float v3 = t3 + sn * __bfloat162float(e[(pos + PAIR_W + 1) * (2 * CP_HALF)]);
             const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
             if (live) out[py * PAIR_WP + px] = v;
           }
         }
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
-        mbar_arrive(zeps_empty);
+        mbar_arrive(&zeps_empty[s]);
       }
     }
   }
@@ -636,7 +644,7 @@ extern "C" int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const
   p.B = B; p.D = D; p.R = R;
   p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = PAIR_HP; p.Wp = PAIR_WP;
   p.rows_per_image = H * W; p.stage_rows = PAIR_STAGE_ROWS; p.zbufs = 1; p.antithetic = antithetic;
-  const size_t fixed = 1024 + size_t(taps) * CP_M * 64 + size_t(PAIR_N) * CP_HALF * 4 + 256;
+  const size_t fixed = 1024 + size_t(taps) * CP_M * 64 + 2 * size_t(CP_N) * CP_HALF * 4 + 256;
   const size_t stage = size_t(PAIR_STAGE_ROWS) * 64;
   p.stages = int((227 * 1024 - fixed) / stage);
   if (p.stages > CP_MAX_STAGES) p.stages = CP_MAX_STAGES;
