@@ -310,7 +310,10 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
   // eps rows as bf16 pairs (image 0, image 1) per [position][channel], two buffers
   __nv_bfloat162* zeps0 = reinterpret_cast<__nv_bfloat162*>(stage0 + size_t(stages) * STAGE_BYTES);
   constexpr int ZBUF = CP_N * CP_HALF;                 // elements per buffer
-  uint64_t* bars = reinterpret_cast<uint64_t*>(zeps0 + 2 * size_t(ZBUF));
+  // per pooling warp: its 32 channels x 25 pooled values of one image, staged for full-line stores
+  float* ostage0 = reinterpret_cast<float*>(zeps0 + 2 * size_t(ZBUF));
+  constexpr int OSTAGE = 32 * PAIR_HP * PAIR_WP;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ostage0 + 4 * OSTAGE);
   uint64_t* full = bars;
   uint64_t* empty = bars + CP_MAX_STAGES;
   uint64_t* acc_full = bars + 2 * CP_MAX_STAGES;      // [2]
@@ -429,38 +432,59 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
         if (!mbar_wait_relaxed(&zeps_full[s], (i >> 1) & 1, 3)) break;
         tc_fence_after();
-        float* out = p.y + (b * p.Cout + c) * pooled;
+        float* ost = ostage0 + (q + 2 * img) * OSTAGE + lane * pooled;      // row stride 25 words: no bank conflicts
         const uint32_t acc = lane_addr + uint32_t(s * PAIR_N);
         // this image's half of the bf16 pair at [position][permuted channel]
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(zeps0 + size_t(s) * ZBUF + so) + img;
+        // windows of pooled row py use positions 26*py .. 26*py + 22: columns 52*py .. 52*py + 45 (+ image);
+        // the columns of the next pooled row are requested before this row is pooled
+        uint32_t r[2][48];
+        tmem_ld32_nowait(acc, r[0]);
+        tmem_ld16_nowait(acc + 32u, r[0] + 32);
+        tmem_ld_wait();
 #pragma unroll
         for (int py = 0; py < PAIR_HP; ++py) {
-          // windows of pooled row py use positions 26*py .. 26*py + 22: columns 52*py .. 52*py + 45 (+ image)
-          uint32_t r[48];
-          const uint32_t col0 = uint32_t(2 * (2 * py * PAIR_W));
-          tmem_ld32_nowait(acc + col0, r);
-          tmem_ld16_nowait(acc + col0 + 32u, r + 32);
-          tmem_ld_wait();
+          if (py + 1 < PAIR_HP) {
+            const uint32_t col0 = uint32_t(2 * (2 * (py + 1) * PAIR_W));
+            tmem_ld32_nowait(acc + col0, r[(py + 1) & 1]);
+            tmem_ld16_nowait(acc + col0 + 32u, r[(py + 1) & 1] + 32);
+          }
+          const uint32_t* rr = r[py & 1];
 #pragma unroll
           for (int px = 0; px < PAIR_WP; ++px) {
             const int rel = 2 * px;                              // position relative to 26*py
             const int pos = 2 * py * PAIR_W + rel;
             // both images' candidate values are in registers; the image is uniform in the warp
-            const float t0 = __uint_as_float(img ? r[2 * rel + 1] : r[2 * rel]);
-            const float t1 = __uint_as_float(img ? r[2 * (rel + 1) + 1] : r[2 * (rel + 1)]);
-            const float t2 = __uint_as_float(img ? r[2 * (rel + PAIR_W) + 1] : r[2 * (rel + PAIR_W)]);
-            const float t3 = __uint_as_float(img ? r[2 * (rel + PAIR_W + 1) + 1] : r[2 * (rel + PAIR_W + 1)]);
+            const float t0 = __uint_as_float(img ? rr[2 * rel + 1] : rr[2 * rel]);
+            const float t1 = __uint_as_float(img ? rr[2 * (rel + 1) + 1] : rr[2 * (rel + 1)]);
+            const float t2 = __uint_as_float(img ? rr[2 * (rel + PAIR_W) + 1] : rr[2 * (rel + PAIR_W)]);
+            const float t3 = __uint_as_float(img ? rr[2 * (rel + PAIR_W + 1) + 1] : rr[2 * (rel + PAIR_W + 1)]);
             const float v0 = t0 + sn * __bfloat162float(e[pos * (2 * CP_HALF)]);
             const float v1 = t1 + sn * __bfloat162float(e[(pos + 1) * (2 * CP_HALF)]);
             const float v2 = t2 + sn * __bfloat162float(e[(pos + PAIR_W) * (2 * CP_HALF)]);
             const float v3 = t3 + sn * __bfloat162float(e[(pos + PAIR_W + 1) * (2 * CP_HALF)]);
             const float v = fmaxf(fmaxf(fmaxf(v0, v1), fmaxf(v2, v3)) + add, 0.f);
-            if (live) out[py * PAIR_WP + px] = v;
+            ost[py * PAIR_WP + px] = v;
           }
+          if (py + 1 < PAIR_HP) tmem_ld_wait();
         }
         tc_fence_before();
         mbar_arrive(&acc_empty[s]);
         mbar_arrive(&zeps_empty[s]);
+        // the warp's 32 channels are one contiguous run of 800 floats in y: write it in order
+        __syncwarp();
+        {
+          const float* src = ostage0 + (q + 2 * img) * OSTAGE;
+          const int nlive = (p.Cout - q * 32 < 32 ? p.Cout - q * 32 : 32) * pooled;       // floats that exist
+          float* dst = p.y + (b * p.Cout + q * 32) * pooled;
+          if (nlive == OSTAGE && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+            for (int e4 = lane; e4 < OSTAGE / 4; e4 += 32)
+              reinterpret_cast<float4*>(dst)[e4] = reinterpret_cast<const float4*>(src)[e4];
+          } else {
+            for (int e1 = lane; e1 < nlive; e1 += 32) dst[e1] = src[e1];
+          }
+        }
+        __syncwarp();
       }
     }
   }
@@ -644,7 +668,7 @@ extern "C" int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const
   p.B = B; p.D = D; p.R = R;
   p.Cout = Cout; p.osp = out_sp; p.W = W; p.kh = kh; p.kw = kw; p.Hp = PAIR_HP; p.Wp = PAIR_WP;
   p.rows_per_image = H * W; p.stage_rows = PAIR_STAGE_ROWS; p.zbufs = 1; p.antithetic = antithetic;
-  const size_t fixed = 1024 + size_t(taps) * CP_M * 64 + 2 * size_t(CP_N) * CP_HALF * 4 + 256;
+  const size_t fixed = 1024 + size_t(taps) * CP_M * 64 + 2 * size_t(CP_N) * CP_HALF * 4 + 4 * 32 * PAIR_HP * PAIR_WP * 4 + 256;
   const size_t stage = size_t(PAIR_STAGE_ROWS) * 64;
   p.stages = int((227 * 1024 - fixed) / stage);
   if (p.stages > CP_MAX_STAGES) p.stages = CP_MAX_STAGES;
