@@ -600,7 +600,8 @@ class EsCnn(Workload):
 
     def _update(self, fit):
         from nesgpu_b200 import dist as ndist
-        everyone = ndist.gather_fitness(fit)
+        sizes = [self.D] * self.world if self.world > 1 else None      # equal slices: no size exchange, no host sync
+        everyone = ndist.gather_fitness(fit, sizes=sizes)
         w_all = self.es.centered_ranks(everyone)
         rank = torch.distributed.get_rank() if self.world > 1 else 0
         lo, hi = ndist.member_slice(everyone.numel(), rank, self.world)

@@ -29,20 +29,34 @@ def local_rows(batch, directions, rank, world_size):
     return batch.view(R, directions, *batch.shape[1:])[:, lo:hi].reshape(R * (hi - lo), *batch.shape[1:])
 
 
-def gather_fitness(local_fitness, group=None):
-    """All ranks' per-member fitness, concatenated in rank order (ranks may own unequal slices)."""
+def gather_fitness(local_fitness, group=None, sizes=None):
+    """All ranks' per-member fitness, concatenated in rank order (ranks may own unequal slices).
+
+    ``sizes`` (members per rank, in rank order) avoids the exchange of the slice sizes and, with it, the
+    host synchronisation that reading them back costs: pass it whenever the split is known, e.g.
+    ``[hi - lo for lo, hi in (member_slice(population, r, world) for r in range(world))]``."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
         return local_fitness
     world = dist.get_world_size(group)
-    sizes = [torch.zeros(1, dtype=torch.int64, device=local_fitness.device) for _ in range(world)]
-    dist.all_gather(sizes, torch.tensor([local_fitness.numel()], dtype=torch.int64, device=local_fitness.device),
-                    group=group)
-    n_max = int(max(s.item() for s in sizes))
-    padded = torch.zeros(n_max, dtype=local_fitness.dtype, device=local_fitness.device)
-    padded[:local_fitness.numel()] = local_fitness.flatten()
+    if sizes is None:
+        counts = [torch.zeros(1, dtype=torch.int64, device=local_fitness.device) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([local_fitness.numel()], dtype=torch.int64, device=local_fitness.device),
+                        group=group)
+        sizes = [int(c.item()) for c in counts]
+    else:
+        sizes = [int(n) for n in sizes]
+        if len(sizes) != world or sizes[dist.get_rank(group)] != local_fitness.numel():
+            raise ValueError("sizes must list every rank's member count, this rank's included")
+    n_max = max(sizes)
+    flat = local_fitness.flatten()
+    if flat.numel() == n_max:
+        padded = flat.contiguous()
+    else:
+        padded = torch.zeros(n_max, dtype=local_fitness.dtype, device=local_fitness.device)
+        padded[:flat.numel()] = flat
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
-    return torch.cat([p[:int(s.item())] for p, s in zip(parts, sizes)])
+    return torch.cat([p[:n] for p, n in zip(parts, sizes)])
 
 
 class UpdateBucket:

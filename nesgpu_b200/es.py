@@ -52,18 +52,21 @@ def population_fitness(perturbed_model, inputs, labels, directions, chunk=16):
 
 
 def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=16, bucket=None, group=None,
-            new_noise=True):
+            new_noise=True, population=None):
     """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
 
-    ``directions`` is the number of members owned by this rank.  Returns (local fitness, bucket); the
+    ``directions`` is the number of members owned by this rank; ``population`` (optional) the number of members
+    over all ranks, split as :func:`nesgpu_b200.dist.member_slice` does.  Returns (local fitness, bucket); the
     full-population gradient is left in ``.grad`` of the model's parameters on every rank."""
     if new_noise:
         perturbed_model.set_noise(noise_scale)
     fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk)
-    everyone = ndist.gather_fitness(fitness, group)
-    weights_all = centered_ranks(everyone)
     rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
     world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
+    # with the population size given, every rank knows the split and the step needs no host synchronisation
+    known = None if population is None else [hi - lo for lo, hi in (ndist.member_slice(population, r, world) for r in range(world))]
+    everyone = ndist.gather_fitness(fitness, group, known)
+    weights_all = centered_ranks(everyone)
     # ranks own contiguous member slices in rank order (sizes may differ by one)
     sizes = [ndist.member_slice(everyone.numel(), r, world) for r in range(world)]
     lo, hi = sizes[rank]

@@ -41,6 +41,14 @@ def _worker(rank, world, port, out):
     # fitness gathered in rank order with unequal slice sizes
     allfit = nd.gather_fitness(fitness[lo:hi].clone())
     ok &= torch.equal(allfit, fitness)
+    # the same with the split given (no size exchange); a wrong split is refused
+    known = [h - l for l, h in (nd.member_slice(D, r, world) for r in range(world))]
+    ok &= torch.equal(nd.gather_fitness(fitness[lo:hi].clone(), sizes=known), fitness)
+    try:
+        nd.gather_fitness(fitness[lo:hi].clone(), sizes=[D, D])
+        ok = False
+    except ValueError:
+        pass
     # partial updates summed through one bucket
     wgt = O.centered_ranks(allfit)
     wpar = torch.nn.Parameter(W.clone())
