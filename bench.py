@@ -850,6 +850,37 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
 
+    # ---- the metric's second half, ES steps/s: one ES step of the small CNN (BASELINE configs[4]) timed the same
+    #      way (5 steps after 3 warm-up steps, barrier on both sides, max over ranks), in both stated modes
+    es_extra = None
+    if args.workload == "perturbed_linear_1024" and not args.no_es and not args.members:
+        es_extra = {"workload": "es_cnn_8192", "images_per_member": EsCnn.R, "directions_per_gpu": EsCnn.D,
+                    "population": EsCnn.D * world, "steps": 5, "warmup": 3}
+        for mode in ("tf32", "bf16"):
+            try:
+                es = EsCnn()
+                es.tc = mode
+                es.setup(dev, rank, world)
+                for _ in range(3):
+                    es.step(null_mark)
+                barrier()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(5):
+                    es.step(null_mark)
+                a1.record()
+                barrier()
+                t = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = t.item() / 5
+                es_extra[mode] = {"ms_per_step": round(ms, 3), "es_steps_per_s": round(1e3 / ms, 2),
+                                  "member_image_pairs_per_s": round(es.D * es.R * world / (ms * 1e-3), 1)}
+                del es
+            except Exception as exc:      # the headline line must not depend on this extra
+                es_extra[mode] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+        torch.cuda.empty_cache()
+
     if rank == 0:
         unit = "member-samples/s"
         ms_per_step = total_ms / args.steps
@@ -865,6 +896,8 @@ def run_ours(args, rank, world, local_rank):
                 "cuda_graph": graph is not None, "phase_ms": {k: round(v, 4) for k, v in phase_ms.items()},
                 "wall_s_timed_region": round(wall, 4), "clocks": clocks,
                 "roofline": wl.roofline(phase_ms, peaks)}
+        if es_extra is not None:
+            line["es_step"] = es_extra
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             line["cpu_baseline"] = cpu_baseline(wl, 5, unit)
@@ -886,6 +919,8 @@ def main():
                     help="permuted_linear_256: launch every step from Python instead of replaying a captured CUDA graph")
     ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32", "bf16"],
                     help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
+    ap.add_argument("--no-es", action="store_true",
+                    help="default workload: skip the extra ES-step measurement (es_step in the JSON line)")
     ap.add_argument("--unfused", action="store_true",
                     help="es_cnn_8192: separate Conv / ReLU / MaxPool2d modules and per-member input copies instead of the fused layers")
     ap.add_argument("--members", type=int, default=0,
