@@ -73,18 +73,28 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
     const bool live = c < Cout;
     const int cc = live ? c : 0;
     const float* base = wmaps + cc * pitch;
-    for (int pp = warp; pp < pooled; pp += CP_WARPS) {
+    // a warp takes two pooling windows per pass (pp and pp + CP_WARPS): the member's table reads and the loop
+    // bookkeeping are shared by the two stored values
+    for (int pp = warp; pp < pooled; pp += 2 * CP_WARPS) {
+      const int pq = pp + CP_WARPS;
+      const bool two = pq < pooled;
       const int py = pp / Wp, px = pp - py * Wp;
       const int p00 = (2 * py) * Wo + 2 * px;
+      const int qy = two ? pq / Wp : py, qx = two ? pq - qy * Wp : px;
+      const int q00 = (2 * qy) * Wo + 2 * qx;
       const float b00 = base[p00], b01 = base[p00 + 1], b10 = base[p00 + Wo], b11 = base[p00 + Wo + 1];
+      const float c00 = base[q00], c01 = base[q00 + 1], c10 = base[q00 + Wo], c11 = base[q00 + Wo + 1];
       // MODE 3: images b = 2q and 2q + 1 share rows, [q][pooled pixel][image][channel]; d0 and D are even there
       out_t* o = (MODE == 3) ? y + (((r * D + d0) / 2 * pooled + pp) * 2) * Cout + c
                              : y + ((r * D + d0) * pooled + pp) * Cout + c;
+      const int64_t o_second = int64_t(pq - pp) * Cout * (MODE == 3 ? 2 : 1);     // from window pp to window pq
       const float* np = nmaps + p00 * npitch;
+      const int nq = (q00 - p00) * npitch;
       const int16_t* sp = so_tab + cc;               // this channel's column of the member tables
       const float2* tp = tab + cc;
       const int o1 = npitch, o2 = row, o3 = row + npitch;
-#pragma unroll 4
+      const bool live2 = live && two;
+#pragma unroll 2
       for (int m = 0; m < nm; ++m, o += ((MODE == 3) ? ((m & 1) ? int64_t(Cout) : 2 * member_stride - Cout) : member_stride),   // m: the member stepped to
                                  sp += Cout, tp += Cout) {
         // the 32 channels of a member point at 32 different noise maps = 32 different banks
@@ -92,7 +102,11 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
         const float2 t = *tp;
         const out_t v = pool_value<MODE>(fmaf(t.x, n[0], b00), fmaf(t.x, n[o1], b01), fmaf(t.x, n[o2], b10),
                                          fmaf(t.x, n[o3], b11), t.y);
+        const float* n2 = n + nq;
+        const out_t w = pool_value<MODE>(fmaf(t.x, n2[0], c00), fmaf(t.x, n2[o1], c01), fmaf(t.x, n2[o2], c10),
+                                         fmaf(t.x, n2[o3], c11), t.y);
         if (live) *o = v;
+        if (live2) o[o_second] = w;
       }
     }
   }
