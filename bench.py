@@ -624,7 +624,7 @@ class EsCnn(Workload):
         flops = self.FLOP_PER_PAIR * self.D * self.R
         ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
         peak = peaks["bf16_sustained"] / 2
-        kernels = ("shared_conv_pool_kernel, conv_pool_tf32_kernel, permuted_operand_kernel + gemm_tf32_kernel, fc2, CE"
+        kernels = ("shared_conv_pool_kernel, conv_pool_tc_kernel / conv_pool_pair_kernel, permuted_operand_kernel + gemm_tf32_kernel, CE"
                    if self.fused else "conv1, conv2, fc1, fc2 kernels + torch ReLU / MaxPool / CE")
         return {"kernel": "population forward (%s), forward phase" % kernels,
                 "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s", "frac": round(ach / peak, 4),
