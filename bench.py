@@ -592,7 +592,7 @@ class EsCnn(Workload):
         pm, es = self.pm, self.es
         pm.set_noise()
         mark("set_noise")
-        fit = es.population_fitness(pm, self.images, self.labels, self.D, chunk=16)
+        fit = es.population_fitness(pm, self.images, self.labels, self.D)
         mark("forward")
         _, self.bucket = self._update(fit)
         mark("update")

@@ -30,9 +30,23 @@ def takes_shared_input(perturbed_model):
     return False
 
 
-def population_fitness(perturbed_model, inputs, labels, directions, chunk=16):
-    """Negative mean cross-entropy of every member on the shared minibatch: (directions,) tensor."""
+PAIRS_PER_CHUNK = 16384      # member-image pairs per forward call: enough to fill the GPU, bounded activations
+
+
+def auto_chunk(directions, examples):
+    """Examples per forward call such that a call evaluates about ``PAIRS_PER_CHUNK`` member-example pairs
+    (16 for 1024 members; the whole minibatch for small populations, where launches would dominate)."""
+    return max(1, min(int(examples), PAIRS_PER_CHUNK // max(int(directions), 1)))
+
+
+def population_fitness(perturbed_model, inputs, labels, directions, chunk=None):
+    """Negative mean cross-entropy of every member on the shared minibatch: (directions,) tensor.
+    ``chunk`` = examples per forward call (default: :func:`auto_chunk`).  With antithetic layers every call is split
+    into its own + half and - half (``modules/base.py:377-378`` applies the sign by position in the call's batch), so
+    the chunk size then decides which examples meet which sign; pass ``chunk=len(inputs)`` for the reference's split."""
     R = inputs.shape[0]
+    if chunk is None:
+        chunk = auto_chunk(directions, R)
     loss_sum = torch.zeros(directions, device=inputs.device, dtype=torch.float32)
     shared = takes_shared_input(perturbed_model)
     with torch.no_grad():
@@ -51,7 +65,7 @@ def population_fitness(perturbed_model, inputs, labels, directions, chunk=16):
     return -(loss_sum / R)
 
 
-def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=16, bucket=None, group=None,
+def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=None, bucket=None, group=None,
             new_noise=True, population=None):
     """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
 

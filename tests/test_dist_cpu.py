@@ -85,3 +85,9 @@ def test_two_ranks_gloo():
         out = m.dict()
         mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
         assert dict(out) == {0: True, 1: True}
+
+
+def test_auto_chunk():
+    from nesgpu_b200 import es
+    assert es.auto_chunk(1024, 256) == 16 and es.auto_chunk(64, 256) == 256 and es.auto_chunk(8192, 256) == 2
+    assert es.auto_chunk(100000, 256) == 1 and es.auto_chunk(1, 7) == 7
