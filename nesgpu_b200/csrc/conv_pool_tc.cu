@@ -430,7 +430,6 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
         const float sn = noisy ? sgn : 0.f;
         const float add = bc + ((live && p.bias_noise) ? sgn * p.bias_noise[d * p.Cout + c] : 0.f);
         if (!mbar_wait_relaxed(&acc_full[s], (i >> 1) & 1, 3)) break;
-        if (!mbar_wait_relaxed(&zeps_full[s], (i >> 1) & 1, 3)) break;
         tc_fence_after();
         float* ost = ostage0 + (q + 2 * img) * OSTAGE + lane * pooled;      // row stride 25 words: no bank conflicts
         const uint32_t acc = lane_addr + uint32_t(s * PAIR_N);
@@ -441,7 +440,10 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
         uint32_t r[2][48];
         tmem_ld32_nowait(acc, r[0]);
         tmem_ld16_nowait(acc + 32u, r[0] + 32);
+        // the first accumulator columns travel while the eps warps finish their copy
+        const bool eps_ready = mbar_wait_relaxed(&zeps_full[s], (i >> 1) & 1, 3);
         tmem_ld_wait();
+        if (!eps_ready) break;
 #pragma unroll
         for (int py = 0; py < PAIR_HP; ++py) {
           if (py + 1 < PAIR_HP) {
