@@ -712,6 +712,15 @@ def run_reference(args, rank, world):
             "gpu_launches": 0,
             "note": "CPU restatement (oracle/) of the reference's algorithm on the host cores; the reference itself is "
                     "a Python tree without a package, and no checkout of it exists on the GPU box; each step is the bounded sample"}
+    if args.workload == "perturbed_linear_1024" and not args.no_es:
+        # the ES step of the small CNN on the host cores, next to the es_step entry of the GPU arm
+        try:
+            es_units, es_times, es_sample = EsCnn().cpu_sample(2)
+            med = statistics.median(es_times)
+            line["es_step"] = {"workload": "es_cnn_8192", "member_image_pairs_per_s": round(es_units / med, 1),
+                               "seconds_per_repetition": round(med, 4), "cores": cores, "kind": "port", "sample": es_sample}
+        except Exception as exc:
+            line["es_step"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
     print(json.dumps(line), flush=True)
 
 
