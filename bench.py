@@ -590,6 +590,7 @@ class EsCnn(Workload):
 
     def step(self, mark):
         pm, es = self.pm, self.es
+        pm.set_seed()             # new seeds every step, as the reference's trainer does (mnisttest.py:128-131)
         pm.set_noise()
         mark("set_noise")
         fit = es.population_fitness(pm, self.images, self.labels, self.D)

@@ -66,13 +66,17 @@ def population_fitness(perturbed_model, inputs, labels, directions, chunk=None):
 
 
 def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=None, bucket=None, group=None,
-            new_noise=True, population=None):
+            new_noise=True, population=None, reseed=True):
     """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
 
     ``directions`` is the number of members owned by this rank; ``population`` (optional) the number of members
     over all ranks, split as :func:`nesgpu_b200.dist.member_slice` does.  Returns (local fitness, bucket); the
     full-population gradient is left in ``.grad`` of the model's parameters on every rank."""
     if new_noise:
+        # noise is a pure function of each layer's seed, so a step draws new seeds first, as the reference's
+        # trainer does (mnisttest.py:128-131); reseed=False keeps the seeds that are set
+        if reseed:
+            perturbed_model.set_seed()
         perturbed_model.set_noise(noise_scale)
     fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk)
     rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
