@@ -30,12 +30,12 @@ def takes_shared_input(perturbed_model):
     return False
 
 
-PAIRS_PER_CHUNK = 16384      # member-image pairs per forward call: enough to fill the GPU, bounded activations
+PAIRS_PER_CHUNK = 65536      # member-example pairs per forward call: launches amortised, activations bounded (a few GB)
 
 
 def auto_chunk(directions, examples):
     """Examples per forward call such that a call evaluates about ``PAIRS_PER_CHUNK`` member-example pairs
-    (16 for 1024 members; the whole minibatch for small populations, where launches would dominate)."""
+    (64 for 1024 members; the whole minibatch for small populations, where launches would dominate)."""
     return max(1, min(int(examples), PAIRS_PER_CHUNK // max(int(directions), 1)))
 
 

@@ -89,5 +89,5 @@ def test_two_ranks_gloo():
 
 def test_auto_chunk():
     from nesgpu_b200 import es
-    assert es.auto_chunk(1024, 256) == 16 and es.auto_chunk(64, 256) == 256 and es.auto_chunk(8192, 256) == 2
-    assert es.auto_chunk(100000, 256) == 1 and es.auto_chunk(1, 7) == 7
+    assert es.auto_chunk(1024, 256) == 64 and es.auto_chunk(64, 256) == 256 and es.auto_chunk(8192, 256) == 8
+    assert es.auto_chunk(100000, 256) == 1 and es.auto_chunk(1, 7) == 7 and es.auto_chunk(65536, 256) == 1
