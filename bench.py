@@ -593,7 +593,7 @@ class EsCnn(Workload):
         pm.set_seed()             # new seeds every step, as the reference's trainer does (mnisttest.py:128-131)
         pm.set_noise()
         mark("set_noise")
-        fit = es.population_fitness(pm, self.images, self.labels, self.D)
+        fit = es.population_fitness(pm, self.images, self.labels, self.D, streams=2 if self.tc == "bf16" else 1)
         mark("forward")
         _, self.bucket = self._update(fit)
         mark("update")

@@ -39,34 +39,71 @@ def auto_chunk(directions, examples):
     return max(1, min(int(examples), PAIRS_PER_CHUNK // max(int(directions), 1)))
 
 
-def population_fitness(perturbed_model, inputs, labels, directions, chunk=None):
+_side_streams = {}
+
+
+def _streams(device, n):
+    """The launching stream plus n - 1 side streams of the device (created once)."""
+    main = torch.cuda.current_stream(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), n)
+    if key not in _side_streams:
+        _side_streams[key] = [torch.cuda.Stream(device=device) for _ in range(n - 1)]
+    return [main] + _side_streams[key]
+
+
+def population_fitness(perturbed_model, inputs, labels, directions, chunk=None, streams=1):
     """Negative mean cross-entropy of every member on the shared minibatch: (directions,) tensor.
     ``chunk`` = examples per forward call (default: :func:`auto_chunk`).  With antithetic layers every call is split
     into its own + half and - half (``modules/base.py:377-378`` applies the sign by position in the call's batch), so
-    the chunk size then decides which examples meet which sign; pass ``chunk=len(inputs)`` for the reference's split."""
+    the chunk size then decides which examples meet which sign; pass ``chunk=len(inputs)`` for the reference's split.
+
+    With ``streams`` > 1 successive calls alternate over that many CUDA streams (the launching one and side
+    streams), so that kernels of neighbouring calls that do not compete for the same resource (a streaming pre-pass
+    next to a tensor-core kernel) can overlap; everything is joined back into the launching stream before the result
+    is returned.  Whether it pays depends on the kernels: on the small CNN two streams saved 0.28 ms of 6.1 ms in the
+    bf16 mode and cost 0.9 ms in the TF32 mode, whose fp32 activations are four times larger."""
     R = inputs.shape[0]
     if chunk is None:
         chunk = auto_chunk(directions, R)
-    loss_sum = torch.zeros(directions, device=inputs.device, dtype=torch.float32)
     shared = takes_shared_input(perturbed_model)
+    starts = list(range(0, R, chunk))
+    lanes = _streams(inputs.device, max(1, min(int(streams), len(starts)))) if inputs.is_cuda else [None]
+    main = lanes[0]
+    partial = [torch.zeros(directions, device=inputs.device, dtype=torch.float32) for _ in lanes]
+    for side in lanes[1:]:
+        side.wait_stream(main)            # inputs, labels and the zeroed sums are ready
     with torch.no_grad():
-        for r0 in range(0, R, chunk):
+        for i, r0 in enumerate(starts):
+            lane = i % len(lanes)
             r1 = min(R, r0 + chunk)
             rc = r1 - r0
-            if shared:
-                xb = inputs[r0:r1].contiguous()
-            else:
-                xb = inputs[r0:r1].unsqueeze(1).expand(rc, directions, *inputs.shape[1:]).reshape(
-                    rc * directions, *inputs.shape[1:])
-            logits = perturbed_model.forward(xb)
-            target = labels[r0:r1].repeat_interleave(directions)
-            ce = F.cross_entropy(logits.view(rc * directions, -1), target, reduction="none")
-            loss_sum += ce.view(rc, directions).sum(dim=0)
+            with torch.cuda.stream(lanes[lane]) if lanes[lane] is not None else _Null():
+                if shared:
+                    xb = inputs[r0:r1].contiguous()
+                else:
+                    xb = inputs[r0:r1].unsqueeze(1).expand(rc, directions, *inputs.shape[1:]).reshape(
+                        rc * directions, *inputs.shape[1:])
+                logits = perturbed_model.forward(xb)
+                target = labels[r0:r1].repeat_interleave(directions)
+                ce = F.cross_entropy(logits.view(rc * directions, -1), target, reduction="none")
+                partial[lane] += ce.view(rc, directions).sum(dim=0)
+    loss_sum = partial[0]
+    for side, part in zip(lanes[1:], partial[1:]):
+        main.wait_stream(side)
+        loss_sum = loss_sum + part
     return -(loss_sum / R)
 
 
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=None, bucket=None, group=None,
-            new_noise=True, population=None, reseed=True):
+            new_noise=True, population=None, reseed=True, streams=1):
     """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
 
     ``directions`` is the number of members owned by this rank; ``population`` (optional) the number of members
@@ -78,7 +115,7 @@ def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk
         if reseed:
             perturbed_model.set_seed()
         perturbed_model.set_noise(noise_scale)
-    fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk)
+    fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk, streams)
     rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
     world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
     # with the population size given, every rank knows the split and the step needs no host synchronisation

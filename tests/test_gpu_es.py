@@ -135,3 +135,21 @@ def test_es_step_fused_layers_match_the_module_by_module_network(tc, tol):
     # inference (perturbed flag off): both networks are the plain CNN
     with torch.no_grad():
         assert_close(fused(images), plain(images).cpu(), tol=1e-4, what="inference")
+
+
+def test_population_fitness_on_two_streams_equals_one_stream():
+    from nesgpu_b200 import base, es
+    D, R = 16, 12
+    torch.manual_seed(3)
+    net = build_fused(base, D, "bf16x2")
+    pm = base.PerturbedModel(net, D)
+    pm.set_noise_scale(0.02)
+    pm.set_seed(21)
+    pm.set_noise()
+    images = torch.rand(R, 1, 28, 28, device=DEV)
+    labels = torch.randint(10, (R,), device=DEV)
+    one = es.population_fitness(pm, images, labels, D, chunk=3, streams=1)
+    two = es.population_fitness(pm, images, labels, D, chunk=3, streams=2)
+    three = es.population_fitness(pm, images, labels, D, chunk=3, streams=3)
+    torch.cuda.synchronize()
+    assert rel_err(two, one.cpu()) <= 1e-6 and rel_err(three, one.cpu()) <= 1e-6
