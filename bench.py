@@ -25,6 +25,17 @@ import sys
 import threading
 import time
 
+# stdout of this program is ONE JSON line.  Libraries write to file descriptor 1 too (NCCL prints its version
+# banner there), so descriptor 1 is pointed at stderr and the JSON line goes to a private copy of the real stdout.
+_JSON_OUT = os.fdopen(os.dup(1), "w")
+os.dup2(2, 1)
+
+
+def emit(line):
+    _JSON_OUT.write(json.dumps(line) + "\n")
+    _JSON_OUT.flush()
+
+
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -722,7 +733,7 @@ def run_reference(args, rank, world):
                                "seconds_per_repetition": round(med, 4), "cores": cores, "kind": "port", "sample": es_sample}
         except Exception as exc:
             line["es_step"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def _cpu_layer_state(wl):
@@ -911,7 +922,7 @@ def run_ours(args, rank, world, local_rank):
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             line["cpu_baseline"] = cpu_baseline(wl, 5, unit)
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
