@@ -66,9 +66,11 @@ int64_t nes_linear_fwd_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int mod
 int nes_linear_fwd_tc(const float* x, const float* weight, const float* bias, float* y,
                       int64_t M, int64_t N, int64_t K, int mode,
                       void* scratch, int64_t scratch_bytes, nes_stream_t stream);
-/* Reads (synchronously) the device word in which a tensor-core kernel records that one of its bounded
- * waits ran out: 0 = none, 1 = producer, 2 = MMA issuer, 3 = epilogue.  Diagnostic; no counterpart in
- * the reference. */
+/* Reads (synchronously) the device words in which the tensor-core kernels record that one of their
+ * bounded waits ran out (0 = none, 1 = producer, 2 = MMA issuer, 3 = epilogue, 4 = filter builder /
+ * operand splitter) and clears them: a call reports what happened since the previous call.  A kernel whose
+ * own wait ran out skips its stores, so its output is undefined; kernels launched afterwards are not
+ * affected.  Call it where the host synchronises anyway (end of a step).  No counterpart in the reference. */
 int nes_tc_error_flag(int* flag);
 
 /* NCHW convolution, groups == 1, zero padding.  x (B,Cin,H,W), weight (Cout,Cin,kh,kw),
@@ -108,6 +110,13 @@ int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n);
 int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
                          int64_t D, int64_t n, float l1, float l2,
                          void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+/* The same reduction for "direct" storage (modules/base.py:111-117, 126-133), where the per-member
+ * tensors hold parameter + noise:  grad[i] = sum_d w[d] * (stored[d,i] - param[i]) + l1/l2 terms.
+ * The parameter is subtracted from each member's row before the row is weighted, as the reference does,
+ * so the result does not lose digits to (sum_d w[d]) * param. */
+int nes_perturbed_update_direct(const float* stored, const float* w, const float* param, const float* weight,
+                                float* grad, int64_t D, int64_t n, float l1, float l2,
+                                void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
 /* nes_perturbed_update for callers that have no workspace to give.  (No counterpart in the
  * reference: there the reduction is one library GEMV that allocates whatever it likes.)
@@ -153,6 +162,16 @@ int nes_sparse_perturbed_update(const int32_t* idx, const float* val, const floa
 
 /* ------------------------------------------- fp32: shared noise + member permutations */
 
+/* Permuted.update for layers with output permutations only, in one launch (modules/base.py:261-266 scatter,
+ * :513-518 / :590-599 product, :120-138 l1 / l2 and the bias gradient `weights @ bias_noise`):
+ *   grad[k,m,t] = sum_s G[k,s] * eps[s,m,t] + l1 * sign(weight) + l2 * weight,
+ *   G[k,s] = sum_d w[d] * [pout[d,k] == s and s < out_sp];   bias_grad[k] = sum_d w[d] * bias_noise[d,k].
+ * bias_noise and bias_grad may both be NULL; weight may be NULL when l1 == l2 == 0.  No scratch memory. */
+int nes_permuted_update_out(const float* eps, const float* w, const int16_t* pout, const float* weight,
+                            const float* bias_noise, float* grad, float* bias_grad,
+                            int64_t D, int in, int out, int out_sp, int ksize, float l1, float l2,
+                            nes_stream_t stream);
+
 /* PermutedLinear.forward, default branch (modules/base.py:487-508):
  *   xg[b,j] = x[b, pin[d,j]]            (j < in_sp; identity when pin == NULL)
  *   p[b,s]  = sum_j xg[b,j] * eps[s,j]  (s < out_sp)
@@ -181,6 +200,22 @@ int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float*
                                float* y, int64_t D, int64_t R, int64_t in, int64_t out,
                                int64_t in_sp, int64_t out_sp, int antithetic, int mode,
                                void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* The same layer with output permutations only (pin == NULL, in_sp == in; pout may be NULL when
+ * out_sp == out) as ONE tensor-core kernel and one launch: a thread-block cluster per tile of 128 batch
+ * rows multiplies the rows by the stacked matrix [weight; eps] (tcgen05.mma kind::tf32, both accumulators
+ * in tensor memory, operands brought in by TMA and split into tf32 hi + lo parts in shared memory), and
+ * the epilogue gathers p[b, pout[d,k]] from the cluster's shared memory, applies s(r), adds bias_noise,
+ * bias and the base product and stores y.  No scratch memory.  mode 3: 3xTF32, fp32-level accuracy;
+ * mode 1: operands rounded to TF32 (relative error ~1e-3; for callers that state it).
+ * nes_permuted_linear_out_fwd_tc_supported returns 1 when the shape is covered (in a positive multiple
+ * of 4, out + out_sp <= 2048, out <= 32767), else 0; x, weight and eps must be 16-byte aligned.
+ * Replaces F.linear + apply_output_permutation + the adds at modules/base.py:487-508,236-240. */
+int nes_permuted_linear_out_fwd_tc_supported(int64_t D, int64_t R, int64_t in, int64_t out, int64_t out_sp, int mode);
+int nes_permuted_linear_out_fwd_tc(const float* x, const float* weight, const float* bias,
+                                   const float* eps, const float* bias_noise, const int16_t* pout,
+                                   float* y, int64_t D, int64_t R, int64_t in, int64_t out, int64_t out_sp,
+                                   int antithetic, int mode, nes_stream_t stream);
 
 /* Out-permuted convolution of an input shared by all members, fused with ReLU and 2x2/2 max-pooling
  * (floor mode).  z (R, Cout + out_sp, Ho, Wo) is the plain convolution of the R shared images with
@@ -352,9 +387,11 @@ int nes_fill_signs(int8_t* out, int64_t n, uint64_t seed, uint64_t offset, nes_s
 /* D independent uniform permutations of [0,n), first `keep` entries of each stored
  * (out is (D,keep) int16); with_replacement != 0 draws keep independent indices instead.
  * Replaces the per-member CPU randperm loop / randint at modules/base.py:209-227.  n <= 16384
- * without replacement (the sort runs in shared memory), n <= 32767 with replacement. */
+ * without replacement (the sort runs in shared memory), n <= 32767 with replacement.  Row i is the draw
+ * of member first_member + i: a rank that owns members [lo, hi) of a population passes first_member = lo
+ * and gets rows lo..hi-1 of the table a single process would draw with the same seed. */
 int nes_sample_permutations(int16_t* out, int64_t D, int n, int keep, int with_replacement,
-                            uint64_t seed, nes_stream_t stream);
+                            uint64_t seed, int64_t first_member, nes_stream_t stream);
 
 /* ---------------------------------------------------------------------- bit-packed ops
  * word_bits is 64 (int64 words) or 32 (int32 words), as the reference's KernelWrapper

@@ -29,6 +29,7 @@ SIGNATURES = {
     "nes_perturbed_conv2d_fwd": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr],
     "nes_perturbed_update_scratch_bytes": [c_i64, c_i64],
     "nes_perturbed_update": [c_ptr] * 4 + [c_i64, c_i64, c_f32, c_f32, c_ptr, c_i64, c_ptr],
+    "nes_perturbed_update_direct": [c_ptr] * 5 + [c_i64, c_i64, c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_perturbed_update_noalloc": [c_ptr] * 4 + [c_i64, c_i64, c_f32, c_f32, c_ptr],
     "nes_sparse_perturbed_linear_fwd": [c_ptr] * 7 + [c_i64] * 4 + [c_int, c_int, c_ptr],
     "nes_sparse_perturbed_update": [c_ptr] * 5 + [c_i64] * 3 + [c_int, c_f32, c_f32, c_ptr],
@@ -36,6 +37,8 @@ SIGNATURES = {
     "nes_permuted_linear_fwd": [c_ptr] * 8 + [c_i64] * 6 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_linear_fwd_tc_scratch_bytes": [c_i64] * 5 + [c_int],
     "nes_permuted_linear_fwd_tc": [c_ptr] * 7 + [c_i64] * 6 + [c_int, c_int, c_ptr, c_i64, c_ptr],
+    "nes_permuted_linear_out_fwd_tc_supported": [c_i64] * 5 + [c_int],
+    "nes_permuted_linear_out_fwd_tc": [c_ptr] * 7 + [c_i64] * 5 + [c_int, c_int, c_ptr],
     "nes_shared_conv_pool_fwd": [c_ptr] * 5 + [c_i64, c_i64] + [c_int] * 6 + [c_ptr],
     "nes_permuted_conv_pool_fwd_tc_scratch_bytes": [c_int, c_int],
     "nes_permuted_conv_pool_fwd_tc": [c_ptr] * 7 + [c_i64, c_i64] + [c_int] * 8 + [c_ptr, c_i64, c_ptr],
@@ -50,6 +53,7 @@ SIGNATURES = {
     "nes_perturbed_conv2d_fwd_bf16": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_bf16": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_dense_noise": [c_ptr] * 4 + [c_i64] + [c_int] * 5 + [c_ptr],
+    "nes_permuted_update_out": [c_ptr] * 7 + [c_i64] + [c_int] * 4 + [c_f32, c_f32, c_ptr],
     "nes_permuted_update_scratch_bytes": [c_int] * 4,
     "nes_permuted_update": [c_ptr] * 7 + [c_i64] + [c_int] * 5 + [c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_synthetic_linear_fwd_scratch_bytes": [c_i64] * 3,
@@ -59,7 +63,7 @@ SIGNATURES = {
     "nes_fill_signs": [c_ptr, c_i64, c_u64, c_u64, c_ptr],
     "nes_fill_normal": [c_ptr, c_i64, c_f32, c_f32, c_u64, c_u64, c_ptr],
     "nes_fill_uniform": [c_ptr, c_i64, c_f32, c_f32, c_u64, c_u64, c_ptr],
-    "nes_sample_permutations": [c_ptr, c_i64, c_int, c_int, c_int, c_u64, c_ptr],
+    "nes_sample_permutations": [c_ptr, c_i64, c_int, c_int, c_int, c_u64, c_i64, c_ptr],
     "nes_bin_pack": [c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr],
     "nes_bin_int8pack": [c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr],
     "nes_bin_pack8": [c_ptr, c_ptr, c_i64, c_i64, c_ptr],
@@ -89,6 +93,7 @@ _RETURNS = {
     "nes_permuted_conv2d_fwd_scratch_bytes": c_i64,
     "nes_permuted_update_scratch_bytes": c_i64,
     "nes_bin_weighted_sum_scratch_bytes": c_i64,
+    "nes_permuted_linear_out_fwd_tc_supported": c_int,
 }
 _NO_STATUS = set(_RETURNS) | {"nes_abi_version"}
 
@@ -128,6 +133,19 @@ def call(name, *args):
             raise NotImplementedError("%s: %s (%s)" % (name, what, detail))
         raise NesError("%s: %s (%s)" % (name, what, detail))
     return rc
+
+
+def check_device_errors():
+    """Raise if a tensor-core kernel gave up on one of its bounded waits since the last check.
+
+    Reading the device words synchronises the host with the device, so call this where the host waits
+    anyway (after a step's results have been read); the words are cleared by the read."""
+    flag = ctypes.c_int(0)
+    call("nes_tc_error_flag", ctypes.byref(flag))
+    if flag.value:
+        role = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "filter builder / operand splitter"}
+        raise NesError("a tensor-core kernel timed out in its %s wait (code %d); the outputs of that launch "
+                       "are undefined" % (role.get(flag.value, "?"), flag.value))
 
 
 def ptr(t):

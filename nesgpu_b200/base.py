@@ -79,11 +79,21 @@ class Perturbed:
         self.seed = None
         self.antithetic = antithetic
         self.options = options
+        self.member_offset = 0
         self.free_memory()
 
     # -- state ---------------------------------------------------------------------------
     def set_noise_scale(self, noise_scale):
         self.noise_scale = noise_scale
+
+    def set_member_offset(self, first_member=0):
+        """Global index of this layer's member 0 when the population is sharded over processes.
+
+        Per-member draws (dense noise, bias noise, permutations, sign flips) are keyed on
+        ``member_offset + d``, so ranks that share a seed draw disjoint members -- with row lengths that are
+        multiples of the generator's group size, exactly the slice a single process would draw -- while the
+        noise every member shares (``Permuted`` / ``Synthetic`` ``weight_noise``) stays identical on all ranks."""
+        self.member_offset = int(first_member)
 
     def set_seed(self, seed=None):
         self.seed = random.randrange(100000000) if seed is None else seed
@@ -115,11 +125,24 @@ class Perturbed:
             self.allocate_memory()
 
     @staticmethod
-    def _fill_normal(t, std, seed, stream_id):
-        """N(0, std^2) from the device generator; ``stream_id`` separates the tensors of a layer."""
+    def _member_groups(first_member, per_member, group):
+        """Counter offset (in generator groups of ``group`` values) of member ``first_member`` in a
+        ``(members, per_member)`` tensor: the exact position when rows are whole groups, otherwise a
+        spacing that keeps the ranges of different ranks apart."""
+        if not first_member:
+            return 0
+        if per_member % group == 0:
+            return first_member * (per_member // group)
+        return first_member * (per_member // group + 2)
+
+    @classmethod
+    def _fill_normal(cls, t, std, seed, stream_id, first_member=0):
+        """N(0, std^2) from the device generator; ``stream_id`` separates the tensors of a layer,
+        ``first_member`` shifts a per-member tensor to its place in the whole population."""
         C.require_cuda(t, "noise tensor", _F32)
+        per_member = t[0].numel() if t.dim() and t.shape[0] else 1
         C.call("nes_fill_normal", C.ptr(t), t.numel(), 0.0, float(std), int(seed) & (2 ** 64 - 1),
-               int(stream_id) << 40, C.stream())
+               (int(stream_id) << 40) + cls._member_groups(first_member, per_member, 4), C.stream())
 
     def set_noise(self, noise_scale=None):
         """Draw fresh noise on the device (reference ``base.py:59-85``)."""
@@ -131,18 +154,17 @@ class Perturbed:
         for noise, param, sid in pairs:
             if direct and self.antithetic:
                 half = self.directions // 2
-                self._fill_normal(noise[:half], self.noise_scale, self.seed, sid)
+                self._fill_normal(noise[:half], self.noise_scale, self.seed, sid, self.member_offset)
                 noise[half:] = -noise[:half]
             else:
-                self._fill_normal(noise, self.noise_scale, self.seed, sid)
+                self._fill_normal(noise, self.noise_scale, self.seed, sid, self.member_offset)
             if direct:
                 noise += param.detach()
 
     # -- update --------------------------------------------------------------------------
     def _direct_param(self, param):
-        """With "direct" storage the tensors hold ``param + noise`` (reference ``base.py:111-117``):
-        sum_d w_d (N_d - P) = sum_d w_d N_d - (sum_d w_d) P, so the parameter is taken out after
-        the reduction instead of materialising ``noise - param``."""
+        """With "direct" storage the tensors hold ``param + noise`` (reference ``base.py:111-117``); the
+        reduction kernel then subtracts the parameter from every member's row as it streams it."""
         if not self.options.get("direct"):
             return None
         if self.antithetic:
@@ -162,10 +184,14 @@ class Perturbed:
         out = torch.empty(noise.shape[1:], device=noise.device, dtype=_F32)
         nbytes = C.call("nes_perturbed_update_scratch_bytes", D, n)
         buf = C.scratch(nbytes, noise.device)
-        C.call("nes_perturbed_update", C.ptr(noise), C.ptr(weights), C.ptr(_opt(param)) if (l1 or l2) else None,
-               C.ptr(out), D, n, float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
+        reg = C.ptr(_opt(param)) if (l1 or l2) else None
         if direct_param is not None:
-            out.sub_(direct_param * weights.sum())
+            C.call("nes_perturbed_update_direct", C.ptr(noise), C.ptr(weights),
+                   C.ptr(C.require_cuda(direct_param, "parameter", _F32)), reg, C.ptr(out), D, n, float(l1), float(l2),
+                   C.ptr(buf), nbytes, C.stream())
+        else:
+            C.call("nes_perturbed_update", C.ptr(noise), C.ptr(weights), reg, C.ptr(out), D, n, float(l1), float(l2),
+                   C.ptr(buf), nbytes, C.stream())
         return out
 
     def weight_grad(self, weights):
@@ -246,7 +272,7 @@ class Permuted(Perturbed):
         out = torch.empty((self.directions, keep), dtype=torch.int16, device=self.weight.device)
         C.call("nes_sample_permutations", C.ptr(out), self.directions, n, keep,
                1 if self.options.get("allow_repeats") else 0,
-               (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1), C.stream())
+               (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1), self.member_offset, C.stream())
         return out
 
     def set_noise(self, noise_scale=None):
@@ -256,7 +282,7 @@ class Permuted(Perturbed):
         rescale = (self.out_degree * self.in_degree / self.out_sparsity / self.in_sparsity) ** .5
         self._fill_normal(self.weight_noise, self.noise_scale * rescale, self.seed, 0)
         if self.bias is not None:
-            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1, self.member_offset)
         if self.permute_outputs:
             self.output_permutations = self._sample_permutations(self.out_degree, self.out_degree, 2)
         if self.permute_inputs:
@@ -303,6 +329,34 @@ class Permuted(Perturbed):
                self.directions, self.in_degree, self.out_degree, self.in_sparsity, self.out_sparsity, ksize,
                float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
         return grad, pw
+
+    def update(self, weights, l1=0, l2=0):
+        """Layers with output permutations only get weight gradient, l1 / l2 terms and bias gradient from one
+        launch; everything else takes the generic route (reference ``base.py:120-138``)."""
+        if self.permute_inputs or not self.permute_outputs or self.out_sparsity * 32 > 200 * 1024:
+            return Perturbed.update(self, weights, l1, l2)
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        if weights.numel() != self.directions:
+            raise RuntimeError("update weights must have one entry per direction")
+        _, pout = self._perms()
+        ksize = 1
+        for s in self.weight.shape[2:]:
+            ksize *= s
+        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        beta = bias_grad = None
+        if self.bias is not None:
+            beta = C.require_cuda(self.bias_noise, "bias_noise", _F32)
+            bias_grad = torch.empty_like(self.bias)
+        C.call("nes_permuted_update_out", C.ptr(eps), C.ptr(weights), C.ptr(pout),
+               C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(beta), C.ptr(grad), C.ptr(bias_grad),
+               self.directions, self.in_degree, self.out_degree, self.out_sparsity, ksize, float(l1), float(l2),
+               C.stream())
+        self.weight.grad = grad if self.weight.grad is None else self.weight.grad + grad
+        if self.bias is None:
+            return grad
+        self.bias.grad = bias_grad if self.bias.grad is None else self.bias.grad + bias_grad
+        return grad, bias_grad
 
     def get_permutation_weights(self, weights):
         """The scatter-add matrix of reference ``base.py:254-267`` for the single-sided modes."""
@@ -409,11 +463,13 @@ class SparsePerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
 
     def set_noise(self, noise_scale=None):
         self._prepare_noise(noise_scale)
-        self._fill_normal(self.weight_noise, self.noise_scale * (self.in_features / self.k) ** .5, self.seed, 0)
+        self._fill_normal(self.weight_noise, self.noise_scale * (self.in_features / self.k) ** .5, self.seed, 0,
+                          self.member_offset)
         if self.bias is not None:
-            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1, self.member_offset)
         u = torch.empty(self.noise_indices.shape, device=self.weight.device, dtype=_F32)
-        C.call("nes_fill_uniform", C.ptr(u), u.numel(), 0.0, 1.0, (int(self.seed) * 4 + 2) & (2 ** 64 - 1), 0, C.stream())
+        C.call("nes_fill_uniform", C.ptr(u), u.numel(), 0.0, 1.0, (int(self.seed) * 4 + 2) & (2 ** 64 - 1),
+               self._member_groups(self.member_offset, self.out_features * self.k, 4), C.stream())
         self.noise_indices = (u * self.in_features).clamp_(max=self.in_features - 1).to(torch.int32)
 
     def forward(self, input):
@@ -476,6 +532,21 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
             return 3 if rows >= self.SINGLE_PRODUCT_MIN_ROWS else 0
         return {"3xtf32": 3, "tf32": 1, "bf16": 2}[mode]
 
+    def _cluster_kernel_mode(self, x, R, pin):
+        """Mode (3 = 3xTF32, 1 = TF32) of the one-launch tensor-core forward for layers without input
+        permutations, or 0 when the CUDA-core kernels have to run (``options["tc"] = "fp32"``, or a shape the
+        kernel does not cover).  ``"auto"`` and ``"3xtf32"`` give the error-compensated form that holds the fp32
+        bar; ``"tf32"`` is the stated reduced-precision mode."""
+        mode = self.options.get("tc", "auto")
+        if pin is not None or mode in ("fp32", "bf16") or x.shape[0] == 0:
+            return 0
+        m = 1 if mode == "tf32" else 3
+        if x.data_ptr() % 16 or self.weight.data_ptr() % 16 or self.weight_noise.data_ptr() % 16:
+            return 0
+        ok = C.call("nes_permuted_linear_out_fwd_tc_supported", self.directions, R, self.in_features,
+                    self.out_features, self.out_sparsity, m)
+        return m if ok else 0
+
     def forward(self, input):
         if not self.perturbed_flag:
             return self._plain_forward(input)
@@ -486,6 +557,12 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         pin, pout = self._perms()
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
         mode = self._single_product_mode(x.shape[0], pout)
+        cluster_mode = self._cluster_kernel_mode(x, R, pin)
+        if cluster_mode:
+            C.call("nes_permuted_linear_out_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
+                   C.ptr(eps), C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, self.in_features,
+                   self.out_features, self.out_sparsity, 1 if self.antithetic else 0, cluster_mode, C.stream())
+            return y.view(*lead, self.out_features)
         if mode:
             nbytes = C.call("nes_permuted_linear_fwd_tc_scratch_bytes", self.directions, R, self.in_features,
                             self.out_features, self.in_sparsity, mode)
@@ -810,7 +887,8 @@ class Synthetic(Perturbed):
 
     def _sample_flips(self, n, stream_id):
         out = torch.empty((self.directions, n), dtype=torch.int8, device=self.weight.device)
-        C.call("nes_fill_signs", C.ptr(out), out.numel(), (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1), 0, C.stream())
+        C.call("nes_fill_signs", C.ptr(out), out.numel(), (int(self.seed) * 4 + stream_id) & (2 ** 64 - 1),
+               self._member_groups(self.member_offset, n, 128), C.stream())
         return out
 
     def set_noise(self, noise_scale=None):
@@ -818,7 +896,7 @@ class Synthetic(Perturbed):
         self._prepare_noise(noise_scale)
         self._fill_normal(self.weight_noise, self.noise_scale, self.seed, 0)
         if self.bias is not None:
-            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1)
+            self._fill_normal(self.bias_noise, self.noise_scale, self.seed, 1, self.member_offset)
         if self.flip_outputs:
             self.output_flips = self._sample_flips(self.out_degree, 2)
         if self.flip_inputs:

@@ -69,6 +69,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfloat16* __restrict__ xs, const ConvBfParams p) {
   extern __shared__ unsigned char dyn_raw[];
+  const unsigned int timeouts_at_start = timeouts_so_far();
   const uint32_t raw = smem_u32(dyn_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
   unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B]
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             const uint32_t buf = t & 1;
             if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
             tc_fence_after();
-            const bool live = (g_tc_error == 0);
+            const bool live = (timeouts_so_far() == timeouts_at_start);
             for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               uint32_t acc[32];
               tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(BF_NT) + uint32_t(c0), acc);
@@ -423,11 +424,7 @@ __global__ void reorder_filter_bf_kernel(const float* __restrict__ src, float* _
   dst[idx] = src[(size_t(n) * C + c) * ksz + tap];
 }
 
-int conv_bf16_error_word(int* v) {
-  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
-  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
-  return NES_OK;
-}
+int conv_bf16_error_word(int* v, bool clear) { return read_error_word(v, clear, "tc_error_flag"); }
 
 static int64_t bf_align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 

@@ -512,11 +512,7 @@ __global__ void stack_filter_kernel(const float* __restrict__ w, const float* __
   else static_cast<float*>(out)[idx] = round_tf32(v);
 }
 
-int conv_pool_error_word(int* v) {
-  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
-  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
-  return NES_OK;
-}
+int conv_pool_error_word(int* v, bool clear) { return read_error_word(v, clear, "tc_error_flag"); }
 
 // (rows, 32 channels) row-major tensor, box = box_rows whole rows, swizzle span = one row
 static int make_rows_map(CUtensorMap* map, const void* base, bool bf16, int64_t rows, int box_rows, const char* what) {

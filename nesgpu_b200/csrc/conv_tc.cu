@@ -56,6 +56,7 @@ __device__ __forceinline__ void unit_range(const ConvTcParams& p, int sg, long l
 
 __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float* __restrict__ xs, const ConvTcParams p) {
   extern __shared__ unsigned char dyn_raw[];
+  const unsigned int timeouts_at_start = timeouts_so_far();
   const uint32_t raw = smem_u32(dyn_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
   unsigned char* wd = dyn_raw + pad;                                   // [kchunks][Cout][128 B]
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float*
               tc_fence_after();
               const int qpos = ti * 128 + pix;
               const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
-              const bool valid = (oy < p.Ho) && (ox < p.Wo) && (g_tc_error == 0);
+              const bool valid = (oy < p.Ho) && (ox < p.Wo) && (timeouts_so_far() == timeouts_at_start);
               float* yb = p.y + size_t(b) * p.Cout * HoWo + size_t(oy) * p.Wo + ox;
               for (int c0 = 0; c0 < p.Cout; c0 += 32) {
                 uint32_t acc[32];
@@ -385,11 +386,7 @@ __global__ void reorder_filter_kernel(const float* __restrict__ src, float* __re
   dst[idx] = src[(size_t(n) * C + c) * ksz + tap];
 }
 
-int conv_tc_error_word(int* v) {
-  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
-  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
-  return NES_OK;
-}
+int conv_tc_error_word(int* v, bool clear) { return read_error_word(v, clear, "tc_error_flag"); }
 
 static int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 

@@ -38,6 +38,7 @@ template <int TERMS, bool BF16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_constant__ Maps maps, const float* __restrict__ bias,
                                                                  const RowTerm rt, float* __restrict__ C, int M, int N, int K, int stages) {
   extern __shared__ unsigned char dyn_raw[];
+  const unsigned int timeouts_at_start = timeouts_so_far();
   constexpr int OPERANDS = (TERMS == 3) ? 4 : 2;
   constexpr int STAGE_BYTES = OPERANDS * TILE_BYTES;
   // 1 KiB-aligned tile area, then the barriers
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
     const int q = warp & 3;
     const bool ok = mbar_wait_relaxed(accum, 0, 3);
     tc_fence_after();
-    if (ok && g_tc_error == 0 && nk > 0) {
+    if (ok && timeouts_so_far() == timeouts_at_start && nk > 0) {
       const int64_t gm = int64_t(m0) + q * 32 + lane;
       const float* bn_row = nullptr;
       float bn_sign = 1.f;
@@ -411,22 +412,26 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
   return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, rt, y, B, out, K2, mode, st, "permuted_linear_fwd_tc");
 }
 
-namespace nes { namespace tc { int conv_tc_error_word(int* v); int conv_bf16_error_word(int* v); int conv_pool_error_word(int* v); } }
+namespace nes { namespace tc {
+int conv_tc_error_word(int* v, bool clear);
+int conv_bf16_error_word(int* v, bool clear);
+int conv_pool_error_word(int* v, bool clear);
+int permuted_out_error_word(int* v, bool clear);
+} }
 
+// Reads the error words of all tensor-core translation units, reports the first non-zero code and clears
+// them, so that a later call reports only what has happened since this one.
 extern "C" int nes_tc_error_flag(int* flag) {
   NES_REQUIRE(flag != nullptr, NES_ERR_BAD_ARG, "tc_error_flag: null pointer");
-  int v = 0, vc = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int));
-  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "tc_error_flag: %s", cudaGetErrorString(e));
-  int vb = 0;
-  int rc = nes::tc::conv_tc_error_word(&vc);
+  int v[5] = {0, 0, 0, 0, 0};
+  int rc = read_error_word(&v[0], true, "tc_error_flag");
   if (rc != NES_OK) return rc;
-  rc = nes::tc::conv_bf16_error_word(&vb);
-  if (rc != NES_OK) return rc;
-  int vp = 0;
-  rc = nes::tc::conv_pool_error_word(&vp);
-  if (rc != NES_OK) return rc;
-  if (!vb) vb = vp;
-  *flag = v ? v : (vc ? vc : vb);
+  if ((rc = nes::tc::conv_tc_error_word(&v[1], true)) != NES_OK) return rc;
+  if ((rc = nes::tc::conv_bf16_error_word(&v[2], true)) != NES_OK) return rc;
+  if ((rc = nes::tc::conv_pool_error_word(&v[3], true)) != NES_OK) return rc;
+  if ((rc = nes::tc::permuted_out_error_word(&v[4], true)) != NES_OK) return rc;
+  *flag = 0;
+  for (int i = 0; i < 5; ++i)
+    if (v[i]) { *flag = v[i]; break; }
   return NES_OK;
 }

@@ -43,14 +43,16 @@ __global__ void fill_uniform_kernel(float* __restrict__ out, int64_t n, float lo
 // One block per member: draw a 32-bit key per position, sort (key, position) pairs with a
 // bitonic network in shared memory, emit the positions of the `keep` smallest keys.  Ties in
 // the key are broken by position (probability ~ n^2 / 2^33 per member).
-__global__ void sample_permutations_kernel(int16_t* __restrict__ out, int n, int n_pow2, int keep, uint64_t seed) {
+__global__ void sample_permutations_kernel(int16_t* __restrict__ out, int n, int n_pow2, int keep, uint64_t seed,
+                                           int64_t first_member) {
   extern __shared__ __align__(16) unsigned char dyn[];
   uint64_t* keys = reinterpret_cast<uint64_t*>(dyn);
   const int64_t d = blockIdx.x;
+  const uint64_t member = uint64_t(first_member + d);      // the draw depends on the global member index only
   Philox ph(seed);
   for (int q = threadIdx.x; q * 4 < n_pow2; q += blockDim.x) {
     uint32_t r[4];
-    ph(uint32_t(q), uint32_t(d), uint32_t(uint64_t(d) >> 32), 1u, r);
+    ph(uint32_t(q), uint32_t(member), uint32_t(member >> 32), 1u, r);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int i = q * 4 + j;
@@ -73,12 +75,13 @@ __global__ void sample_permutations_kernel(int16_t* __restrict__ out, int n, int
   for (int i = threadIdx.x; i < keep; i += blockDim.x) out[d * keep + i] = int16_t(keys[i] & 0xFFFFu);
 }
 
-__global__ void sample_indices_kernel(int16_t* __restrict__ out, int64_t total, int n, uint64_t seed) {
+__global__ void sample_indices_kernel(int16_t* __restrict__ out, int64_t total, int n, uint64_t seed, uint64_t offset) {
   const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (q * 4 >= total) return;
   uint32_t r[4];
   Philox ph(seed);
-  ph(uint32_t(q), uint32_t(uint64_t(q) >> 32), 0u, 3u, r);
+  const uint64_t ctr = offset + uint64_t(q);
+  ph(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 3u, r);
 #pragma unroll
   for (int j = 0; j < 4; ++j)
     if (q * 4 + j < total) out[q * 4 + j] = int16_t((uint64_t(r[j]) * uint64_t(n)) >> 32);
@@ -131,15 +134,16 @@ extern "C" int nes_fill_uniform(float* out, int64_t n, float lo, float hi, uint6
 }
 
 extern "C" int nes_sample_permutations(int16_t* out, int64_t D, int n, int keep, int with_replacement,
-                                       uint64_t seed, nes_stream_t stream) {
-  NES_REQUIRE(D >= 0 && n > 0 && keep >= 0, NES_ERR_BAD_ARG, "sample_permutations: bad extent");
+                                       uint64_t seed, int64_t first_member, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && n > 0 && keep >= 0 && first_member >= 0, NES_ERR_BAD_ARG, "sample_permutations: bad extent");
   NES_REQUIRE(n <= 32767, NES_ERR_UNSUPPORTED, "sample_permutations: n=%d does not fit int16", n);
   if (D == 0 || keep == 0) return NES_OK;
   NES_REQUIRE(out, NES_ERR_BAD_ARG, "sample_permutations: null pointer");
   cudaStream_t st = as_stream(stream);
   if (with_replacement) {
     const int64_t total = D * keep;
-    sample_indices_kernel<<<(unsigned)ceil_div<int64_t>(ceil_div<int64_t>(total, 4), 256), 256, 0, st>>>(out, total, n, seed);
+    sample_indices_kernel<<<(unsigned)ceil_div<int64_t>(ceil_div<int64_t>(total, 4), 256), 256, 0, st>>>(out, total, n, seed,
+                                                                                                      uint64_t(first_member) * uint64_t(ceil_div(keep, 4) + 1));
     return check_launch("sample_permutations(indices)");
   }
   NES_REQUIRE(keep <= n, NES_ERR_BAD_ARG, "sample_permutations: keep > n without replacement");
@@ -153,6 +157,6 @@ extern "C" int nes_sample_permutations(int16_t* out, int64_t D, int n, int keep,
     if (e != cudaSuccess) return fail(NES_ERR_UNSUPPORTED, "sample_permutations: %zu B of shared memory refused", smem);
   }
   const int threads = n_pow2 / 2 < 32 ? 32 : (n_pow2 / 2 > 512 ? 512 : n_pow2 / 2);
-  sample_permutations_kernel<<<(unsigned)D, threads, smem, st>>>(out, n, n_pow2, keep, seed);
+  sample_permutations_kernel<<<(unsigned)D, threads, smem, st>>>(out, n, n_pow2, keep, seed, first_member);
   return check_launch("sample_permutations");
 }

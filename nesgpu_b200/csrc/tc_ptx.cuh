@@ -10,9 +10,15 @@ namespace tc {
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about one second at B200 clocks
 
-// Set (once) to a non-zero code when a bounded wait runs out: 1 producer, 2 MMA issuer, 3 epilogue,
-// 4 filter builder.
+// Set to a non-zero code when a bounded wait runs out (the first code since the word was last read and
+// cleared by the host is kept): 1 producer, 2 MMA issuer, 3 epilogue, 4 filter builder / operand splitter.
 static __device__ int g_tc_error = 0;
+// Number of waits that have run out since the library was loaded.  A kernel notes the count when it starts
+// and only skips its stores when the count has moved since, i.e. when one of its own waits (or one of a
+// kernel running beside it) gave up -- an error left behind by an earlier launch does not silence later ones.
+static __device__ unsigned int g_tc_timeouts = 0;
+
+__device__ __forceinline__ unsigned int timeouts_so_far() { return *reinterpret_cast<volatile unsigned int*>(&g_tc_timeouts); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -48,6 +54,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, i
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
   }
   atomicCAS(&g_tc_error, 0, code);
+  atomicAdd(&g_tc_timeouts, 1u);
   return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
@@ -194,6 +201,19 @@ inline EncodeTiledFn encode_fn() {
       fn = reinterpret_cast<EncodeTiledFn>(p);
   }
   return fn;
+}
+
+// Host side of the error word of the translation unit that includes this header: copies the code to *v and,
+// when `clear` is set, resets the word so that the next read reports only what happened since.
+static inline int read_error_word(int* v, bool clear, const char* what) {
+  cudaError_t e = cudaMemcpyFromSymbol(v, g_tc_error, sizeof(int));
+  if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  if (clear && *v != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return NES_OK;
 }
 
 }  // namespace tc

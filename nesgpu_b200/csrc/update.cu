@@ -14,10 +14,12 @@ constexpr int UPD_THREADS = 256;
 constexpr int UPD_BLOCKS_PER_SM = 4;
 constexpr int UPD_MAX_SPLITS = 16;
 
-template <bool VEC>
+// SUB: the tensors hold parameter + noise ("direct" storage); the parameter row `sub` is taken out of every
+// member's row before it is weighted, so the sum never carries (sum_d w_d) * parameter around.
+template <bool VEC, bool SUB>
 __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise_sum_kernel(
-    const float* __restrict__ noise, const float* __restrict__ w, float* __restrict__ out,
-    int64_t D, int64_t n, int64_t d_per_split) {
+    const float* __restrict__ noise, const float* __restrict__ w, const float* __restrict__ sub,
+    float* __restrict__ out, int64_t D, int64_t n, int64_t d_per_split) {
   const int64_t d0 = blockIdx.y * d_per_split;
   const int64_t d1 = (d0 + d_per_split < D) ? d0 + d_per_split : D;
   float* dst = out + blockIdx.y * n;
@@ -27,6 +29,8 @@ __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise
     const float4* src = reinterpret_cast<const float4*>(noise) + i4;
     const int64_t stride = n / 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (SUB) pv = __ldg(reinterpret_cast<const float4*>(sub) + i4);
     int64_t d = d0;
     for (; d + 8 <= d1; d += 8) {
       float4 v[8];
@@ -35,13 +39,15 @@ __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const float wd = __ldg(w + d + u);
+        if (SUB) { v[u].x -= pv.x; v[u].y -= pv.y; v[u].z -= pv.z; v[u].w -= pv.w; }
         acc.x = fmaf(wd, v[u].x, acc.x); acc.y = fmaf(wd, v[u].y, acc.y);
         acc.z = fmaf(wd, v[u].z, acc.z); acc.w = fmaf(wd, v[u].w, acc.w);
       }
     }
     for (; d < d1; ++d) {
-      const float4 v = __ldcs(src + d * stride);
+      float4 v = __ldcs(src + d * stride);
       const float wd = __ldg(w + d);
+      if (SUB) { v.x -= pv.x; v.y -= pv.y; v.z -= pv.z; v.w -= pv.w; }
       acc.x = fmaf(wd, v.x, acc.x); acc.y = fmaf(wd, v.y, acc.y);
       acc.z = fmaf(wd, v.z, acc.z); acc.w = fmaf(wd, v.w, acc.w);
     }
@@ -50,7 +56,8 @@ __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise
     const int64_t i = int64_t(blockIdx.x) * UPD_THREADS + threadIdx.x;
     if (i >= n) return;
     float acc = 0.f;
-    for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), __ldcs(noise + d * n + i), acc);
+    const float pv = SUB ? __ldg(sub + i) : 0.f;
+    for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), __ldcs(noise + d * n + i) - pv, acc);
     dst[i] = acc;
   }
 }
@@ -131,6 +138,78 @@ __global__ void grad_from_out_hist_kernel(const float* __restrict__ G, const flo
   }
   for (; s < out_sp; ++s) a0 = fmaf(__ldg(g + s), __ldg(eps + s * inner + e), a0);
   grad[size_t(k) * inner + e] = (a0 + a1) + (a2 + a3);
+}
+
+// Output-permuted update in ONE launch (weight gradient, bias gradient, l1 / l2 terms):
+//   grad[k, e]  = sum_s G[k,s] * eps[s, e] (+ l1 sign(W) + l2 W),   G[k,s] = sum_d w_d [pout[d,k] == s, s < out_sp]
+//   bias_grad[k] = sum_d w_d * beta[d,k]
+// Blocks 0 .. gblocks-1 own PU_ROWS output rows each: the rows' slice of G is built in shared memory with
+// shared-memory atomics straight from the permutation table (no histogram in global memory, nothing to
+// clear), then every thread walks eps down a column e with the PU_ROWS histogram values of each noise row
+// read as two broadcast 128-bit loads.  The remaining blocks own 32 columns of the bias gradient each.
+constexpr int PU_ROWS = 8, PU_THREADS = 256;
+
+__global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
+    const float* __restrict__ eps, const float* __restrict__ w, const int16_t* __restrict__ pout,
+    const float* __restrict__ weight, const float* __restrict__ beta, float* __restrict__ grad,
+    float* __restrict__ bias_grad, int64_t D, int out, int out_sp, int64_t inner, int gblocks, float l1, float l2) {
+  extern __shared__ __align__(16) float pu_smem[];
+  const int t = threadIdx.x;
+  if (int(blockIdx.x) >= gblocks) {
+    // ---- bias gradient: 32 columns, eight member lanes, tree over the lanes
+    const int c = (int(blockIdx.x) - gblocks) * 32 + (t & 31);
+    const int lane_d = t >> 5;
+    float acc = 0.f;
+    if (c < out)
+      for (int64_t d = lane_d; d < D; d += PU_THREADS / 32) acc = fmaf(__ldg(w + d), __ldg(beta + d * out + c), acc);
+    pu_smem[t] = acc;
+    __syncthreads();
+    if (t < 32 && c < out) {
+      float s = 0.f;
+#pragma unroll
+      for (int u = 0; u < PU_THREADS / 32; ++u) s += pu_smem[u * 32 + t];
+      bias_grad[c] = s;
+    }
+    return;
+  }
+  float* Gs = pu_smem;                                  // [out_sp][PU_ROWS]
+  const int k0 = blockIdx.x * PU_ROWS;
+  for (int i = t; i < out_sp * PU_ROWS; i += PU_THREADS) Gs[i] = 0.f;
+  __syncthreads();
+  for (int64_t i = t; i < D * PU_ROWS; i += PU_THREADS) {
+    const int64_t d = i / PU_ROWS;
+    const int kk = int(i - d * PU_ROWS);
+    if (k0 + kk < out) {
+      const int s = pout[d * out + k0 + kk];
+      if (s < out_sp) atomicAdd(&Gs[s * PU_ROWS + kk], __ldg(w + d));
+    }
+  }
+  __syncthreads();
+  for (int64_t e = t; e < inner; e += PU_THREADS) {
+    float a[PU_ROWS];
+#pragma unroll
+    for (int u = 0; u < PU_ROWS; ++u) a[u] = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < out_sp; ++s) {
+      const float ev = __ldg(eps + int64_t(s) * inner + e);
+      const float4 g0 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS);
+      const float4 g1 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS + 4);
+      a[0] = fmaf(g0.x, ev, a[0]); a[1] = fmaf(g0.y, ev, a[1]); a[2] = fmaf(g0.z, ev, a[2]); a[3] = fmaf(g0.w, ev, a[3]);
+      a[4] = fmaf(g1.x, ev, a[4]); a[5] = fmaf(g1.y, ev, a[5]); a[6] = fmaf(g1.z, ev, a[6]); a[7] = fmaf(g1.w, ev, a[7]);
+    }
+#pragma unroll
+    for (int u = 0; u < PU_ROWS; ++u) {
+      if (k0 + u >= out) break;
+      const int64_t o = int64_t(k0 + u) * inner + e;
+      float v = a[u];
+      if (weight) {
+        const float wv = __ldg(weight + o);
+        if (l1 != 0.f) v += l1 * ((wv > 0.f) - (wv < 0.f));
+        if (l2 != 0.f) v += l2 * wv;
+      }
+      grad[o] = v;
+    }
+  }
 }
 
 // grad[k,m,t] = sum_j eps[k,j,t] * H[j,m]      (in-only)
@@ -250,25 +329,36 @@ static int finish(const float* partial, int splits, const float* weight, float* 
 
 using namespace nes;
 
-extern "C" int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n) {
+// Workspace of the widest plan the reduction can choose for (D, n): the 128-bit form when the pointers allow
+// it, the scalar form (four times as many column blocks, possibly another split count) when they do not.
+static int64_t update_scratch_floats(int64_t D, int64_t n) {
   if (D <= 0 || n <= 0) return 0;
-  const UpdatePlan p = plan_update(D, n, n % 4 == 0);
-  return (p.splits > 1 ? p.splits : 0) * n * (int64_t)sizeof(float);
+  int64_t need = 0;
+  const UpdatePlan ps = plan_update(D, n, false);
+  if (ps.splits > 1) need = int64_t(ps.splits) * n;
+  if (n % 4 == 0) {
+    const UpdatePlan pv = plan_update(D, n, true);
+    if (pv.splits > 1 && int64_t(pv.splits) * n > need) need = int64_t(pv.splits) * n;
+  }
+  return need;
 }
 
-extern "C" int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
-                                    int64_t D, int64_t n, float l1, float l2,
-                                    void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+extern "C" int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n) {
+  return update_scratch_floats(D, n) * (int64_t)sizeof(float);
+}
+
+static int run_perturbed_update(const float* noise, const float* w, const float* sub, const float* weight, float* grad,
+                                int64_t D, int64_t n, float l1, float l2, void* scratch, int64_t scratch_bytes,
+                                cudaStream_t st) {
   NES_REQUIRE(D >= 0 && n >= 0, NES_ERR_BAD_ARG, "perturbed_update: negative extent");
   if (n == 0) return NES_OK;
   NES_REQUIRE(grad && (D == 0 || (noise && w)), NES_ERR_BAD_ARG, "perturbed_update: null pointer");
   NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "perturbed_update: l1/l2 given without weight");
-  cudaStream_t st = as_stream(stream);
   if (D == 0) {
     cudaMemsetAsync(grad, 0, n * sizeof(float), st);
     return finish(nullptr, 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
   }
-  const bool vec = (n % 4 == 0) && aligned16(noise) && aligned16(grad) && aligned16(scratch);
+  const bool vec = (n % 4 == 0) && aligned16(noise) && aligned16(grad) && aligned16(scratch) && (!sub || aligned16(sub));
   const UpdatePlan p = plan_update(D, n, vec);
   NES_REQUIRE(p.bx <= INT32_MAX, NES_ERR_UNSUPPORTED, "perturbed_update: n too large");
   float* dst = grad;
@@ -278,11 +368,29 @@ extern "C" int nes_perturbed_update(const float* noise, const float* w, const fl
     dst = static_cast<float*>(scratch);
   }
   dim3 grid((unsigned)p.bx, (unsigned)p.splits);
-  if (vec) weighted_noise_sum_kernel<true><<<grid, UPD_THREADS, 0, st>>>(noise, w, dst, D, n, p.d_per_split);
-  else weighted_noise_sum_kernel<false><<<grid, UPD_THREADS, 0, st>>>(noise, w, dst, D, n, p.d_per_split);
+  if (sub) {
+    if (vec) weighted_noise_sum_kernel<true, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split);
+    else weighted_noise_sum_kernel<false, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split);
+  } else {
+    if (vec) weighted_noise_sum_kernel<true, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split);
+    else weighted_noise_sum_kernel<false, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split);
+  }
   int rc = check_launch("perturbed_update");
   if (rc != NES_OK) return rc;
   return finish(dst, p.splits > 1 ? p.splits : 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
+}
+
+extern "C" int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
+                                    int64_t D, int64_t n, float l1, float l2,
+                                    void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return run_perturbed_update(noise, w, nullptr, weight, grad, D, n, l1, l2, scratch, scratch_bytes, as_stream(stream));
+}
+
+extern "C" int nes_perturbed_update_direct(const float* stored, const float* w, const float* param, const float* weight,
+                                           float* grad, int64_t D, int64_t n, float l1, float l2,
+                                           void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  NES_REQUIRE(param != nullptr || n == 0, NES_ERR_BAD_ARG, "perturbed_update_direct: null parameter");
+  return run_perturbed_update(stored, w, param, weight, grad, D, n, l1, l2, scratch, scratch_bytes, as_stream(stream));
 }
 
 // ---- the same reduction for callers that cannot supply a workspace -------------------------
@@ -314,11 +422,8 @@ extern "C" int nes_perturbed_update_noalloc(const float* noise, const float* w, 
                                             int64_t D, int64_t n, float l1, float l2, nes_stream_t stream) {
   NES_REQUIRE(D >= 0 && n >= 0, NES_ERR_BAD_ARG, "perturbed_update_noalloc: negative extent");
   if (n == 0) return NES_OK;
-  int64_t need_floats = 0;
-  if (D > 0) {
-    const UpdatePlan p = plan_update(D, n, n % 4 == 0);
-    if (p.splits > 1) need_floats = int64_t(p.splits) * n;
-  }
+  // the workspace of whichever plan (128-bit or scalar columns) the pointers' alignment will select
+  const int64_t need_floats = update_scratch_floats(D, n);
   NES_REQUIRE(need_floats <= (int64_t)NES_NOALLOC_SCRATCH_FLOATS, NES_ERR_UNSUPPORTED,
               "perturbed_update_noalloc: D=%lld, n=%lld needs %lld floats of workspace but the built-in one holds %lld; "
               "use nes_perturbed_update with a caller-owned scratch buffer",
@@ -394,6 +499,31 @@ extern "C" int nes_permuted_update(const float* eps, const float* w, const int16
     if (perm_weights_out) cudaMemcpyAsync(perm_weights_out, hist, hn * sizeof(float), cudaMemcpyDeviceToDevice, st);
   }
   return finish(nullptr, 0, weight, grad, n, l1, l2, st, "permuted_update(finish)");
+}
+
+extern "C" int nes_permuted_update_out(const float* eps, const float* w, const int16_t* pout, const float* weight,
+                                       const float* bias_noise, float* grad, float* bias_grad,
+                                       int64_t D, int in, int out, int out_sp, int ksize, float l1, float l2,
+                                       nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && in > 0 && out > 0 && out_sp > 0 && ksize > 0 && out_sp <= out, NES_ERR_BAD_ARG,
+              "permuted_update_out: bad extent");
+  NES_REQUIRE(eps && grad && pout && (D == 0 || w), NES_ERR_BAD_ARG, "permuted_update_out: null pointer");
+  NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "permuted_update_out: l1/l2 given without weight");
+  NES_REQUIRE((bias_noise == nullptr) == (bias_grad == nullptr), NES_ERR_BAD_ARG,
+              "permuted_update_out: bias_noise and bias_grad go together");
+  const size_t smem = size_t(out_sp) * PU_ROWS * sizeof(float);
+  NES_REQUIRE(smem <= 200 * 1024, NES_ERR_UNSUPPORTED, "permuted_update_out: out_sp=%d needs %zu B of shared memory", out_sp, smem);
+  const size_t smem_all = smem > PU_THREADS * sizeof(float) ? smem : PU_THREADS * sizeof(float);
+  if (smem_all > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(permuted_update_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_all);
+    if (e != cudaSuccess) return fail(NES_ERR_UNSUPPORTED, "permuted_update_out: %zu B of shared memory refused", smem_all);
+  }
+  const int gblocks = ceil_div(out, PU_ROWS);
+  const int bblocks = bias_grad ? ceil_div(out, 32) : 0;
+  permuted_update_out_kernel<<<gblocks + bblocks, PU_THREADS, smem_all, as_stream(stream)>>>(
+      eps, w, pout, (l1 != 0.f || l2 != 0.f) ? weight : nullptr, bias_noise, grad, bias_grad, D, out, out_sp,
+      int64_t(in) * ksize, gblocks, l1, l2);
+  return check_launch("permuted_update_out");
 }
 
 extern "C" int nes_sparse_perturbed_update(const int32_t* idx, const float* val, const float* w,

@@ -21,6 +21,27 @@ def centered_ranks(fitness):
     return ranks / max(n - 1, 1) - 0.5
 
 
+def update_weights(fitness, noise_scale=None, lr_scale=1.0):
+    """Per-member weights handed to ``update`` so that ``.grad`` is a DESCENT direction of the loss, as in the
+    reference's trainer: there ``update`` receives ``(loss - loss.mean()) * lr_scale / noise_scale``
+    (``mnisttest.py:136-146``), ``.grad`` estimates +grad(loss) and ``torch.optim.SGD.step()`` descends.
+
+    Here the fitness is the NEGATIVE loss and is rank-normalised, so the weights are
+    ``-centered_ranks(fitness) * lr_scale / noise_scale``: the members with the highest loss (lowest fitness)
+    get the largest positive weights.  ``noise_scale=None`` leaves the division out."""
+    w = -centered_ranks(fitness)
+    scale = float(lr_scale) / float(noise_scale) if noise_scale else float(lr_scale)
+    return w if scale == 1.0 else w * scale
+
+
+def model_noise_scale(perturbed_model):
+    """The noise scale the model's perturbed layers are set to (that of the first layer that has one)."""
+    for layer in perturbed_model.perturbed_layers:
+        if getattr(layer, "noise_scale", None):
+            return layer.noise_scale
+    return None
+
+
 def takes_shared_input(perturbed_model):
     """True when the model's first perturbed layer declares ``options["shared_input"]``: it then receives the
     minibatch itself instead of its copy per member."""
@@ -103,12 +124,24 @@ class _Null:
 
 
 def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk=None, bucket=None, group=None,
-            new_noise=True, population=None, reseed=True, streams=1):
+            new_noise=True, population=None, reseed=True, streams=1, lr_scale=1.0):
     """set_noise -> fitness of the local members -> global centred ranks -> local update -> one all-reduce.
 
     ``directions`` is the number of members owned by this rank; ``population`` (optional) the number of members
     over all ranks, split as :func:`nesgpu_b200.dist.member_slice` does.  Returns (local fitness, bucket); the
-    full-population gradient is left in ``.grad`` of the model's parameters on every rank."""
+    full-population gradient is left in ``.grad`` of the model's parameters on every rank.  It is a descent
+    gradient (see :func:`update_weights`): follow the step with an ordinary minimising optimiser
+    (``torch.optim.SGD(...).step()``), as the reference's trainer does.
+
+    With ``population`` given and more than one rank, every layer is told the global index of its first member
+    (``set_member_offset``), so that ranks which share seeds still draw different members: the population is then
+    ``population`` distinct members, not copies of one rank's slice.  Layers must share their seeds across ranks
+    for the noise that all members share (``Permuted`` / ``Synthetic`` weight noise): seed Python's ``random``
+    identically on all ranks, or pass ``reseed=False`` after setting the same seeds everywhere."""
+    rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
+    world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
+    if population is not None:
+        perturbed_model.set_member_offset(ndist.member_slice(population, rank, world)[0])
     if new_noise:
         # noise is a pure function of each layer's seed, so a step draws new seeds first, as the reference's
         # trainer does (mnisttest.py:128-131); reseed=False keeps the seeds that are set
@@ -116,12 +149,10 @@ def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk
             perturbed_model.set_seed()
         perturbed_model.set_noise(noise_scale)
     fitness = population_fitness(perturbed_model, inputs, labels, directions, chunk, streams)
-    rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
-    world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
     # with the population size given, every rank knows the split and the step needs no host synchronisation
     known = None if population is None else [hi - lo for lo, hi in (ndist.member_slice(population, r, world) for r in range(world))]
     everyone = ndist.gather_fitness(fitness, group, known)
-    weights_all = centered_ranks(everyone)
+    weights_all = update_weights(everyone, model_noise_scale(perturbed_model), lr_scale)
     # ranks own contiguous member slices in rank order (sizes may differ by one)
     sizes = [ndist.member_slice(everyone.numel(), r, world) for r in range(world)]
     lo, hi = sizes[rank]

@@ -51,8 +51,11 @@ def test_es_step_small_population():
     ce = F.cross_entropy(logits, labels.cpu().repeat_interleave(D), reduction="none").view(R, D)
     want_fit = -ce.mean(dim=0)
     assert_close(fitness, want_fit, tol=1e-4, what="fitness")
-    w = O.centered_ranks(want_fit)
-    assert torch.equal(es.centered_ranks(fitness).cpu(), w)
+    assert torch.equal(es.centered_ranks(fitness).cpu(), O.centered_ranks(want_fit))
+    # .grad is a descent gradient: the reference's trainer weights members by (loss - mean) / noise_scale
+    # (mnisttest.py:141-146); with rank-normalised negative loss that is -ranks / noise_scale
+    w = -O.centered_ranks(want_fit) / 0.02
+    assert torch.allclose(es.update_weights(fitness, 0.02).cpu(), w, rtol=1e-6, atol=0)
     c = lambda t: None if t is None else t.detach().cpu()
     for layer in pm.perturbed_layers:
         if type(layer).__name__ == "PermutedConv2d":
@@ -153,3 +156,62 @@ def test_population_fitness_on_two_streams_equals_one_stream():
     three = es.population_fitness(pm, images, labels, D, chunk=3, streams=3)
     torch.cuda.synchronize()
     assert rel_err(two, one.cpu()) <= 1e-6 and rel_err(three, one.cpu()) <= 1e-6
+
+
+def test_es_steps_followed_by_sgd_lower_the_loss():
+    """.grad left by es_step is a descent direction: a few steps of plain SGD (minimising, as the reference's trainer
+    uses, mnisttest.py:108,152) must lower the mean cross-entropy of the unperturbed network."""
+    from nesgpu_b200 import base, es
+    import random
+    D, R = 256, 64
+    torch.manual_seed(4)
+    random.seed(4)
+    net = torch.nn.Sequential(base.PermutedLinear(32, 64, D), torch.nn.ReLU(), base.PermutedLinear(64, 10, D)).to(DEV)
+    pm = base.PerturbedModel(net, D)
+    pm.set_noise_scale(0.05)
+    x = torch.randn(R, 32, device=DEV)
+    labels = torch.randint(10, (R,), device=DEV)
+    opt = torch.optim.SGD(net.parameters(), lr=0.02)
+    with torch.no_grad():
+        before = F.cross_entropy(net(x), labels).item()
+    for _ in range(10):
+        es.es_step(pm, x, labels, D)
+        opt.step()
+        opt.zero_grad()
+    with torch.no_grad():
+        after = F.cross_entropy(net(x), labels).item()
+    assert after < before - 0.05, (before, after)
+
+
+def test_member_offset_gives_each_rank_its_slice_of_the_population():
+    """Two "ranks" with the same seeds and member offsets 0 and 4 draw exactly the members 0-3 and 4-7 of an
+    8-member layer (per-member tensors); the noise that all members share is identical everywhere."""
+    from nesgpu_b200 import base
+    whole = base.PermutedLinear(64, 48, 8, permutation="both").to(DEV)
+    whole.set_seed(77)
+    whole.set_noise(0.1)
+    dense = base.PerturbedLinear(16, 8, 8).to(DEV)
+    dense.set_seed(78)
+    dense.set_noise(0.1)
+    for lo in (0, 4):
+        part = base.PermutedLinear(64, 48, 4, permutation="both").to(DEV)
+        part.set_seed(77)
+        part.set_member_offset(lo)
+        part.set_noise(0.1)
+        assert torch.equal(part.weight_noise, whole.weight_noise)
+        assert torch.equal(part.bias_noise, whole.bias_noise[lo:lo + 4])
+        assert torch.equal(part.input_permutations, whole.input_permutations[lo:lo + 4])
+        assert torch.equal(part.output_permutations, whole.output_permutations[lo:lo + 4])
+        dpart = base.PerturbedLinear(16, 8, 4).to(DEV)
+        dpart.set_seed(78)
+        dpart.set_member_offset(lo)
+        dpart.set_noise(0.1)
+        assert torch.equal(dpart.weight_noise, dense.weight_noise[lo:lo + 4])
+        assert torch.equal(dpart.bias_noise, dense.bias_noise[lo:lo + 4])
+    # rows that are not whole generator groups: the slices are not reproduced, but ranks never share draws
+    odd_a, odd_b = base.PerturbedLinear(3, 3, 4).to(DEV), base.PerturbedLinear(3, 3, 4).to(DEV)
+    for layer, lo in ((odd_a, 0), (odd_b, 4)):
+        layer.set_seed(5)
+        layer.set_member_offset(lo)
+        layer.set_noise(0.1)
+    assert not torch.isin(odd_a.weight_noise.flatten(), odd_b.weight_noise.flatten()).any()

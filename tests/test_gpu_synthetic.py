@@ -109,8 +109,9 @@ def test_synthetic_set_noise_and_affine(base, perturbed_golden):
         aff.perturbed_flag = False
         grad, bgrad = aff.update(G(c["w"]))
     assert_close(y, c["y"], what="affine forward")
-    assert_close(grad, c["grad"], tol=1e-3, what="affine grad")       # (noise + W) - W cancellation in fp32
-    assert_close(bgrad, c["bias_grad"], tol=1e-3, what="affine bias grad")
+    # the stored tensors are W + noise; the kernel subtracts W row by row, as the reference does, so the fp32 bar holds
+    assert_close(grad, c["grad"], what="affine grad")
+    assert_close(bgrad, c["bias_grad"], what="affine bias grad")
     aff.set_seed(1)
     aff.set_noise(0.1)
     assert aff.weight_noise.shape == (m["D"],) + tuple(m["shape"])

@@ -453,3 +453,81 @@ def test_pair_kernel_full_size_matches_single_image_kernel():
     assert rel_err(y2, y1.cpu()) <= 1e-3
     # every image of every block was written (no stale rows): compare a few single images exactly in structure
     assert torch.isfinite(y2).all() and (y2 >= 0).all()
+
+
+# ------------------------------------------------------------------ output-permuted PermutedLinear, one cluster kernel
+
+def _perm_out_case(D, R, in_f, out_f, out_sp, seed, bias=True, beta=True, identity=False, antithetic=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(R * D, in_f, generator=g)
+    W = torch.randn(out_f, in_f, generator=g) / in_f ** .5
+    b = torch.randn(out_f, generator=g) if bias else None
+    eps = 0.05 * torch.randn(out_sp, in_f, generator=g)
+    bn = 0.02 * torch.randn(D, out_f, generator=g) if beta else None
+    pout = None if identity else torch.stack([torch.randperm(out_f, generator=g) for _ in range(D)]).short()
+    return x, W, b, eps, bn, pout
+
+
+def _perm_out_run(C, case, D, R, mode, antithetic=True):
+    x, W, b, eps, bn, pout = case
+    in_f, out_f, out_sp = x.shape[1], W.shape[0], eps.shape[0]
+    assert C.call("nes_permuted_linear_out_fwd_tc_supported", D, R, in_f, out_f, out_sp, mode) == 1
+    y = torch.full((R * D, out_f), float("nan"), device=DEV)
+    gx, gW, gb, ge, gbn, gp = G(x), G(W), G(b), G(eps), G(bn), G(pout)
+    before = C.call("nes_launch_count")
+    C.call("nes_permuted_linear_out_fwd_tc", C.ptr(gx), C.ptr(gW), C.ptr(gb), C.ptr(ge), C.ptr(gbn), C.ptr(gp), C.ptr(y),
+           D, R, in_f, out_f, out_sp, 1 if antithetic else 0, mode, C.stream())
+    launches = C.call("nes_launch_count") - before
+    torch.cuda.synchronize()
+    return y, launches
+
+
+@pytest.mark.parametrize("D,R,in_f,out_f,out_sp", [
+    (512, 2, 256, 256, 256),      # the 256x256 benchmark layer: four blocks per cluster, 64 + 64 columns each
+    (48, 2, 200, 136, 136),       # K tail (200 = 6 * 32 + 8), ragged column slices
+    (48, 2, 200, 136, 34),        # sparse noise rows: most gathers hit the zero rule
+    (7, 3, 36, 10, 10),           # one partial row tile, a single block per cluster
+    (300, 1, 64, 1000, 500),      # wide layer: eight blocks per cluster
+    (1, 1, 4, 1, 1),
+    (130, 2, 128, 48, 16),
+])
+def test_permuted_linear_out_cluster_kernel_vs_oracle(D, R, in_f, out_f, out_sp):
+    from nesgpu_b200 import _cabi as C
+    from oracle import perturbed_ref as O
+    case = _perm_out_case(D, R, in_f, out_f, out_sp, seed=D + in_f + out_f)
+    x, W, b, eps, bn, pout = case
+    want = O.permuted_linear_forward(x, W, b, eps, bn, None, pout, D, True)
+    base_only = x @ W.t() + b
+    y3, launches = _perm_out_run(C, case, D, R, 3)
+    assert launches == 1                                        # no pre-pass, no scratch: one kernel
+    assert_close(y3, want, tol=1e-4, what="3xTF32")
+    # the perturbation term on its own (it is what the ES update sees) within 1e-3
+    assert_close(y3.cpu() - base_only, want - base_only, tol=1e-3, what="perturbation term")
+    y1, _ = _perm_out_run(C, case, D, R, 1)
+    assert_close(y1, want, tol=2e-2, what="TF32 (stated mode)")
+    assert _flag(C) == 0
+
+
+def test_permuted_linear_out_cluster_kernel_options():
+    """No bias, no bias noise, identity output map (pout NULL), non-antithetic repeats."""
+    from nesgpu_b200 import _cabi as C
+    from oracle import perturbed_ref as O
+    D, R, in_f, out_f = 40, 3, 96, 80
+    for bias, beta, identity, anti in [(False, True, False, True), (True, False, False, False), (True, True, True, True),
+                                       (False, False, True, False)]:
+        case = _perm_out_case(D, R, in_f, out_f, out_f, seed=5, bias=bias, beta=beta, identity=identity)
+        x, W, b, eps, bn, pout = case
+        want = O.permuted_linear_forward(x, W, b, eps, bn, None, pout, D, anti)
+        y, _ = _perm_out_run(C, case, D, R, 3, antithetic=anti)
+        assert_close(y, want, tol=1e-4, what="bias=%s beta=%s identity=%s anti=%s" % (bias, beta, identity, anti))
+
+
+def test_permuted_linear_out_cluster_kernel_refuses_uncovered_shapes():
+    from nesgpu_b200 import _cabi as C
+    assert C.call("nes_permuted_linear_out_fwd_tc_supported", 8, 1, 30, 16, 16, 3) == 0        # in % 4 != 0
+    assert C.call("nes_permuted_linear_out_fwd_tc_supported", 8, 1, 32, 2000, 2000, 3) == 0    # out + out_sp > 2048
+    assert C.call("nes_permuted_linear_out_fwd_tc_supported", 8, 1, 32, 16, 16, 2) == 0        # no bf16 form
+    d = torch.zeros(64, device=DEV)
+    with pytest.raises(NotImplementedError):
+        C.call("nes_permuted_linear_out_fwd_tc", C.ptr(d), C.ptr(d), None, C.ptr(d), None, None, C.ptr(d),
+               8, 1, 30, 16, 16, 0, 3, C.stream())
