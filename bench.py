@@ -12,9 +12,13 @@ and the update is summed with one NCCL all-reduce.  Other workloads: ``permuted_
 One JSON line is printed by rank 0.  ``value`` is member-samples per second with inputs
 resident in HBM; ``e2e`` is the same through the layer API with pinned host buffers and the
 host<->device copies inside the timed region; ``roofline`` describes the dominant kernel;
-``cpu_baseline`` is the CPU oracle timed on the host cores on a bounded sample.
-``--impl reference`` times that CPU restatement of the reference's algorithm only (the
-reference is Python and is not present on the GPU box).
+``cpu_baseline`` is the reference's own CPU path (its unmodified ``modules/base.py``, a copy of
+which the build step keeps under ``oracle/_ref``) or, where the reference has none, the CPU
+restatement under ``oracle/``, timed on the host cores on a bounded sample.  The default run adds
+``sustained`` (the same step repeated for at least a second), ``es_step`` (ES steps/s of the small
+CNN), ``per_config`` (the other single-layer configurations) and ``gpu_reference`` (the reference's
+PyTorch layers on the same GPU); at N > 1 ``strong`` (the population of 1024 split over the GPUs)
+and ``allreduce_check``.  ``--impl reference`` runs the CPU arm only.
 """
 import argparse
 import json
@@ -131,13 +135,16 @@ class Workload:
     tc = None                   # tensor-core mode override (--tc)
     units_per_step = 0          # member-samples one rank processes per step
     resident_bytes = 0          # working set touched per step (decides whether L2 must be flushed)
+    cpu_cores = None            # threads the CPU sample uses when it is not torch's pool
 
-    def marks(self):
-        return []
+    def mode(self):
+        """Arithmetic path the layer took (its ``last_path``), or the requested mode."""
+        layer = getattr(self, "layer", None)
+        return getattr(layer, "last_path", None) or self.tc or "default"
 
 
 class PerturbedLinear1024(Workload):
-    """BASELINE configuration 2."""
+    """PerturbedLinear 1024x1024 with 1024 dense Gaussian noise matrices (4 GiB), antithetic: forward + update."""
     name = "perturbed_linear_1024"
     D, R, n = 1024, 2, 1024
 
@@ -258,11 +265,11 @@ class PerturbedLinear1024(Workload):
 
 
 class PermutedLinear256(Workload):
-    """BASELINE configuration 1."""
+    """PermutedLinear 256x256, 512 antithetic pairs sharing one permuted noise matrix: forward + rank-normalised update."""
     name = "permuted_linear_256"
     D, R, n = 512, 2, 256
     use_graph = True            # 134 MFLOP per step: launch-bound, so the resident-data number replays a CUDA graph
-    launches_per_step = 8       # 2 GEMMs (forward) + histogram, grad, 2 x (sum + finish) for weight / bias (update)
+    launches_per_step = 2       # one cluster kernel (forward) + one update kernel (weight and bias gradient)
 
     def __init__(self):
         self.units_per_step = self.D * self.R
@@ -329,12 +336,13 @@ class PermutedLinear256(Workload):
         phase_ms = dict(phase_ms, forward=fwd_ms)
         ach = flops / (fwd_ms * 1e-3) / 1e12
         peak = peaks["bf16"] / 2
-        return {"kernel": "gemm_kernel x2 (noise GEMM + base GEMM with permuted epilogue)" +
+        return {"kernel": "permuted_linear_out_kernel<3> (tcgen05 3xTF32, stacked [W; eps], cluster gather epilogue)" +
                           (", forward phase" if "step" not in phase_ms else "; whole graph-replayed step (forward + update) timed"),
                 "bound": "tensor", "achieved": round(ach, 3), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(ach / peak, 5), "peak_source": peaks["source"] + " bf16 burst / 2 taken as TF32",
                 "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 4), "traffic": None,
-                "note": "134 MFLOP / 3.4 MB per step: launch-latency bound; fp32 CUDA-core path"}
+                "note": "134 MFLOP / 3.4 MB per step: latency bound (32 blocks, 8 K stages each); the tensor pipe issues 6x the "
+                        "algorithmic flops (stacked product x 3xTF32 terms)"}
 
     def cpu_sample(self, reps):
         from oracle import perturbed_ref as O
@@ -354,7 +362,7 @@ class PermutedLinear256(Workload):
 
 
 class PermutedConv64(Workload):
-    """BASELINE configuration 3."""
+    """PermutedConv2d 64 -> 64 channels, 3x3, 32x32 input, 1024 members, out_sparsity 0.5: forward + update."""
     name = "permuted_conv_64"
     D, c, hw = 1024, 64, 32
 
@@ -375,7 +383,7 @@ class PermutedConv64(Workload):
         self.ndist, self.world = ndist, world
         g = torch.Generator().manual_seed(1003 + rank)
         self.layer = base.PermutedConv2d(self.c, self.c, 3, self.D, padding=1, out_sparsity=.5,
-                                         options={"tc": self.tc or "fp32"}).to(dev)
+                                         options={"tc": self.tc} if self.tc else {}).to(dev)
         with torch.no_grad():
             self.layer.weight.copy_(torch.randn(self.c, self.c, 3, 3, generator=g) * (2 / 576) ** .5)
             self.layer.bias.zero_()
@@ -422,18 +430,20 @@ class PermutedConv64(Workload):
     def roofline(self, phase_ms, peaks):
         flops = 2.0 * self.D * self.hw * self.hw * self.c * 9 * self.c
         ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
-        peak = peaks["bf16_sustained"] / 2
-        mode = self.layer.options.get("tc")
-        tf32 = mode in ("tf32", "bf16")
-        if mode == "bf16":
-            peak = peaks["bf16_sustained"]
-        return {"kernel": ("conv_%s_kernel (tcgen05) + stage_input_%s_kernel, forward phase" % (mode, mode) if tf32 else
-                           "gemm_kernel<ConvProb<PermutedNoise>> (implicit-GEMM conv, forward phase)"),
-                "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s",
-                "frac": round(ach / peak, 4), "peak_source": peaks["source"] + (" bf16 sustained" if mode == "bf16" else " bf16 sustained / 2 taken as TF32"),
+        mode = self.mode()
+        bf = mode in ("bf16", "bf16x3")
+        peak = peaks["bf16_sustained"] if bf else peaks["bf16_sustained"] / 2
+        kernel = {"tf32": "conv_tf32_kernel (tcgen05 kind::tf32) + stage_input_tf32_kernel",
+                  "bf16": "conv_bf16_kernel<1> (tcgen05 kind::f16) + stage_input_bf16_kernel",
+                  "bf16x3": "conv_bf16_kernel<3> (tcgen05 kind::f16, three products on bf16 hi/lo splits) + stage_input_bf16_kernel",
+                  }.get(mode, "gemm_kernel<ConvProb<...>> (implicit-GEMM conv on CUDA cores)")
+        note = {"tf32": "TF32 operands (stated reduced precision, bar 2e-2)", "bf16": "bf16 operands (stated reduced precision, bar 2e-2)",
+                "bf16x3": "split-bf16 three-product form: holds the fp32 bar (rel err ~5e-6); the tensor pipe issues 3x the algorithmic flops",
+                }.get(mode, "fp32 CUDA-core path (exact-fp32 parity)")
+        return {"kernel": kernel + ", forward phase", "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s",
+                "frac": round(ach / peak, 4), "peak_source": peaks["source"] + (" bf16 sustained" if bf else " bf16 sustained / 2 taken as TF32"),
                 "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 4), "traffic": None,
-                "note": ("%s tensor-core mode (stated reduced precision, bar 2e-2)" % mode if tf32 else
-                         "fp32 CUDA-core path (exact-fp32 parity)") + "; flops counted for the minimal form N=64"}
+                "note": note + "; flops counted for the minimal form N=64"}
 
     def cpu_sample(self, reps):
         from oracle import perturbed_ref as O
@@ -454,9 +464,11 @@ class PermutedConv64(Workload):
 
 
 class Binary1024(Workload):
-    """BASELINE configuration 4."""
+    """Bit-packed layer: 1024 members x 1024x1024 Bernoulli weight bits, one 1024-bit input per member: sample, pack, bmm,
+    weighted sum, max-pool."""
     name = "binary_1024"
     dtype = "u64"
+    cpu_cores = 1
     D = n = 1024
 
     def __init__(self):
@@ -538,8 +550,283 @@ class Binary1024(Workload):
 
 
 
+class PerturbedConv64(PermutedConv64):
+    """PerturbedConv2d with one dense noise filter per member at the shape of the permuted configuration (64 -> 64, 3x3,
+    32x32 input, 1024 members; 144 MiB of noise): forward + update."""
+    name = "perturbed_conv_64"
+
+    def describe(self, world):
+        return dict(PermutedConv64.describe(self, world), layer="PerturbedConv2d(64,64,3,padding=1), dense noise per member")
+
+    def setup(self, dev, rank, world):
+        from nesgpu_b200 import base, dist as ndist
+        self.ndist, self.world = ndist, world
+        g = torch.Generator().manual_seed(1013 + rank)
+        self.layer = base.PerturbedConv2d(self.c, self.c, 3, self.D, padding=1,
+                                          options={"tc": self.tc} if self.tc else {}).to(dev)
+        with torch.no_grad():
+            self.layer.weight.copy_(torch.randn(self.c, self.c, 3, 3, generator=g) * (2 / 576) ** .5)
+            self.layer.bias.zero_()
+        self.layer.set_seed(7100 + rank)
+        self.layer.set_noise(0.02)
+        self.x_host = torch.randn(self.D, self.c, self.hw, self.hw, generator=g).pin_memory()
+        self.w_host = torch.randn(self.D, generator=g).pin_memory()
+        self.x, self.w = self.x_host.to(dev), self.w_host.to(dev)
+        self.y_host = torch.empty_like(self.x_host).pin_memory()
+        self.grad_host = torch.empty(self.c, self.c, 3, 3).pin_memory()
+        self.bucket = None
+        self.h2d = (self.x_host.numel() + self.w_host.numel()) * 4
+        self.d2h = (self.y_host.numel() + self.grad_host.numel()) * 4
+
+    def cpu_sample(self, reps):
+        from oracle import perturbed_ref as O
+        Ds = 64
+        c = lambda t: t.detach().cpu()
+        W, b = c(self.layer.weight), c(self.layer.bias)
+        E, beta = c(self.layer.weight_noise[:Ds]), c(self.layer.bias_noise[:Ds])
+        x, w = self.x_host[:Ds].clone(), self.w_host[:Ds].clone()
+
+        def once():
+            t0 = time.perf_counter()
+            O.perturbed_conv2d_forward(x, W, b, E, beta, Ds, 1, 1, 1, False)
+            O.perturbed_update(W, E, beta, w)
+            return time.perf_counter() - t0
+        once()
+        return Ds, [once() for _ in range(reps)], "64 of 1024 members: forward + update per repetition"
+
+
+class _Linear1024(Workload):
+    """Shared scaffolding of the 1024x1024 linear layers with cheap per-member noise (batch 2048, antithetic)."""
+    D, R, n = 1024, 2, 1024
+    what = ""
+
+    def __init__(self):
+        self.units_per_step = self.D * self.R
+        self.resident_bytes = 4 * (2 * self.D * self.R * self.n + 2 * self.n * self.n)
+
+    def describe(self, world):
+        return {"workload": self.name, "layer": self.what, "directions_per_gpu": self.D, "population": self.D * world,
+                "batch_per_gpu": self.D * self.R, "antithetic": True, "step": "forward + update",
+                "l2": "L2 flushed between timed steps", "sharding": "members"}
+
+    def make_layer(self, base, dev):
+        raise NotImplementedError
+
+    def setup(self, dev, rank, world):
+        from nesgpu_b200 import base
+        self.world = world
+        g = torch.Generator().manual_seed(1020 + rank)
+        self.layer = self.make_layer(base, dev)
+        with torch.no_grad():
+            self.layer.weight.copy_(torch.randn(self.n, self.n, generator=g) / self.n ** .5)
+            self.layer.bias.zero_()
+        self.layer.set_seed(7200 + rank)
+        self.layer.set_noise(0.02)
+        self.x_host = torch.randn(self.D * self.R, self.n, generator=g).pin_memory()
+        self.w_host = (torch.rand(self.D, generator=g) * 2 - 1).pin_memory()
+        self.x, self.w = self.x_host.to(dev), self.w_host.to(dev)
+        self.y_host = torch.empty(self.D * self.R, self.n).pin_memory()
+        self.grad_host = torch.empty(self.n, self.n).pin_memory()
+        self.h2d = (self.x_host.numel() + self.w_host.numel()) * 4
+        self.d2h = (self.y_host.numel() + self.grad_host.numel()) * 4
+
+    def step(self, mark):
+        with torch.no_grad():
+            self.layer.perturbed_flag = True
+            y = self.layer.forward(self.x)
+            self.layer.perturbed_flag = False
+            mark("forward")
+            self.layer.weight.grad = None
+            self.layer.bias.grad = None
+            self.layer.update(self.w)
+            mark("update")
+        return y, self.layer.weight.grad
+
+    def step_e2e(self):
+        with torch.no_grad():
+            self.x.copy_(self.x_host, non_blocking=True)
+            self.w.copy_(self.w_host, non_blocking=True)
+            y, g = self.step(lambda name: None)
+            self.y_host.copy_(y, non_blocking=True)
+            self.grad_host.copy_(g, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def roofline(self, phase_ms, peaks):
+        flops = 2.0 * self.D * self.R * self.n * self.n
+        ach = flops / (phase_ms["forward"] * 1e-3) / 1e12
+        peak = peaks["bf16"] / 2
+        return {"kernel": self.kernels + ", forward phase", "bound": "tensor", "achieved": round(ach, 2), "peak": peak,
+                "unit": "TFLOP/s", "frac": round(ach / peak, 4), "peak_source": peaks["source"] + " bf16 burst / 2 taken as TF32",
+                "algorithmic_flops_per_launch": flops, "ms_per_launch": round(phase_ms["forward"], 4), "traffic": None,
+                "note": "flops of the base product x.W^T only (4.3 GFLOP); the per-member term is O(batch * out * k)"}
+
+
+class SparseLinear1024(_Linear1024):
+    """SparsePerturbedLinear(1024,1024), k = 2 noise entries per member and output row (the README's sparse variant)."""
+    name = "sparse_linear_1024"
+    what = "SparsePerturbedLinear(1024,1024,k=2)"
+    kernels = "gemm_tf32_kernel<3> (tcgen05 3xTF32 base product) + sparse_noise_kernel"
+
+    def make_layer(self, base, dev):
+        return base.SparsePerturbedLinear(self.n, self.n, self.D, antithetic=True, k=2,
+                                          options={"tc": self.tc} if self.tc else {}).to(dev)
+
+    def cpu_sample(self, reps):
+        from oracle import perturbed_ref as O
+        Ds = 128
+        c = lambda t: t.detach().cpu()
+        W, b = c(self.layer.weight), c(self.layer.bias)
+        E = O.densify_sparse_noise(c(self.layer.noise_indices[:Ds]).long(), c(self.layer.weight_noise[:Ds]), self.n)
+        beta = c(self.layer.bias_noise[:Ds])
+        x = torch.cat([self.x_host[:Ds], self.x_host[self.D:self.D + Ds]]).clone()
+        w = self.w_host[:Ds].clone()
+
+        def once():
+            t0 = time.perf_counter()
+            O.perturbed_linear_forward(x, W, b, E, beta, Ds, True)
+            O.perturbed_update(W, E, beta, w)
+            return time.perf_counter() - t0
+        once()
+        return Ds * self.R, [once() for _ in range(reps)], "128 of 1024 members on the densified noise: forward + update per repetition"
+
+
+class SyntheticLinear1024(_Linear1024):
+    """SyntheticLinear(1024,1024): one shared noise matrix, per-member sign flips (the reference paper's fastest sampler)."""
+    name = "synthetic_linear_1024"
+    what = "SyntheticLinear(1024,1024) auto->out flips"
+    kernels = "synthetic_linear kernels"
+
+    def make_layer(self, base, dev):
+        return base.SyntheticLinear(self.n, self.n, self.D, antithetic=True,
+                                    options={"tc": self.tc} if self.tc else {}).to(dev)
+
+    def cpu_sample(self, reps):
+        from oracle import perturbed_ref as O
+        c = lambda t: None if t is None else t.detach().cpu()
+        L = self.layer
+        W, b, eps, beta, fin, fout = c(L.weight), c(L.bias), c(L.weight_noise), c(L.bias_noise), c(L.input_flips), c(L.output_flips)
+        x, w = self.x_host.clone(), self.w_host.clone()
+
+        def once():
+            t0 = time.perf_counter()
+            O.synthetic_linear_forward(x, W, b, eps, beta, fin, fout, self.D, True)
+            O.synthetic_weight_grad(eps, w, fin, fout)
+            return time.perf_counter() - t0
+        once()
+        return self.D * self.R, [once() for _ in range(reps)], "full configuration: forward + update per repetition"
+
+
+class BinaryBmm64(Workload):
+    """General bit-packed bmm: 1024 members, 1024 x 1024-bit weights against 64 packed input columns each."""
+    name = "binary_bmm_n64"
+    dtype = "u64"
+    cpu_cores = 1
+    D, n, N = 1024, 1024, 64
+
+    def __init__(self):
+        self.units_per_step = self.D * self.N
+        self.resident_bytes = self.D * self.n * self.n // 8
+
+    def describe(self, world):
+        return {"workload": self.name, "layer": "bmm of (1024, 1024, 16) by (1024, 16, 64) int64 words -> int32 counts",
+                "directions_per_gpu": self.D, "population": self.D * world, "step": "bmm", "l2": "operands exceed L2",
+                "sharding": "members"}
+
+    def setup(self, dev, rank, world):
+        import nesgpu_b200.boolean_operations as ops
+        self.ops = ops
+        g = torch.Generator().manual_seed(1030 + rank)
+        self.A = torch.randint(-2 ** 62, 2 ** 62, (self.D, self.n, self.n // 64), generator=g).to(dev)
+        self.B = torch.randint(-2 ** 62, 2 ** 62, (self.D, self.n // 64, self.N), generator=g).to(dev)
+
+    def step(self, mark):
+        c = self.ops.bmm(self.A, self.B)
+        mark("bmm")
+        return c
+
+    def roofline(self, phase_ms, peaks):
+        nbytes = self.A.numel() * 8 + self.B.numel() * 8 + self.D * self.n * self.N * 4
+        ach = nbytes / (phase_ms["bmm"] * 1e-3) / 1e9
+        words = self.D * self.n * (self.n // 64) * self.N
+        return {"kernel": "bin_gemm_kernel (64x64 XOR-popcount tile)", "bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm"],
+                "unit": "GB/s", "frac": round(ach / peaks["hbm"], 4), "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": round(phase_ms["bmm"], 4), "traffic": None,
+                "word_xor_popc_per_s": round(words / (phase_ms["bmm"] * 1e-3), 1),
+                "note": "A 128 MiB + C 256 MiB: the int32 output dominates the traffic"}
+
+    def cpu_sample(self, reps):
+        import numpy as np
+        from oracle import binary_ref as B
+        Ds = 8
+        rng = np.random.default_rng(4)
+        A = rng.integers(-2 ** 62, 2 ** 62, (Ds, self.n, self.n // 64), dtype=np.int64)
+        Bm = rng.integers(-2 ** 62, 2 ** 62, (Ds, self.n // 64, self.N), dtype=np.int64)
+
+        def once():
+            t0 = time.perf_counter()
+            B.bmm(A, Bm)
+            return time.perf_counter() - t0
+        return Ds * self.N, [once() for _ in range(max(1, min(reps, 2)))], "8 of 1024 members (numpy port, single thread)"
+
+
+class BinaryConv512(Workload):
+    """Bit-packed convolution at the shape the reference's own timing script uses (booloptests.py:231-236): 128 members,
+    512 -> 512 channels, 3x3, 7x7 input, padding 1."""
+    name = "binary_conv_512"
+    dtype = "u32"
+    cpu_cores = 1
+    P, cin, cout, hw = 128, 512, 512, 7
+
+    def __init__(self):
+        self.units_per_step = self.P
+        self.resident_bytes = self.P * 9 * (self.cin // 32) * self.cout * 4
+
+    def describe(self, world):
+        return {"workload": self.name, "layer": "binary conv 512->512, 3x3, pad 1, 7x7 input, int32 words, per-member filters",
+                "directions_per_gpu": self.P, "population": self.P * world, "step": "conv (im2col-free)",
+                "l2": "L2 flushed between timed steps", "sharding": "members"}
+
+    def setup(self, dev, rank, world):
+        import nesgpu_b200.boolean_operations as ops
+        self.ops = ops
+        g = torch.Generator().manual_seed(1031 + rank)
+        cw = self.cin // 32
+        self.x = torch.randint(-2 ** 31, 2 ** 31 - 1, (self.P, self.hw, self.hw, cw), generator=g, dtype=torch.int64).int().to(dev)
+        self.f = torch.randint(-2 ** 31, 2 ** 31 - 1, (self.P, 9 * cw, self.cout), generator=g, dtype=torch.int64).int().to(dev)
+
+    def step(self, mark):
+        c = self.ops.conv(self.x, self.f, 3, 3, 1, 1, 1, 1)
+        mark("conv")
+        return c
+
+    def roofline(self, phase_ms, peaks):
+        nbytes = self.x.numel() * 4 + self.f.numel() * 4 + self.P * self.hw * self.hw * self.cout * 4
+        ach = nbytes / (phase_ms["conv"] * 1e-3) / 1e9
+        words = self.P * self.hw * self.hw * 9 * (self.cin // 32) * self.cout
+        return {"kernel": "bin_gemm_kernel<WindowA> (im2col-free XOR-popcount conv)", "bound": "hbm", "achieved": round(ach, 1),
+                "peak": peaks["hbm"], "unit": "GB/s", "frac": round(ach / peaks["hbm"], 4), "peak_source": peaks["source"],
+                "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": round(phase_ms["conv"], 4), "traffic": None,
+                "word_xor_popc_per_s": round(words / (phase_ms["conv"] * 1e-3), 1),
+                "note": "filters 36 MiB + counts 12.3 MiB; 0.46 G word operations on 49 positions per member"}
+
+    def cpu_sample(self, reps):
+        import numpy as np
+        from oracle import binary_ref as B
+        Ps = 4
+        rng = np.random.default_rng(5)
+        cw = self.cin // 32
+        x = rng.integers(-2 ** 31, 2 ** 31 - 1, (Ps, self.hw, self.hw, cw)).astype(np.int32)
+        f = rng.integers(-2 ** 31, 2 ** 31 - 1, (Ps, 9 * cw, self.cout)).astype(np.int32)
+
+        def once():
+            t0 = time.perf_counter()
+            B.conv(x, f, 3, 3, 1, 1, 1, 1)
+            return time.perf_counter() - t0
+        return Ps, [once() for _ in range(max(1, min(reps, 2)))], "4 of 128 members (numpy port, single thread)"
+
+
 class EsCnn(Workload):
-    """BASELINE configuration 5: one ES step of the small CNN, 1024 members per GPU (8192 over 8 GPUs)."""
+    """One ES step of the small CNN (Conv-ReLU-Pool x 2, two linear layers), 1024 members per GPU (8192 over 8 GPUs)."""
     name = "es_cnn_8192"
     D, R = 1024, 256
     fused = True                  # --unfused: module-by-module Conv / ReLU / MaxPool2d, per-member input copies
@@ -565,7 +852,7 @@ class EsCnn(Workload):
         D = self.D
         torch.manual_seed(1005)       # same initial weights on every rank
         if self.tc is None:
-            self.tc = "tf32"       # default for this workload: the stated TF32 tensor-core mode (--tc fp32 for CUDA cores)
+            self.tc = "tf32"       # default for this workload: the stated TF32 tensor-core mode (--tc fp32 holds the fp32 bar)
         self.dtype = {"tf32": "tf32", "bf16": "bf16"}.get(self.tc, "f32")
         opts = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}
         lin = {"tc": self.tc} if self.tc in ("tf32", "bf16") else {}  # the stated reduced-precision modes cover the linear layers
@@ -614,7 +901,7 @@ class EsCnn(Workload):
         from nesgpu_b200 import dist as ndist
         sizes = [self.D] * self.world if self.world > 1 else None      # equal slices: no size exchange, no host sync
         everyone = ndist.gather_fitness(fit, sizes=sizes)
-        w_all = self.es.centered_ranks(everyone)
+        w_all = self.es.update_weights(everyone, 0.02)
         rank = torch.distributed.get_rank() if self.world > 1 else 0
         lo, hi = ndist.member_slice(everyone.numel(), rank, self.world)
         for p in self.net.parameters():
@@ -688,56 +975,431 @@ class EsCnn(Workload):
         return Ds * Rs, [once() for _ in range(reps)], "16 members x 32 images of the same net: forward + CE + ranks + update per repetition"
 
 
-WORKLOADS = {w.name: w for w in (PerturbedLinear1024, PermutedLinear256, PermutedConv64, Binary1024, EsCnn)}
+WORKLOADS = {w.name: w for w in (PerturbedLinear1024, PermutedLinear256, PermutedConv64, PerturbedConv64, SparseLinear1024,
+                                 SyntheticLinear1024, Binary1024, BinaryBmm64, BinaryConv512, EsCnn)}
 
 
 # ---------------------------------------------------------------------------------- runs
 
+UNIT = "member-samples/s"
+METRIC = "perturbed-member samples/sec per layer (forward + update)"
+
+
+def bind_to_gpu_numa_node(local_rank):
+    """Run this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned host buffers it allocates
+    afterwards (first touch) and its copy threads are local to that GPU.  Returns the node or None."""
+    try:
+        props = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return node
+    except (OSError, ValueError, AttributeError):
+        pass
+    return None
+
+
+def _sync_all(world):
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def _max_over_ranks(ms, dev, world):
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return t.item()
+
+
+def _flush_buffer(wl, dev):
+    """L2 flush between timed steps for workloads whose working set fits in L2 twice over."""
+    if wl.resident_bytes < 2 * L2_BYTES:
+        return torch.empty(2 * L2_BYTES // 4, dtype=torch.float32, device=dev)
+    return None
+
+
+def time_steps(wl, steps, warmup, dev, world, use_graph=True, sampler=None):
+    """W untimed steps, then exactly K timed steps between barriers, CUDA events on the launching stream; the time
+    is the max over ranks.  Launch-bound workloads (``wl.use_graph``) replay a captured CUDA graph at N = 1."""
+    from nesgpu_b200 import _cabi
+    flush = _flush_buffer(wl, dev)
+    null_mark = lambda name: None
+    for _ in range(warmup):
+        wl.step(null_mark)
+        if flush is not None:
+            flush.fill_(1.0)
+    _sync_all(world)
+    graph = None
+    if getattr(wl, "use_graph", False) and world == 1 and use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            wl.step(null_mark)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            wl.step(null_mark)
+        for _ in range(3):
+            graph.replay()
+        _sync_all(world)
+    if sampler:
+        sampler.wait_first_sample()
+    names, events = [], []
+    launches0 = _cabi.lib.nes_launch_count()
+    _sync_all(world)
+    if sampler:
+        sampler.begin()
+    t_wall0 = time.perf_counter()
+    for i in range(steps):
+        ev = [torch.cuda.Event(enable_timing=True)]
+        ev[0].record()
+
+        def mark(name, ev=ev, i=i):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            ev.append(e)
+            if i == 0:
+                names.append(name)
+        if graph is not None:
+            graph.replay()
+            mark("step")
+        else:
+            wl.step(mark)
+        events.append(ev)
+        if flush is not None:
+            flush.fill_(1.0)
+    _sync_all(world)
+    wall = time.perf_counter() - t_wall0
+    if sampler:
+        sampler.end()
+    launches = _cabi.lib.nes_launch_count() - launches0
+    total_ms = sum(ev[0].elapsed_time(ev[-1]) for ev in events)
+    if flush is None:      # contiguous region: first start to last end
+        total_ms = events[0][0].elapsed_time(events[-1][-1])
+    phase_ms = {n: statistics.mean(ev[j].elapsed_time(ev[j + 1]) for ev in events) for j, n in enumerate(names)}
+    total_ms = _max_over_ranks(total_ms, dev, world)
+    _cabi.check_device_errors()
+    return {"ms_per_step": total_ms / steps, "phase_ms": phase_ms, "graph": graph, "flush": flush, "wall": wall,
+            "launches": int(launches) if graph is None else int(wl.launches_per_step * steps)}
+
+
+def time_sustained(wl, timing, ms_per_step, dev, world, local_rank, rank, seconds=1.0):
+    """The same step repeated until the block spans at least ``seconds`` (the step count is derived from the
+    headline time, so every rank runs the same number of steps), with clock samples taken inside it."""
+    graph, flush = timing["graph"], timing["flush"]
+    steps = max(10, int(seconds * 1e3 / max(ms_per_step, 1e-3)) + 1)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        sampler.wait_first_sample()
+    null_mark = lambda name: None
+    _sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.begin()
+    e0.record()
+    for _ in range(steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            wl.step(null_mark)
+        if flush is not None:
+            flush.fill_(1.0)
+    e1.record()
+    _sync_all(world)
+    if sampler:
+        sampler.end()
+    ms = _max_over_ranks(e0.elapsed_time(e1), dev, world) / steps
+    out = {"steps": steps, "ms_per_step": round(ms, 4), "seconds": round(ms * steps * 1e-3, 3),
+           "value": round(wl.units_per_step * world / (ms * 1e-3), 1),
+           "clocks": sampler.stop() if sampler else None}
+    if flush is not None:
+        out["note"] = "includes the L2 flush between steps (the headline times the steps only)"
+    return out
+
+
+def time_e2e(wl, steps, dev, world):
+    for _ in range(2):
+        wl.step_e2e()
+    _sync_all(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(steps, 20))
+    e0.record()
+    for _ in range(e2e_steps):
+        wl.step_e2e()
+    e1.record()
+    _sync_all(world)
+    return _max_over_ranks(e0.elapsed_time(e1), dev, world) / e2e_steps, e2e_steps
+
+
+def es_step_extra(dev, rank, world):
+    """The metric's second half, ES steps/s: one ES step of the small CNN (1024 members x 256 images per GPU) timed the
+    same way (5 steps after 3 warm-up steps, barrier on both sides, max over ranks) at the fp32 bar and in the two
+    stated reduced-precision modes."""
+    out = {"workload": "es_cnn_8192", "images_per_member": EsCnn.R, "directions_per_gpu": EsCnn.D,
+           "population": EsCnn.D * world, "steps": 5, "warmup": 3}
+    null_mark = lambda name: None
+    for mode in ("fp32", "tf32", "bf16"):
+        try:
+            es = EsCnn()
+            es.tc = mode
+            es.setup(dev, rank, world)
+            for _ in range(3):
+                es.step(null_mark)
+            _sync_all(world)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(5):
+                es.step(null_mark)
+            a1.record()
+            _sync_all(world)
+            ms = _max_over_ranks(a0.elapsed_time(a1), dev, world) / 5
+            out[mode] = {"ms_per_step": round(ms, 3), "es_steps_per_s": round(1e3 / ms, 2),
+                         "member_image_pairs_per_s": round(es.D * es.R * world / (ms * 1e-3), 1)}
+            del es
+        except Exception as exc:      # the headline line must not depend on this extra
+            out[mode] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+    torch.cuda.empty_cache()
+    return out
+
+
+# the other single-layer configurations, measured in the default run next to the headline (N = 1)
+PER_CONFIG = [
+    ("permuted_linear_256", "permuted_linear_256", None, 200),
+    ("permuted_conv_64", "permuted_conv_64", None, 20),
+    ("permuted_conv_64_tf32", "permuted_conv_64", "tf32", 20),
+    ("permuted_conv_64_bf16", "permuted_conv_64", "bf16", 20),
+    ("perturbed_conv_64", "perturbed_conv_64", None, 20),
+    ("sparse_linear_1024", "sparse_linear_1024", None, 50),
+    ("synthetic_linear_1024", "synthetic_linear_1024", None, 50),
+    ("binary_1024", "binary_1024", None, 30),
+    ("binary_bmm_n64", "binary_bmm_n64", None, 30),
+    ("binary_conv_512", "binary_conv_512", None, 30),
+]
+
+
+def per_config_extra(dev, rank, peaks):
+    out = {}
+    for key, name, tc, steps in PER_CONFIG:
+        if name not in WORKLOADS:
+            continue
+        try:
+            wl = WORKLOADS[name]()
+            wl.tc = tc
+            wl.setup(dev, rank, 1)
+            t = time_steps(wl, steps, 3, dev, 1)
+            e2e_ms, _ = time_e2e(wl, 10, dev, 1) if hasattr(wl, "step_e2e") else (None, 0)
+            entry = {"config": wl.describe(1), "precision_mode": wl.mode(), "steps": steps,
+                     "ms_per_step": round(t["ms_per_step"], 4),
+                     "value": round(wl.units_per_step / (t["ms_per_step"] * 1e-3), 1), "unit": UNIT,
+                     "phase_ms": {k: round(v, 4) for k, v in t["phase_ms"].items()}, "cuda_graph": t["graph"] is not None,
+                     "gpu_launches_per_step": t["launches"] / steps, "roofline": wl.roofline(t["phase_ms"], peaks)}
+            if e2e_ms:
+                entry["e2e"] = {"value": round(wl.units_per_step / (e2e_ms * 1e-3), 1), "ms_per_step": round(e2e_ms, 4),
+                                "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
+            out[key] = entry
+            del wl, t
+        except Exception as exc:
+            out[key] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+        torch.cuda.empty_cache()
+    return out
+
+
+# ---- the reference's own layer file (oracle/_ref, a copy made by the build step where a checkout exists)
+
+def reference_module():
+    from oracle import reference_copy
+    return reference_copy.load()
+
+
+def reference_state(ref, name, dev, members=None):
+    """A layer of the reference's ``modules/base.py`` on ``dev`` with seeded noise / permutation tensors assigned
+    (``set_noise`` is bypassed: its generator is device-specific), plus a closure that runs one forward + update.
+    Returns (units per step, step function, description)."""
+    g = torch.Generator().manual_seed(4242)
+    if name == "perturbed_linear_1024":
+        n, R = 1024, 2
+        D = members or 1024
+        layer = ref.PerturbedLinear(n, n, D, antithetic=True).to(dev)
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(n, n, generator=g) / n ** .5)
+            layer.bias.zero_()
+        layer.weight_noise = torch.empty(D, n, n, device=dev).normal_(0, 0.02)
+        layer.bias_noise = torch.empty(D, n, device=dev).normal_(0, 0.02)
+        x = torch.randn(D * R, n, generator=g).to(dev)
+        w = (torch.rand(D, generator=g) * 2 - 1).to(dev)
+        units, what = D * R, "%d of 1024 members, PerturbedLinear(1024,1024) antithetic: forward + update" % D
+    elif name == "permuted_linear_256":
+        n, R, D = 256, 2, 512
+        layer = ref.PermutedLinear(n, n, D, antithetic=True).to(dev)
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(n, n, generator=g) / n ** .5)
+            layer.bias.zero_()
+        layer.weight_noise = (0.02 * torch.randn(n, n, generator=g)).to(dev)
+        layer.bias_noise = (0.02 * torch.randn(D, n, generator=g)).to(dev)
+        layer.output_permutations = torch.stack([torch.randperm(n, generator=g) for _ in range(D)]).short().to(dev)
+        x = torch.randn(D * R, n, generator=g).to(dev)
+        w = torch.randn(D, generator=g).to(dev)
+        units, what = D * R, "full configuration, PermutedLinear(256,256) x 512 antithetic pairs: forward + update"
+    elif name == "permuted_conv_64":
+        c, hw = 64, 32
+        D = members or 1024
+        layer = ref.PermutedConv2d(c, c, 3, D, padding=1, out_sparsity=.5).to(dev)
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(c, c, 3, 3, generator=g) * (2 / 576) ** .5)
+            layer.bias.zero_()
+        layer.weight_noise = (0.02 * 2 ** .5 * torch.randn(32, c, 3, 3, generator=g)).to(dev)
+        layer.bias_noise = (0.02 * torch.randn(D, c, generator=g)).to(dev)
+        layer.output_permutations = torch.stack([torch.randperm(c, generator=g) for _ in range(D)]).short().to(dev)
+        x = torch.randn(D, c, hw, hw, generator=g).to(dev)
+        w = torch.randn(D, generator=g).to(dev)
+        units, what = D, "%d of 1024 members, PermutedConv2d(64,64,3,padding=1,out_sparsity=.5) on 32x32: forward + update" % D
+    else:
+        return None
+
+    def step():
+        with torch.no_grad():
+            layer.perturbed_flag = True
+            y = layer.forward(x)
+            layer.perturbed_flag = False
+            layer.weight.grad = None
+            if layer.bias is not None:
+                layer.bias.grad = None
+            layer.update(w)
+        return y
+    return units, step, what
+
+
+def gpu_reference_extra(dev):
+    """Informational: the reference's own PyTorch layers (cuBLAS / cuDNN / ATen chains) on the same GPU for the three
+    fp32 single-layer configurations -- the library chains the kernels of this repository replace."""
+    ref = reference_module()
+    if ref is None:
+        return {"unavailable": "no copy of the reference's modules/base.py under oracle/_ref on this machine"}
+    out = {"kind": "reference (modules/base.py, unmodified) on cuda", "statistic": "median of 20 after 5 warm-up steps, CUDA events"}
+    for name in ("permuted_linear_256", "perturbed_linear_1024", "permuted_conv_64"):
+        try:
+            units, step, what = reference_state(ref, name, dev)
+            for _ in range(5):
+                step()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(20):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            med = statistics.median(times)
+            out[name] = {"ms_per_step": round(med, 4), "value": round(units / (med * 1e-3), 1), "unit": UNIT, "sample": what}
+            del step
+        except Exception as exc:
+            out[name] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+        torch.cuda.empty_cache()
+    return out
+
+
 def cpu_baseline(wl, reps, unit):
+    """The CPU arm beside the GPU number: the reference's own layer file where a copy exists and covers the workload
+    (``kind: "reference"``), else the CPU restatement under oracle/ (``kind: "port"``); all host cores."""
+    ref = reference_module()
+    state = reference_state(ref, wl.name, "cpu", members=128 if wl.name != "permuted_linear_256" else None) if ref else None
+    if state is not None:
+        units, step, what = state
+        step()
+        times = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            step()
+            times.append(time.perf_counter() - t0)
+        med = statistics.median(times)
+        return {"value": round(units / med, 2), "unit": unit, "cores": torch.get_num_threads(), "kind": "reference",
+                "sample": what, "seconds_per_repetition": round(med, 4), "repetitions": len(times)}
     units, times, sample = wl.cpu_sample(reps)
     med = statistics.median(times)
-    cores = torch.get_num_threads() if wl.name != "binary_1024" else 1
+    cores = getattr(wl, "cpu_cores", None) or torch.get_num_threads()
     return {"value": round(units / med, 2), "unit": unit, "cores": cores, "kind": "port",
             "sample": sample, "seconds_per_repetition": round(med, 4), "repetitions": len(times)}
 
 
 def run_reference(args, rank, world):
+    """The reference arm: the reference's own CPU implementation of the workload on the host cores (its unmodified
+    ``modules/base.py`` from oracle/_ref with seeded tensors assigned, the whole configuration when it fits the host's
+    memory), else the CPU restatement under oracle/.  Rank 0 alone runs it."""
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
     wl = WORKLOADS[args.workload]()
-    # configurations whose CPU sample reads layer state build it on the CPU side here
-    if args.workload in ("permuted_linear_256", "permuted_conv_64"):
-        _cpu_layer_state(wl)
-    unit = "member-samples/s"
-    units, times, sample = wl.cpu_sample(args.steps + args.warmup)
-    times = times[args.warmup:] if len(times) > args.warmup else times
+    ref = reference_module()
+    state = None
+    if ref is not None:
+        try:
+            import psutil
+            roomy = psutil.virtual_memory().available > 12 * 2 ** 30
+        except Exception:
+            roomy = False
+        members = None if (roomy or args.workload == "permuted_linear_256") else 128
+        state = reference_state(ref, args.workload, "cpu", members=members)
+    if state is not None:
+        units, step, sample = state
+        kind = "reference"
+        for _ in range(max(1, args.warmup)):
+            step()
+        times = []
+        budget = time.perf_counter() + 150.0            # the whole arm ends within a few minutes
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            step()
+            times.append(time.perf_counter() - t0)
+            if time.perf_counter() > budget:
+                break
+        cores = torch.get_num_threads()
+        note = ("the reference's own modules/base.py (unmodified copy under oracle/_ref) on the host cores with seeded "
+                "noise and permutation tensors assigned; each step is one forward + update of the sample")
+    else:
+        kind = "port"
+        if args.workload in ("permuted_linear_256", "permuted_conv_64"):
+            _cpu_layer_state(wl)
+        units, times, sample = wl.cpu_sample(args.steps + args.warmup)
+        times = times[args.warmup:] if len(times) > args.warmup else times
+        cores = getattr(wl, "cpu_cores", None) or torch.get_num_threads()
+        note = ("CPU restatement (oracle/) of the reference's algorithm on the host cores: the reference has no CPU path "
+                "for this workload or no copy of it exists on this machine; each step is the bounded sample")
     total = sum(times)
     value = units * len(times) / total
-    cores = torch.get_num_threads() if wl.name != "binary_1024" else 1
-    line = {"impl": "reference", "metric": "perturbed-member samples/sec per layer (forward + update)",
-            "value": round(value, 2), "unit": unit, "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
-            "ms_per_step": round(1e3 * total / len(times), 3), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": wl.describe(1),
-            "cpu_baseline": {"value": round(value, 2), "unit": unit, "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": round(value, 2), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0,
-            "note": "CPU restatement (oracle/) of the reference's algorithm on the host cores; the reference itself is "
-                    "a Python tree without a package, and no checkout of it exists on the GPU box; each step is the bounded sample"}
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": args.gpus,
+            "steps": len(times), "warmup": args.warmup, "ms_per_step": round(1e3 * total / len(times), 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": wl.describe(1),
+            "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "note": note}
     if args.workload == "perturbed_linear_1024" and not args.no_es:
         # the ES step of the small CNN on the host cores, next to the es_step entry of the GPU arm
         try:
             es_units, es_times, es_sample = EsCnn().cpu_sample(2)
             med = statistics.median(es_times)
             line["es_step"] = {"workload": "es_cnn_8192", "member_image_pairs_per_s": round(es_units / med, 1),
-                               "seconds_per_repetition": round(med, 4), "cores": cores, "kind": "port", "sample": es_sample}
+                               "seconds_per_repetition": round(med, 4), "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": es_sample}
         except Exception as exc:
             line["es_step"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
     emit(line)
 
 
 def _cpu_layer_state(wl):
-    """Layer state for the CPU-only reference arm, drawn with torch's CPU generator."""
+    """Layer state for the CPU-only port arm, drawn with torch's CPU generator."""
     g = torch.Generator().manual_seed(4242)
 
     class S:
@@ -764,11 +1426,29 @@ def _cpu_layer_state(wl):
     wl.layer = s
 
 
+def allreduce_check(wl, dev, world):
+    """Correctness of the NCCL path: the all-reduced weight gradient against the sum of the ranks' all-gathered partial
+    gradients, on the first 4096 entries."""
+    import torch.distributed as dist
+    layer = wl.layer
+    with torch.no_grad():
+        layer.weight.grad = None
+        layer.bias.grad = None
+        partial = layer.weight_grad(wl.w).flatten()[:4096].double().contiguous()
+        parts = [torch.empty_like(partial) for _ in range(world)]
+        dist.all_gather(parts, partial)
+        want = torch.stack(parts).sum(dim=0)
+        grad, _ = wl._update(wl.w)
+        got = grad.flatten()[:4096].double()
+    err = ((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+    return {"entries": 4096, "max_rel_err": err, "ranks": world}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
-    from nesgpu_b200 import _cabi
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    numa_node = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     wl = WORKLOADS[args.workload](args.members) if args.members else WORKLOADS[args.workload]()
@@ -777,151 +1457,69 @@ def run_ours(args, rank, world, local_rank):
         wl.fused = False
     wl.setup(dev, rank, world)
     peaks = measured_peaks()
-    flush = None
-    if wl.resident_bytes < 2 * L2_BYTES:
-        flush = torch.empty(2 * L2_BYTES // 4, dtype=torch.float32, device=dev)
-    null_mark = lambda name: None
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    default_run = args.workload == "perturbed_linear_1024" and not args.members
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    for _ in range(args.warmup):
-        wl.step(null_mark)
-        if flush is not None:
-            flush.fill_(1.0)
-    barrier()
-    # launch-bound workload: capture one step in a CUDA graph and replay it (streams and graphs, no tracing compiler)
-    graph = None
-    if getattr(wl, "use_graph", False) and world == 1 and not args.no_graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            wl.step(null_mark)
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            wl.step(null_mark)
-        for _ in range(3):
-            graph.replay()
-        barrier()
-    if sampler:
-        sampler.wait_first_sample()
-
-    # ---- timed region: exactly K steps, CUDA events on the launching stream
-    names = []
-    events = []
-    launches0 = _cabi.lib.nes_launch_count()
-    barrier()
-    if sampler:
-        sampler.begin()
-    t_wall0 = time.perf_counter()
-    for i in range(args.steps):
-        ev = [torch.cuda.Event(enable_timing=True)]
-        ev[0].record()
-
-        def mark(name, ev=ev, i=i):
-            e = torch.cuda.Event(enable_timing=True)
-            e.record()
-            ev.append(e)
-            if i == 0:
-                names.append(name)
-        if graph is not None:
-            graph.replay()
-            mark("step")
-        else:
-            wl.step(mark)
-        events.append(ev)
-        if flush is not None:
-            flush.fill_(1.0)
-    barrier()
-    wall = time.perf_counter() - t_wall0
-    if sampler:
-        sampler.end()
-    launches = _cabi.lib.nes_launch_count() - launches0
+    timing = time_steps(wl, args.steps, args.warmup, dev, world, use_graph=not args.no_graph, sampler=sampler)
     clocks = sampler.stop() if sampler else None
-    step_ms = [ev[0].elapsed_time(ev[-1]) for ev in events]
-    total_ms = sum(step_ms)
-    phase_ms = {n: statistics.mean(ev[j].elapsed_time(ev[j + 1]) for ev in events) for j, n in enumerate(names)}
-    if flush is None:      # contiguous region: first start to last end
-        total_ms = events[0][0].elapsed_time(events[-1][-1])
-    t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = t.item()
+    ms_per_step = timing["ms_per_step"]
+    e2e_ms, e2e_steps = time_e2e(wl, args.steps, dev, world)
+    sustained = time_sustained(wl, timing, ms_per_step, dev, world, local_rank, rank) if not args.no_extras else None
 
-    # ---- end to end through the layer API with host buffers
-    for _ in range(2):
-        wl.step_e2e()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(3, min(args.steps, 20))
-    e0.record()
-    for _ in range(e2e_steps):
-        wl.step_e2e()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = t.item() / e2e_steps
-
-    # ---- the metric's second half, ES steps/s: one ES step of the small CNN (BASELINE configs[4]) timed the same
-    #      way (5 steps after 3 warm-up steps, barrier on both sides, max over ranks), in both stated modes
-    es_extra = None
-    if args.workload == "perturbed_linear_1024" and not args.no_es and not args.members:
-        es_extra = {"workload": "es_cnn_8192", "images_per_member": EsCnn.R, "directions_per_gpu": EsCnn.D,
-                    "population": EsCnn.D * world, "steps": 5, "warmup": 3}
-        for mode in ("tf32", "bf16"):
-            try:
-                es = EsCnn()
-                es.tc = mode
-                es.setup(dev, rank, world)
-                for _ in range(3):
-                    es.step(null_mark)
-                barrier()
-                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a0.record()
-                for _ in range(5):
-                    es.step(null_mark)
-                a1.record()
-                barrier()
-                t = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=dev)
-                if world > 1:
-                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = t.item() / 5
-                es_extra[mode] = {"ms_per_step": round(ms, 3), "es_steps_per_s": round(1e3 / ms, 2),
-                                  "member_image_pairs_per_s": round(es.D * es.R * world / (ms * 1e-3), 1)}
-                del es
-            except Exception as exc:      # the headline line must not depend on this extra
-                es_extra[mode] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+    extras = {}
+    if world > 1 and args.workload == "perturbed_linear_1024" and not args.no_extras:
+        try:
+            extras["allreduce_check"] = allreduce_check(wl, dev, world)
+        except Exception as exc:
+            extras["allreduce_check"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+        try:
+            # strong scaling: the configuration's own population of 1024 members split over the GPUs
+            sw = PerturbedLinear1024(max(1, 1024 // world))
+            sw.tc = args.tc
+            sw.setup(dev, rank, world)
+            st = time_steps(sw, min(args.steps, 200), args.warmup, dev, world)
+            extras["strong"] = {"population": sw.D * world, "members_per_gpu": sw.D, "ms_per_step": round(st["ms_per_step"], 4),
+                                "value": round(sw.units_per_step * world / (st["ms_per_step"] * 1e-3), 1), "unit": UNIT,
+                                "phase_ms": {k: round(v, 4) for k, v in st["phase_ms"].items()}}
+            del sw, st
+            torch.cuda.empty_cache()
+        except Exception as exc:
+            extras["strong"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+    if default_run and not args.no_es:
+        extras["es_step"] = es_step_extra(dev, rank, world)
+    roofline = wl.roofline(timing["phase_ms"], peaks) if rank == 0 else None
+    config = wl.describe(world)
+    mode = wl.mode()
+    timing["graph"] = timing["flush"] = None
+    if default_run and world == 1 and not args.no_extras:
+        del wl                                    # 4 GiB of noise: the other configurations get a clean device
         torch.cuda.empty_cache()
+        extras["per_config"] = per_config_extra(dev, rank, peaks)
+        extras["gpu_reference"] = gpu_reference_extra(dev)
+        wl = WORKLOADS[args.workload]()           # for the CPU baseline below (no device state needed)
 
     if rank == 0:
-        unit = "member-samples/s"
-        ms_per_step = total_ms / args.steps
         value = wl.units_per_step * world / (ms_per_step * 1e-3)
-        line = {"metric": "perturbed-member samples/sec per layer (forward + update)", "value": round(value, 1),
-                "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": wl.dtype, "data": "synthetic", "config": dict(wl.describe(world), tc=getattr(wl.layer, "options", {}).get("tc") if hasattr(wl, "layer") else wl.tc),
-                "e2e": {"value": round(wl.units_per_step * world / (e2e_ms * 1e-3), 1), "unit": unit,
-                        "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(e2e_ms, 4),
-                        "steps": e2e_steps},
-                "gpu_launches": int(launches) if graph is None else int(wl.launches_per_step * args.steps),
-                "cuda_graph": graph is not None, "phase_ms": {k: round(v, 4) for k, v in phase_ms.items()},
-                "wall_s_timed_region": round(wall, 4), "clocks": clocks,
-                "roofline": wl.roofline(phase_ms, peaks)}
-        if es_extra is not None:
-            line["es_step"] = es_extra
+        line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": config, "precision_mode": mode,
+                "e2e": {"value": round(wl.units_per_step * world / (e2e_ms * 1e-3), 1), "unit": UNIT,
+                        "h2d_bytes_per_step": wl.h2d if hasattr(wl, "h2d") else None,
+                        "d2h_bytes_per_step": wl.d2h if hasattr(wl, "d2h") else None,
+                        "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
+                "gpu_launches": timing["launches"], "cuda_graph": timing["launches"] is not None and getattr(wl, "use_graph", False) and world == 1 and not args.no_graph,
+                "phase_ms": {k: round(v, 4) for k, v in timing["phase_ms"].items()},
+                "wall_s_timed_region": round(timing["wall"], 4), "clocks": clocks, "roofline": roofline}
+        if sustained is not None:
+            line["sustained"] = sustained
+        if numa_node is not None:
+            line["numa_node_rank0"] = numa_node
+        line.update(extras)
         if world == 1 and not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
-            line["cpu_baseline"] = cpu_baseline(wl, 5, unit)
+            line["cpu_baseline"] = cpu_baseline(wl, 5, UNIT)
         emit(line)
     if world > 1:
         dist.barrier()
@@ -938,10 +1536,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="permuted_linear_256: launch every step from Python instead of replaying a captured CUDA graph")
-    ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32", "bf16"],
-                    help="tensor-core mode of the layer (default: 3xtf32 for the linear base product, fp32 for convolutions)")
+    ap.add_argument("--tc", default=None, choices=["fp32", "tf32", "3xtf32", "bf16", "bf16x3", "auto"],
+                    help="tensor-core mode of the layer (default: the layer's own default, which holds the fp32 bar)")
     ap.add_argument("--no-es", action="store_true",
                     help="default workload: skip the extra ES-step measurement (es_step in the JSON line)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the sustained block, the other configurations (per_config), the same-GPU run of the "
+                         "reference's layers (gpu_reference) and, at N > 1, the strong-scaling and all-reduce checks")
     ap.add_argument("--unfused", action="store_true",
                     help="es_cnn_8192: separate Conv / ReLU / MaxPool2d modules and per-member input copies instead of the fused layers")
     ap.add_argument("--members", type=int, default=0,

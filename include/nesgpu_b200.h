@@ -323,6 +323,30 @@ int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const floa
                                  int in_sp, int out_sp, int antithetic,
                                  void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
+/* The same kernels in their split form, which holds the fp32 bar on the tensor cores: filter and input are
+ * each split into two bf16 parts (v = hi + lo + O(2^-18 |v|)) and the fp32 accumulator takes
+ * W_hi.x_hi + W_lo.x_hi + W_hi.x_lo; relative error a few 1e-6.  Tiles are 128 positions; scratch holds two
+ * staged copies of x.  nes_conv2d_fwd_bf16x3_supported returns 1 when the geometry is covered (stride 1,
+ * Cin % 64 == 0, Cout % 8 == 0 and <= 128, dilation <= 8, both filter copies plus two input slots within
+ * shared memory), else 0.  Replaces the same reference lines as the fp32 entry points
+ * (modules/base.py:410-425, 557-588). */
+int nes_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, int kh, int kw, int sh, int sw,
+                                    int ph, int pw, int dh, int dw);
+int64_t nes_conv2d_fwd_bf16x3_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                            int ph, int pw);
+int nes_perturbed_conv2d_fwd_bf16x3(const float* x, const float* weight, const float* bias,
+                                    const float* noise, const float* bias_noise, float* y,
+                                    int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                    int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                    int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+int nes_permuted_conv2d_fwd_bf16x3(const float* x, const float* weight, const float* bias,
+                                   const float* eps, const float* bias_noise,
+                                   const int16_t* pin, const int16_t* pout, float* y,
+                                   int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                   int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                   int in_sp, int out_sp, int antithetic,
+                                   void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
 /* The dense noise a Permuted layer is equal to (derived from modules/base.py:487-508):
  *   E[d,k,m,t] = sum_j [pin[d,j] == m] * eps[pout[d,k], j, t]   (0 where pout[d,k] >= out_sp).
  * E (D,out,in,ksize) is fully overwritten.  Repeated pin entries add. */
@@ -466,6 +490,52 @@ int nes_bin_weighted_sum(const void* in, const uint16_t* w_half, uint16_t* out_h
  * fx, fy only enter the output size, as in max_pool2d_kernel (extensions/src/max_pool2d.cu:3-36). */
 int nes_bin_maxpool2d(const void* in, void* out, int64_t P, int H, int W, int Cw, int fx, int fy,
                       int px, int py, int sx, int sy, int word_bits, nes_stream_t stream);
+
+/* ------------------------------------------------------- bit-packed layers (modules/binary.py)
+ * fp16 tensors are passed as uint16_t pointers.  Every fp16 step rounds once, as the reference's tensor
+ * ops do; sums over fp16 values accumulate in fp32. */
+
+/* Binarized.set_noise, probabilities (modules/binary.py:59-60):
+ *   p = half(sigmoid(float(half(half(w / half(half(mean|w|) + 1e-5)) * 5)))).  scratch_sum: one float. */
+int nes_binarized_probabilities(const uint16_t* weight_half, uint16_t* p_half, float* scratch_sum, int64_t n,
+                                nes_stream_t stream);
+/* Binarized.set_noise, bias noise (modules/binary.py:63-64): half(half(u - 0.5) * 6), u uniform on the fp16
+ * grid of [0, 1), from Philox keyed by (seed, offset + i / 4). */
+int nes_binarized_bias_noise(uint16_t* out_half, int64_t n, uint64_t seed, uint64_t offset, nes_stream_t stream);
+
+/* Binarized.update (modules/binary.py:67-77): w = half(fitness), w -= mean(w); grad (rows, zbits) fp16 =
+ * weighted bit sum of noise_bits (D, rows, words) with w, then += l1 * sign(weight), += l2 * weight;
+ * bias_grad (out_degree) = w @ bias_noise (D, out_degree).  bias_noise / bias_grad may both be NULL. */
+int64_t nes_binarized_update_scratch_bytes(int64_t D, int64_t rows, int64_t words, int word_bits);
+int nes_binarized_update(const void* noise_bits, const float* fitness, const uint16_t* weight_half,
+                         const uint16_t* bias_noise_half, uint16_t* grad_half, uint16_t* bias_grad_half,
+                         int64_t D, int64_t rows, int64_t words, int64_t zbits, int64_t out_degree, int word_bits,
+                         float l1, float l2, void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* BinarizedLinear.forward (modules/binary.py:93-103) on packed inputs x_packed (D, words): one streaming pass
+ * over weight_bits (D, out, words), act = 2 * popcount(w ^ x) - in_bits.  out_kind 0: act as int32 (D, out);
+ * 1: bool bytes half(act) > half(bias + bias_noise) (+ half(mean over the members of half(act)) when
+ * batch_norm); 2: the same bits packed along `out` into word_bits-wide words (D, ceil(out / word_bits)), the
+ * form the next packed layer reads.  Rows must be whole 16-byte chunks (at most 32 of them), D <= 65535.
+ * scratch is used by batch_norm only. */
+int64_t nes_binarized_linear_fwd_scratch_bytes(int64_t D, int64_t out, int batch_norm);
+int nes_binarized_linear_fwd(const void* weight_bits, const void* x_packed, const uint16_t* bias_half,
+                             const uint16_t* bias_noise_half, void* out, int64_t D, int64_t out_f, int64_t words,
+                             int in_bits, int word_bits, int out_kind, int batch_norm,
+                             void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
+/* Threshold epilogue of BinarizedConv2d.forward (modules/binary.py:147-155) on the counts (P, S, N) of
+ * nes_bin_conv, S = h * w positions: act = 2 * counts - offset; bit = half(act) > half(bias + bias_noise
+ * (+ half(mean over the member's positions of half(act)) when batch_norm)).  out_kind 0: act as int32 (out may
+ * be counts itself); 1: bool bytes (P, S, N); 2: bits packed along N (packed NHWC for the next layer).
+ * sums: P * N floats of scratch for batch_norm. */
+int nes_binarized_conv_epilogue(const int32_t* counts, const uint16_t* bias_half, const uint16_t* bias_noise_half,
+                                void* out, int64_t P, int64_t S, int64_t N, int offset, int word_bits,
+                                int out_kind, int batch_norm, float* sums, nes_stream_t stream);
+/* int32 thresholds of the reference's conv_act call (modules/binary.py:156-157):
+ *   out[p, n] = int(half(bias[n] + bias_noise[p, n])) + offset  (truncation toward zero). */
+int nes_binarized_int_threshold(const uint16_t* bias_half, const uint16_t* bias_noise_half, int32_t* out,
+                                int64_t P, int64_t N, int offset, nes_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -52,6 +52,10 @@ SIGNATURES = {
     "nes_conv2d_fwd_bf16_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
     "nes_perturbed_conv2d_fwd_bf16": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_bf16": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
+    "nes_conv2d_fwd_bf16x3_supported": [c_int] * 12,
+    "nes_conv2d_fwd_bf16x3_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
+    "nes_perturbed_conv2d_fwd_bf16x3": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
+    "nes_permuted_conv2d_fwd_bf16x3": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_dense_noise": [c_ptr] * 4 + [c_i64] + [c_int] * 5 + [c_ptr],
     "nes_permuted_update_out": [c_ptr] * 7 + [c_i64] + [c_int] * 4 + [c_f32, c_f32, c_ptr],
     "nes_permuted_update_scratch_bytes": [c_int] * 4,
@@ -77,6 +81,14 @@ SIGNATURES = {
     "nes_bin_weighted_sum_scratch_bytes": [c_i64, c_i64, c_i64, c_int],
     "nes_bin_weighted_sum": [c_ptr] * 3 + [c_i64] * 4 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_bin_maxpool2d": [c_ptr, c_ptr, c_i64] + [c_int] * 10 + [c_ptr],
+    "nes_binarized_probabilities": [c_ptr, c_ptr, c_ptr, c_i64, c_ptr],
+    "nes_binarized_bias_noise": [c_ptr, c_i64, c_u64, c_u64, c_ptr],
+    "nes_binarized_update_scratch_bytes": [c_i64, c_i64, c_i64, c_int],
+    "nes_binarized_update": [c_ptr] * 6 + [c_i64] * 5 + [c_int, c_f32, c_f32, c_ptr, c_i64, c_ptr],
+    "nes_binarized_linear_fwd_scratch_bytes": [c_i64, c_i64, c_int],
+    "nes_binarized_linear_fwd": [c_ptr] * 5 + [c_i64] * 3 + [c_int] * 4 + [c_ptr, c_i64, c_ptr],
+    "nes_binarized_conv_epilogue": [c_ptr] * 4 + [c_i64] * 3 + [c_int] * 4 + [c_ptr, c_ptr],
+    "nes_binarized_int_threshold": [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_ptr],
 }
 _RETURNS = {
     "nes_status_string": ctypes.c_char_p,
@@ -94,6 +106,10 @@ _RETURNS = {
     "nes_permuted_update_scratch_bytes": c_i64,
     "nes_bin_weighted_sum_scratch_bytes": c_i64,
     "nes_permuted_linear_out_fwd_tc_supported": c_int,
+    "nes_conv2d_fwd_bf16x3_supported": c_int,
+    "nes_conv2d_fwd_bf16x3_scratch_bytes": c_i64,
+    "nes_binarized_update_scratch_bytes": c_i64,
+    "nes_binarized_linear_fwd_scratch_bytes": c_i64,
 }
 _NO_STATUS = set(_RETURNS) | {"nes_abi_version"}
 

@@ -333,7 +333,7 @@ class Permuted(Perturbed):
     def update(self, weights, l1=0, l2=0):
         """Layers with output permutations only get weight gradient, l1 / l2 terms and bias gradient from one
         launch; everything else takes the generic route (reference ``base.py:120-138``)."""
-        if self.permute_inputs or not self.permute_outputs or self.out_sparsity * 32 > 200 * 1024:
+        if self.permute_inputs or not self.permute_outputs or self.out_sparsity * 32 + 65536 > 200 * 1024:
             return Perturbed.update(self, weights, l1, l2)
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         weights = C.require_cuda(weights, "weights", _F32)
@@ -426,8 +426,10 @@ class PerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
         noise = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        self.last_path = "fp32"
         if not direct and self._tensor_core_base(x, y):
             direct = 2          # y now holds x W^T + b; the streaming kernel adds the per-member term
+            self.last_path = self.options.get("tc", "3xtf32")
         C.call("nes_perturbed_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                C.ptr(noise), C.ptr(beta), C.ptr(y), self.directions, R, self.in_features, self.out_features,
                1 if self.antithetic else 0, direct, C.stream())
@@ -558,6 +560,8 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
         mode = self._single_product_mode(x.shape[0], pout)
         cluster_mode = self._cluster_kernel_mode(x, R, pin)
+        self.last_path = ("3xtf32" if cluster_mode == 3 else "tf32") if cluster_mode else (
+            {1: "tf32", 2: "bf16", 3: "3xtf32"}[mode] if mode else "fp32")
         if cluster_mode:
             C.call("nes_permuted_linear_out_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(eps), C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, self.in_features,
@@ -609,13 +613,25 @@ class _ConvMixin:
                x.shape[0], *geom, C.stream())
         return y
 
-    def _tensor_core_mode(self):
-        """``options["tc"]``: ``"fp32"`` (default) is exact fp32 on CUDA cores; ``"tf32"`` and ``"bf16"`` select the
-        tcgen05 paths (operands rounded to TF32 / bf16, fp32 accumulation): stated reduced-precision modes with
-        relative error ~1e-3 / ~3e-3.  Returns the entry-point suffix or None."""
-        mode = self.options.get("tc", "fp32")
-        if mode not in ("fp32", "tf32", "bf16"):
-            raise NotImplementedError('options["tc"] for convolutions must be "fp32", "tf32" or "bf16"')
+    def _tensor_core_mode(self, geom=None):
+        """``options["tc"]`` -> entry-point suffix of the tcgen05 path, or None for the CUDA-core kernel.
+
+        ``"auto"`` (default) and ``"bf16x3"``: the split-bf16 three-product form, which holds the fp32 bar (relative
+        error a few 1e-6), wherever the geometry is covered (stride 1, in_channels a multiple of 64, out_channels a
+        multiple of 8 up to 128); ``"auto"`` falls back to exact fp32 on CUDA cores elsewhere.  ``"fp32"``: CUDA cores.
+        ``"tf32"`` / ``"bf16"``: operands rounded to TF32 / bf16, fp32 accumulation -- stated reduced-precision modes
+        with relative error ~1e-3 / ~3e-3."""
+        mode = self.options.get("tc", "auto")
+        if mode not in ("auto", "fp32", "tf32", "bf16", "bf16x3"):
+            raise NotImplementedError('options["tc"] for convolutions must be "auto", "fp32", "bf16x3", "tf32" or "bf16"')
+        if mode in ("auto", "bf16x3"):
+            covered = geom is not None and C.call("nes_conv2d_fwd_bf16x3_supported", geom[0], geom[1], geom[2], geom[3],
+                                                  *geom[4:12]) == 1
+            if covered:
+                return "bf16x3"
+            if mode == "bf16x3":
+                raise NotImplementedError('options["tc"] = "bf16x3" does not cover this geometry')
+            return None
         return {"fp32": None, "tf32": "tc", "bf16": "bf16"}[mode]
 
     def _tc_scratch(self, x, R, geom, suffix):
@@ -628,7 +644,8 @@ class _ConvMixin:
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        suffix = self._tensor_core_mode()
+        suffix = self._tensor_core_mode(geom) if x.shape[0] <= 65535 else None
+        self.last_path = {None: "fp32", "tc": "tf32"}.get(suffix, suffix)
         if suffix and x.shape[0]:
             buf, nbytes = self._tc_scratch(x, R, geom, suffix)
             C.call("nes_perturbed_conv2d_fwd_" + suffix, C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
@@ -835,7 +852,10 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        suffix = self._tensor_core_mode()
+        suffix = self._tensor_core_mode(geom) if x.shape[0] <= 65535 else None
+        if suffix in ("bf16", "bf16x3") and pin is None and self.in_sparsity % 8:
+            suffix = None if self.options.get("tc", "auto") == "auto" else suffix
+        self.last_path = {None: "fp32", "tc": "tf32"}.get(suffix, suffix)
         if suffix and x.shape[0]:
             buf, nbytes = self._tc_scratch(x, R, geom, suffix)
             C.call("nes_permuted_conv2d_fwd_" + suffix, C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),

@@ -506,6 +506,10 @@ static int launch_bin_gemm(const ALoad& al, const void* B, const int32_t* thresh
   return check_launch(what);
 }
 
+// row-streaming N = 1 product of the layer file (binary_layers.cu)
+bool bmv_rows_covers(const void* A, const void* X, int64_t P, int64_t K, int word_bits);
+int bmv_rows_counts(const void* A, const void* X, int32_t* counts, int64_t P, int64_t M, int64_t K, int word_bits, cudaStream_t st);
+
 static int bin_bmm_common(const void* A, const void* B, const int32_t* thresh, int32_t* counts, uint8_t* bools,
                           int64_t P, int64_t M, int64_t K, int64_t N, int word_bits, cudaStream_t st,
                           const char* what) {
@@ -516,6 +520,7 @@ static int bin_bmm_common(const void* A, const void* B, const int32_t* thresh, i
   const int64_t row_bytes = K * (word_bits / 8);
   const int64_t cpr = row_bytes / 16;
   const bool pow2 = cpr > 0 && (cpr & (cpr - 1)) == 0;
+  if (N == 1 && !thresh && bmv_rows_covers(A, B, P, K, word_bits)) return bmv_rows_counts(A, B, counts, P, M, K, word_bits, st);
   if (N == 1 && K > 0 && row_bytes % 16 == 0 && pow2 && cpr <= 32 && aligned16(A) && aligned16(B) && P <= 65535) {
     // streaming fast path
     const int rows_per_block = int(256 * 8 / cpr);   // eight 16-byte chunks per thread
@@ -546,6 +551,10 @@ static int make_window(WindowA& wa, const void* in, int64_t P, int H, int W, int
   wa.wo = wo; wa.M = int64_t(ho) * wo; wa.K = fx * fy * Cw;
   return NES_OK;
 }
+
+int bin_weighted_sum_impl(const void* in, const uint16_t* w_half, uint16_t* out_half, int64_t D, int64_t rows,
+                          int64_t words, int64_t zbits, int word_bits, void* scratch, int64_t scratch_bytes,
+                          cudaStream_t st);
 
 }  // namespace nes
 
@@ -674,12 +683,17 @@ extern "C" int64_t nes_bin_weighted_sum_scratch_bytes(int64_t D, int64_t rows, i
 extern "C" int nes_bin_weighted_sum(const void* in, const uint16_t* w_half, uint16_t* out_half, int64_t D,
                                     int64_t rows, int64_t words, int64_t zbits, int word_bits,
                                     void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return nes::bin_weighted_sum_impl(in, w_half, out_half, D, rows, words, zbits, word_bits, scratch, scratch_bytes, as_stream(stream));
+}
+
+int nes::bin_weighted_sum_impl(const void* in, const uint16_t* w_half, uint16_t* out_half, int64_t D,
+                               int64_t rows, int64_t words, int64_t zbits, int word_bits,
+                               void* scratch, int64_t scratch_bytes, cudaStream_t st) {
   NES_REQUIRE(D >= 0 && rows >= 0 && words >= 0 && zbits >= 0, NES_ERR_BAD_ARG, "bin_weighted_sum: negative extent");
   NES_REQUIRE(word_bits == 32 || word_bits == 64, NES_ERR_BAD_ARG, "bin_weighted_sum: word_bits must be 32 or 64");
   NES_REQUIRE(zbits <= words * word_bits, NES_ERR_BAD_ARG, "bin_weighted_sum: zbits exceeds the packed row");
   if (rows == 0 || zbits == 0) return NES_OK;
   NES_REQUIRE(out_half && (D == 0 || (in && w_half)), NES_ERR_BAD_ARG, "bin_weighted_sum: null pointer");
-  cudaStream_t st = as_stream(stream);
   if (D == 0) { cudaMemsetAsync(out_half, 0, rows * zbits * sizeof(uint16_t), st); return NES_OK; }
   const int64_t row_u32 = words * (word_bits / 32);
   const WsPlan p = plan_weighted_sum(D, rows, row_u32);

@@ -14,6 +14,14 @@
 // own one output channel each, and a per-warp shared-memory transpose turns that into stores of 32
 // consecutive positions of one channel plane.  All eight builder warps drain (two per lane quadrant).
 // Reduced precision (bf16 operands, fp32 accumulation): a stated mode, relative error ~3e-3.
+//
+// TERMS = 3 is the split form that holds the fp32 bar on the same tensor-core path: both operands are split
+// into two bf16 parts, v = hi + lo + O(2^-18 |v|) with hi = bf16(v), lo = bf16(v - hi), and the accumulator
+// takes W_hi.x_hi + W_lo.x_hi + W_hi.x_lo (the dropped W_lo.x_lo term is of the same order as the
+// residuals): relative error of a few 1e-6.  The filter builders write W_d twice (hi and lo copies of the
+// same layout), the layout pre-pass writes x twice, and per (tile, channel chunk) the producer fetches the
+// hi run and the lo run into two consecutive pipeline slots; tiles are 128 positions wide so that two slots
+// of each kind fit next to the two filter copies.
 #include <cuda_bf16.h>
 #include "tc_ptx.cuh"
 
@@ -25,7 +33,8 @@ int launch_permuted_maps(const int16_t* pin, const int16_t* pout, int16_t* omap,
 namespace tc {
 
 constexpr int BF_THREADS = 320;     // producer, MMA issuer, 4 epilogue + builder warps, 4 builder warps
-constexpr int BF_NT = 256;          // pixels (positions) per tile = MMA N
+constexpr int BF_NT = 256;          // pixels (positions) per tile = MMA N (one-term form)
+constexpr int BF_NT3 = 128;         // the same for the three-term form
 
 struct ConvBfParams {
   int Cin, H, W, Cout, kh, kw, ph, pw, dh, dw, Ho, Wo;
@@ -34,6 +43,7 @@ struct ConvBfParams {
   long long D, R;
   int antithetic, sign_groups, units;
   int stages, kchunks, cchunks;
+  long long lo_offset;           // three-term form: element offset of the lo copy of the staged input
   const float* weight; const float* bias; const float* bias_noise; float* y;
   int noise_kind;                // 1 dense (D,Cout,Cin,ksz), 2 permuted (out_sp,in_sp,ksz) through omap / imap
   const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
@@ -67,14 +77,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// hi = bf16(v), lo = bf16(v - hi)
+__device__ __forceinline__ void split_bf16(float v, float& hi, float& lo) {
+  hi = __bfloat162float(__float2bfloat16_rn(v));
+  lo = v - hi;
+}
+
+template <int TERMS, int NT>
 __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfloat16* __restrict__ xs, const ConvBfParams p) {
   extern __shared__ unsigned char dyn_raw[];
   const unsigned int timeouts_at_start = timeouts_so_far();
   const uint32_t raw = smem_u32(dyn_raw);
   const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
-  unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B]
+  unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B] (x 2 with TERMS == 3: hi, lo)
   const int wd_chunk_bytes = p.M * 128;
-  unsigned char* stages_base = wd + size_t(p.kchunks) * wd_chunk_bytes;
+  const size_t wd_copy_bytes = size_t(p.kchunks) * wd_chunk_bytes;
+  unsigned char* stages_base = wd + (TERMS == 3 ? 2 : 1) * wd_copy_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(stages_base + size_t(p.stages) * p.stage_bytes);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;     // [2]
@@ -107,11 +125,13 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       const int jc = e / ((p.M - p.Cout) * 8);
       const int r = e - jc * (p.M - p.Cout) * 8;
       const int n = p.Cout + r / 8, g16 = r & 7;
-      *reinterpret_cast<uint4*>(wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 + (g16 << 4)) = make_uint4(0, 0, 0, 0);
+      const size_t off = size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 + (g16 << 4);
+      *reinterpret_cast<uint4*>(wd + off) = make_uint4(0, 0, 0, 0);
+      if (TERMS == 3) *reinterpret_cast<uint4*>(wd + wd_copy_bytes + off) = make_uint4(0, 0, 0, 0);
     }
     fence_proxy_async_smem();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 512u);
+  if (warp == 1) tmem_alloc(tmem_slot, uint32_t(2 * NT));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -133,9 +153,18 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
               const int st = g % p.stages;
               const uint32_t phs = (g / p.stages) & 1;
               if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
-              const long long row0 = (b * p.cchunks + cc) * (long long)p.img_rows + (long long)ti * BF_NT;
+              const long long row0 = (b * p.cchunks + cc) * (long long)p.img_rows + (long long)ti * NT;
               mbar_expect_tx(&full[st], uint32_t(p.load_bytes));
               bulk_load_1d(stages_base + size_t(st) * p.stage_bytes, xs + row0 * 64, uint32_t(p.load_bytes), &full[st]);
+              if (TERMS == 3) {
+                // the lo run of the same positions goes into the next pipeline slot
+                ++g;
+                const int st2 = g % p.stages;
+                const uint32_t phs2 = (g / p.stages) & 1;
+                if (!mbar_wait(&empty[st2], phs2 ^ 1, 1)) { ok = false; break; }
+                mbar_expect_tx(&full[st2], uint32_t(p.load_bytes));
+                bulk_load_1d(stages_base + size_t(st2) * p.stage_bytes, xs + p.lo_offset + row0 * 64, uint32_t(p.load_bytes), &full[st2]);
+              }
             }
         }
       }
@@ -144,7 +173,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     if (lane == 0) {
       // ------------------------------------------------------------------ MMA issuer
       // D = fp32, A = B = bf16, both K-major, N = 256 pixels, M = filter rows
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(BF_NT >> 3) << 17) | (uint32_t(p.M >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(p.M >> 4) << 24);
       const uint32_t desc_hi = uint32_t(smem_desc_sw128(0) >> 32);
       const uint32_t desc_lo0 = uint32_t(smem_desc_sw128(0));
       for (int tap = 0; tap < ksz; ++tap) {
@@ -154,6 +183,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       }
       const uint32_t wd_lo = desc_lo0 + (smem_u32(wd) >> 4);
       const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
+      const uint32_t wd_copy_units = uint32_t(wd_copy_bytes >> 4);      // from the hi filter copy to the lo copy
       uint32_t g = 0, t = 0, ul = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
@@ -167,7 +197,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
           const uint32_t buf = t & 1;
           if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * uint32_t(BF_NT);
+          const uint32_t tmem_d = tmem_base + buf * uint32_t(NT);
           for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
             const int st = g % p.stages;
             const uint32_t phs = (g / p.stages) & 1;
@@ -182,9 +212,26 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
               for (int k = 0; k < 4; ++k) {
                 mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
                 accumulate = 1u;
+                // W_lo . x_hi on the same staged run
+                if (TERMS == 3) mma_bf16_lohi(tmem_d, al + wd_copy_units + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
               }
             }
             mma_commit(&empty[st]);
+            if (TERMS == 3) {
+              // W_hi . x_lo: the lo run sits in the next slot
+              ++g;
+              const int st2 = g % p.stages;
+              const uint32_t phs2 = (g / p.stages) & 1;
+              if (!mbar_wait(&full[st2], phs2, 2)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t x2 = desc_lo0 + (smem_u32(stages_base + size_t(st2) * p.stage_bytes) >> 4);
+              for (int tap = 0; tap < ksz; ++tap) {
+                const uint32_t bl = x2 + tap_off[2 * tap], al = w_lo + tap_off[2 * tap + 1];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
+              }
+              mma_commit(&empty[st2]);
+            }
           }
           mma_commit(&acc_full[buf]);
         }
@@ -248,7 +295,10 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             const int jc = kk >> 6, col = kk & 63;
             unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
                                  ((((col >> 3) ^ (n & 7))) << 4) + (col & 7) * 2;
-            *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(fmaf(s, ev[i], wv[i]));
+            const float v = fmaf(s, ev[i], wv[i]);
+            const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+            *reinterpret_cast<__nv_bfloat16*>(dst) = vh;
+            if (TERMS == 3) *reinterpret_cast<__nv_bfloat16*>(dst + wd_copy_bytes) = __float2bfloat16_rn(v - __bfloat162float(vh));
           }
         }
       } else {
@@ -297,12 +347,17 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             const int jc = kk[i] >> 6, col = kk[i] & 63;
             unsigned char* dst = wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 +
                                  ((((col >> 3) ^ (n & 7))) << 4);
-            uint4 v;
-            v.x = pack_bf16(fmaf(s, ea[i].x, wa[i].x), fmaf(s, ea[i].y, wa[i].y));
-            v.y = pack_bf16(fmaf(s, ea[i].z, wa[i].z), fmaf(s, ea[i].w, wa[i].w));
-            v.z = pack_bf16(fmaf(s, eb[i].x, wb[i].x), fmaf(s, eb[i].y, wb[i].y));
-            v.w = pack_bf16(fmaf(s, eb[i].z, wb[i].z), fmaf(s, eb[i].w, wb[i].w));
-            *reinterpret_cast<uint4*>(dst) = v;
+            const float f[8] = {fmaf(s, ea[i].x, wa[i].x), fmaf(s, ea[i].y, wa[i].y), fmaf(s, ea[i].z, wa[i].z), fmaf(s, ea[i].w, wa[i].w),
+                                fmaf(s, eb[i].x, wb[i].x), fmaf(s, eb[i].y, wb[i].y), fmaf(s, eb[i].z, wb[i].z), fmaf(s, eb[i].w, wb[i].w)};
+            if (TERMS == 3) {
+              float h[8], l[8];
+#pragma unroll
+              for (int z = 0; z < 8; ++z) split_bf16(f[z], h[z], l[z]);
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(h[0], h[1]), pack_bf16(h[2], h[3]), pack_bf16(h[4], h[5]), pack_bf16(h[6], h[7]));
+              *reinterpret_cast<uint4*>(dst + wd_copy_bytes) = make_uint4(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]), pack_bf16(l[4], l[5]), pack_bf16(l[6], l[7]));
+            } else {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+            }
           }
         }
       }
@@ -320,7 +375,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
         const int rows_per_warp = (p.M == 128) ? 32 : 16;
         const int chan0 = (p.M == 128) ? q * 32 : q * 16;
         float* xp = xpose + size_t(warp - 2) * rows_per_warp * 33;
-        const int col_lo = (warp < 6) ? 0 : BF_NT / 2, col_hi = col_lo + BF_NT / 2;
+        const int col_lo = (warp < 6) ? 0 : NT / 2, col_hi = col_lo + NT / 2;
         for (long long r = r0; r < r1 && ok; ++r) {
           const long long b = r * p.D + d;
           float* img = p.y + size_t(b) * p.Cout * HoWo;
@@ -331,13 +386,13 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             const bool live = (timeouts_so_far() == timeouts_at_start);
             for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               uint32_t acc[32];
-              tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(BF_NT) + uint32_t(c0), acc);
+              tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(NT) + uint32_t(c0), acc);
               if (lane_has_row) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]) + add;
               }
               __syncwarp();
-              const int qpos = ti * BF_NT + c0 + lane;
+              const int qpos = ti * NT + c0 + lane;
               const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
               if (live && oy < p.Ho && ox < p.Wo) {
                 float* dst = img + size_t(chan0) * HoWo + oy * p.Wo + ox;
@@ -358,7 +413,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512u);
+    tmem_dealloc(tmem_base, uint32_t(2 * NT));
   }
 }
 
@@ -367,10 +422,12 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
 // as the 128-byte shared-memory swizzle does.  One block per (image, chunk), strips of 4 padded rows.
 constexpr int BF_STRIP = 4;
 
-template <bool VEC>
+// With SPLIT the lo copy (the bf16 rounding of what the hi copy left over) is written `lo_words` 32-bit words
+// behind the hi copy, in the same layout.
+template <bool VEC, bool SPLIT>
 __global__ void __launch_bounds__(256) stage_input_bf16_kernel(const float* __restrict__ x, uint32_t* __restrict__ out,
                                                                int C, int H, int W, int Hp, int Wp, int ph, int pw,
-                                                               int img_rows) {
+                                                               int img_rows, long long lo_words) {
   extern __shared__ float tile[];                 // [64][pitch]
   const int pitch = (BF_STRIP * Wp) | 1;
   const size_t b = blockIdx.y;
@@ -408,8 +465,17 @@ __global__ void __launch_bounds__(256) stage_input_bf16_kernel(const float* __re
     for (int r = warp; r < rows * Wp; r += 8) {
       const int row = first + r;
       // lane holds channels 2*lane, 2*lane+1 -> 4-byte unit `lane` of the row; units 4g..4g+3 form 16-byte group g
-      dst[size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3))] =
-          pack_bf16(tile[(2 * lane) * pitch + r], tile[(2 * lane + 1) * pitch + r]);
+      const size_t o = size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3));
+      const float v0 = tile[(2 * lane) * pitch + r], v1 = tile[(2 * lane + 1) * pitch + r];
+      if (SPLIT) {
+        float h0, l0, h1, l1;
+        split_bf16(v0, h0, l0);
+        split_bf16(v1, h1, l1);
+        dst[o] = pack_bf16(h0, h1);
+        dst[o + lo_words] = pack_bf16(l0, l1);
+      } else {
+        dst[o] = pack_bf16(v0, v1);
+      }
     }
     __syncthreads();
   }
@@ -431,7 +497,8 @@ static int64_t bf_align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 struct ConvBfPlan { ConvBfParams p; size_t smem; int64_t x_bytes, map_bytes, filt_bytes; };
 
 static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
-                          int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what) {
+                          int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what, int terms = 1) {
+  const int NT = terms == 3 ? BF_NT3 : BF_NT;
   NES_REQUIRE(D >= 0 && R >= 0 && Cin > 0 && H > 0 && W > 0 && Cout > 0 && kh > 0 && kw > 0 && ph >= 0 && pw >= 0 &&
               dh > 0 && dw > 0, NES_ERR_BAD_ARG, "%s: bad geometry", what);
   NES_REQUIRE(sh == 1 && sw == 1, NES_ERR_UNSUPPORTED, "%s: the bf16 tensor-core path needs stride 1", what);
@@ -444,10 +511,10 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   NES_REQUIRE(p.Ho > 0 && p.Wo > 0, NES_ERR_BAD_ARG, "%s: empty output", what);
   p.Hp = H + 2 * ph; p.Wp = W + 2 * pw;
   p.M = Cout <= 64 ? 64 : 128;
-  p.tiles_img = ceil_div(p.Ho * p.Wp, BF_NT);
+  p.tiles_img = ceil_div(p.Ho * p.Wp, NT);
   const int max_shift = (kh - 1) * dh * p.Wp + (kw - 1) * dw;
   p.img_rows = (p.Hp * p.Wp + 7) & ~7;
-  p.load_bytes = (BF_NT + max_shift) * 128;
+  p.load_bytes = (NT + max_shift) * 128;
   p.stage_bytes = (p.load_bytes + 1023) & ~1023;
   p.D = D; p.R = R; p.antithetic = antithetic;
   p.sign_groups = antithetic ? 2 : 1;
@@ -455,7 +522,7 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   p.units = int(D * p.sign_groups);
   p.cchunks = Cin / 64;
   p.kchunks = kh * kw * p.cchunks;
-  const size_t wd_bytes = size_t(p.kchunks) * p.M * 128;
+  const size_t wd_bytes = size_t(terms == 3 ? 2 : 1) * p.kchunks * p.M * 128;
   const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
   const size_t xpose_bytes = 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
   const size_t fixed = 1024 + wd_bytes + 64 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
@@ -465,33 +532,43 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
               "bf16 tensor-core path", what, wd_bytes, p.stage_bytes);
   int stages = int((limit - fixed) / (size_t(p.stage_bytes) + 16));
   if (stages > 6) stages = 6;
+  if (terms == 3 && stages > 4) stages = 4;
   p.stages = stages;
   pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 7) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
             8 * size_t(kh) * kw + xpose_bytes;
-  pl.x_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
+  const int64_t copy_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
+  p.lo_offset = copy_bytes / 2;                    // bf16 elements
+  pl.x_bytes = (terms == 3 ? 2 : 1) * copy_bytes;
   pl.map_bytes = bf_align256(D * (int64_t(Cin) + Cout) * 2);
   pl.filt_bytes = bf_align256(int64_t(Cout) * Cin * kh * kw * 4);
   return NES_OK;
 }
 
-static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStream_t st, const char* what) {
+static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStream_t st, const char* what, int terms = 1) {
   ConvBfParams& p = pl.p;
   const int64_t B = p.D * p.R;
   NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
   const size_t tsmem = size_t(64) * ((BF_STRIP * p.Wp) | 1) * sizeof(float);
   NES_REQUIRE(tsmem <= 48 * 1024, NES_ERR_UNSUPPORTED, "%s: image row too wide for the layout pre-pass (%zu bytes)", what, tsmem);
   dim3 tgrid((unsigned)p.cchunks, (unsigned)B);
-  if (p.W % 4 == 0 && aligned16(x))
-    stage_input_bf16_kernel<true><<<tgrid, 256, tsmem, st>>>(x, static_cast<uint32_t*>(x_staged), p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
-  else
-    stage_input_bf16_kernel<false><<<tgrid, 256, tsmem, st>>>(x, static_cast<uint32_t*>(x_staged), p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
+  const bool vec = p.W % 4 == 0 && aligned16(x);
+  const long long lo_words = p.lo_offset / 2;
+  uint32_t* xo = static_cast<uint32_t*>(x_staged);
+  if (terms == 3) {
+    if (vec) stage_input_bf16_kernel<true, true><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, lo_words);
+    else stage_input_bf16_kernel<false, true><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, lo_words);
+  } else {
+    if (vec) stage_input_bf16_kernel<true, false><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, 0);
+    else stage_input_bf16_kernel<false, false><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, 0);
+  }
   int rc = check_launch(what);
   if (rc != NES_OK) return rc;
-  cudaError_t e = cudaFuncSetAttribute(conv_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+  auto kern = terms == 3 ? conv_bf16_kernel<3, BF_NT3> : conv_bf16_kernel<1, BF_NT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
   int grid = p.units < sm_count() ? p.units : sm_count();
   if (grid < 1) grid = 1;
-  conv_bf16_kernel<<<grid, BF_THREADS, pl.smem, st>>>(static_cast<const __nv_bfloat16*>(x_staged), p);
+  kern<<<grid, BF_THREADS, pl.smem, st>>>(static_cast<const __nv_bfloat16*>(x_staged), p);
   return check_launch(what);
 }
 
@@ -501,23 +578,43 @@ static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStr
 using namespace nes;
 using namespace nes::tc;
 
-extern "C" int64_t nes_conv2d_fwd_bf16_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
-                                                     int ph, int pw) {
+static int64_t bf16_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw, int ph, int pw, int copies) {
   if (D <= 0 || R <= 0) return 0;
   const int64_t hp = H + 2 * ph, wp = W + 2 * pw;
   const int64_t img_rows = (hp * wp + 7) & ~int64_t(7);
   const int64_t tail = ((BF_NT + (kh - 1) * wp * 8 + (kw - 1) * 8) * 128 + 1023) & ~int64_t(1023);   // covers any dilation <= 8
-  return bf_align256(D * R * int64_t((Cin + 63) / 64) * img_rows * 128 + tail) + bf_align256(D * (int64_t(Cin) + Cout) * 2) +
+  return copies * bf_align256(D * R * int64_t((Cin + 63) / 64) * img_rows * 128 + tail) + bf_align256(D * (int64_t(Cin) + Cout) * 2) +
          2 * bf_align256(int64_t(Cout) * Cin * kh * kw * 4);
 }
 
-extern "C" int nes_perturbed_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
-                                             const float* noise, const float* bias_noise, float* y,
-                                             int64_t D, int64_t R, int Cin, int H, int W, int Cout,
-                                             int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
-                                             int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+extern "C" int64_t nes_conv2d_fwd_bf16_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                     int ph, int pw) {
+  return bf16_scratch_bytes(D, R, Cin, H, W, Cout, kh, kw, ph, pw, 1);
+}
+
+extern "C" int64_t nes_conv2d_fwd_bf16x3_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                       int ph, int pw) {
+  return bf16_scratch_bytes(D, R, Cin, H, W, Cout, kh, kw, ph, pw, 2);
+}
+
+// 1 when the split-bf16 tensor-core form covers the geometry (stride 1, Cin a multiple of 64, Cout a multiple of 8 up
+// to 128, both filter copies plus two input slots within shared memory), else 0
+extern "C" int nes_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, int kh, int kw, int sh, int sw,
+                                               int ph, int pw, int dh, int dw) {
   ConvBfPlan pl;
-  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "perturbed_conv2d_fwd_bf16");
+  if (Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || dh <= 0 || dw <= 0) return 0;
+  if (dh > 8 || dw > 8) return 0;
+  if (size_t(64) * ((BF_STRIP * (W + 2 * pw)) | 1) * sizeof(float) > 48 * 1024) return 0;
+  return plan_conv_bf16(pl, 1, 1, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, 0, "conv2d_fwd_bf16x3", 3) == NES_OK ? 1 : 0;
+}
+
+static int perturbed_conv_bf16(int terms, const float* x, const float* weight, const float* bias,
+                               const float* noise, const float* bias_noise, float* y,
+                               int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                               int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                               int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  ConvBfPlan pl;
+  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "perturbed_conv2d_fwd_bf16", terms);
   if (rc != NES_OK) return rc;
   if (D == 0 || R == 0) return NES_OK;
   NES_REQUIRE(x && weight && noise && y, NES_ERR_BAD_ARG, "perturbed_conv2d_fwd_bf16: null pointer");
@@ -526,18 +623,36 @@ extern "C" int nes_perturbed_conv2d_fwd_bf16(const float* x, const float* weight
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 1; pl.p.noise = noise; pl.p.omap = nullptr; pl.p.imap = nullptr; pl.p.in_sp = Cin;
   pl.p.weight_t = nullptr; pl.p.noise_t = nullptr; pl.p.identity_in = 1;
-  return run_conv_bf16(pl, x, scratch, as_stream(stream), "perturbed_conv2d_fwd_bf16");
+  return run_conv_bf16(pl, x, scratch, as_stream(stream), "perturbed_conv2d_fwd_bf16", terms);
 }
 
-extern "C" int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
-                                            const float* eps, const float* bias_noise,
-                                            const int16_t* pin, const int16_t* pout, float* y,
-                                            int64_t D, int64_t R, int Cin, int H, int W, int Cout,
-                                            int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
-                                            int in_sp, int out_sp, int antithetic,
-                                            void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+extern "C" int nes_perturbed_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                             const float* noise, const float* bias_noise, float* y,
+                                             int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                             int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                             int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return perturbed_conv_bf16(1, x, weight, bias, noise, bias_noise, y, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw,
+                             antithetic, scratch, scratch_bytes, stream);
+}
+
+extern "C" int nes_perturbed_conv2d_fwd_bf16x3(const float* x, const float* weight, const float* bias,
+                                               const float* noise, const float* bias_noise, float* y,
+                                               int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                               int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                               int antithetic, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return perturbed_conv_bf16(3, x, weight, bias, noise, bias_noise, y, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw,
+                             antithetic, scratch, scratch_bytes, stream);
+}
+
+static int permuted_conv_bf16(int terms, const float* x, const float* weight, const float* bias,
+                              const float* eps, const float* bias_noise,
+                              const int16_t* pin, const int16_t* pout, float* y,
+                              int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                              int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                              int in_sp, int out_sp, int antithetic,
+                              void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
   ConvBfPlan pl;
-  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16");
+  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16", terms);
   if (rc != NES_OK) return rc;
   if (D == 0 || R == 0) return NES_OK;
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_conv2d_fwd_bf16: null pointer");
@@ -565,5 +680,27 @@ extern "C" int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight,
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 2; pl.p.noise = eps; pl.p.omap = omap; pl.p.imap = imap; pl.p.in_sp = in_sp;
   pl.p.weight_t = weight_t; pl.p.noise_t = eps_t; pl.p.identity_in = (pin == nullptr) ? 1 : 0;
-  return run_conv_bf16(pl, x, scratch, st, "permuted_conv2d_fwd_bf16");
+  return run_conv_bf16(pl, x, scratch, st, "permuted_conv2d_fwd_bf16", terms);
+}
+
+extern "C" int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const float* bias,
+                                            const float* eps, const float* bias_noise,
+                                            const int16_t* pin, const int16_t* pout, float* y,
+                                            int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                            int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                            int in_sp, int out_sp, int antithetic,
+                                            void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return permuted_conv_bf16(1, x, weight, bias, eps, bias_noise, pin, pout, y, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw,
+                            dh, dw, in_sp, out_sp, antithetic, scratch, scratch_bytes, stream);
+}
+
+extern "C" int nes_permuted_conv2d_fwd_bf16x3(const float* x, const float* weight, const float* bias,
+                                              const float* eps, const float* bias_noise,
+                                              const int16_t* pin, const int16_t* pout, float* y,
+                                              int64_t D, int64_t R, int Cin, int H, int W, int Cout,
+                                              int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw,
+                                              int in_sp, int out_sp, int antithetic,
+                                              void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return permuted_conv_bf16(3, x, weight, bias, eps, bias_noise, pin, pout, y, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw,
+                            dh, dw, in_sp, out_sp, antithetic, scratch, scratch_bytes, stream);
 }

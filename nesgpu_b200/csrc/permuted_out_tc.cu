@@ -11,10 +11,14 @@
 // cluster owns the base columns [j*NB, (j+1)*NB) and the noise columns [j*NP, (j+1)*NP), i.e. it
 // multiplies the row tile by the NB + NP stacked rows [W_j; eps_j] with ONE tcgen05.mma per K step
 // (M = 128, N = NB + NP <= 256, K = 8, kind::tf32, fp32 accumulators in tensor memory).  After the K
-// loop every block copies its noise accumulator (128 x NP) into shared memory; the gather then reads
-// p[row, pout[d,k]] from the shared memory of whichever block of the cluster owns that noise column
-// (distributed shared memory, ld.shared::cluster), and the block adds base, bias, sign and beta and
-// stores its NB columns of y.  Nothing but x, W, eps, pout, beta and y touches global memory.
+// loop every block copies its noise accumulator (128 x NP) into shared memory and the blocks of the
+// cluster exchange these slices through distributed shared memory: when the whole 128 x out_sp noise
+// tile fits beside nothing else (the operand ring is idle by then), each block pushes its slice to its
+// peers with one bulk copy per peer (cp.async.bulk shared::cta -> shared::cluster, completion counted
+// on the receiver's mbarrier) and the gather p[row, pout[d,k]] runs on local shared memory; otherwise
+// the gather reads single values from the owning block (ld.shared::cluster; about four cycles per
+// value and SM, measured).  The block then adds base, bias, sign and beta and stores its NB columns of
+// y.  Nothing but x, W, eps, pout, beta and y touches global memory.
 //
 // Operand path.  The fp32 tiles of x, W and eps arrive by TMA (128-byte swizzle) exactly as they lie in
 // memory.  Four warps then split every tile in place: hi = tf32(a) overwrites the tile, lo = a - hi goes
@@ -23,7 +27,8 @@
 // callers that state it).  No pre-pass, no scratch memory, one launch.
 //
 // Pipeline per block: warp 0 = TMA producer, warp 1 = MMA issuer (and owner of the tensor-memory
-// allocation), warps 2-5 = operand splitters during the K loop and epilogue afterwards.  Stage hand-over
+// allocation), warps 2-9 = operand splitters during the K loop and epilogue afterwards (two warps per
+// tensor-memory lane quadrant, which take alternate 16-column chunks).  Stage hand-over
 // by mbarriers: full (TMA bytes landed) -> split (hi/lo written, made visible to the async proxy) ->
 // tcgen05.commit -> empty.  Every mbarrier wait is bounded; a wait that runs out records a code (see
 // tc_ptx.cuh), the role stops issuing work and all threads still reach the two cluster barriers and the
@@ -36,7 +41,8 @@ namespace tc {
 
 constexpr int PO_BM = 128;                 // batch rows per cluster
 constexpr int PO_BK = 32;                  // fp32 K elements per stage = one 128-byte swizzle row
-constexpr int PO_THREADS = 192;
+constexpr int PO_THREADS = 320;
+constexpr int PO_WORKERS = PO_THREADS - 64;   // splitter / epilogue threads
 constexpr int PO_A_BYTES = PO_BM * PO_BK * 4;
 constexpr int PO_MIN_SMEM = 116 * 1024;    // more than half an SM's shared memory: one block per SM, so a block
                                            // that waits for its cluster never holds tensor memory a peer needs
@@ -50,6 +56,7 @@ struct PermOutParams {
   int stages, tmem_cols, antithetic;
   unsigned int np_magic;                    // ceil(2^32 / NP): so / NP == umulhi(so, np_magic) for so < 2^24
   int vec_y, vec_pout, vec_beta;
+  int local_gather;                         // 1: slices are pushed to the peers and the gather is local
 };
 
 __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
@@ -74,6 +81,19 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+// own shared memory -> the same place in a peer's shared memory; the peer's mbarrier counts the bytes
+__device__ __forceinline__ void bulk_push(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_bar)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   float v;
@@ -81,6 +101,22 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
+
+// Optional phase timestamps (build with -DNES_PO_TRACE): slot [block * 16 + phase] holds %globaltimer in ns.
+#ifdef NES_PO_TRACE
+__device__ long long g_po_trace[64 * 16];
+__device__ __forceinline__ void po_trace(int phase) {
+  const int blk = blockIdx.y * gridDim.x + blockIdx.x;
+  if (blk < 64) {
+    long long tns;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tns));
+    g_po_trace[blk * 16 + phase] = tns;
+  }
+}
+#define PO_TRACE(cond, phase) do { if (cond) po_trace(phase); } while (0)
+#else
+#define PO_TRACE(cond, phase) do { } while (0)
+#endif
 
 template <int TERMS>
 __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(const __grid_constant__ PermOutParams p) {
@@ -92,26 +128,32 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
   const int NC = p.NB + p.NP;
   const int b_bytes = NC * PO_BK * 4;
   const int stage_bytes = (TERMS == 3 ? 2 : 1) * (PO_A_BYTES + b_bytes);
-  // barriers sit behind the larger of the stage ring and the exchange buffer that reuses it
+  // barriers sit behind the larger of the stage ring and the exchange area that reuses it
   const int pitch = p.NP + 4;                                  // floats per exchange row: 16-byte rows, rows 4 banks apart
+  const int S = int(gridDim.x);
+  const uint32_t slice_floats = uint32_t(PO_BM) * uint32_t(pitch);
   const size_t ring_bytes = size_t(p.stages) * stage_bytes;
-  const size_t xchg_bytes = size_t(PO_BM) * pitch * 4;
+  const size_t xchg_bytes = size_t(p.local_gather ? S : 1) * slice_floats * 4;
   const size_t body = ((ring_bytes > xchg_bytes ? ring_bytes : xchg_bytes) + 15) & ~size_t(15);
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + body);
   uint64_t* split = full + p.stages;
   uint64_t* empty = split + p.stages;
   uint64_t* accum = empty + p.stages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  uint64_t* xbar = accum + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 1);
   float* xchg = reinterpret_cast<float*>(tiles);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t j = cluster_rank();                           // column slice of this block
   const long long m0 = (long long)blockIdx.y * PO_BM;
   const int nk = (p.K + PO_BK - 1) / PO_BK;
+  float* my_slice = xchg + (p.local_gather ? size_t(j) * slice_floats : 0);
+  PO_TRACE(threadIdx.x == 0, 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&split[s], 4); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&split[s], PO_WORKERS / 32); mbar_init(&empty[s], 1); }
     mbar_init(accum, 1);
+    mbar_init(xbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, uint32_t(p.tmem_cols));
@@ -119,6 +161,14 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  PO_TRACE(threadIdx.x == 0, 1);
+
+  // epilogue geometry of this thread (warps 2-9): accumulator row and the 16-column chunks it takes
+  const int q = warp & 3;
+  const int row = q * 32 + lane;
+  const int chunk0 = (warp - 2) >> 2;                          // 0 for warps 2-5, 1 for warps 6-9
+  const long long gm = m0 + row;
+  const int kbase = int(j) * p.NB;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -133,6 +183,7 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
         tma_load_2d(st, &p.map_x, &full[s], kt * PO_BK, int(m0));
         tma_load_2d(bt, &p.map_w, &full[s], kt * PO_BK, int(j) * p.NB);
         tma_load_2d(bt + size_t(p.NB) * PO_BK * 4, &p.map_eps, &full[s], kt * PO_BK, int(j) * p.NP);
+        PO_TRACE(kt == 0, 2);
       }
     }
   } else if (warp == 1) {
@@ -145,6 +196,7 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
         const uint32_t ph = (kt / p.stages) & 1;
         ok = mbar_wait(&split[s], ph, 2);
         if (!ok) break;
+        PO_TRACE(kt == 0, 5);
         tc_fence_after();
         const uint32_t st = smem_u32(tiles + size_t(s) * stage_bytes);
         const uint64_t a_hi = smem_desc_sw128(st);
@@ -167,30 +219,39 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
         mma_commit(&empty[s]);
       }
       mma_commit(accum);
+      PO_TRACE(true, 6);
     }
   } else {
     // ---- operand splitters, then the first half of the epilogue
-    const int t = threadIdx.x - 64;                             // 0..127
+    const int t = threadIdx.x - 64;                             // 0 .. PO_WORKERS-1
+    // the epilogue's per-row tables are cold: start them on their way to L2 now
+    if (chunk0 == 0 && gm < p.B) {
+      const long long d = gm % p.D;
+      const int cols = (kbase + p.NB <= p.out) ? p.NB : (p.out > kbase ? p.out - kbase : 0);
+      if (p.pout) for (int o = 0; o < cols * 2; o += 128) prefetch_l2(reinterpret_cast<const char*>(p.pout + d * p.out + kbase) + o);
+      if (p.beta) for (int o = 0; o < cols * 4; o += 128) prefetch_l2(reinterpret_cast<const char*>(p.beta + d * p.out + kbase) + o);
+    }
     bool ok = true;
     for (int kt = 0; kt < nk && ok; ++kt) {
       const int s = kt % p.stages;
       const uint32_t ph = (kt / p.stages) & 1;
       ok = mbar_wait_relaxed(&full[s], ph, 4);
       if (!ok) break;
+      PO_TRACE(kt == 0 && t == 0, 3);
       unsigned char* st = tiles + size_t(s) * stage_bytes;
       float4* a_hi = reinterpret_cast<float4*>(st);
       float4* a_lo = reinterpret_cast<float4*>(st + PO_A_BYTES);
       float4* b_hi = reinterpret_cast<float4*>(st + (TERMS == 3 ? 2 : 1) * PO_A_BYTES);
       float4* b_lo = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(b_hi) + b_bytes);
 #pragma unroll
-      for (int u = 0; u < PO_A_BYTES / 16 / 128; ++u) {
-        const int i = t + u * 128;
+      for (int u = 0; u < PO_A_BYTES / 16 / PO_WORKERS; ++u) {
+        const int i = t + u * PO_WORKERS;
         const float4 v = a_hi[i];
         const float4 h = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
         a_hi[i] = h;
         if (TERMS == 3) a_lo[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
       }
-      for (int i = t; i < b_bytes / 16; i += 128) {
+      for (int i = t; i < b_bytes / 16; i += PO_WORKERS) {
         const float4 v = b_hi[i];
         const float4 h = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
         b_hi[i] = h;
@@ -199,15 +260,15 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
       fence_proxy_async_smem();                                 // these writes are read by tcgen05.mma (async proxy)
       __syncwarp();
       if (lane == 0) mbar_arrive(&split[s]);
+      PO_TRACE(kt == 0 && t == 0, 4);
     }
-    // noise accumulator -> exchange buffer (the stage ring is free once every MMA has completed)
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
+    // noise accumulator -> this block's slice of the exchange area (the stage ring is free once every MMA has completed)
     const bool done = mbar_wait_relaxed(accum, 0, 3);
+    PO_TRACE(t == 0, 7);
     tc_fence_after();
     if (done && nk > 0) {
-      float* prow = xchg + size_t(row) * pitch;
-      for (int c = 0; c < p.NP; c += 16) {
+      float* prow = my_slice + size_t(row) * pitch;
+      for (int c = chunk0 * 16; c < p.NP; c += 32) {
         uint32_t r[16];
         tmem_ld16_nowait(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(p.NB + c), r);
         tmem_ld_wait();
@@ -216,25 +277,40 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
           *reinterpret_cast<float4*>(prow + c + u) = make_float4(__uint_as_float(r[u]), __uint_as_float(r[u + 1]),
                                                                  __uint_as_float(r[u + 2]), __uint_as_float(r[u + 3]));
       }
+      if (p.local_gather) fence_proxy_async_smem();             // the slice is about to be read by bulk copies
+    }
+    PO_TRACE(t == 0, 8);
+  }
+  static_assert(PO_A_BYTES / 16 % PO_WORKERS == 0, "the A tile must split evenly over the splitter threads");
+  __syncthreads();                       // re-converges the single-thread roles before the warp-aligned cluster barrier
+  cluster_sync_all();                    // every block has finished its MMAs and written its slice
+  PO_TRACE(threadIdx.x == 64, 9);
+
+  if (p.local_gather && S > 1 && threadIdx.x == 64) {
+    // push this block's slice into the same place of every peer; each block's xbar counts what it receives
+    const uint32_t bytes = slice_floats * 4u;
+    mbar_expect_tx(xbar, uint32_t(S - 1) * bytes);
+    const uint32_t src = smem_u32(my_slice), bar = smem_u32(xbar);
+    for (int r = 1; r < S; ++r) {
+      const uint32_t peer = (j + uint32_t(r)) % uint32_t(S);
+      bulk_push(map_to_rank(src, peer), src, bytes, map_to_rank(bar, peer));
     }
   }
-  __syncthreads();                       // re-converges the single-thread roles before the warp-aligned cluster barrier
-  cluster_sync_all();                    // every block's noise rows are in its shared memory
 
   if (warp >= 2) {
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    const long long gm = m0 + row;
-    const bool live = (timeouts_so_far() == timeouts_at_start) && nk > 0;
+    bool arrived = true;
+    if (p.local_gather && S > 1) arrived = mbar_wait_relaxed(xbar, 0, 3);
+    PO_TRACE(threadIdx.x == 64, 12);
+    const bool live = arrived && (timeouts_so_far() == timeouts_at_start) && nk > 0;
     const bool row_ok = live && gm < p.B;
     long long d = 0;
     float sgn = 1.f;
     if (row_ok) { d = gm % p.D; sgn = anti_sign(gm / p.D, p.R, p.antithetic); }
+    const float* lrow = xchg + size_t(row) * pitch;                       // local gather: + owner * slice_floats + column
     const uint32_t xrow = smem_u32(xchg) + uint32_t(row) * uint32_t(pitch) * 4u;
-    const int kbase = int(j) * p.NB;
-    for (int c = 0; c < p.NB; c += 16) {
+    for (int c = chunk0 * 16; c < p.NB; c += 32) {
       const int k0 = kbase + c;
-      if (k0 >= p.out) break;                                    // uniform over the block
+      if (k0 >= p.out) break;                                    // uniform over the warp
       uint32_t acc[16];
       tmem_ld16_nowait(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c), acc);
       tmem_ld_wait();
@@ -264,7 +340,8 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
         if (so[u] < p.out_sp) {
           const uint32_t owner = __umulhi(uint32_t(so[u]), p.np_magic);
           const uint32_t col = uint32_t(so[u]) - owner * uint32_t(p.NP);
-          qv[u] = ld_cluster_f32(xrow + col * 4u, owner);
+          if (p.local_gather) qv[u] = lrow[size_t(owner) * slice_floats + col];
+          else qv[u] = ld_cluster_f32(xrow + col * 4u, owner);
         }
       }
       float bn[16];
@@ -301,14 +378,23 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
       }
     }
   }
+  PO_TRACE(threadIdx.x == 64, 10);
   tc_fence_before();
   __syncthreads();
-  cluster_sync_all();                    // no block leaves while a peer may still read its exchange buffer
+  cluster_sync_all();                    // no block leaves while a peer may still read or fill its exchange area
+  PO_TRACE(threadIdx.x == 64, 11);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, uint32_t(p.tmem_cols));
   }
 }
+
+#ifdef NES_PO_TRACE
+int po_trace_read(long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_po_trace, sizeof(long long) * 64 * 16);
+  return e == cudaSuccess ? NES_OK : fail(NES_ERR_LAUNCH, "po_trace: %s", cudaGetErrorString(e));
+}
+#endif
 
 int permuted_out_error_word(int* v, bool clear) { return read_error_word(v, clear, "tc_error_flag"); }
 
@@ -328,7 +414,7 @@ static int encode_rows(CUtensorMap* map, const float* base, int64_t rows, int64_
 
 static int ceil16(int64_t v) { return int((v + 15) & ~int64_t(15)); }
 
-struct PermOutPlan { int S, NB, NP, stages, tmem_cols; size_t smem; };
+struct PermOutPlan { int S, NB, NP, stages, tmem_cols, local_gather; size_t smem; };
 
 // Column split: S blocks per 128-row tile.  A block's MMAs take about max(92, 0.74 * N) cycles each
 // (measured: an M128 kind::tf32 MMA is issue-bound below N = 128), so the split that minimises
@@ -355,12 +441,14 @@ static bool plan_perm_out(int64_t B, int64_t out, int64_t out_sp, int64_t K, int
     if (stages > 4) stages = 4;
     if (stages > nk) stages = nk;
     if (stages < 1) stages = 1;
-    const size_t xchg = size_t(PO_BM) * (c.NP + 4) * 4;
+    const size_t slice = size_t(PO_BM) * (c.NP + 4) * 4;
+    c.local_gather = (slice * S <= budget) ? 1 : 0;            // the whole 128 x out_sp noise tile fits: gather locally
+    const size_t xchg = c.local_gather ? slice * S : slice;
     size_t body = size_t(stages) * stage_bytes;
     if (xchg > body) body = xchg;
     if (body > budget) continue;
     c.stages = stages;
-    c.smem = 1024 + ((body + 15) & ~size_t(15)) + (3 * stages + 1) * sizeof(uint64_t) + 16;
+    c.smem = 1024 + ((body + 15) & ~size_t(15)) + (3 * stages + 2) * sizeof(uint64_t) + 16;
     if (c.smem < size_t(PO_MIN_SMEM)) c.smem = PO_MIN_SMEM;
     c.tmem_cols = 32;
     while (c.tmem_cols < NC) c.tmem_cols <<= 1;
@@ -441,7 +529,13 @@ extern "C" int nes_permuted_linear_out_fwd_tc(const float* x, const float* weigh
   prm.vec_y = (out % 4 == 0) && aligned16(y);
   prm.vec_pout = pout && (out % 8 == 0) && aligned16(pout);
   prm.vec_beta = bias_noise && (out % 4 == 0) && aligned16(bias_noise);
+  prm.local_gather = plan.local_gather;
   const int64_t mtiles = ceil_div<int64_t>(B, PO_BM);
   cudaStream_t st = as_stream(stream);
   return mode == 3 ? launch_perm_out<3>(prm, plan, mtiles, st) : launch_perm_out<1>(prm, plan, mtiles, st);
 }
+
+#ifdef NES_PO_TRACE
+// instrumented builds only: copies the 64 x 16 phase timestamps of the last launches to host memory
+extern "C" int nes_debug_po_trace(long long* out) { return nes::tc::po_trace_read(out); }
+#endif

@@ -143,25 +143,30 @@ __global__ void grad_from_out_hist_kernel(const float* __restrict__ G, const flo
 // Output-permuted update in ONE launch (weight gradient, bias gradient, l1 / l2 terms):
 //   grad[k, e]  = sum_s G[k,s] * eps[s, e] (+ l1 sign(W) + l2 W),   G[k,s] = sum_d w_d [pout[d,k] == s, s < out_sp]
 //   bias_grad[k] = sum_d w_d * beta[d,k]
-// Blocks 0 .. gblocks-1 own PU_ROWS output rows each: the rows' slice of G is built in shared memory with
-// shared-memory atomics straight from the permutation table (no histogram in global memory, nothing to
-// clear), then every thread walks eps down a column e with the PU_ROWS histogram values of each noise row
-// read as two broadcast 128-bit loads.  The remaining blocks own 32 columns of the bias gradient each.
-constexpr int PU_ROWS = 8, PU_THREADS = 256;
+// Blocks 0 .. gblocks-1 own PU_ROWS output rows each.  The rows' slice of G is built in shared memory with
+// shared-memory atomics straight from the permutation table (no histogram in global memory, nothing to clear;
+// a thread first loads the eight entries of a member, then adds them).  The product is latency-bound (every
+// block reads all of eps from L2), so the noise rows are dealt round-robin to PU_SGROUPS thread groups that
+// each walk their rows with PU_UNROLL 128-bit loads in flight per thread over 256 columns at a time; the
+// groups' partial sums meet in shared memory.  The remaining blocks own 32 columns of the bias gradient each.
+constexpr int PU_ROWS = 8, PU_THREADS = 512, PU_SGROUPS = 8, PU_COLS = 256, PU_UNROLL = 8;
 
 __global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
     const float* __restrict__ eps, const float* __restrict__ w, const int16_t* __restrict__ pout,
     const float* __restrict__ weight, const float* __restrict__ beta, float* __restrict__ grad,
-    float* __restrict__ bias_grad, int64_t D, int out, int out_sp, int64_t inner, int gblocks, float l1, float l2) {
+    float* __restrict__ bias_grad, int64_t D, int out, int out_sp, int64_t inner, int gblocks, float l1, float l2,
+    int vec_eps, int vec_pout) {
   extern __shared__ __align__(16) float pu_smem[];
   const int t = threadIdx.x;
   if (int(blockIdx.x) >= gblocks) {
-    // ---- bias gradient: 32 columns, eight member lanes, tree over the lanes
+    // ---- bias gradient: 32 columns x 16 member lanes, the lanes' sums added in lane order
     const int c = (int(blockIdx.x) - gblocks) * 32 + (t & 31);
     const int lane_d = t >> 5;
     float acc = 0.f;
-    if (c < out)
+    if (c < out) {
+#pragma unroll 8
       for (int64_t d = lane_d; d < D; d += PU_THREADS / 32) acc = fmaf(__ldg(w + d), __ldg(beta + d * out + c), acc);
+    }
     pu_smem[t] = acc;
     __syncthreads();
     if (t < 32 && c < out) {
@@ -172,36 +177,87 @@ __global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
     }
     return;
   }
-  float* Gs = pu_smem;                                  // [out_sp][PU_ROWS]
+  float* Gs = pu_smem;                                            // [out_sp][PU_ROWS]
+  float* red = pu_smem + size_t(out_sp) * PU_ROWS;                // [PU_SGROUPS][PU_ROWS][PU_COLS]
   const int k0 = blockIdx.x * PU_ROWS;
   for (int i = t; i < out_sp * PU_ROWS; i += PU_THREADS) Gs[i] = 0.f;
   __syncthreads();
-  for (int64_t i = t; i < D * PU_ROWS; i += PU_THREADS) {
-    const int64_t d = i / PU_ROWS;
-    const int kk = int(i - d * PU_ROWS);
-    if (k0 + kk < out) {
-      const int s = pout[d * out + k0 + kk];
-      if (s < out_sp) atomicAdd(&Gs[s * PU_ROWS + kk], __ldg(w + d));
+  if (vec_pout && k0 + PU_ROWS <= out) {
+    for (int64_t d = t; d < D; d += PU_THREADS) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(pout + d * out + k0));
+      const float wd = __ldg(w + d);
+      const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int s0 = int(q[u] & 0xFFFFu), s1 = int(q[u] >> 16);
+        if (s0 < out_sp) atomicAdd(&Gs[s0 * PU_ROWS + 2 * u], wd);
+        if (s1 < out_sp) atomicAdd(&Gs[s1 * PU_ROWS + 2 * u + 1], wd);
+      }
+    }
+  } else {
+    for (int64_t i = t; i < D * PU_ROWS; i += PU_THREADS) {
+      const int64_t d = i / PU_ROWS;
+      const int kk = int(i - d * PU_ROWS);
+      if (k0 + kk < out) {
+        const int s = int(uint16_t(pout[d * out + k0 + kk]));
+        if (s < out_sp) atomicAdd(&Gs[s * PU_ROWS + kk], __ldg(w + d));
+      }
     }
   }
   __syncthreads();
-  for (int64_t e = t; e < inner; e += PU_THREADS) {
-    float a[PU_ROWS];
+  const int cg = t % (PU_COLS / 4), sg = t / (PU_COLS / 4);       // four columns and one group of noise rows per thread
+  for (int64_t c0 = 0; c0 < inner; c0 += PU_COLS) {
+    const int64_t e = c0 + 4 * cg;
+    float a[PU_ROWS][4];
 #pragma unroll
-    for (int u = 0; u < PU_ROWS; ++u) a[u] = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < out_sp; ++s) {
-      const float ev = __ldg(eps + int64_t(s) * inner + e);
-      const float4 g0 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS);
-      const float4 g1 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS + 4);
-      a[0] = fmaf(g0.x, ev, a[0]); a[1] = fmaf(g0.y, ev, a[1]); a[2] = fmaf(g0.z, ev, a[2]); a[3] = fmaf(g0.w, ev, a[3]);
-      a[4] = fmaf(g1.x, ev, a[4]); a[5] = fmaf(g1.y, ev, a[5]); a[6] = fmaf(g1.z, ev, a[6]); a[7] = fmaf(g1.w, ev, a[7]);
+    for (int u = 0; u < PU_ROWS; ++u) { a[u][0] = a[u][1] = a[u][2] = a[u][3] = 0.f; }
+    if (e < inner) {
+      for (int sb = sg; sb < out_sp; sb += PU_SGROUPS * PU_UNROLL) {
+        float4 ev[PU_UNROLL];
+#pragma unroll
+        for (int i = 0; i < PU_UNROLL; ++i) {
+          const int s = sb + i * PU_SGROUPS;
+          ev[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (s < out_sp) {
+            const float* src = eps + int64_t(s) * inner + e;
+            if (vec_eps) {
+              ev[i] = __ldg(reinterpret_cast<const float4*>(src));
+            } else {
+              ev[i].x = __ldg(src);
+              if (e + 1 < inner) ev[i].y = __ldg(src + 1);
+              if (e + 2 < inner) ev[i].z = __ldg(src + 2);
+              if (e + 3 < inner) ev[i].w = __ldg(src + 3);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < PU_UNROLL; ++i) {
+          const int s = sb + i * PU_SGROUPS;
+          if (s < out_sp) {
+            const float4 g0 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS);
+            const float4 g1 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS + 4);
+            const float g[PU_ROWS] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+            for (int u = 0; u < PU_ROWS; ++u) {
+              a[u][0] = fmaf(g[u], ev[i].x, a[u][0]); a[u][1] = fmaf(g[u], ev[i].y, a[u][1]);
+              a[u][2] = fmaf(g[u], ev[i].z, a[u][2]); a[u][3] = fmaf(g[u], ev[i].w, a[u][3]);
+            }
+          }
+        }
+      }
     }
+    __syncthreads();                                              // previous pass has finished reading red
 #pragma unroll
-    for (int u = 0; u < PU_ROWS; ++u) {
-      if (k0 + u >= out) break;
-      const int64_t o = int64_t(k0 + u) * inner + e;
-      float v = a[u];
+    for (int u = 0; u < PU_ROWS; ++u)
+      *reinterpret_cast<float4*>(red + (size_t(sg) * PU_ROWS + u) * PU_COLS + 4 * cg) = make_float4(a[u][0], a[u][1], a[u][2], a[u][3]);
+    __syncthreads();
+    for (int i = t; i < PU_ROWS * PU_COLS; i += PU_THREADS) {
+      const int u = i / PU_COLS, col = i - u * PU_COLS;
+      if (k0 + u >= out || c0 + col >= inner) continue;
+      float v = 0.f;
+#pragma unroll
+      for (int g = 0; g < PU_SGROUPS; ++g) v += red[(size_t(g) * PU_ROWS + u) * PU_COLS + col];
+      const int64_t o = int64_t(k0 + u) * inner + c0 + col;
       if (weight) {
         const float wv = __ldg(weight + o);
         if (l1 != 0.f) v += l1 * ((wv > 0.f) - (wv < 0.f));
@@ -511,9 +567,9 @@ extern "C" int nes_permuted_update_out(const float* eps, const float* w, const i
   NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "permuted_update_out: l1/l2 given without weight");
   NES_REQUIRE((bias_noise == nullptr) == (bias_grad == nullptr), NES_ERR_BAD_ARG,
               "permuted_update_out: bias_noise and bias_grad go together");
-  const size_t smem = size_t(out_sp) * PU_ROWS * sizeof(float);
+  const size_t smem = (size_t(out_sp) * PU_ROWS + size_t(PU_SGROUPS) * PU_ROWS * PU_COLS) * sizeof(float);
   NES_REQUIRE(smem <= 200 * 1024, NES_ERR_UNSUPPORTED, "permuted_update_out: out_sp=%d needs %zu B of shared memory", out_sp, smem);
-  const size_t smem_all = smem > PU_THREADS * sizeof(float) ? smem : PU_THREADS * sizeof(float);
+  const size_t smem_all = smem;
   if (smem_all > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(permuted_update_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_all);
     if (e != cudaSuccess) return fail(NES_ERR_UNSUPPORTED, "permuted_update_out: %zu B of shared memory refused", smem_all);
@@ -522,7 +578,8 @@ extern "C" int nes_permuted_update_out(const float* eps, const float* w, const i
   const int bblocks = bias_grad ? ceil_div(out, 32) : 0;
   permuted_update_out_kernel<<<gblocks + bblocks, PU_THREADS, smem_all, as_stream(stream)>>>(
       eps, w, pout, (l1 != 0.f || l2 != 0.f) ? weight : nullptr, bias_noise, grad, bias_grad, D, out, out_sp,
-      int64_t(in) * ksize, gblocks, l1, l2);
+      int64_t(in) * ksize, gblocks, l1, l2,
+      ((int64_t(in) * ksize) % 4 == 0 && aligned16(eps)) ? 1 : 0, (out % 8 == 0 && aligned16(pout)) ? 1 : 0);
   return check_launch("permuted_update_out");
 }
 

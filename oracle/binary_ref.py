@@ -196,3 +196,68 @@ def binarized_linear_forward(weight_bits, inputs_bool, in_features, threshold=No
     if threshold is None:
         return act
     return act > threshold
+
+
+# ----------------------------------------------------------------------------------
+# Layer glue of modules/binary.py with torch's fp16 semantics spelled out: every fp16 tensor
+# op is computed in fp32 and rounded once to fp16; an int32 tensor compared with an fp16 tensor
+# is first converted to fp16.
+# ----------------------------------------------------------------------------------
+
+def _h(x):
+    return np.asarray(x, dtype=np.float32).astype(np.float16)
+
+
+def _f(x):
+    return np.asarray(x, dtype=np.float16).astype(np.float32)
+
+
+def threshold_bits(act, bias_half, bias_noise_half, mean_half=None):
+    """``activation > thresh`` of modules/binary.py:98-102 and :150-153.  act (..., N) int32; bias (N,);
+    bias_noise broadcastable to act; mean_half (optional) broadcastable to act."""
+    th = _h(_f(bias_half) + _f(bias_noise_half))
+    if mean_half is not None:
+        th = _h(_f(th) + _f(mean_half))
+    return np.asarray(act).astype(np.float16) > th
+
+
+def binarized_linear_layer(weight_bits, inputs_bool, in_features, bias_half, bias_noise_half, batch_norm, bits=64):
+    """BinarizedLinear.forward with threshold=True (modules/binary.py:93-103): the batch mean is taken over the
+    members (dim 0) of the fp16 activation."""
+    act = binarized_linear_forward(weight_bits, inputs_bool, in_features, None, bits)
+    mean = None
+    if batch_norm:
+        mean = _h(_f(act.astype(np.float16)).sum(axis=0, keepdims=True, dtype=np.float32) / np.float32(act.shape[0]))
+    return threshold_bits(act, bias_half, bias_noise_half, mean)
+
+
+def binarized_conv_layer(counts, offset, bias_half, bias_noise_half, batch_norm):
+    """BinarizedConv2d.forward with threshold=True (modules/binary.py:139-157) on the conv counts (P, h, w, N).
+    batch_norm: fp16 compare against bias + bias_noise + mean over the member's positions; otherwise the
+    integer compare ``2 * counts > int(bias + bias_noise) + offset`` of the conv_act call."""
+    counts = np.asarray(counts, dtype=np.int64)
+    P = counts.shape[0]
+    if not batch_norm:
+        th = _h(_f(bias_half) + _f(bias_noise_half)).astype(np.float32)
+        thresh = np.trunc(th).astype(np.int64) + offset
+        return 2 * counts > thresh.reshape(P, 1, 1, -1)
+    act = (2 * counts - offset).astype(np.int32)
+    a16 = _f(act.astype(np.float16))
+    mean = _h(a16.sum(axis=(1, 2), dtype=np.float32) / np.float32(act.shape[1] * act.shape[2]))      # (P, N)
+    th = _h(_f(_h(_f(bias_half) + _f(bias_noise_half))) + _f(mean))
+    return act.astype(np.float16) > th.reshape(P, 1, 1, -1)
+
+
+def binarized_update(weight_bits, fitness, weight_half, bias_noise_half, in_degree, l1=0.0, l2=1e-3):
+    """Binarized.update (modules/binary.py:67-77).  Returns (weight grad fp16, bias grad fp16)."""
+    w16 = _h(fitness)
+    mean = _h(_f(w16).sum(dtype=np.float32) / np.float32(w16.size))
+    w = _h(_f(w16) - _f(mean))
+    grad = weighted_sum(weight_bits, w, in_degree)
+    wf = _f(weight_half)
+    if l1:
+        grad = _h(_f(grad) + _f(_h(np.float32(l1) * np.sign(wf))))
+    if l2:
+        grad = _h(_f(grad) + _f(_h(np.float32(l2) * wf)))
+    bias_grad = _h((_f(w)[:, None] * _f(bias_noise_half)).sum(axis=0, dtype=np.float32))
+    return grad, bias_grad

@@ -229,3 +229,99 @@ def test_seeded_bmv_equals_sample_then_bmm(ops, bits, n, rows, cols):
     stored = ops.bmm(ops.sample_bits(p, n, DT[bits], 1234), xb.view(n, -1, 1)).squeeze(2)
     assert torch.equal(fused, stored)
     assert not torch.equal(fused, ops.binary_seeded_bmv(p, xb, 1235)) or n * rows * cols < 64
+
+
+# ------------------------------------------------------------------ layer arithmetic behind the C ABI
+
+def _linear_layer(binary, D, out_f, in_f, batch_norm, seed, dtype=torch.int64):
+    layer = binary.BinarizedLinear(in_f, out_f, D, threshold=True, batch_norm=batch_norm, dtype=dtype, device=DEV)
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        layer.weight.copy_(torch.randn(out_f, in_f, generator=g).half())
+        layer.bias.copy_((4 * torch.randn(out_f, generator=g)).half())
+    layer.set_seed(seed)
+    layer.set_noise()
+    layer.perturbed_flag = True
+    return layer, g
+
+
+@pytest.mark.parametrize("D,out_f,in_f,bits", [(16, 24, 256, 64), (40, 100, 1024, 64), (9, 33, 128, 32), (5, 70, 4096, 64)])
+@pytest.mark.parametrize("batch_norm", [False, True])
+def test_binarized_linear_thresholds_and_packed_output(ops, D, out_f, in_f, bits, batch_norm):
+    """One streaming kernel (two more launches with the batch mean): bit-exact against the restated layer, as bools
+    and as packed words; the fp16 steps are the reference's (int32 activation compared in fp16)."""
+    from nesgpu_b200 import binary
+    layer, g = _linear_layer(binary, D, out_f, in_f, batch_norm, seed=D + out_f, dtype=DT[bits])
+    x = torch.randint(2, (D, in_f), generator=g).bool()
+    wbits, beta, bias = npy(layer.weight_noise), npy(layer.bias_noise), npy(layer.bias)
+    want = B.binarized_linear_layer(wbits, x.numpy(), in_f, bias, beta, batch_norm, bits)
+    got = layer.forward(x.to(DEV))
+    assert got.dtype == torch.bool
+    np.testing.assert_array_equal(npy(got), want)
+    layer.packed_output = True
+    packed = layer.forward(ops.pack(x.to(DEV), DT[bits]))         # packed input, packed output
+    np.testing.assert_array_equal(npy(packed), B.pack(want, bits))
+    layer.threshold = False
+    np.testing.assert_array_equal(npy(layer.forward(x.to(DEV))), B.binarized_linear_forward(wbits, x.numpy(), in_f, None, bits))
+
+
+def test_binarized_linear_rows_that_are_not_whole_chunks(ops):
+    """in_features = 200 with int32 words: 7 words = 28 bytes per row, the tiled product + shared epilogue path."""
+    from nesgpu_b200 import binary
+    layer, g = _linear_layer(binary, 6, 10, 200, False, seed=3, dtype=torch.int32)
+    x = torch.randint(2, (6, 200), generator=g).bool()
+    want = B.binarized_linear_layer(npy(layer.weight_noise), x.numpy(), 200, npy(layer.bias), npy(layer.bias_noise), False, 32)
+    np.testing.assert_array_equal(npy(layer.forward(x.to(DEV))), want)
+
+
+@pytest.mark.parametrize("batch_norm", [False, True])
+def test_binarized_conv_thresholds(ops, batch_norm):
+    from nesgpu_b200 import binary
+    D, cin, cout, size = 5, 96, 40, 8
+    conv = binary.BinarizedConv2d(cin, cout, D, 3, padding=1, threshold=True, batch_norm=batch_norm, device=DEV)
+    g = torch.Generator().manual_seed(12)
+    with torch.no_grad():
+        conv.weight.copy_(torch.randn(conv.weight.shape, generator=g).half())
+        conv.bias.copy_((6 * torch.randn(cout, generator=g)).half())
+    conv.set_seed(2)
+    conv.set_noise()
+    conv.perturbed_flag = True
+    x = torch.randint(2, (D, size, size, cin), generator=g).bool()
+    wb = npy(conv.weight_noise).reshape(D, cout, 3, 3, -1).transpose(0, 2, 3, 4, 1).reshape(D, -1, cout)
+    xin = B.pack(x.numpy().reshape(-1, cin), 64).reshape(D, size, size, -1)
+    counts = B.conv(xin, wb, 3, 3, 1, 1, 1, 1)
+    want = B.binarized_conv_layer(counts, cin * 9, npy(conv.bias), npy(conv.bias_noise), batch_norm)
+    got = conv.forward(x.to(DEV))
+    np.testing.assert_array_equal(npy(got), want)
+    conv.packed_output = True
+    packed = conv.forward(x.to(DEV))
+    # packed NHWC words for the next layer
+    np.testing.assert_array_equal(npy(packed), B.pack(want.reshape(-1, cout), 64).reshape(D, size, size, -1))
+
+
+def test_binarized_update_matches_the_restated_layer(ops):
+    from nesgpu_b200 import binary
+    layer, g = _linear_layer(binary, 64, 48, 256, False, seed=8)
+    fitness = torch.randn(64, generator=g)
+    layer.update(fitness.to(DEV), l1=0.01, l2=0.02)
+    wg, bg = B.binarized_update(npy(layer.weight_noise), fitness.numpy(), npy(layer.weight), npy(layer.bias_noise), 256,
+                                l1=0.01, l2=0.02)
+    got_w, got_b = npy(layer.weight.grad).astype(np.float64), npy(layer.bias.grad).astype(np.float64)
+    # fp16 results of fp32 sums taken in another order: one fp16 rounding step of slack
+    assert np.all(np.abs(got_w - wg.astype(np.float64)) <= 2.0 ** -9 * np.maximum(np.abs(wg.astype(np.float64)), 1.0) + 2e-3)
+    assert np.all(np.abs(got_b - bg.astype(np.float64)) <= 2.0 ** -9 * np.maximum(np.abs(bg.astype(np.float64)), 1.0) + 2e-3)
+
+
+def test_binarized_noise_statistics_and_probabilities(ops):
+    from nesgpu_b200 import binary
+    layer, _ = _linear_layer(binary, 256, 64, 512, False, seed=6)
+    bn = layer.bias_noise.float()
+    assert bn.min().item() >= -3.0 and bn.max().item() < 3.0
+    assert abs(bn.mean().item()) < 0.05 and abs(bn.std().item() - 3 ** .5) < 0.05      # uniform on [-3, 3)
+    P = npy(layer.bernoulli_probabilities()).astype(np.float32)
+    np.testing.assert_allclose(P, B.bernoulli_probabilities(npy(layer.weight)).astype(np.float32), atol=2e-3)
+    other = binary.BinarizedLinear(512, 64, 256, device=DEV)
+    other.set_seed(6)
+    other.set_member_offset(256)
+    other.set_noise()
+    assert not torch.equal(other.bias_noise, layer.bias_noise)

@@ -5,7 +5,7 @@ Tolerances: mode 3 (3xTF32, error-compensated) must hold the fp32 bar (rel err <
 import pytest
 import torch
 
-from gpu_util import DEV, rel_err
+from gpu_util import DEV, G, assert_close, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -531,3 +531,83 @@ def test_permuted_linear_out_cluster_kernel_refuses_uncovered_shapes():
     with pytest.raises(NotImplementedError):
         C.call("nes_permuted_linear_out_fwd_tc", C.ptr(d), C.ptr(d), None, C.ptr(d), None, None, C.ptr(d),
                8, 1, 30, 16, 16, 0, 3, C.stream())
+
+
+# ------------------------------------------------------------------ split-bf16 convolutions: the fp32 bar on the tensor cores
+
+@pytest.mark.parametrize("mode,in_sp,out_sp,R,anti,hw,k,pad,cout,cin", [
+    ("out", 0, 0.5, 1, False, 13, 3, 1, 64, 64), ("in", 0, 0, 2, True, 9, 3, 1, 32, 64), ("both", 0, 0, 3, True, 8, 3, 0, 64, 64),
+    ("out", 0, 0, 2, True, 33, 1, 0, 128, 128), ("auto", 0.5, 0, 1, False, 20, 3, 2, 24, 64), ("out", 0, 0, 2, True, 32, 3, 1, 64, 64),
+])
+def test_permuted_conv_split_bf16_holds_the_fp32_bar(mode, in_sp, out_sp, R, anti, hw, k, pad, cout, cin):
+    """Default mode of a covered geometry: three bf16 products on hi/lo splits; 1e-4 on the output and 1e-3 on the
+    perturbation term alone (the part the ES update sees)."""
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import set_params
+    D = 5
+    g = torch.Generator().manual_seed(hw + k + cout)
+    layer = base.PermutedConv2d(cin, cout, k, D, padding=pad, antithetic=anti, permutation=mode, in_sparsity=in_sp,
+                                out_sparsity=out_sp).to(DEV)
+    isp, osp = layer.in_sparsity, layer.out_sparsity
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g)
+    eps = 0.05 * torch.randn(osp, isp, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    pin = _perms(g, D, cin, isp) if layer.permute_inputs else None
+    pout = _perms(g, D, cout) if layer.permute_outputs else None
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(eps), G(beta)
+    layer.input_permutations, layer.output_permutations = G(pin), G(pout)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert layer.last_path == "bf16x3" and _flag(C) == 0
+    want = O.permuted_conv2d_forward(x, W, b, eps, beta, pin, pout, D, 1, pad, 1, anti)
+    assert_close(y, want, tol=1e-4, what="split-bf16 conv")
+    basey = torch.nn.functional.conv2d(x, W, b, 1, pad)
+    assert_close(y.cpu() - basey, want - basey, tol=1e-3, what="perturbation term")
+    layer.options = {"tc": "fp32"}
+    with torch.no_grad():
+        y32 = layer.forward(G(x))
+    assert layer.last_path == "fp32"
+    assert_close(y32, want, tol=1e-4, what="CUDA-core conv")
+
+
+def test_perturbed_conv_split_bf16_holds_the_fp32_bar():
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import set_params
+    D, R, cin, cout, hw, k = 4, 2, 64, 64, 12, 3
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g)
+    E = 0.05 * torch.randn(D, cout, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    layer = base.PerturbedConv2d(cin, cout, k, D, padding=1, antithetic=True).to(DEV)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(E), G(beta)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert layer.last_path == "bf16x3" and _flag(C) == 0
+    want = O.perturbed_conv2d_forward(x, W, b, E, beta, D, 1, 1, 1, True)
+    assert_close(y, want, tol=1e-4, what="split-bf16 conv")
+    basey = torch.nn.functional.conv2d(x, W, b, 1, 1)
+    assert_close(y.cpu() - basey, want - basey, tol=1e-3, what="perturbation term")
+
+
+def test_split_bf16_is_not_taken_for_uncovered_geometries():
+    from nesgpu_b200 import base, _cabi as C
+    assert C.call("nes_conv2d_fwd_bf16x3_supported", 64, 32, 32, 64, 3, 3, 1, 1, 1, 1, 1, 1) == 1
+    assert C.call("nes_conv2d_fwd_bf16x3_supported", 32, 13, 13, 64, 3, 3, 1, 1, 0, 0, 1, 1) == 0      # 32 input channels
+    assert C.call("nes_conv2d_fwd_bf16x3_supported", 64, 32, 32, 64, 3, 3, 2, 2, 1, 1, 1, 1) == 0      # stride 2
+    layer = base.PermutedConv2d(64, 64, 3, 4, padding=1, options={"tc": "bf16x3"}, stride=2).to(DEV)
+    layer.set_noise(0.02)
+    layer.perturbed_flag = True
+    with pytest.raises(NotImplementedError):
+        layer.forward(torch.zeros(4, 64, 8, 8, device=DEV))
