@@ -169,7 +169,8 @@ class PerturbedLinear1024(Workload):
         with torch.no_grad():
             self.layer.weight.copy_(torch.randn(self.n, self.n, generator=g) / self.n ** .5)
             self.layer.bias.zero_()
-        self.layer.set_seed(5000 + rank)
+        self.layer.set_seed(5000)                       # one seed everywhere: the member offset keeps the ranks' draws apart
+        self.layer.set_member_offset(rank * self.D)
         self.layer.set_noise(0.02)
         self.x_host = torch.randn(self.D * self.R, self.n, generator=g).pin_memory()
         self.w_host = (torch.rand(self.D, generator=g) * 2 - 1).pin_memory()
@@ -874,7 +875,9 @@ class EsCnn(Workload):
                 base.PermutedLinear(1600, 128, D), torch.nn.ReLU(), base.PermutedLinear(128, 10, D)).to(dev)
         self.pm = base.PerturbedModel(self.net, D)
         self.pm.set_noise_scale(0.02)
-        self.pm.set_seed(9000 + rank)
+        import random
+        random.seed(9000)                               # the per-step seeds agree on all ranks ...
+        self.pm.set_member_offset(rank * D)             # ... and the member offset keeps their members apart
         g = torch.Generator().manual_seed(2005)
         self.images_host = torch.rand(self.R, 1, 28, 28, generator=g).pin_memory()
         self.labels_host = torch.randint(10, (self.R,), generator=g).pin_memory()
@@ -1492,6 +1495,7 @@ def run_ours(args, rank, world, local_rank):
     roofline = wl.roofline(timing["phase_ms"], peaks) if rank == 0 else None
     config = wl.describe(world)
     mode = wl.mode()
+    h2d, d2h = getattr(wl, "h2d", None), getattr(wl, "d2h", None)
     timing["graph"] = timing["flush"] = None
     if default_run and world == 1 and not args.no_extras:
         del wl                                    # 4 GiB of noise: the other configurations get a clean device
@@ -1506,8 +1510,7 @@ def run_ours(args, rank, world, local_rank):
                 "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": config, "precision_mode": mode,
                 "e2e": {"value": round(wl.units_per_step * world / (e2e_ms * 1e-3), 1), "unit": UNIT,
-                        "h2d_bytes_per_step": wl.h2d if hasattr(wl, "h2d") else None,
-                        "d2h_bytes_per_step": wl.d2h if hasattr(wl, "d2h") else None,
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
                 "gpu_launches": timing["launches"], "cuda_graph": timing["launches"] is not None and getattr(wl, "use_graph", False) and world == 1 and not args.no_graph,
                 "phase_ms": {k: round(v, 4) for k, v in timing["phase_ms"].items()},

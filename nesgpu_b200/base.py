@@ -26,6 +26,18 @@ def _opt(t):
     return None if t is None else C.require_cuda(t.detach(), "parameter", _F32)
 
 
+def _grad_destination(param):
+    """Where an update may write ``param``'s gradient instead of a fresh tensor: the slice of an all-reduce bucket
+    that :mod:`nesgpu_b200.dist` attached to the parameter.  Only while ``.grad`` is empty (an accumulating update
+    must not overwrite what ``.grad`` already holds, which may be that very slice)."""
+    view = getattr(param, "_nes_grad_out", None)
+    if view is None or param.grad is not None:
+        return None
+    if view.shape != param.shape or view.device != param.device or view.dtype != _F32 or not view.is_contiguous():
+        return None
+    return view
+
+
 class PerturbedModel:
     """Wraps a model whose layers derive from :class:`Perturbed` (reference ``base.py:9-41``).
 
@@ -173,15 +185,17 @@ class Perturbed:
         return param.detach()
 
     @staticmethod
-    def _weighted_sum(noise, weights, param, l1, l2, direct_param=None):
-        """sum_d weights[d] * noise[d] (+ l1 sign(param) + l2 param) as a tensor shaped like noise[0]."""
+    def _weighted_sum(noise, weights, param, l1, l2, direct_param=None, out=None):
+        """sum_d weights[d] * noise[d] (+ l1 sign(param) + l2 param) as a tensor shaped like noise[0] (written
+        into ``out`` when given)."""
         noise = C.require_cuda(noise, "noise", _F32)
         weights = C.require_cuda(weights, "weights", _F32)
         D = noise.shape[0]
         n = noise[0].numel() if D else 0
         if weights.numel() != D:
             raise RuntimeError("update weights must have one entry per direction")
-        out = torch.empty(noise.shape[1:], device=noise.device, dtype=_F32)
+        if out is None:
+            out = torch.empty(noise.shape[1:], device=noise.device, dtype=_F32)
         nbytes = C.call("nes_perturbed_update_scratch_bytes", D, n)
         buf = C.scratch(nbytes, noise.device)
         reg = C.ptr(_opt(param)) if (l1 or l2) else None
@@ -197,16 +211,17 @@ class Perturbed:
     def weight_grad(self, weights):
         return self._weighted_sum(self.weight_noise, weights, None, 0, 0, self._direct_param(self.weight))
 
-    def _weight_grad_regularised(self, weights, l1, l2):
-        return self._weighted_sum(self.weight_noise, weights, self.weight, l1, l2, self._direct_param(self.weight))
+    def _weight_grad_regularised(self, weights, l1, l2, out=None):
+        return self._weighted_sum(self.weight_noise, weights, self.weight, l1, l2, self._direct_param(self.weight), out)
 
     def update(self, weights, l1=0, l2=0):
         """Accumulate the fitness-weighted noise sum into ``.grad`` (reference ``base.py:120-138``)."""
-        grad = self._weight_grad_regularised(weights, l1, l2)
+        grad = self._weight_grad_regularised(weights, l1, l2, _grad_destination(self.weight))
         self.weight.grad = grad if self.weight.grad is None else self.weight.grad + grad
         if self.bias is None:
             return grad
-        bias_grad = self._weighted_sum(self.bias_noise, weights, None, 0, 0, self._direct_param(self.bias))
+        bias_grad = self._weighted_sum(self.bias_noise, weights, None, 0, 0, self._direct_param(self.bias),
+                                       _grad_destination(self.bias))
         self.bias.grad = bias_grad if self.bias.grad is None else self.bias.grad + bias_grad
         return grad, bias_grad
 
@@ -307,7 +322,7 @@ class Permuted(Perturbed):
         pout = C.require_cuda(self.output_permutations, "output_permutations", torch.int16) if self.permute_outputs else None
         return pin, pout
 
-    def _permuted_update(self, weights, l1, l2, want_perm_weights=False):
+    def _permuted_update(self, weights, l1, l2, want_perm_weights=False, out=None):
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         weights = C.require_cuda(weights, "weights", _F32)
         if weights.numel() != self.directions:
@@ -316,7 +331,7 @@ class Permuted(Perturbed):
         ksize = 1
         for s in self.weight.shape[2:]:
             ksize *= s
-        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        grad = out if out is not None else torch.empty_like(self.weight, memory_format=torch.contiguous_format)
         pw = None
         if want_perm_weights:
             shape = (self.in_sparsity, self.in_degree) if pin is not None else (self.out_degree, self.out_sparsity)
@@ -343,11 +358,15 @@ class Permuted(Perturbed):
         ksize = 1
         for s in self.weight.shape[2:]:
             ksize *= s
-        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        grad = _grad_destination(self.weight)
+        if grad is None:
+            grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
         beta = bias_grad = None
         if self.bias is not None:
             beta = C.require_cuda(self.bias_noise, "bias_noise", _F32)
-            bias_grad = torch.empty_like(self.bias)
+            bias_grad = _grad_destination(self.bias)
+            if bias_grad is None:
+                bias_grad = torch.empty_like(self.bias)
         C.call("nes_permuted_update_out", C.ptr(eps), C.ptr(weights), C.ptr(pout),
                C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(beta), C.ptr(grad), C.ptr(bias_grad),
                self.directions, self.in_degree, self.out_degree, self.out_sparsity, ksize, float(l1), float(l2),
@@ -368,8 +387,8 @@ class Permuted(Perturbed):
     def weight_grad(self, weights):
         return self._permuted_update(weights, 0, 0)[0]
 
-    def _weight_grad_regularised(self, weights, l1, l2):
-        return self._permuted_update(weights, l1, l2)[0]
+    def _weight_grad_regularised(self, weights, l1, l2, out=None):
+        return self._permuted_update(weights, l1, l2, out=out)[0]
 
 
 _TC_MODES = {"3xtf32": 3, "tf32": 1}
@@ -488,11 +507,11 @@ class SparsePerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
                self.out_features, self.k, 1 if self.antithetic else 0, C.stream())
         return y.view(*lead, self.out_features)
 
-    def _weight_grad_regularised(self, weights, l1, l2):
+    def _weight_grad_regularised(self, weights, l1, l2, out=None):
         val = C.require_cuda(self.weight_noise, "weight_noise", _F32)
         idx = C.require_cuda(self.noise_indices, "noise_indices", torch.int32)
         weights = C.require_cuda(weights, "weights", _F32)
-        grad = torch.empty_like(self.weight)
+        grad = out if out is not None else torch.empty_like(self.weight)
         C.call("nes_sparse_perturbed_update", C.ptr(idx), C.ptr(val), C.ptr(weights),
                C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), self.directions,
                self.in_features, self.out_features, self.k, float(l1), float(l2), C.stream())
@@ -927,7 +946,7 @@ class Synthetic(Perturbed):
         fout = C.require_cuda(self.output_flips, "output_flips", torch.int8) if self.flip_outputs else None
         return fin, fout
 
-    def _weight_grad_regularised(self, weights, l1, l2):
+    def _weight_grad_regularised(self, weights, l1, l2, out=None):
         """eps * sum_d w_d f_out[d] f_in[d]^T (reference ``base.py:338-347``; the reference's two-sided
         einsum multiplies by w_d twice, ``base.py:340`` -- here it is the plain fitness-weighted sum)."""
         eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
@@ -938,7 +957,7 @@ class Synthetic(Perturbed):
         ksize = 1
         for sdim in self.weight.shape[2:]:
             ksize *= sdim
-        grad = torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        grad = out if out is not None else torch.empty_like(self.weight, memory_format=torch.contiguous_format)
         C.call("nes_synthetic_update", C.ptr(eps), C.ptr(weights), C.ptr(fin), C.ptr(fout),
                C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), self.directions, self.in_degree,
                self.out_degree, ksize, float(l1), float(l2), C.stream())

@@ -55,7 +55,7 @@ struct PermOutParams {
   int NB, NP;                               // base / noise columns per block (multiples of 16)
   int stages, tmem_cols, antithetic;
   unsigned int np_magic;                    // ceil(2^32 / NP): so / NP == umulhi(so, np_magic) for so < 2^24
-  int vec_y, vec_pout, vec_beta;
+  int vec_y, vec_pout, vec_beta, vec_bias;
   int local_gather;                         // 1: slices are pushed to the peers and the gather is local
 };
 
@@ -94,6 +94,10 @@ __device__ __forceinline__ void bulk_push(uint32_t remote_dst, uint32_t local_sr
       : "memory");
 }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// asks the TMA unit to bring one box of a tiled tensor into L2 (no shared-memory destination, no barrier)
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   float v;
@@ -164,6 +168,9 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
   PO_TRACE(threadIdx.x == 0, 1);
 
   // epilogue geometry of this thread (warps 2-9): accumulator row and the 16-column chunks it takes
+  constexpr int PO_PRE = 2;                                    // chunks whose tables are preloaded into registers
+  uint4 pre_so[PO_PRE][2];
+  float4 pre_bn[PO_PRE][4], pre_bias[PO_PRE][4];
   const int q = warp & 3;
   const int row = q * 32 + lane;
   const int chunk0 = (warp - 2) >> 2;                          // 0 for warps 2-5, 1 for warps 6-9
@@ -172,8 +179,17 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---- producer: the raw fp32 tiles of x, W_j and eps_j
+      // ---- producer: the raw fp32 tiles of x, W_j and eps_j.  Once the ring is full, everything else this
+      // block will read is requested into L2 (the ring holds only a few K steps, and a cold tile would cost an
+      // HBM round trip each time a stage is refilled)
       for (int kt = 0; kt < nk; ++kt) {
+        if (kt == p.stages) {
+          for (int kp = p.stages; kp < nk; ++kp) {
+            tma_prefetch_2d(&p.map_x, kp * PO_BK, int(m0));
+            tma_prefetch_2d(&p.map_w, kp * PO_BK, int(j) * p.NB);
+            tma_prefetch_2d(&p.map_eps, kp * PO_BK, int(j) * p.NP);
+          }
+        }
         const int s = kt % p.stages;
         const uint32_t ph = (kt / p.stages) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, 1)) break;
@@ -224,12 +240,36 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
   } else {
     // ---- operand splitters, then the first half of the epilogue
     const int t = threadIdx.x - 64;                             // 0 .. PO_WORKERS-1
-    // the epilogue's per-row tables are cold: start them on their way to L2 now
-    if (chunk0 == 0 && gm < p.B) {
+    // The epilogue's per-row tables (permutation entries, bias noise, bias) are cold in HBM.  The first PO_PRE
+    // chunks of this thread are loaded into registers now, where the whole K loop hides the latency; what lies
+    // beyond is at least started on its way to L2.
+    if (gm < p.B) {
       const long long d = gm % p.D;
-      const int cols = (kbase + p.NB <= p.out) ? p.NB : (p.out > kbase ? p.out - kbase : 0);
-      if (p.pout) for (int o = 0; o < cols * 2; o += 128) prefetch_l2(reinterpret_cast<const char*>(p.pout + d * p.out + kbase) + o);
-      if (p.beta) for (int o = 0; o < cols * 4; o += 128) prefetch_l2(reinterpret_cast<const char*>(p.beta + d * p.out + kbase) + o);
+#pragma unroll
+      for (int ci = 0; ci < PO_PRE; ++ci) {
+        const int c = chunk0 * 16 + ci * 32;
+        const int k0 = kbase + c;
+        if (c < p.NB && k0 + 16 <= p.out) {
+          if (p.pout && p.vec_pout) {
+            const uint4* pr = reinterpret_cast<const uint4*>(p.pout + d * p.out + k0);
+            pre_so[ci][0] = __ldg(pr); pre_so[ci][1] = __ldg(pr + 1);
+          }
+          if (p.beta && p.vec_beta) {
+            const float4* br = reinterpret_cast<const float4*>(p.beta + d * p.out + k0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) pre_bn[ci][u] = __ldg(br + u);
+          }
+          if (p.bias && p.vec_bias) {
+            const float4* br = reinterpret_cast<const float4*>(p.bias + k0);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) pre_bias[ci][u] = __ldg(br + u);
+          }
+        }
+      }
+      for (int c = chunk0 * 16 + PO_PRE * 32; c < p.NB && kbase + c < p.out; c += 32) {
+        if (p.pout) prefetch_l2(p.pout + d * p.out + kbase + c);
+        if (p.beta) prefetch_l2(p.beta + d * p.out + kbase + c);
+      }
     }
     bool ok = true;
     for (int kt = 0; kt < nk && ok; ++kt) {
@@ -308,9 +348,11 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
     if (row_ok) { d = gm % p.D; sgn = anti_sign(gm / p.D, p.R, p.antithetic); }
     const float* lrow = xchg + size_t(row) * pitch;                       // local gather: + owner * slice_floats + column
     const uint32_t xrow = smem_u32(xchg) + uint32_t(row) * uint32_t(pitch) * 4u;
+#pragma unroll 2
     for (int c = chunk0 * 16; c < p.NB; c += 32) {
       const int k0 = kbase + c;
       if (k0 >= p.out) break;                                    // uniform over the warp
+      const int ci = (c - chunk0 * 16) >> 5;
       uint32_t acc[16];
       tmem_ld16_nowait(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(c), acc);
       tmem_ld_wait();
@@ -320,8 +362,10 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
       if (p.pout) {
         const int16_t* pr = p.pout + d * p.out + k0;
         if (whole && p.vec_pout) {
-          const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(pr));
-          const uint4 v1 = __ldg(reinterpret_cast<const uint4*>(pr) + 1);
+          uint4 v0, v1;
+          if (ci == 0) { v0 = pre_so[0][0]; v1 = pre_so[0][1]; }
+          else if (ci == 1) { v0 = pre_so[1][0]; v1 = pre_so[1][1]; }
+          else { v0 = __ldg(reinterpret_cast<const uint4*>(pr)); v1 = __ldg(reinterpret_cast<const uint4*>(pr) + 1); }
           const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
           for (int u = 0; u < 8; ++u) { so[2 * u] = int(w[u] & 0xFFFFu); so[2 * u + 1] = int(w[u] >> 16); }
@@ -350,7 +394,10 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
         if (whole && p.vec_beta) {
 #pragma unroll
           for (int u = 0; u < 16; u += 4) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(br + u));
+            float4 v;
+            if (ci == 0) v = pre_bn[0][u >> 2];
+            else if (ci == 1) v = pre_bn[1][u >> 2];
+            else v = __ldg(reinterpret_cast<const float4*>(br + u));
             bn[u] = v.x; bn[u + 1] = v.y; bn[u + 2] = v.z; bn[u + 3] = v.w;
           }
         } else {
@@ -361,13 +408,20 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
 #pragma unroll
         for (int u = 0; u < 16; ++u) bn[u] = 0.f;
       }
+      float bs[16];
+      if (p.bias && whole && p.vec_bias && ci < PO_PRE) {
+#pragma unroll
+        for (int u = 0; u < 16; u += 4) {
+          const float4 v = (ci == 0) ? pre_bias[0][u >> 2] : pre_bias[1][u >> 2];
+          bs[u] = v.x; bs[u + 1] = v.y; bs[u + 2] = v.z; bs[u + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) bs[u] = (p.bias && k0 + u < p.out) ? __ldg(p.bias + k0 + u) : 0.f;
+      }
       float o[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        float v = __uint_as_float(acc[u]) + sgn * (qv[u] + bn[u]);
-        if (p.bias && k0 + u < p.out) v += __ldg(p.bias + k0 + u);
-        o[u] = v;
-      }
+      for (int u = 0; u < 16; ++u) o[u] = __uint_as_float(acc[u]) + bs[u] + sgn * (qv[u] + bn[u]);
       float* dst = p.y + gm * p.out + k0;
       if (whole && p.vec_y) {
 #pragma unroll
@@ -529,6 +583,7 @@ extern "C" int nes_permuted_linear_out_fwd_tc(const float* x, const float* weigh
   prm.vec_y = (out % 4 == 0) && aligned16(y);
   prm.vec_pout = pout && (out % 8 == 0) && aligned16(pout);
   prm.vec_beta = bias_noise && (out % 4 == 0) && aligned16(bias_noise);
+  prm.vec_bias = bias && aligned16(bias);
   prm.local_gather = plan.local_gather;
   const int64_t mtiles = ceil_div<int64_t>(B, PO_BM);
   cudaStream_t st = as_stream(stream);

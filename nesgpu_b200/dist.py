@@ -78,7 +78,18 @@ class UpdateBucket:
 
     def pack(self, tensors):
         for v, t in zip(self.views(), tensors):
-            v.copy_(t)
+            if v.data_ptr() != t.data_ptr():
+                v.copy_(t)
+
+    def attach(self, params):
+        """Tell the layers to write the next gradients straight into this bucket: every parameter gets its slice
+        as ``_nes_grad_out``, which the update kernels take as their output while ``.grad`` is empty."""
+        for p, v in zip(params, self.views()):
+            p._nes_grad_out = v
+
+    def holds(self, tensors):
+        """True when every tensor IS its slice of the bucket (nothing to pack, nothing to copy back)."""
+        return all(v.data_ptr() == t.data_ptr() and v.shape == t.shape for v, t in zip(self.views(), tensors))
 
     def all_reduce(self, group=None):
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
@@ -88,14 +99,24 @@ class UpdateBucket:
 
 def all_reduce_grads(parameters, bucket=None, group=None):
     """Sum ``.grad`` of the given parameters over the ranks through one bucket; every rank ends
-    with the full-population update and applies the same optimiser step."""
+    with the full-population update and applies the same optimiser step.
+
+    The first call builds the bucket and attaches its slices to the parameters; from then on an update that
+    starts from ``.grad = None`` writes its gradients directly into the bucket, the all-reduce runs in place and
+    ``.grad`` is the reduced slice -- no packing and no copy back.  Gradients that live elsewhere (an accumulating
+    update, a layer without the hook) are packed first and ``.grad`` is pointed at the reduced slice."""
     params = [p for p in parameters if p.grad is not None]
     if not params:
         return bucket
     grads = [p.grad for p in params]
     if bucket is None or bucket.sizes != [g.numel() for g in grads]:
         bucket = UpdateBucket(grads)
-    bucket.pack(grads)
-    for p, v in zip(params, bucket.all_reduce(group)):
-        p.grad.copy_(v)
+        bucket.attach(params)
+    in_place = bucket.holds(grads)
+    if not in_place:
+        bucket.pack(grads)
+    views = bucket.all_reduce(group)
+    if not in_place:
+        for p, v in zip(params, views):
+            p.grad = v
     return bucket

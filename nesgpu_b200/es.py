@@ -42,6 +42,17 @@ def model_noise_scale(perturbed_model):
     return None
 
 
+def assign_member_offsets(perturbed_model, population, group=None):
+    """Tell every perturbed layer the global index of this rank's first member (``set_member_offset``), so that
+    ranks which share seeds draw different members.  Returns that index."""
+    on = torch.distributed.is_available() and torch.distributed.is_initialized()
+    rank = torch.distributed.get_rank(group) if on else 0
+    world = torch.distributed.get_world_size(group) if on else 1
+    lo = ndist.member_slice(population, rank, world)[0]
+    perturbed_model.set_member_offset(lo)
+    return lo
+
+
 def takes_shared_input(perturbed_model):
     """True when the model's first perturbed layer declares ``options["shared_input"]``: it then receives the
     minibatch itself instead of its copy per member."""
@@ -141,7 +152,7 @@ def es_step(perturbed_model, inputs, labels, directions, noise_scale=None, chunk
     rank = torch.distributed.get_rank(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 0
     world = torch.distributed.get_world_size(group) if (torch.distributed.is_available() and torch.distributed.is_initialized()) else 1
     if population is not None:
-        perturbed_model.set_member_offset(ndist.member_slice(population, rank, world)[0])
+        assign_member_offsets(perturbed_model, population, group)
     if new_noise:
         # noise is a pure function of each layer's seed, so a step draws new seeds first, as the reference's
         # trainer does (mnisttest.py:128-131); reseed=False keeps the seeds that are set

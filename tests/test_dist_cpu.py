@@ -62,6 +62,29 @@ def _worker(rank, world, port, out):
     wpar.grad, bpar.grad = O.perturbed_update(W, E[lo:hi], beta[lo:hi], 2 * wgt[lo:hi])
     ok &= nd.all_reduce_grads([wpar, bpar], bucket) is bucket
     ok &= torch.allclose(wpar.grad, 2 * full_w, atol=1e-5)
+    # the first call attached the bucket's slices to the parameters: an update that writes there is reduced in place
+    ok &= wpar._nes_grad_out.data_ptr() == bucket.views()[0].data_ptr()
+    part_w, part_b = O.perturbed_update(W, E[lo:hi], beta[lo:hi], wgt[lo:hi])
+    wpar.grad = bpar.grad = None
+    wpar._nes_grad_out.copy_(part_w)
+    bpar._nes_grad_out.copy_(part_b)
+    wpar.grad, bpar.grad = wpar._nes_grad_out, bpar._nes_grad_out
+    ok &= bucket.holds([wpar.grad, bpar.grad])
+    ok &= nd.all_reduce_grads([wpar, bpar], bucket) is bucket
+    ok &= torch.allclose(wpar.grad, full_w, atol=1e-5) and wpar.grad.data_ptr() == bucket.views()[0].data_ptr()
+    # every rank tells its layers where its member slice starts in the population
+    from nesgpu_b200 import es
+
+    class Recorder:
+        offset = None
+
+        def set_member_offset(self, first):
+            self.offset = first
+    rec = Recorder()
+    ok &= es.assign_member_offsets(rec, D) == lo and rec.offset == lo
+    firsts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(firsts, torch.tensor([rec.offset]))
+    ok &= len({int(f) for f in firsts}) == world                  # distinct on every rank
     out[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()
