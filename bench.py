@@ -147,6 +147,7 @@ class PerturbedLinear1024(Workload):
     """PerturbedLinear 1024x1024 with 1024 dense Gaussian noise matrices (4 GiB), antithetic: forward + update."""
     name = "perturbed_linear_1024"
     D, R, n = 1024, 2, 1024
+    overlap_blocks = 0          # --overlap-update N: gradient in N column blocks, each all-reduced while the next streams
 
     def __init__(self, members=None):
         if members:
@@ -187,9 +188,13 @@ class PerturbedLinear1024(Workload):
         layer = self.layer
         layer.weight.grad = None
         layer.bias.grad = None
-        grad, bgrad = layer.update(w)
-        if self.world > 1:
-            self.bucket = self.ndist.all_reduce_grads([layer.weight, layer.bias], self.bucket)
+        if self.world > 1 and self.overlap_blocks:
+            # column blocks of the gradient go to the all-reduce while the next block streams
+            self.bucket = self.ndist.overlapped_dense_update(layer, w, self.bucket, blocks=self.overlap_blocks)
+        else:
+            layer.update(w)                  # from the second step on the gradients land in the bucket directly
+            if self.world > 1:
+                self.bucket = self.ndist.all_reduce_grads([layer.weight, layer.bias], self.bucket)
         return layer.weight.grad, layer.bias.grad
 
     def step(self, mark):
@@ -990,13 +995,14 @@ METRIC = "perturbed-member samples/sec per layer (forward + update)"
 
 def bind_to_gpu_numa_node(local_rank):
     """Run this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned host buffers it allocates
-    afterwards (first touch) and its copy threads are local to that GPU.  Returns the node or None."""
+    afterwards (first touch) and its copy threads are local to that GPU.  Returns the node, or a string that
+    says why nothing was bound."""
     try:
         props = torch.cuda.get_device_properties(local_rank)
         bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
         node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read().strip())
         if node < 0:
-            return None
+            return "no NUMA node reported for %s" % bdf
         cpus = set()
         for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
             lo, _, hi = part.partition("-")
@@ -1005,9 +1011,9 @@ def bind_to_gpu_numa_node(local_rank):
         if allowed:
             os.sched_setaffinity(0, allowed)
             return node
-    except (OSError, ValueError, AttributeError):
-        pass
-    return None
+        return "node %d has no CPU this process may use" % node
+    except (OSError, ValueError, AttributeError) as exc:
+        return "%s: %s" % (type(exc).__name__, exc)
 
 
 def _sync_all(world):
@@ -1458,6 +1464,8 @@ def run_ours(args, rank, world, local_rank):
     wl.tc = args.tc
     if args.unfused:
         wl.fused = False
+    if args.overlap_update:
+        wl.overlap_blocks = args.overlap_update
     wl.setup(dev, rank, world)
     peaks = measured_peaks()
     default_run = args.workload == "perturbed_linear_1024" and not args.members
@@ -1546,6 +1554,9 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the sustained block, the other configurations (per_config), the same-GPU run of the "
                          "reference's layers (gpu_reference) and, at N > 1, the strong-scaling and all-reduce checks")
+    ap.add_argument("--overlap-update", type=int, default=0,
+                    help="perturbed_linear_1024 at N > 1: form the gradient in this many column blocks and all-reduce each "
+                         "while the next one streams (default 0: one update kernel, one in-place all-reduce)")
     ap.add_argument("--unfused", action="store_true",
                     help="es_cnn_8192: separate Conv / ReLU / MaxPool2d modules and per-member input copies instead of the fused layers")
     ap.add_argument("--members", type=int, default=0,

@@ -110,6 +110,13 @@ int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n);
 int nes_perturbed_update(const float* noise, const float* w, const float* weight, float* grad,
                          int64_t D, int64_t n, float l1, float l2,
                          void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+/* The same reduction on a block of n columns of a wider noise matrix: member d's row starts at noise + d * ld
+ * (ld >= n elements; ld == n is nes_perturbed_update).  Lets a caller form the gradient block by block, for
+ * instance to hand finished blocks to an all-reduce while the next one streams.  weight / grad point at the
+ * block's first element. */
+int nes_perturbed_update_columns(const float* noise, const float* w, const float* weight, float* grad,
+                                 int64_t D, int64_t n, int64_t ld, float l1, float l2,
+                                 void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 /* The same reduction for "direct" storage (modules/base.py:111-117, 126-133), where the per-member
  * tensors hold parameter + noise:  grad[i] = sum_d w[d] * (stored[d,i] - param[i]) + l1/l2 terms.
  * The parameter is subtracted from each member's row before the row is weighted, as the reference does,

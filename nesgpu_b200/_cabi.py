@@ -29,6 +29,7 @@ SIGNATURES = {
     "nes_perturbed_conv2d_fwd": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr],
     "nes_perturbed_update_scratch_bytes": [c_i64, c_i64],
     "nes_perturbed_update": [c_ptr] * 4 + [c_i64, c_i64, c_f32, c_f32, c_ptr, c_i64, c_ptr],
+    "nes_perturbed_update_columns": [c_ptr] * 4 + [c_i64, c_i64, c_i64, c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_perturbed_update_direct": [c_ptr] * 5 + [c_i64, c_i64, c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_perturbed_update_noalloc": [c_ptr] * 4 + [c_i64, c_i64, c_f32, c_f32, c_ptr],
     "nes_sparse_perturbed_linear_fwd": [c_ptr] * 7 + [c_i64] * 4 + [c_int, c_int, c_ptr],

@@ -211,6 +211,25 @@ class Perturbed:
     def weight_grad(self, weights):
         return self._weighted_sum(self.weight_noise, weights, None, 0, 0, self._direct_param(self.weight))
 
+    def weight_grad_columns(self, weights, lo, hi, out, l1=0, l2=0):
+        """Entries [lo, hi) of the flattened weight gradient, written into ``out`` (a contiguous fp32 tensor of
+        hi - lo elements): the block-by-block form of :meth:`weight_grad` for dense per-member noise, so that a
+        finished block can go to an all-reduce while the next one streams."""
+        if self.options.get("direct"):
+            raise NotImplementedError("column blocks are not provided for direct storage")
+        noise = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        weights = C.require_cuda(weights, "weights", _F32)
+        D = noise.shape[0]
+        n = noise[0].numel()
+        if not (0 <= lo <= hi <= n) or out.numel() != hi - lo or not out.is_contiguous():
+            raise RuntimeError("bad column block")
+        nbytes = C.call("nes_perturbed_update_scratch_bytes", D, hi - lo)
+        buf = C.scratch(nbytes, noise.device)
+        reg = _opt(self.weight).view(-1)[lo:hi] if (l1 or l2) else None
+        C.call("nes_perturbed_update_columns", noise.data_ptr() + 4 * lo, C.ptr(weights), C.ptr(reg), C.ptr(out),
+               D, hi - lo, n, float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
+        return out
+
     def _weight_grad_regularised(self, weights, l1, l2, out=None):
         return self._weighted_sum(self.weight_noise, weights, self.weight, l1, l2, self._direct_param(self.weight), out)
 

@@ -19,7 +19,7 @@ constexpr int UPD_MAX_SPLITS = 16;
 template <bool VEC, bool SUB>
 __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise_sum_kernel(
     const float* __restrict__ noise, const float* __restrict__ w, const float* __restrict__ sub,
-    float* __restrict__ out, int64_t D, int64_t n, int64_t d_per_split) {
+    float* __restrict__ out, int64_t D, int64_t n, int64_t d_per_split, int64_t ld) {
   const int64_t d0 = blockIdx.y * d_per_split;
   const int64_t d1 = (d0 + d_per_split < D) ? d0 + d_per_split : D;
   float* dst = out + blockIdx.y * n;
@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise
     const int64_t i4 = int64_t(blockIdx.x) * UPD_THREADS + threadIdx.x;
     if (i4 * 4 >= n) return;
     const float4* src = reinterpret_cast<const float4*>(noise) + i4;
-    const int64_t stride = n / 4;
+    const int64_t stride = ld / 4;                  // row pitch of the noise in 128-bit units (ld == n unless a column block)
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 pv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (SUB) pv = __ldg(reinterpret_cast<const float4*>(sub) + i4);
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(UPD_THREADS, UPD_BLOCKS_PER_SM) weighted_noise
     if (i >= n) return;
     float acc = 0.f;
     const float pv = SUB ? __ldg(sub + i) : 0.f;
-    for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), __ldcs(noise + d * n + i) - pv, acc);
+    for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), __ldcs(noise + d * ld + i) - pv, acc);
     dst[i] = acc;
   }
 }
@@ -405,8 +405,9 @@ extern "C" int64_t nes_perturbed_update_scratch_bytes(int64_t D, int64_t n) {
 
 static int run_perturbed_update(const float* noise, const float* w, const float* sub, const float* weight, float* grad,
                                 int64_t D, int64_t n, float l1, float l2, void* scratch, int64_t scratch_bytes,
-                                cudaStream_t st) {
-  NES_REQUIRE(D >= 0 && n >= 0, NES_ERR_BAD_ARG, "perturbed_update: negative extent");
+                                cudaStream_t st, int64_t ld = -1) {
+  if (ld < 0) ld = n;
+  NES_REQUIRE(D >= 0 && n >= 0 && ld >= n, NES_ERR_BAD_ARG, "perturbed_update: bad extent");
   if (n == 0) return NES_OK;
   NES_REQUIRE(grad && (D == 0 || (noise && w)), NES_ERR_BAD_ARG, "perturbed_update: null pointer");
   NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "perturbed_update: l1/l2 given without weight");
@@ -414,7 +415,7 @@ static int run_perturbed_update(const float* noise, const float* w, const float*
     cudaMemsetAsync(grad, 0, n * sizeof(float), st);
     return finish(nullptr, 0, weight, grad, n, l1, l2, st, "perturbed_update(finish)");
   }
-  const bool vec = (n % 4 == 0) && aligned16(noise) && aligned16(grad) && aligned16(scratch) && (!sub || aligned16(sub));
+  const bool vec = (n % 4 == 0) && (ld % 4 == 0) && aligned16(noise) && aligned16(grad) && aligned16(scratch) && (!sub || aligned16(sub));
   const UpdatePlan p = plan_update(D, n, vec);
   NES_REQUIRE(p.bx <= INT32_MAX, NES_ERR_UNSUPPORTED, "perturbed_update: n too large");
   float* dst = grad;
@@ -425,11 +426,11 @@ static int run_perturbed_update(const float* noise, const float* w, const float*
   }
   dim3 grid((unsigned)p.bx, (unsigned)p.splits);
   if (sub) {
-    if (vec) weighted_noise_sum_kernel<true, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split);
-    else weighted_noise_sum_kernel<false, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split);
+    if (vec) weighted_noise_sum_kernel<true, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split, ld);
+    else weighted_noise_sum_kernel<false, true><<<grid, UPD_THREADS, 0, st>>>(noise, w, sub, dst, D, n, p.d_per_split, ld);
   } else {
-    if (vec) weighted_noise_sum_kernel<true, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split);
-    else weighted_noise_sum_kernel<false, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split);
+    if (vec) weighted_noise_sum_kernel<true, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split, ld);
+    else weighted_noise_sum_kernel<false, false><<<grid, UPD_THREADS, 0, st>>>(noise, w, nullptr, dst, D, n, p.d_per_split, ld);
   }
   int rc = check_launch("perturbed_update");
   if (rc != NES_OK) return rc;
@@ -440,6 +441,12 @@ extern "C" int nes_perturbed_update(const float* noise, const float* w, const fl
                                     int64_t D, int64_t n, float l1, float l2,
                                     void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
   return run_perturbed_update(noise, w, nullptr, weight, grad, D, n, l1, l2, scratch, scratch_bytes, as_stream(stream));
+}
+
+extern "C" int nes_perturbed_update_columns(const float* noise, const float* w, const float* weight, float* grad,
+                                            int64_t D, int64_t n, int64_t ld, float l1, float l2,
+                                            void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  return run_perturbed_update(noise, w, nullptr, weight, grad, D, n, l1, l2, scratch, scratch_bytes, as_stream(stream), ld);
 }
 
 extern "C" int nes_perturbed_update_direct(const float* stored, const float* w, const float* param, const float* weight,

@@ -97,6 +97,40 @@ class UpdateBucket:
         return self.views()
 
 
+def overlapped_dense_update(layer, weights, bucket=None, group=None, blocks=4, l1=0, l2=0):
+    """Update of a dense-noise layer (``PerturbedLinear`` / ``PerturbedConv2d``) with the all-reduce taken off the
+    critical path: the weight gradient is formed in ``blocks`` column blocks written straight into the bucket, and
+    the all-reduce of block k is issued asynchronously while block k + 1 streams its share of the noise; only the
+    last block's reduction (and the small bias reduction) is exposed.  Leaves the full-population gradients in
+    ``.grad`` (slices of the bucket) and returns the bucket."""
+    params = [layer.weight] + ([layer.bias] if layer.bias is not None else [])
+    if bucket is None or bucket.sizes != [p.numel() for p in params]:
+        bucket = UpdateBucket([p.detach() for p in params])
+        bucket.attach(params)
+    views = bucket.views()
+    flat = views[0].view(-1)
+    n = flat.numel()
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    step = -(-n // max(1, int(blocks)))
+    step = (step + 1023) // 1024 * 1024            # whole 4 KiB pieces: the 128-bit path and aligned collectives
+    pending = []
+    for lo in range(0, n, step):
+        hi = min(n, lo + step)
+        layer.weight_grad_columns(weights, lo, hi, flat[lo:hi], l1, l2)
+        if multi:
+            pending.append(dist.all_reduce(flat[lo:hi], op=dist.ReduceOp.SUM, group=group, async_op=True))
+    layer.weight.grad = views[0]
+    if layer.bias is not None:
+        layer.bias.grad = None
+        layer._weighted_sum(layer.bias_noise, weights, None, 0, 0, None, views[1])
+        layer.bias.grad = views[1]
+        if multi:
+            pending.append(dist.all_reduce(views[1], op=dist.ReduceOp.SUM, group=group, async_op=True))
+    for work in pending:
+        work.wait()
+    return bucket
+
+
 def all_reduce_grads(parameters, bucket=None, group=None):
     """Sum ``.grad`` of the given parameters over the ranks through one bucket; every rank ends
     with the full-population update and applies the same optimiser step.

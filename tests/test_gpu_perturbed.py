@@ -540,3 +540,34 @@ def test_fused_layer_edge_cases(base):
     bad = base.PermutedConv2d(1, 8, 3, D, options={"fuse": "relu"}).to(DEV)
     with pytest.raises(NotImplementedError):
         bad.forward(torch.zeros(D, 1, 10, 10, device=DEV))
+
+
+def test_weight_gradient_in_column_blocks_and_overlapped_update(base):
+    """The block-by-block form of the dense update (the one that feeds an all-reduce block by block) against the
+    oracle and against the one-shot update; with a single process the overlapped update is just the blocks."""
+    from nesgpu_b200 import dist as ndist
+    D, in_f, out_f = 40, 96, 50
+    g = gen(77)
+    layer = base.PerturbedLinear(in_f, out_f, D).to(DEV)
+    E = 0.1 * torch.randn(D, out_f, in_f, generator=g)
+    beta = 0.1 * torch.randn(D, out_f, generator=g)
+    w = torch.randn(D, generator=g)
+    layer.weight_noise, layer.bias_noise = G(E), G(beta)
+    want = O.perturbed_weight_grad(E, w).flatten()
+    n = out_f * in_f
+    for lo, hi in [(0, n), (0, 1024), (1024, 4096), (4096, n), (3, 1001)]:
+        out = torch.empty(hi - lo, device=DEV)
+        layer.weight_grad_columns(G(w), lo, hi, out)
+        assert_close(out, want[lo:hi], what="columns %d:%d" % (lo, hi))
+    with torch.no_grad():
+        bucket = ndist.overlapped_dense_update(layer, G(w), blocks=3, l2=0.01)
+    og, obg = O.perturbed_update(layer.weight.detach().cpu(), E, beta, w, 0, 0.01)
+    assert_close(layer.weight.grad, og, what="overlapped grad")
+    assert_close(layer.bias.grad, obg, what="overlapped bias grad")
+    assert layer.weight.grad.data_ptr() == bucket.views()[0].data_ptr()
+    # the next plain update starts from an empty .grad and lands in the same bucket slice
+    layer.weight.grad = layer.bias.grad = None
+    with torch.no_grad():
+        grad, bgrad = layer.update(G(w), l2=0.01)
+    assert grad.data_ptr() == bucket.views()[0].data_ptr() and bgrad.data_ptr() == bucket.views()[1].data_ptr()
+    assert_close(grad, og, what="bucket-resident grad")
