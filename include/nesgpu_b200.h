@@ -167,6 +167,12 @@ int nes_sparse_perturbed_update(const int32_t* idx, const float* val, const floa
                                 const float* weight, float* grad, int64_t D, int64_t in,
                                 int64_t out, int k, float l1, float l2, nes_stream_t stream);
 
+/* The per-member term of nes_sparse_perturbed_linear_fwd on its own, added to a y that already holds
+ * x.weight^T + bias (for instance from nes_linear_fwd_tc, which puts the base product on the tensor cores):
+ *   y[b,o] += s(r) * (sum_t x[b, idx[d,o,t]] * val[d,o,t] + bias_noise[d,o]). */
+int nes_sparse_noise_add(float* y, const float* x, const int32_t* idx, const float* val, const float* bias_noise,
+                         int64_t D, int64_t R, int64_t in, int64_t out, int k, int antithetic, nes_stream_t stream);
+
 /* ------------------------------------------- fp32: shared noise + member permutations */
 
 /* Permuted.update for layers with output permutations only, in one launch (modules/base.py:261-266 scatter,
@@ -387,6 +393,16 @@ int nes_synthetic_linear_fwd(const float* x, const float* weight, const float* b
                              int64_t D, int64_t R, int64_t in, int64_t out, int antithetic,
                              void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
+/* The same layer with both products on the tensor cores (tcgen05 kind::tf32 on operands split into tf32
+ * hi + lo parts; mode 3: 3xTF32, fp32-level accuracy; mode 1: plain TF32, for callers that state it):
+ * y = x.weight^T + bias, p = (x * fin).eps^T, then one pass adds s(r) * (fout * p + bias_noise).  in must be
+ * a multiple of 4.  scratch holds the split operands and p. */
+int64_t nes_synthetic_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out, int mode);
+int nes_synthetic_linear_fwd_tc(const float* x, const float* weight, const float* bias, const float* eps,
+                                const float* bias_noise, const int8_t* fin, const int8_t* fout, float* y,
+                                int64_t D, int64_t R, int64_t in, int64_t out, int antithetic, int mode,
+                                void* scratch, int64_t scratch_bytes, nes_stream_t stream);
+
 /* SyntheticConv2d.forward (modules/base.py:642-668), evaluated as one convolution per member with the
  * effective filter W[k,c] + s(r) * fout[d,k] * fin[d,c] * eps[k,c]. */
 int nes_synthetic_conv2d_fwd(const float* x, const float* weight, const float* bias,
@@ -399,10 +415,13 @@ int nes_synthetic_conv2d_fwd(const float* x, const float* weight, const float* b
 /* Synthetic.weight_grad (modules/base.py:338-347) plus the l1/l2 terms of update:
  *   grad[k,m,t] = eps[k,m,t] * sum_d w_d * fout[d,k] * fin[d,m]   (a missing side counts as +1).
  * For two-sided flips the reference's einsum multiplies by w_d twice (modules/base.py:340); this
- * entry point computes the fitness-weighted sum sum_d w_d E_d, which is what the one-sided branches do. */
+ * entry point computes the fitness-weighted sum sum_d w_d E_d, which is what the one-sided branches do.
+ * With one flipped side the flip weights are summed once into `scratch` (max(in, out) floats) and eps is
+ * scaled by them; without scratch, and for two-sided flips, every gradient entry walks the members. */
+int64_t nes_synthetic_update_scratch_bytes(int in, int out);
 int nes_synthetic_update(const float* eps, const float* w, const int8_t* fin, const int8_t* fout,
                          const float* weight, float* grad, int64_t D, int in, int out, int ksize,
-                         float l1, float l2, nes_stream_t stream);
+                         float l1, float l2, void* scratch, int64_t scratch_bytes, nes_stream_t stream);
 
 /* ---------------------------------------------------------------- noise set-up (device) */
 

@@ -63,8 +63,12 @@ SIGNATURES = {
     "nes_permuted_update": [c_ptr] * 7 + [c_i64] + [c_int] * 5 + [c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_synthetic_linear_fwd_scratch_bytes": [c_i64] * 3,
     "nes_synthetic_linear_fwd": [c_ptr] * 8 + [c_i64] * 4 + [c_int, c_ptr, c_i64, c_ptr],
+    "nes_synthetic_linear_fwd_tc_scratch_bytes": [c_i64] * 4 + [c_int],
+    "nes_synthetic_linear_fwd_tc": [c_ptr] * 8 + [c_i64] * 4 + [c_int, c_int, c_ptr, c_i64, c_ptr],
+    "nes_sparse_noise_add": [c_ptr] * 5 + [c_i64] * 4 + [c_int, c_int, c_ptr],
     "nes_synthetic_conv2d_fwd": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr],
-    "nes_synthetic_update": [c_ptr] * 6 + [c_i64] + [c_int] * 3 + [c_f32, c_f32, c_ptr],
+    "nes_synthetic_update_scratch_bytes": [c_int, c_int],
+    "nes_synthetic_update": [c_ptr] * 6 + [c_i64] + [c_int] * 3 + [c_f32, c_f32, c_ptr, c_i64, c_ptr],
     "nes_fill_signs": [c_ptr, c_i64, c_u64, c_u64, c_ptr],
     "nes_fill_normal": [c_ptr, c_i64, c_f32, c_f32, c_u64, c_u64, c_ptr],
     "nes_fill_uniform": [c_ptr, c_i64, c_f32, c_f32, c_u64, c_u64, c_ptr],
@@ -98,6 +102,8 @@ _RETURNS = {
     "nes_perturbed_update_scratch_bytes": c_i64,
     "nes_linear_fwd_tc_scratch_bytes": c_i64,
     "nes_synthetic_linear_fwd_scratch_bytes": c_i64,
+    "nes_synthetic_linear_fwd_tc_scratch_bytes": c_i64,
+    "nes_synthetic_update_scratch_bytes": c_i64,
     "nes_conv2d_fwd_tc_scratch_bytes": c_i64,
     "nes_conv2d_fwd_bf16_scratch_bytes": c_i64,
     "nes_permuted_linear_fwd_scratch_bytes": c_i64,

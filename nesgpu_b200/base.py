@@ -521,6 +521,13 @@ class SparsePerturbedLinear(nn.Linear, _LinearMixin, Perturbed):
         idx = C.require_cuda(self.noise_indices, "noise_indices", torch.int32)
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        if self._tensor_core_base(x, y):
+            # base product on the tensor cores (3xTF32 unless options["tc"] says otherwise), then the k-entry gather
+            self.last_path = self.options.get("tc", "3xtf32")
+            C.call("nes_sparse_noise_add", C.ptr(y), C.ptr(x), C.ptr(idx), C.ptr(val), C.ptr(beta), self.directions, R,
+                   self.in_features, self.out_features, self.k, 1 if self.antithetic else 0, C.stream())
+            return y.view(*lead, self.out_features)
+        self.last_path = "fp32"
         C.call("nes_sparse_perturbed_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                C.ptr(idx), C.ptr(val), C.ptr(beta), C.ptr(y), self.directions, R, self.in_features,
                self.out_features, self.k, 1 if self.antithetic else 0, C.stream())
@@ -977,9 +984,11 @@ class Synthetic(Perturbed):
         for sdim in self.weight.shape[2:]:
             ksize *= sdim
         grad = out if out is not None else torch.empty_like(self.weight, memory_format=torch.contiguous_format)
+        nbytes = C.call("nes_synthetic_update_scratch_bytes", self.in_degree, self.out_degree)
+        buf = C.scratch(nbytes, eps.device)
         C.call("nes_synthetic_update", C.ptr(eps), C.ptr(weights), C.ptr(fin), C.ptr(fout),
                C.ptr(_opt(self.weight)) if (l1 or l2) else None, C.ptr(grad), self.directions, self.in_degree,
-               self.out_degree, ksize, float(l1), float(l2), C.stream())
+               self.out_degree, ksize, float(l1), float(l2), C.ptr(buf), nbytes, C.stream())
         return grad
 
     def weight_grad(self, weights):
@@ -1004,6 +1013,20 @@ class SyntheticLinear(nn.Linear, _LinearMixin, Synthetic):
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         fin, fout = self._flips()
         y = torch.empty((x.shape[0], self.out_features), device=x.device, dtype=_F32)
+        mode = self.options.get("tc", "3xtf32")
+        if mode not in ("3xtf32", "tf32", "fp32"):
+            raise NotImplementedError('options["tc"] must be "3xtf32", "tf32" or "fp32"')
+        if mode != "fp32" and self.in_features % 4 == 0 and x.shape[0]:
+            self.last_path = mode
+            m = _TC_MODES[mode]
+            nbytes = C.call("nes_synthetic_linear_fwd_tc_scratch_bytes", self.directions, R, self.in_features,
+                            self.out_features, m)
+            buf = C.scratch(nbytes, x.device)
+            C.call("nes_synthetic_linear_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),
+                   C.ptr(beta), C.ptr(fin), C.ptr(fout), C.ptr(y), self.directions, R, self.in_features,
+                   self.out_features, 1 if self.antithetic else 0, m, C.ptr(buf), nbytes, C.stream())
+            return y.view(*lead, self.out_features)
+        self.last_path = "fp32"
         nbytes = C.call("nes_synthetic_linear_fwd_scratch_bytes", self.directions, R, self.out_features)
         buf = C.scratch(nbytes, x.device)
         C.call("nes_synthetic_linear_fwd", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)), C.ptr(eps),

@@ -261,6 +261,48 @@ __global__ void permuted_filter_kernel(const float* __restrict__ w, const float*
   }
 }
 
+// hi / lo split of x[b, :] * flips[b % D, :] (sign-flip sampling: the noise product's A operand)
+__global__ void split_flipped_kernel(const float* __restrict__ x, const int8_t* __restrict__ flips, float* __restrict__ hi,
+                                     float* __restrict__ lo, int64_t B, int64_t D, int64_t in) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= B * in) return;
+  const int64_t b = i / in, c = i - b * in;
+  const float a = x[i] * float(flips[(b % D) * in + c]);
+  const float h = round_tf32(a);
+  hi[i] = h;
+  if (lo) lo[i] = a - h;
+}
+
+// y[b, o] += s(r) * (p[b, o] * fout[d, o] + beta[d, o])        (sign-flip sampling, modules/base.py:620-626)
+__global__ void synthetic_combine_kernel(float* __restrict__ y, const float* __restrict__ p, const int8_t* __restrict__ fout,
+                                         const float* __restrict__ beta, int64_t B, int64_t D, int64_t R, int64_t out,
+                                         int antithetic) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= B * out) return;
+  const int64_t b = i / out, o = i - b * out;
+  const int64_t d = b % D;
+  float q = p[i];
+  if (fout) q *= float(fout[d * out + o]);
+  if (beta) q += __ldg(beta + d * out + o);
+  y[i] += anti_sign(b / D, R, antithetic) * q;
+}
+
+// y[b, o] += s(r) * (sum_t x[b, idx[d, o, t]] * val[d, o, t] + beta[d, o])     (sparse per-member noise)
+__global__ void sparse_noise_add_kernel(float* __restrict__ y, const float* __restrict__ x, const int32_t* __restrict__ idx,
+                                        const float* __restrict__ val, const float* __restrict__ beta, int64_t B, int64_t D,
+                                        int64_t R, int64_t in, int64_t out, int k, int antithetic) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= B * out) return;
+  const int64_t b = i / out, o = i - b * out;
+  const int64_t d = b % D;
+  const int64_t e = (d * out + o) * k;
+  const float* xr = x + b * in;
+  float q = 0.f;
+  for (int t = 0; t < k; ++t) q = fmaf(__ldg(xr + idx[e + t]), __ldg(val + e + t), q);
+  if (beta) q += __ldg(beta + d * out + o);
+  y[i] += anti_sign(b / D, R, antithetic) * q;
+}
+
 // 2-D fp32 row-major [rows][cols] tensor, box = 32 columns x box_rows rows, 128-byte swizzle, zero fill
 static int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int box_rows, const char* what,
                     bool bf16 = false) {
@@ -357,6 +399,68 @@ extern "C" int nes_linear_fwd_tc(const float* x, const float* weight, const floa
 
   const RowTerm none = {nullptr, 1, 1, 0};
   return run_gemm(a_hi, a_lo, b_hi, b_lo, bias, none, y, M, N, K, mode, st, "linear_fwd_tc");
+}
+
+extern "C" int nes_sparse_noise_add(float* y, const float* x, const int32_t* idx, const float* val, const float* bias_noise,
+                                    int64_t D, int64_t R, int64_t in, int64_t out, int k, int antithetic, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0 && k >= 0, NES_ERR_BAD_ARG, "sparse_noise_add: negative extent");
+  const int64_t total = D * R * out;
+  if (total == 0) return NES_OK;
+  NES_REQUIRE(y && x && (k == 0 || (idx && val)), NES_ERR_BAD_ARG, "sparse_noise_add: null pointer");
+  NES_REQUIRE(ceil_div<int64_t>(total, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "sparse_noise_add: too large");
+  sparse_noise_add_kernel<<<(unsigned)ceil_div<int64_t>(total, 256), 256, 0, as_stream(stream)>>>(y, x, idx, val, bias_noise, D * R, D, R,
+                                                                                                 in, out, k, antithetic);
+  return check_launch("sparse_noise_add");
+}
+
+extern "C" int64_t nes_synthetic_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out, int mode) {
+  if (D <= 0 || R <= 0 || in <= 0 || out <= 0) return 0;
+  const int64_t a = align256(D * R * in * 4), b = align256(out * in * 4), p = align256(D * R * out * 4);
+  return (mode == 3 ? 2 : 1) * (a + b) + p;
+}
+
+// SyntheticLinear.forward on the tensor cores: y = x.W^T + bias, p = (x * fin).eps^T (two tcgen05 products on
+// split operands), then y += s * (fout * p + beta).
+extern "C" int nes_synthetic_linear_fwd_tc(const float* x, const float* weight, const float* bias, const float* eps,
+                                           const float* bias_noise, const int8_t* fin, const int8_t* fout, float* y,
+                                           int64_t D, int64_t R, int64_t in, int64_t out, int antithetic, int mode,
+                                           void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
+  NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0, NES_ERR_BAD_ARG, "synthetic_linear_fwd_tc: negative extent");
+  NES_REQUIRE(mode == 1 || mode == 3, NES_ERR_BAD_ARG, "synthetic_linear_fwd_tc: mode must be 1 (TF32) or 3 (3xTF32)");
+  if (D == 0 || R == 0 || out == 0) return NES_OK;
+  NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "synthetic_linear_fwd_tc: null pointer");
+  NES_REQUIRE(in > 0 && in % 4 == 0, NES_ERR_UNSUPPORTED, "synthetic_linear_fwd_tc: in=%lld must be a positive multiple of 4", (long long)in);
+  const int64_t B = D * R;
+  NES_REQUIRE(B <= INT32_MAX && out <= INT32_MAX && in <= INT32_MAX && ceil_div<int64_t>(out, BN) <= 65535, NES_ERR_UNSUPPORTED,
+              "synthetic_linear_fwd_tc: extent too large");
+  const int64_t need = nes_synthetic_linear_fwd_tc_scratch_bytes(D, R, in, out, mode);
+  NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
+              "synthetic_linear_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)need);
+  cudaStream_t st = as_stream(stream);
+  unsigned char* sp = static_cast<unsigned char*>(scratch);
+  const int64_t a_bytes = align256(B * in * 4), b_bytes = align256(out * in * 4);
+  float* a_hi = reinterpret_cast<float*>(sp);
+  float* b_hi = reinterpret_cast<float*>(sp + a_bytes);
+  float* a_lo = mode == 3 ? reinterpret_cast<float*>(sp + a_bytes + b_bytes) : nullptr;
+  float* b_lo = mode == 3 ? reinterpret_cast<float*>(sp + 2 * a_bytes + b_bytes) : nullptr;
+  float* p = reinterpret_cast<float*>(sp + (mode == 3 ? 2 : 1) * (a_bytes + b_bytes));
+  const unsigned ablocks = (unsigned)ceil_div<int64_t>(B * in, 256), bblocks = (unsigned)ceil_div<int64_t>(out * in, 256);
+  const RowTerm none = {nullptr, 1, 1, 0};
+  int rc;
+  split_tf32_kernel<<<ablocks, 256, 0, st>>>(x, a_hi, a_lo, B * in);
+  if ((rc = check_launch("synthetic_linear_fwd_tc(split x)")) != NES_OK) return rc;
+  split_tf32_kernel<<<bblocks, 256, 0, st>>>(weight, b_hi, b_lo, out * in);
+  if ((rc = check_launch("synthetic_linear_fwd_tc(split W)")) != NES_OK) return rc;
+  if ((rc = run_gemm(a_hi, a_lo, b_hi, b_lo, bias, none, y, B, out, in, mode, st, "synthetic_linear_fwd_tc(base)")) != NES_OK) return rc;
+  split_tf32_kernel<<<bblocks, 256, 0, st>>>(eps, b_hi, b_lo, out * in);
+  if ((rc = check_launch("synthetic_linear_fwd_tc(split eps)")) != NES_OK) return rc;
+  if (fin) {
+    split_flipped_kernel<<<ablocks, 256, 0, st>>>(x, fin, a_hi, a_lo, B, D, in);
+    if ((rc = check_launch("synthetic_linear_fwd_tc(flip x)")) != NES_OK) return rc;
+  }
+  if ((rc = run_gemm(a_hi, a_lo, b_hi, b_lo, nullptr, none, p, B, out, in, mode, st, "synthetic_linear_fwd_tc(noise)")) != NES_OK) return rc;
+  synthetic_combine_kernel<<<(unsigned)ceil_div<int64_t>(B * out, 256), 256, 0, st>>>(y, p, fout, bias_noise, B, D, R, out, antithetic);
+  return check_launch("synthetic_linear_fwd_tc(combine)");
 }
 
 // row length of the concatenated operand: a multiple of 16 bytes (4 fp32 / 8 bf16)

@@ -374,6 +374,31 @@ __global__ void grad_synthetic_kernel(const float* __restrict__ eps, const float
   for (int t = 0; t < ksz; ++t) grad[base + t] = fw * __ldg(eps + base + t);
 }
 
+// One-sided sign flips: the flip weights do not depend on the other index, so they are summed once,
+//   fw[c] = sum_d w_d * flips[d, c],
+// (members split over blockIdx.y, fp32 atomics on the n sums) and the gradient is eps scaled by fw along that
+// side: grad[k,m,t] = eps[k,m,t] * fw[k] (output flips) or * fw[m] (input flips).
+__global__ void __launch_bounds__(128) flip_weight_sums_kernel(const float* __restrict__ w, const int8_t* __restrict__ flips,
+                                                               float* __restrict__ fw, int64_t D, int n, int64_t d_per_block) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  const int64_t d0 = blockIdx.y * d_per_block;
+  const int64_t d1 = (d0 + d_per_block < D) ? d0 + d_per_block : D;
+  float acc = 0.f;
+#pragma unroll 8
+  for (int64_t d = d0; d < d1; ++d) acc = fmaf(__ldg(w + d), float(flips[d * n + c]), acc);
+  atomicAdd(fw + c, acc);
+}
+
+__global__ void grad_one_sided_flip_kernel(const float* __restrict__ eps, const float* __restrict__ fw, float* __restrict__ grad,
+                                           int64_t total, int in, int ksz, int by_output) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int64_t km = e / ksz;                          // k * in + m
+  const int idx = by_output ? int(km / in) : int(km % in);
+  grad[e] = __ldg(eps + e) * __ldg(fw + idx);
+}
+
 static int finish(const float* partial, int splits, const float* weight, float* grad, int64_t n, float l1,
                   float l2, cudaStream_t st, const char* what) {
   if (splits == 0 && (weight == nullptr || (l1 == 0.f && l2 == 0.f))) return NES_OK;
@@ -608,17 +633,37 @@ extern "C" int nes_sparse_perturbed_update(const int32_t* idx, const float* val,
   return finish(nullptr, 0, weight, grad, out * in, l1, l2, st, "sparse_perturbed_update(finish)");
 }
 
+extern "C" int64_t nes_synthetic_update_scratch_bytes(int in, int out) { return int64_t(in > out ? in : out) * 4; }
+
 extern "C" int nes_synthetic_update(const float* eps, const float* w, const int8_t* fin, const int8_t* fout,
                                     const float* weight, float* grad, int64_t D, int in, int out, int ksize,
-                                    float l1, float l2, nes_stream_t stream) {
+                                    float l1, float l2, void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
   NES_REQUIRE(D >= 0 && in > 0 && out > 0 && ksize > 0, NES_ERR_BAD_ARG, "synthetic_update: bad extent");
   NES_REQUIRE(eps && grad && (D == 0 || w) && (fin || fout), NES_ERR_BAD_ARG, "synthetic_update: null pointer");
   NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "synthetic_update: l1/l2 given without weight");
   NES_REQUIRE(out <= 65535, NES_ERR_UNSUPPORTED, "synthetic_update: out > 65535");
   cudaStream_t st = as_stream(stream);
+  int rc;
+  const int64_t total = int64_t(out) * in * ksize;
+  if ((fin == nullptr) != (fout == nullptr) && scratch && scratch_bytes >= int64_t(in > out ? in : out) * 4) {
+    // one flipped side: n flip-weight sums, then a scaling of eps
+    const int n = fout ? out : in;
+    float* fw = static_cast<float*>(scratch);
+    cudaMemsetAsync(fw, 0, size_t(n) * sizeof(float), st);
+    if (D > 0) {
+      const int slices = int(D < 64 ? 1 : (D / 32 < 64 ? D / 32 : 64));
+      const int64_t per = ceil_div<int64_t>(D, slices);
+      dim3 sgrid((unsigned)ceil_div(n, 128), (unsigned)ceil_div<int64_t>(D, per));
+      flip_weight_sums_kernel<<<sgrid, 128, 0, st>>>(w, fout ? fout : fin, fw, D, n, per);
+      if ((rc = check_launch("synthetic_update(flip sums)")) != NES_OK) return rc;
+    }
+    grad_one_sided_flip_kernel<<<(unsigned)ceil_div<int64_t>(total, 256), 256, 0, st>>>(eps, fw, grad, total, in, ksize, fout ? 1 : 0);
+    if ((rc = check_launch("synthetic_update(scale)")) != NES_OK) return rc;
+    return finish(nullptr, 0, weight, grad, total, l1, l2, st, "synthetic_update(finish)");
+  }
   dim3 grid((unsigned)ceil_div(in, 128), (unsigned)out);
   grad_synthetic_kernel<<<grid, 128, 0, st>>>(eps, w, fin, fout, grad, D, in, out, ksize);
-  int rc = check_launch("synthetic_update");
+  rc = check_launch("synthetic_update");
   if (rc != NES_OK) return rc;
   return finish(nullptr, 0, weight, grad, int64_t(out) * in * ksize, l1, l2, st, "synthetic_update(finish)");
 }

@@ -281,7 +281,16 @@ def test_sparse_perturbed_linear_vs_dense_reference_form(base, k):
         y = layer.forward(G(x))
         layer.perturbed_flag = False
         grad, bgrad = layer.update(G(w))
-    assert_close(y, O.sparse_perturbed_linear_forward(x, W, b, idx, val, beta, D, True), what="forward")
+    assert layer.last_path == "3xtf32"           # base product on the tensor cores, k-entry gather in a second pass
+    want = O.sparse_perturbed_linear_forward(x, W, b, idx, val, beta, D, True)
+    assert_close(y, want, what="forward")
+    layer.options = {"tc": "fp32"}
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y32 = layer.forward(G(x))
+        layer.perturbed_flag = False
+    assert layer.last_path == "fp32"
+    assert_close(y32, want, what="forward on CUDA cores")
     E = O.densify_sparse_noise(idx, val, in_f)
     assert_close(grad, O.perturbed_weight_grad(E, w), what="grad")
     assert_close(bgrad, w @ beta, what="bias grad")

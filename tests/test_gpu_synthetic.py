@@ -115,3 +115,30 @@ def test_synthetic_set_noise_and_affine(base, perturbed_golden):
     aff.set_seed(1)
     aff.set_noise(0.1)
     assert aff.weight_noise.shape == (m["D"],) + tuple(m["shape"])
+
+
+@pytest.mark.parametrize("flip", ["in", "out", "both"])
+@pytest.mark.parametrize("tc,tol", [("3xtf32", 1e-4), ("tf32", 2e-2), ("fp32", 1e-4)])
+def test_synthetic_linear_tensor_core_products(base, flip, tc, tol):
+    """Row lengths that are multiples of 4 take the two tcgen05 products (3xTF32 by default: the fp32 bar; plain
+    TF32 is the stated reduced-precision mode); the perturbation term is checked on its own as well."""
+    D, R, in_f, out_f = 24, 2, 256, 136
+    g = torch.Generator().manual_seed(13)
+    layer = base.SyntheticLinear(in_f, out_f, D, antithetic=True, flip=flip, options={"tc": tc}).to(DEV)
+    x = torch.randn(R * D, in_f, generator=g)
+    W = torch.randn(out_f, in_f, generator=g) / in_f ** .5
+    b = torch.randn(out_f, generator=g)
+    eps = 0.05 * torch.randn(out_f, in_f, generator=g)
+    beta = 0.02 * torch.randn(D, out_f, generator=g)
+    fin = (2 * torch.randint(2, (D, in_f), generator=g) - 1).to(torch.int8) if layer.flip_inputs else None
+    fout = (2 * torch.randint(2, (D, out_f), generator=g) - 1).to(torch.int8) if layer.flip_outputs else None
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.input_flips, layer.output_flips = G(eps), G(beta), G(fin), G(fout)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    assert layer.last_path == tc
+    want = O.synthetic_linear_forward(x, W, b, eps, beta, fin, fout, D, True)
+    assert_close(y, want, tol=tol, what="forward")
+    base_only = x @ W.t() + b
+    assert_close(y.cpu() - base_only, want - base_only, tol=10 * tol, what="perturbation term")
