@@ -20,61 +20,71 @@ int bin_weighted_sum_impl(const void* in, const uint16_t* w_half, uint16_t* out_
 //
 // HBM-bound: the member's weight rows are streamed once.  Four lanes share a row (each takes every fourth
 // 16-byte chunk, so one load instruction of a warp touches eight rows, 64 contiguous bytes each), a warp
-// covers 32 rows in four passes with all loads of the four passes issued before the first use, the member's
+// covers a group of 32 rows in four passes with all loads issued before the first use, the member's
 // input chunks sit in registers, and after a two-step butterfly the counts are dealt back so that lane L
-// owns row L of the warp's 32: stores are coalesced and one __ballot_sync yields 32 packed output bits.
+// owns row L of the group: stores are coalesced and one __ballot_sync yields 32 packed output bits.
 enum { BMV_COUNTS = 0, BMV_ACT = 1, BMV_BOOL = 2, BMV_PACKED = 3 };
 
-template <int MODE, int CPL>
-__global__ void __launch_bounds__(256) bmv_rows_kernel(const uint4* __restrict__ A, const uint4* __restrict__ X,
-                                                       void* __restrict__ out, const __half* __restrict__ bias,
-                                                       const __half* __restrict__ bias_noise, int64_t M, int cpr,
-                                                       int n_bits, int64_t out_row_u32) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 3, rl = lane >> 2;
-  const int64_t z = blockIdx.y;
-  const int64_t base = (int64_t(blockIdx.x) * 8 + warp) * 32;
-  if (base >= M) return;
+// One group = 32 consecutive rows of one member, handled by one warp.
+template <int CPL>
+struct BmvGroup {
   uint4 xv[CPL];
-#pragma unroll
-  for (int j = 0; j < CPL; ++j) {
-    const int c = sub + 4 * j;
-    xv[j] = (c < cpr) ? __ldg(X + z * cpr + c) : make_uint4(0, 0, 0, 0);
-  }
   uint4 av[4][CPL];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t m = base + 8 * i + rl;
-    const uint4* row = A + (z * M + m) * cpr;
+  int64_t z, base;
+
+  __device__ __forceinline__ void load(const uint4* __restrict__ A, const uint4* __restrict__ X, int64_t g, int64_t gpm, int64_t M,
+                                       int cpr, int sub, int rl) {
+    z = g / gpm;
+    base = (g - z * gpm) * 32;
 #pragma unroll
     for (int j = 0; j < CPL; ++j) {
       const int c = sub + 4 * j;
-      av[i][j] = (m < M && c < cpr) ? __ldcs(row + c) : xv[j];      // padding contributes popc(x ^ x) = 0
+      xv[j] = (c < cpr) ? __ldg(X + z * cpr + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t m = base + 8 * i + rl;
+      const uint4* row = A + (z * M + m) * cpr;
+#pragma unroll
+      for (int j = 0; j < CPL; ++j) {
+        const int c = sub + 4 * j;
+        av[i][j] = (m < M && c < cpr) ? __ldcs(row + c) : xv[j];      // padding contributes popc(x ^ x) = 0
+      }
     }
   }
-  int mine = 0;
+
+  // the count of row base + lane, in every lane
+  __device__ __forceinline__ int reduce(int lane) const {
+    int mine = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    int s = 0;
+    for (int i = 0; i < 4; ++i) {
+      int s = 0;
 #pragma unroll
-    for (int j = 0; j < CPL; ++j)
-      s += __popc(av[i][j].x ^ xv[j].x) + __popc(av[i][j].y ^ xv[j].y) + __popc(av[i][j].z ^ xv[j].z) + __popc(av[i][j].w ^ xv[j].w);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    const int v = __shfl_sync(0xffffffffu, s, 4 * (lane & 7));      // row 8i + (lane & 7) of this pass
-    if ((lane >> 3) == i) mine = v;
+      for (int j = 0; j < CPL; ++j)
+        s += __popc(av[i][j].x ^ xv[j].x) + __popc(av[i][j].y ^ xv[j].y) + __popc(av[i][j].z ^ xv[j].z) + __popc(av[i][j].w ^ xv[j].w);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      const int v = __shfl_sync(0xffffffffu, s, 4 * (lane & 7));      // row 8i + (lane & 7) of this pass
+      if ((lane >> 3) == i) mine = v;
+    }
+    return mine;
   }
+};
+
+template <int MODE>
+__device__ __forceinline__ void bmv_store(void* __restrict__ out, const __half* __restrict__ bias, const __half* __restrict__ bias_noise,
+                                          int64_t z, int64_t base, int lane, int64_t M, int count, int n_bits, int64_t out_row_u32) {
   const int64_t m = base + lane;
   const bool ok = m < M;
   if (MODE == BMV_COUNTS) {
-    if (ok) static_cast<int32_t*>(out)[z * M + m] = mine;
+    if (ok) static_cast<int32_t*>(out)[z * M + m] = count;
   } else if (MODE == BMV_ACT) {
-    if (ok) static_cast<int32_t*>(out)[z * M + m] = 2 * mine - n_bits;
+    if (ok) static_cast<int32_t*>(out)[z * M + m] = 2 * count - n_bits;
   } else {
     bool bit = false;
     if (ok) {
       const __half th = __hadd(bias[m], bias_noise[z * M + m]);
-      bit = __hgt(__int2half_rn(2 * mine - n_bits), th);
+      bit = __hgt(__int2half_rn(2 * count - n_bits), th);
     }
     if (MODE == BMV_BOOL) {
       if (ok) static_cast<uint8_t*>(out)[z * M + m] = uint8_t(bit);
@@ -82,6 +92,26 @@ __global__ void __launch_bounds__(256) bmv_rows_kernel(const uint4* __restrict__
       const uint32_t word = __ballot_sync(0xffffffffu, bit);
       if (lane == 0) static_cast<uint32_t*>(out)[z * out_row_u32 + base / 32] = word;
     }
+  }
+}
+
+// The grid is a few blocks per SM; every warp walks groups g = warp, warp + W, ... two at a time, so that the loads
+// of two groups (sixteen 16-byte loads per lane at 1024-bit rows) are in flight before the first popcount.
+template <int MODE, int CPL>
+__global__ void __launch_bounds__(256) bmv_rows_kernel(const uint4* __restrict__ A, const uint4* __restrict__ X,
+                                                       void* __restrict__ out, const __half* __restrict__ bias,
+                                                       const __half* __restrict__ bias_noise, int64_t M, int cpr,
+                                                       int n_bits, int64_t out_row_u32, int64_t gpm, int64_t groups) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 3, rl = lane >> 2;
+  const int64_t W = int64_t(gridDim.x) * 8;
+  for (int64_t g = int64_t(blockIdx.x) * 8 + warp; g < groups; g += 2 * W) {
+    BmvGroup<CPL> a, b;
+    a.load(A, X, g, gpm, M, cpr, sub, rl);
+    const bool two = g + W < groups;                    // uniform over the warp
+    if (two) b.load(A, X, g + W, gpm, M, cpr, sub, rl);
+    bmv_store<MODE>(out, bias, bias_noise, a.z, a.base, lane, M, a.reduce(lane), n_bits, out_row_u32);
+    if (two) bmv_store<MODE>(out, bias, bias_noise, b.z, b.base, lane, M, b.reduce(lane), n_bits, out_row_u32);
   }
 }
 
@@ -264,20 +294,24 @@ __global__ void __launch_bounds__(256) bias_grad_half_kernel(const __half* __res
 template <int MODE>
 static int launch_bmv_rows(const void* A, const void* X, void* out, const __half* bias, const __half* bn, int64_t P, int64_t M,
                            int cpr, int n_bits, int64_t out_row_u32, cudaStream_t st) {
-  dim3 grid((unsigned)ceil_div<int64_t>(M, 256), (unsigned)P);
+  const int64_t gpm = ceil_div<int64_t>(M, 32), groups = gpm * P;
+  const int64_t want = ceil_div<int64_t>(groups, 16);              // two groups per warp and pass at least
+  const int64_t cap = int64_t(sm_count()) * 4;
+  const unsigned grid = (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
   const uint4* a = static_cast<const uint4*>(A);
   const uint4* x = static_cast<const uint4*>(X);
-  if (cpr <= 4) bmv_rows_kernel<MODE, 1><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32);
-  else if (cpr <= 8) bmv_rows_kernel<MODE, 2><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32);
-  else if (cpr <= 16) bmv_rows_kernel<MODE, 4><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32);
-  else bmv_rows_kernel<MODE, 8><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32);
+  if (cpr <= 4) bmv_rows_kernel<MODE, 1><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else if (cpr <= 8) bmv_rows_kernel<MODE, 2><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else if (cpr <= 16) bmv_rows_kernel<MODE, 4><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else bmv_rows_kernel<MODE, 8><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
   return check_launch("binarized_linear_fwd");
 }
 
 // true when the row-streaming product covers the shape: rows are whole 16-byte chunks, at most 32 of them
 bool bmv_rows_covers(const void* A, const void* X, int64_t P, int64_t K, int word_bits) {
   const int64_t row_bytes = K * (word_bits / 8);
-  return K > 0 && row_bytes % 16 == 0 && row_bytes / 16 <= 32 && aligned16(A) && aligned16(X) && P <= 65535;
+  (void)P;
+  return K > 0 && row_bytes % 16 == 0 && row_bytes / 16 <= 32 && aligned16(A) && aligned16(X);
 }
 
 int bmv_rows_counts(const void* A, const void* X, int32_t* counts, int64_t P, int64_t M, int64_t K, int word_bits, cudaStream_t st) {

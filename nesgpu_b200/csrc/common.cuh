@@ -49,9 +49,16 @@ struct Philox {
   // counter = (c0..c3); returns four 32-bit words in r[0..3]
   __host__ __device__ inline void operator()(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
                                              uint32_t r[4]) const {
+    rounds<10>(c0, c1, c2, c3, r);
+  }
+  // The same generator with ROUNDS rounds.  Ten is the customary conservative choice; seven is the smallest
+  // count its authors report as passing the BigCrush battery, and is what the bulk Gaussian fill uses
+  // (that kernel is bound by its integer arithmetic).
+  template <int ROUNDS>
+  __host__ __device__ inline void rounds(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t r[4]) const {
     uint32_t a = k0, b = k1;
 #pragma unroll
-    for (int i = 0; i < 10; ++i) {
+    for (int i = 0; i < ROUNDS; ++i) {
       uint32_t hi0, lo0, hi1, lo1;
       mulhilo(0xD2511F53u, c0, hi0, lo0);
       mulhilo(0xCD9E8D57u, c2, hi1, lo1);

@@ -3,28 +3,50 @@
 
 namespace nes {
 
-__global__ void fill_normal_kernel(float* __restrict__ out, int64_t n, float mean, float std,
-                                   uint64_t seed, uint64_t offset) {
-  const int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;   // group of four outputs
-  if (q * 4 >= n) return;
-  const uint64_t ctr = offset + uint64_t(q);
+// Four normals from one Philox call (counter ctr): Box-Muller on two uniform pairs.  The hardware's approximate
+// logarithm and sine / cosine are used: their absolute errors (~1e-6 on these ranges) are far below the
+// resolution of the 24-bit uniforms that feed them, and the kernel is bound by its arithmetic, not by memory.
+__device__ __forceinline__ void normal4(const Philox& ph, uint64_t ctr, float mean, float std, float (&z)[4]) {
   uint32_t r[4];
-  Philox ph(seed);
-  ph(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 0u, r);
-  float z[4];
+  ph.rounds<7>(uint32_t(ctr), uint32_t(ctr >> 32), 0u, 0u, r);
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {     // Box-Muller on two uniform pairs
+  for (int h = 0; h < 2; ++h) {
     const float u1 = u32_to_unit(r[2 * h]);
     const float u2 = u32_to_unit(r[2 * h + 1]);
-    const float rad = sqrtf(-2.0f * logf(u1));
+    const float rad = sqrtf(-2.0f * __logf(u1));
     float s, c;
-    sincospif(2.0f * u2, &s, &c);
-    z[2 * h] = rad * c;
-    z[2 * h + 1] = rad * s;
+    __sincosf(fmaf(6.283185307179586f, u2, -3.141592653589793f), &s, &c);      // angle in (-pi, pi]: the accurate range
+    z[2 * h] = fmaf(std, rad * c, mean);
+    z[2 * h + 1] = fmaf(std, rad * s, mean);
   }
+}
+
+// A thread owns two groups of four outputs, one block-width apart (two independent Philox chains in flight, two
+// coalesced 128-bit stores).  Group g always uses counter offset + g, whatever the launch shape.
+template <bool VEC>
+__global__ void __launch_bounds__(256) fill_normal_kernel(float* __restrict__ out, int64_t n, float mean, float std,
+                                                          uint64_t seed, uint64_t offset) {
+  const int64_t g0 = (int64_t(blockIdx.x) * 2) * blockDim.x + threadIdx.x;
+  const int64_t g1 = g0 + blockDim.x;
+  const Philox ph(seed);
+  float za[4], zb[4];
+  if (g0 * 4 >= n) return;
+  normal4(ph, offset + uint64_t(g0), mean, std, za);
+  const bool second = g1 * 4 < n;
+  if (second) normal4(ph, offset + uint64_t(g1), mean, std, zb);
+  if (VEC && g0 * 4 + 3 < n) {
+    __stcs(reinterpret_cast<float4*>(out) + g0, make_float4(za[0], za[1], za[2], za[3]));
+  } else {
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
-    if (q * 4 + j < n) out[q * 4 + j] = fmaf(std, z[j], mean);
+    for (int j = 0; j < 4; ++j) if (g0 * 4 + j < n) out[g0 * 4 + j] = za[j];
+  }
+  if (!second) return;
+  if (VEC && g1 * 4 + 3 < n) {
+    __stcs(reinterpret_cast<float4*>(out) + g1, make_float4(zb[0], zb[1], zb[2], zb[3]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) if (g1 * 4 + j < n) out[g1 * 4 + j] = zb[j];
+  }
 }
 
 __global__ void fill_uniform_kernel(float* __restrict__ out, int64_t n, float lo, float hi,
@@ -117,8 +139,10 @@ extern "C" int nes_fill_normal(float* out, int64_t n, float mean, float std, uin
   if (n == 0) return NES_OK;
   NES_REQUIRE(out, NES_ERR_BAD_ARG, "fill_normal: null pointer");
   const int64_t groups = ceil_div<int64_t>(n, 4);
-  NES_REQUIRE(ceil_div<int64_t>(groups, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "fill_normal: n too large");
-  fill_normal_kernel<<<(unsigned)ceil_div<int64_t>(groups, 256), 256, 0, as_stream(stream)>>>(out, n, mean, std, seed, offset);
+  NES_REQUIRE(ceil_div<int64_t>(groups, 512) <= INT32_MAX, NES_ERR_UNSUPPORTED, "fill_normal: n too large");
+  const unsigned blocks = (unsigned)ceil_div<int64_t>(groups, 512);
+  if (aligned16(out)) fill_normal_kernel<true><<<blocks, 256, 0, as_stream(stream)>>>(out, n, mean, std, seed, offset);
+  else fill_normal_kernel<false><<<blocks, 256, 0, as_stream(stream)>>>(out, n, mean, std, seed, offset);
   return check_launch("fill_normal");
 }
 

@@ -580,3 +580,28 @@ def test_weight_gradient_in_column_blocks_and_overlapped_update(base):
         grad, bgrad = layer.update(G(w), l2=0.01)
     assert grad.data_ptr() == bucket.views()[0].data_ptr() and bgrad.data_ptr() == bucket.views()[1].data_ptr()
     assert_close(grad, og, what="bucket-resident grad")
+
+
+def test_device_normal_fill_distribution_and_layout_independence():
+    """The Philox / Box-Muller fill: moments and tails of 16 M samples, and the value at index i depends only on
+    (seed, offset + i / 4) -- not on the launch shape, the size or the alignment of the tensor."""
+    from nesgpu_b200 import _cabi as C
+    n = 1 << 24
+    t = torch.empty(n, device=DEV)
+    C.call("nes_fill_normal", C.ptr(t), n, 1.5, 2.0, 1234, 0, C.stream())
+    z = (t.double() - 1.5) / 2.0
+    assert abs(z.mean().item()) < 1.5e-3 and abs(z.std().item() - 1) < 1e-3
+    assert abs((z ** 3).mean().item()) < 5e-3 and abs((z ** 4).mean().item() - 3) < 2e-2
+    assert abs((z.abs() > 3).double().mean().item() / 0.0026998 - 1) < 0.05
+    assert 4.5 < z.abs().max().item() < 5.8                       # 24-bit uniforms cap the radius at 5.77
+    # same counters, other shapes: a shorter tensor, and one that starts 4 bytes into an allocation (scalar stores)
+    short = torch.empty(1001, device=DEV)
+    C.call("nes_fill_normal", C.ptr(short), 1001, 1.5, 2.0, 1234, 0, C.stream())
+    assert torch.equal(short, t[:1001])
+    raw = torch.empty(4097, device=DEV)
+    view = raw[1:]
+    C.call("nes_fill_normal", C.ptr(view), 4096, 1.5, 2.0, 1234, 0, C.stream())
+    assert torch.equal(view, t[:4096])
+    later = torch.empty(4096, device=DEV)
+    C.call("nes_fill_normal", C.ptr(later), 4096, 1.5, 2.0, 1234, 1024, C.stream())
+    assert torch.equal(later, t[4096:8192])
