@@ -850,7 +850,9 @@ class EsCnn(Workload):
                 "step": "set_noise + chunked population forward + CE fitness + centred ranks + update (+ all-gather / all-reduce at N>1)",
                 "l2": "activations exceed L2", "sharding": "members", "sigma": 0.02, "fused_layers": self.fused,
                 "precision": {None: "tf32", "tf32": "tf32 operands, fp32 accumulation (stated mode, rel err ~1e-3 per layer)",
-                              "bf16": "bf16 operands in conv2 and the linear layers (rel err ~3e-3 per layer), fp32 accumulation (stated mode)"}.get(self.tc, self.tc)}
+                              "bf16": "bf16 operands in conv2 and the linear layers (rel err ~3e-3 per layer), fp32 accumulation (stated mode)",
+                              "fp32": "fp32 bar (rel err <= 1e-4): conv1 exact fp32, conv2 split-bf16 three-product form, linear layers 3xTF32"
+                              }.get(self.tc, self.tc)}
 
     def setup(self, dev, rank, world):
         from nesgpu_b200 import base, es
@@ -868,6 +870,11 @@ class EsCnn(Workload):
             o1 = {"shared_input": True, "fuse": "relu_maxpool2", "out_dtype": "bf16x2" if pair else (self.tc if opts else "fp32")}
             if pair:
                 opts = dict(opts, in_layout="bf16x2")
+            if self.tc == "fp32":
+                # the fp32 bar on the tensor cores: layer 1 (exact fp32) hands layer 2 its activations as bf16 hi + lo
+                # parts, layer 2 runs the three-product split form, the linear layers their 3xTF32 default
+                o1["out_dtype"] = "bf16x3"
+                opts = {"tc": "bf16x3"}
             self.net = torch.nn.Sequential(
                 base.PermutedConv2d(1, 32, 3, D, options=o1),
                 base.PermutedConv2d(32, 64, 3, D, options=dict(opts, fuse="relu_maxpool2")), torch.nn.Flatten(),

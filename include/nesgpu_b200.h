@@ -273,6 +273,16 @@ int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const float* weight
  * x_pairs_bf16 (R*D/2, H, W, 2, 32) bf16: images 2q and 2q+1 interleaved by pixel (out_mode 3 of
  * nes_shared_conv_pool_fwd).  Covered: Cin == 32, 13x13 images, 3x3 filters, Cout <= 64, R*D even.
  * y, scratch and everything else as for nes_permuted_conv_pool_fwd_bf16. */
+/* The split form of the bf16 kernel, which holds the fp32 bar: the input comes as two bf16 tensors of the
+ * same channels-last layout, x_hi = bf16(x) and x_lo = bf16(x - x_hi) (what nes_shared_conv_pool_fwd stores with
+ * out_mode 4), the stacked filter is split the same way inside, and the accumulator takes
+ * F_hi.x_hi + F_lo.x_hi + F_hi.x_lo: relative error a few 1e-6.  Same coverage as the bf16 kernel. */
+int64_t nes_permuted_conv_pool_fwd_bf16x3_scratch_bytes(int kh, int kw);
+int nes_permuted_conv_pool_fwd_bf16x3(const void* x_hi_bf16, const void* x_lo_bf16, const float* weight, const float* bias,
+                                      const float* eps, const float* bias_noise, const int16_t* pout, float* y,
+                                      int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                      int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                                      nes_stream_t stream);
 int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const float* weight, const float* bias,
                                       const float* eps, const float* bias_noise, const int16_t* pout,
                                       float* y, int64_t D, int64_t R, int Cin, int H, int W, int Cout,

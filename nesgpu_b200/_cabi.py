@@ -44,6 +44,8 @@ SIGNATURES = {
     "nes_permuted_conv_pool_fwd_tc_scratch_bytes": [c_int, c_int],
     "nes_permuted_conv_pool_fwd_tc": [c_ptr] * 7 + [c_i64, c_i64] + [c_int] * 8 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_conv_pool_fwd_bf16": [c_ptr] * 7 + [c_i64, c_i64] + [c_int] * 8 + [c_ptr, c_i64, c_ptr],
+    "nes_permuted_conv_pool_fwd_bf16x3_scratch_bytes": [c_int, c_int],
+    "nes_permuted_conv_pool_fwd_bf16x3": [c_ptr] * 8 + [c_i64, c_i64] + [c_int] * 8 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_conv_pool_fwd_bf16x2": [c_ptr] * 7 + [c_i64, c_i64] + [c_int] * 8 + [c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_scratch_bytes": [c_i64, c_int, c_int],
     "nes_permuted_conv2d_fwd": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
@@ -109,6 +111,7 @@ _RETURNS = {
     "nes_permuted_linear_fwd_scratch_bytes": c_i64,
     "nes_permuted_linear_fwd_tc_scratch_bytes": c_i64,
     "nes_permuted_conv_pool_fwd_tc_scratch_bytes": c_i64,
+    "nes_permuted_conv_pool_fwd_bf16x3_scratch_bytes": c_i64,
     "nes_permuted_conv2d_fwd_scratch_bytes": c_i64,
     "nes_permuted_update_scratch_bytes": c_i64,
     "nes_bin_weighted_sum_scratch_bytes": c_i64,

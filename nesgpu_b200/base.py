@@ -800,15 +800,18 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         out = self.options.get("out_dtype", "fp32")
         if self.options.get("out_tf32"):
             out = "tf32"
-        if out not in ("fp32", "tf32", "bf16", "bf16x2"):
-            raise NotImplementedError('options["out_dtype"] must be "fp32", "tf32", "bf16" or "bf16x2"')
+        if out not in ("fp32", "tf32", "bf16", "bf16x2", "bf16x3"):
+            raise NotImplementedError('options["out_dtype"] must be "fp32", "tf32", "bf16", "bf16x2" or "bf16x3"')
         if out == "bf16x2" and D % 2:
             raise NotImplementedError('options["out_dtype"] = "bf16x2" needs an even number of directions')
-        y = torch.empty((R * D, Ho // 2, Wo // 2, cout), device=x.device,
+        lead = (2, R * D) if out == "bf16x3" else (R * D,)         # split form: a hi and a lo copy of the batch
+        y = torch.empty(lead + (Ho // 2, Wo // 2, cout), device=x.device,
                         dtype=_F32 if out in ("fp32", "tf32") else torch.bfloat16)
         C.call("nes_shared_conv_pool_fwd", C.ptr(z), C.ptr(_opt(self.bias)), C.ptr(beta), C.ptr(pout), C.ptr(y),
-               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0, {"fp32": 0, "tf32": 1, "bf16": 2, "bf16x2": 3}[out],
-               C.stream())
+               R, D, cout, osp, Ho, Wo, 1 if self.antithetic else 0,
+               {"fp32": 0, "tf32": 1, "bf16": 2, "bf16x2": 3, "bf16x3": 4}[out], C.stream())
+        if out == "bf16x3":
+            return y.permute(0, 1, 4, 2, 3)                       # (2, B, C, H, W): bf16 hi and lo parts, channels-last
         if out == "bf16x2":
             # images 2q and 2q+1 interleaved by pixel: a channels-last tensor of R*D/2 "double" images
             return y.view(R * D // 2, Ho // 2, Wo // 2, 2 * cout).permute(0, 3, 1, 2)
@@ -821,8 +824,19 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         mode = self.options.get("tc")
         if self.options.get("in_layout") == "bf16x2":
             return self._fused_pair_forward(input)
-        if mode not in ("tf32", "bf16") or self.options.get("allow_repeats") or self.groups != 1:
+        if mode not in ("tf32", "bf16", "bf16x3") or self.options.get("allow_repeats") or self.groups != 1:
             return None
+        split = mode == "bf16x3"
+        if split:
+            # the split form takes the (2, B, C, H, W) bf16 hi / lo pair a shared-input layer stores with
+            # out_dtype "bf16x3"; an ordinary fp32 batch is split here
+            if isinstance(input, torch.Tensor) and input.dim() == 4 and input.dtype == _F32:
+                hi = input.to(torch.bfloat16)
+                input = torch.stack([hi, (input - hi.float()).to(torch.bfloat16)])
+            if not (isinstance(input, torch.Tensor) and input.is_cuda and input.dim() == 5 and input.shape[0] == 2
+                    and input.dtype == torch.bfloat16):
+                return None
+            pair, input = input, input[0]
         pin, pout = self._perms()
         kh, kw = self.kernel_size
         if (pin is not None or self.in_channels != 32 or self.out_channels > 64 or self.out_sparsity > 64
@@ -839,18 +853,32 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         Hp, Wp = (H - kh + 1) // 2, (W - kw + 1) // 2
         if Hp < 1 or Wp < 1 or (2 * Hp - 1) * W + 2 * Wp > 128 or 128 + (kh - 1) * W + kw - 1 > 256:
             return None
+        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
+        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
+        R = self._repeats(B)
+        if split:
+            xs = pair.permute(0, 1, 3, 4, 2)
+            if not xs.is_contiguous():
+                xs = xs.contiguous()
+            y = torch.empty((B, self.out_channels, Hp, Wp), device=xs.device, dtype=_F32)
+            nbytes = C.call("nes_permuted_conv_pool_fwd_bf16x3_scratch_bytes", kh, kw)
+            buf = C.scratch(nbytes, xs.device)
+            self.last_path = "bf16x3"
+            C.call("nes_permuted_conv_pool_fwd_bf16x3", C.ptr(xs[0]), C.ptr(xs[1]), C.ptr(_opt(self.weight)),
+                   C.ptr(_opt(self.bias)), C.ptr(eps), C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, H, W,
+                   self.out_channels, kh, kw, self.out_sparsity, 1 if self.antithetic else 0, C.ptr(buf), nbytes,
+                   C.stream())
+            return y
         x = input.permute(0, 2, 3, 1)
         want = torch.bfloat16 if mode == "bf16" else _F32
         if x.dtype != want:
             x = x.to(want)
         if not x.is_contiguous():
             x = x.contiguous()
-        eps = C.require_cuda(self.weight_noise, "weight_noise", _F32)
-        beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
-        R = self._repeats(B)
         y = torch.empty((B, self.out_channels, Hp, Wp), device=x.device, dtype=_F32)
         nbytes = C.call("nes_permuted_conv_pool_fwd_tc_scratch_bytes", kh, kw)
         buf = C.scratch(nbytes, x.device)
+        self.last_path = mode
         C.call("nes_permuted_conv_pool_fwd_" + ("bf16" if mode == "bf16" else "tc"), C.ptr(x), C.ptr(_opt(self.weight)),
                C.ptr(_opt(self.bias)), C.ptr(eps),
                C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, 32, H, W, self.out_channels, kh, kw,

@@ -18,36 +18,41 @@ int bin_weighted_sum_impl(const void* in, const uint16_t* w_half, uint16_t* out_
 
 // ---- N = 1 product (one packed input vector per member) with the layer's epilogues ---------------------
 //
-// HBM-bound: the member's weight rows are streamed once.  Four lanes share a row (each takes every fourth
-// 16-byte chunk, so one load instruction of a warp touches eight rows, 64 contiguous bytes each), a warp
-// covers a group of 32 rows in four passes with all loads issued before the first use, the member's
-// input chunks sit in registers, and after a two-step butterfly the counts are dealt back so that lane L
-// owns row L of the group: stores are coalesced and one __ballot_sync yields 32 packed output bits.
+// HBM-bound: the member's weight rows are streamed once.  Four or eight lanes share a row (at 1024-bit rows:
+// eight lanes, one 16-byte chunk each, so a warp-wide load reads four whole rows = 512 contiguous bytes), a
+// warp covers a group of 32 rows in as many passes as lanes share a row, with all loads issued before the
+// first use; the member's input chunks sit in registers, and after a butterfly over the sharing lanes the
+// counts are dealt back so that lane L owns row L of the group: stores are coalesced and one __ballot_sync
+// yields 32 packed output bits.
 enum { BMV_COUNTS = 0, BMV_ACT = 1, BMV_BOOL = 2, BMV_PACKED = 3 };
 
-// One group = 32 consecutive rows of one member, handled by one warp.
-template <int CPL>
+// One group = 32 consecutive rows of one member, handled by one warp.  LPR lanes share a row (lane % LPR takes
+// chunks sub, sub + LPR, ...), so a warp-wide load covers 32 / LPR rows: with LPR * 16 bytes = the row length
+// every load instruction reads one contiguous span of whole rows.
+template <int LPR, int CPL>
 struct BmvGroup {
+  static constexpr int RPP = 32 / LPR;          // rows per pass
   uint4 xv[CPL];
-  uint4 av[4][CPL];
+  uint4 av[LPR][CPL];
   int64_t z, base;
 
   __device__ __forceinline__ void load(const uint4* __restrict__ A, const uint4* __restrict__ X, int64_t g, int64_t gpm, int64_t M,
-                                       int cpr, int sub, int rl) {
+                                       int cpr, int lane) {
+    const int sub = lane % LPR, rl = lane / LPR;
     z = g / gpm;
     base = (g - z * gpm) * 32;
 #pragma unroll
     for (int j = 0; j < CPL; ++j) {
-      const int c = sub + 4 * j;
+      const int c = sub + LPR * j;
       xv[j] = (c < cpr) ? __ldg(X + z * cpr + c) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int64_t m = base + 8 * i + rl;
+    for (int i = 0; i < LPR; ++i) {
+      const int64_t m = base + RPP * i + rl;
       const uint4* row = A + (z * M + m) * cpr;
 #pragma unroll
       for (int j = 0; j < CPL; ++j) {
-        const int c = sub + 4 * j;
+        const int c = sub + LPR * j;
         av[i][j] = (m < M && c < cpr) ? __ldcs(row + c) : xv[j];      // padding contributes popc(x ^ x) = 0
       }
     }
@@ -57,15 +62,15 @@ struct BmvGroup {
   __device__ __forceinline__ int reduce(int lane) const {
     int mine = 0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < LPR; ++i) {
       int s = 0;
 #pragma unroll
       for (int j = 0; j < CPL; ++j)
         s += __popc(av[i][j].x ^ xv[j].x) + __popc(av[i][j].y ^ xv[j].y) + __popc(av[i][j].z ^ xv[j].z) + __popc(av[i][j].w ^ xv[j].w);
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      const int v = __shfl_sync(0xffffffffu, s, 4 * (lane & 7));      // row 8i + (lane & 7) of this pass
-      if ((lane >> 3) == i) mine = v;
+#pragma unroll
+      for (int sh = 1; sh < LPR; sh <<= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
+      const int v = __shfl_sync(0xffffffffu, s, LPR * (lane % RPP));   // row RPP * i + (lane % RPP) of this pass
+      if (lane / RPP == i) mine = v;
     }
     return mine;
   }
@@ -97,19 +102,18 @@ __device__ __forceinline__ void bmv_store(void* __restrict__ out, const __half* 
 
 // The grid is a few blocks per SM; every warp walks groups g = warp, warp + W, ... two at a time, so that the loads
 // of two groups (sixteen 16-byte loads per lane at 1024-bit rows) are in flight before the first popcount.
-template <int MODE, int CPL>
+template <int MODE, int LPR, int CPL>
 __global__ void __launch_bounds__(256) bmv_rows_kernel(const uint4* __restrict__ A, const uint4* __restrict__ X,
                                                        void* __restrict__ out, const __half* __restrict__ bias,
                                                        const __half* __restrict__ bias_noise, int64_t M, int cpr,
                                                        int n_bits, int64_t out_row_u32, int64_t gpm, int64_t groups) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 3, rl = lane >> 2;
   const int64_t W = int64_t(gridDim.x) * 8;
   for (int64_t g = int64_t(blockIdx.x) * 8 + warp; g < groups; g += 2 * W) {
-    BmvGroup<CPL> a, b;
-    a.load(A, X, g, gpm, M, cpr, sub, rl);
+    BmvGroup<LPR, CPL> a, b;
+    a.load(A, X, g, gpm, M, cpr, lane);
     const bool two = g + W < groups;                    // uniform over the warp
-    if (two) b.load(A, X, g + W, gpm, M, cpr, sub, rl);
+    if (two) b.load(A, X, g + W, gpm, M, cpr, lane);
     bmv_store<MODE>(out, bias, bias_noise, a.z, a.base, lane, M, a.reduce(lane), n_bits, out_row_u32);
     if (two) bmv_store<MODE>(out, bias, bias_noise, b.z, b.base, lane, M, b.reduce(lane), n_bits, out_row_u32);
   }
@@ -300,10 +304,10 @@ static int launch_bmv_rows(const void* A, const void* X, void* out, const __half
   const unsigned grid = (unsigned)(want < cap ? (want > 0 ? want : 1) : cap);
   const uint4* a = static_cast<const uint4*>(A);
   const uint4* x = static_cast<const uint4*>(X);
-  if (cpr <= 4) bmv_rows_kernel<MODE, 1><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
-  else if (cpr <= 8) bmv_rows_kernel<MODE, 2><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
-  else if (cpr <= 16) bmv_rows_kernel<MODE, 4><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
-  else bmv_rows_kernel<MODE, 8><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  if (cpr <= 4) bmv_rows_kernel<MODE, 4, 1><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else if (cpr <= 8) bmv_rows_kernel<MODE, 8, 1><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else if (cpr <= 16) bmv_rows_kernel<MODE, 8, 2><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
+  else bmv_rows_kernel<MODE, 8, 4><<<grid, 256, 0, st>>>(a, x, out, bias, bn, M, cpr, n_bits, out_row_u32, gpm, groups);
   return check_launch("binarized_linear_fwd");
 }
 

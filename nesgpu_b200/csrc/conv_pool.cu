@@ -20,17 +20,31 @@ __device__ inline float round_to_tf32(float a) {
   return __uint_as_float(u & 0xFFFFE000u);
 }
 
-// MODE: 0 = fp32, 1 = fp32 rounded to TF32, 2 = bf16, 3 = bf16 with image pairs interleaved by pixel
+// MODE: 0 = fp32, 1 = fp32 rounded to TF32, 2 = bf16, 3 = bf16 with image pairs interleaved by pixel,
+// 4 = split bf16: hi = bf16(v) in the first half of the output, lo = bf16(v - hi) in the second half (same layout)
 template <int MODE> struct OutType { typedef float type; };
 template <> struct OutType<2> { typedef __nv_bfloat16 type; };
 template <> struct OutType<3> { typedef __nv_bfloat16 type; };
+template <> struct OutType<4> { typedef __nv_bfloat16 type; };
 
-template <int MODE>
-__device__ __forceinline__ typename OutType<MODE>::type pool_value(float a0, float a1, float a2, float a3, float add) {
-  const float v = fmaxf(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) + add, 0.f);
-  if constexpr (MODE >= 2) return __float2bfloat16_rn(v);
-  else if constexpr (MODE == 1) return round_to_tf32(v);
-  else return v;
+// what is stored at o (and, for the split form, lo_off elements further on)
+template <int MODE, typename T>
+__device__ __forceinline__ void store_pooled(T* o, int64_t lo_off, float v) {
+  if constexpr (MODE == 4) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    *o = h;
+    o[lo_off] = __float2bfloat16_rn(v - __bfloat162float(h));
+  } else if constexpr (MODE >= 2) {
+    *o = __float2bfloat16_rn(v);
+  } else if constexpr (MODE == 1) {
+    *o = round_to_tf32(v);
+  } else {
+    *o = v;
+  }
+}
+
+__device__ __forceinline__ float pool_value(float a0, float a1, float a2, float a3, float add) {
+  return fmaxf(fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) + add, 0.f);
 }
 
 constexpr int CP_WARPS = 32;          // warps per block
@@ -67,6 +81,7 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
   }
   __syncthreads();
   const int64_t member_stride = int64_t(pooled) * Cout;
+  const int64_t lo_off = R * D * member_stride;                   // split form: the lo copy follows the hi copy
   const int row = Wo * npitch;
   for (int c0 = 0; c0 < Cout; c0 += 32) {
     const int c = c0 + lane;
@@ -100,13 +115,13 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
         // the 32 channels of a member point at 32 different noise maps = 32 different banks
         const float* n = np + int(*sp);
         const float2 t = *tp;
-        const out_t v = pool_value<MODE>(fmaf(t.x, n[0], b00), fmaf(t.x, n[o1], b01), fmaf(t.x, n[o2], b10),
-                                         fmaf(t.x, n[o3], b11), t.y);
+        const float v = pool_value(fmaf(t.x, n[0], b00), fmaf(t.x, n[o1], b01), fmaf(t.x, n[o2], b10),
+                                   fmaf(t.x, n[o3], b11), t.y);
         const float* n2 = n + nq;
-        const out_t w = pool_value<MODE>(fmaf(t.x, n2[0], c00), fmaf(t.x, n2[o1], c01), fmaf(t.x, n2[o2], c10),
-                                         fmaf(t.x, n2[o3], c11), t.y);
-        if (live) *o = v;
-        if (live2) o[o_second] = w;
+        const float w = pool_value(fmaf(t.x, n2[0], c00), fmaf(t.x, n2[o1], c01), fmaf(t.x, n2[o2], c10),
+                                   fmaf(t.x, n2[o3], c11), t.y);
+        if (live) store_pooled<MODE>(o, lo_off, v);
+        if (live2) store_pooled<MODE>(o + o_second, lo_off, w);
       }
     }
   }
@@ -122,8 +137,8 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   NES_REQUIRE(R >= 0 && D >= 0 && Cout >= 0 && out_sp >= 0 && Ho >= 0 && Wo >= 0, NES_ERR_BAD_ARG,
               "shared_conv_pool_fwd: negative extent");
   NES_REQUIRE(out_sp <= Cout, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: out_sp exceeds the channel count");
-  NES_REQUIRE(out_mode >= 0 && out_mode <= 3, NES_ERR_BAD_ARG,
-              "shared_conv_pool_fwd: out_mode must be 0 (fp32), 1 (tf32), 2 (bf16) or 3 (bf16, image pairs interleaved)");
+  NES_REQUIRE(out_mode >= 0 && out_mode <= 4, NES_ERR_BAD_ARG,
+              "shared_conv_pool_fwd: out_mode must be 0 (fp32), 1 (tf32), 2 (bf16), 3 (bf16, image pairs interleaved) or 4 (bf16 hi + lo)");
   NES_REQUIRE(out_mode != 3 || D % 2 == 0, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: the pair layout needs an even number of members");
   if (R == 0 || D == 0 || Cout == 0 || Ho < 2 || Wo < 2) return NES_OK;
   NES_REQUIRE(z && y, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: null pointer");
@@ -159,7 +174,8 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "shared_conv_pool_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); \
   shared_conv_pool_kernel<MODE><<<grid, CP_WARPS * 32, smem, st>>>(z, bias, bias_noise, pout, static_cast<T*>(y), R, D, Cout, out_sp, \
                                                                    Ho, Wo, antithetic, per)
-  if (out_mode == 3) { NES_LAUNCH_SHARED_CONV_POOL(3, __nv_bfloat16); }
+  if (out_mode == 4) { NES_LAUNCH_SHARED_CONV_POOL(4, __nv_bfloat16); }
+  else if (out_mode == 3) { NES_LAUNCH_SHARED_CONV_POOL(3, __nv_bfloat16); }
   else if (out_mode == 2) { NES_LAUNCH_SHARED_CONV_POOL(2, __nv_bfloat16); }
   else if (out_mode == 1) { NES_LAUNCH_SHARED_CONV_POOL(1, float); }
   else { NES_LAUNCH_SHARED_CONV_POOL(0, float); }

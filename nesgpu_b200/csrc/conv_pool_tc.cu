@@ -15,6 +15,10 @@
 //   the maximum, add the bias terms, apply the ReLU and store NCHW.
 // The same kernel runs with bf16 operands (template flag): a pixel is then a 64-byte row, tiles use the
 // 64-byte swizzle, a tap takes two kind::f16 MMAs with K = 16, and four images are staged ahead.
+// TERMS = 3 (bf16 only) is the split form that holds the fp32 bar: the stacked filter is resident twice
+// (hi = bf16(v), lo = bf16(v - hi)), an image arrives as two staged copies (hi, lo: what the shared-input
+// layer stores with out_mode 4) in the two halves of a stage, and the accumulator takes
+// F_hi.x_hi + F_lo.x_hi + F_hi.x_lo per K step.
 // Every mbarrier wait is bounded; on a time-out the role stops, the error word is set and all roles
 // fall through to the common exit that frees tensor memory.
 #include <cuda_bf16.h>
@@ -68,10 +72,12 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // TW / THP / TWP: input width and pooled output size known at compile time (0 = taken from the parameters).
 // With them the W-channel warps read their whole accumulator row into registers with four wide loads
 // and index it statically; the runtime form reads each pooling window with two narrow loads.
-template <int TW, int THP, int TWP, bool BF16>
+template <int TW, int THP, int TWP, bool BF16, int TERMS = 1>
 __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                         const __grid_constant__ CUtensorMap map_f,
+                                                                        const __grid_constant__ CUtensorMap map_x_lo,
                                                                         const ConvPoolParams p) {
+  static_assert(TERMS == 1 || (TERMS == 3 && BF16), "the three-term form exists for bf16 operands only");
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw = smem_u32(dyn_raw);
   unsigned char* base = dyn_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -80,9 +86,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   constexpr int KSTEPS = BF16 ? 2 : 4;                  // MMAs per tap (K = 16 bf16 / 8 tf32 = 32 bytes each)
   const int taps = p.kh * p.kw;
   const int stages = p.stages;
-  const int stage_bytes = p.stage_rows * ROW_BYTES;
+  const int half_bytes = p.stage_rows * ROW_BYTES;             // one staged copy of an image
+  const int stage_bytes = (TERMS == 3 ? 2 : 1) * half_bytes;     // TERMS == 3: hi copy, then lo copy
+  const size_t filt_copy = size_t(taps) * TAP_BYTES;            // TERMS == 3: hi filter, then lo filter
   unsigned char* filt = base;
-  unsigned char* stage0 = filt + size_t(taps) * TAP_BYTES;
+  unsigned char* stage0 = filt + (TERMS == 3 ? 2 : 1) * filt_copy;
   float* zeps0 = reinterpret_cast<float*>(stage0 + size_t(stages) * stage_bytes);  // [zbufs][CP_N][CP_HALF]
   const int zbufs = p.zbufs;
   uint64_t* bars = reinterpret_cast<uint64_t*>(zeps0 + size_t(zbufs) * CP_N * CP_HALF);
@@ -112,17 +120,21 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: the stacked filter once, then one load per image
-      mbar_expect_tx(filt_full, uint32_t(taps) * TAP_BYTES);
-      for (int t = 0; t < taps; ++t) tma_load_2d(filt + size_t(t) * TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
+      mbar_expect_tx(filt_full, uint32_t(TERMS == 3 ? 2 : 1) * uint32_t(taps) * TAP_BYTES);
+      for (int t = 0; t < (TERMS == 3 ? 2 : 1) * taps; ++t) tma_load_2d(filt + size_t(t) * TAP_BYTES, &map_f, filt_full, 0, t * CP_M);
       int i = 0;
       for (int64_t b = blockIdx.x; b < p.B; b += gridDim.x, ++i) {
         const int s = i % stages;
         if (!mbar_wait(&empty[s], ((i / stages) & 1) ^ 1, 1)) break;
         mbar_expect_tx(&full[s], uint32_t(stage_bytes));
         tma_load_2d(stage0 + size_t(s) * stage_bytes, &map_x, &full[s], 0, int(b * p.rows_per_image));
+        if (TERMS == 3) tma_load_2d(stage0 + size_t(s) * stage_bytes + half_bytes, &map_x_lo, &full[s], 0, int(b * p.rows_per_image));
         // the staged images alone may not cover the HBM latency: pull the first image not yet staged into L2
         const int64_t ahead = b + int64_t(stages) * gridDim.x;
-        if (ahead < p.B) tma_prefetch_2d(&map_x, 0, int(ahead * p.rows_per_image));
+        if (ahead < p.B) {
+          tma_prefetch_2d(&map_x, 0, int(ahead * p.rows_per_image));
+          if (TERMS == 3) tma_prefetch_2d(&map_x_lo, 0, int(ahead * p.rows_per_image));
+        }
       }
     }
   } else if (warp == 1) {
@@ -149,6 +161,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
           for (int k = 0; k < KSTEPS; ++k) {
             if (BF16) mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
             else mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+            if (TERMS == 3) {
+              // lo filter on the hi image, hi filter on the lo image (descriptor units are 16 bytes)
+              mma_bf16(acc, a + uint64_t(filt_copy >> 4) + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, 1u);
+              mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(half_bytes >> 4) + uint64_t(2 * k), idesc, 1u);
+            }
           }
         }
         mma_commit(&empty[s]);
@@ -499,7 +516,8 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
 }
 
 // stacked[tap][m][cin], rounded to the operand type: m < Cout -> weight[m], 64 <= m < 64 + osp -> eps[m - 64], else 0
-template <bool BF16>
+// SPLIT (bf16): the lo copy bf16(v - hi) follows the hi copy
+template <bool BF16, bool SPLIT = false>
 __global__ void stack_filter_kernel(const float* __restrict__ w, const float* __restrict__ eps, void* __restrict__ out,
                                     int Cout, int osp, int taps) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -508,8 +526,13 @@ __global__ void stack_filter_kernel(const float* __restrict__ w, const float* __
   float v = 0.f;
   if (m < Cout) v = w[(size_t(m) * CP_CIN + cin) * taps + t];
   else if (m >= CP_HALF && m - CP_HALF < osp) v = eps[(size_t(m - CP_HALF) * CP_CIN + cin) * taps + t];
-  if (BF16) static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
-  else static_cast<float*>(out)[idx] = round_tf32(v);
+  if (BF16) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    static_cast<__nv_bfloat16*>(out)[idx] = h;
+    if (SPLIT) static_cast<__nv_bfloat16*>(out)[size_t(taps) * CP_M * CP_CIN + idx] = __float2bfloat16_rn(v - __bfloat162float(h));
+  } else {
+    static_cast<float*>(out)[idx] = round_tf32(v);
+  }
 }
 
 int conv_pool_error_word(int* v, bool clear) { return read_error_word(v, clear, "tc_error_flag"); }
@@ -534,7 +557,8 @@ static int make_rows_map(CUtensorMap* map, const void* base, bool bf16, int64_t 
 struct ConvPoolPlan { int Ho, Wo, Hp, Wp, taps, stage_rows, stages, zbufs, row_bytes; size_t smem; };
 
 // Shapes the kernel covers; on failure the message says which rule was broken.
-static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what) {
+static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, int Cout, int osp, int kh, int kw, const char* what,
+                          int terms = 1) {
   NES_REQUIRE(Cin == CP_CIN, NES_ERR_UNSUPPORTED, "%s: needs %d input channels (got %d)", what, CP_CIN, Cin);
   NES_REQUIRE(Cout >= 1 && Cout <= CP_HALF && osp >= 0 && osp <= CP_HALF, NES_ERR_UNSUPPORTED,
               "%s: needs at most %d output channels (got %d, %d noise rows)", what, CP_HALF, Cout, osp);
@@ -549,8 +573,9 @@ static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, in
   NES_REQUIRE(pl.stage_rows <= 256, NES_ERR_UNSUPPORTED, "%s: filter reach too large for one staged image", what);
   pl.row_bytes = bf16 ? 64 : 128;
   const size_t zbytes = size_t(CP_N) * CP_HALF * 4;
-  const size_t fixed = 1024 + size_t(pl.taps) * CP_M * pl.row_bytes + zbytes + 256;
-  const size_t stage = size_t(pl.stage_rows) * pl.row_bytes;
+  const size_t copies = terms == 3 ? 2 : 1;                     // filter and image both staged as hi + lo
+  const size_t fixed = 1024 + copies * size_t(pl.taps) * CP_M * pl.row_bytes + zbytes + 256;
+  const size_t stage = copies * size_t(pl.stage_rows) * pl.row_bytes;
   const size_t limit = 227 * 1024;
   NES_REQUIRE(fixed + 2 * stage <= limit, NES_ERR_UNSUPPORTED, "%s: %d filter taps do not fit shared memory", what, pl.taps);
   // a second buffer for the eps rows (lets their copy for the next image overlap this image's pooling) when
@@ -563,30 +588,32 @@ static int plan_conv_pool(ConvPoolPlan& pl, bool bf16, int Cin, int H, int W, in
   return NES_OK;
 }
 
-template <bool BF16>
+template <bool BF16, int TERMS = 1>
 static int run_conv_pool(const void* x_nhwc, const float* weight, const float* bias, const float* eps,
                          const float* bias_noise, const int16_t* pout, float* y, int64_t D, int64_t R, int Cin, int H, int W,
                          int Cout, int kh, int kw, int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
-                         cudaStream_t st, const char* what) {
+                         cudaStream_t st, const char* what, const void* x_lo = nullptr) {
   NES_REQUIRE(D >= 0 && R >= 0, NES_ERR_BAD_ARG, "%s: negative extent", what);
   ConvPoolPlan pl;
-  int rc = plan_conv_pool(pl, BF16, Cin, H, W, Cout, out_sp, kh, kw, what);
+  int rc = plan_conv_pool(pl, BF16, Cin, H, W, Cout, out_sp, kh, kw, what, TERMS);
   if (rc != NES_OK) return rc;
   const int64_t B = D * R;
   if (B == 0) return NES_OK;
-  NES_REQUIRE(x_nhwc && weight && eps && y, NES_ERR_BAD_ARG, "%s: null pointer", what);
-  NES_REQUIRE(aligned16(x_nhwc), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
+  NES_REQUIRE(x_nhwc && weight && eps && y && (TERMS == 1 || x_lo), NES_ERR_BAD_ARG, "%s: null pointer", what);
+  NES_REQUIRE(aligned16(x_nhwc) && aligned16(x_lo), NES_ERR_BAD_ARG, "%s: input must be 16-byte aligned", what);
   NES_REQUIRE(B * H * W <= INT32_MAX, NES_ERR_UNSUPPORTED, "%s: batch too large", what);
-  const int64_t need = int64_t(pl.taps) * CP_M * pl.row_bytes;
+  const int64_t need = int64_t(TERMS == 3 ? 2 : 1) * pl.taps * CP_M * pl.row_bytes;
   NES_REQUIRE(scratch && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, NES_ERR_SCRATCH,
               "%s: scratch needs %lld bytes, 256-byte aligned", what, (long long)need);
   const int n = pl.taps * CP_M * CP_CIN;
-  stack_filter_kernel<BF16><<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, scratch, Cout, out_sp, pl.taps);
+  stack_filter_kernel<BF16, TERMS == 3><<<ceil_div(n, 256), 256, 0, st>>>(weight, eps, scratch, Cout, out_sp, pl.taps);
   rc = check_launch(what);
   if (rc != NES_OK) return rc;
-  CUtensorMap map_x, map_f;
+  CUtensorMap map_x, map_f, map_x_lo;
   if ((rc = make_rows_map(&map_x, x_nhwc, BF16, B * H * W, pl.stage_rows, what)) != NES_OK) return rc;
-  if ((rc = make_rows_map(&map_f, scratch, BF16, int64_t(pl.taps) * CP_M, CP_M, what)) != NES_OK) return rc;
+  if ((rc = make_rows_map(&map_f, scratch, BF16, int64_t(TERMS == 3 ? 2 : 1) * pl.taps * CP_M, CP_M, what)) != NES_OK) return rc;
+  map_x_lo = map_x;
+  if (TERMS == 3 && (rc = make_rows_map(&map_x_lo, x_lo, BF16, B * H * W, pl.stage_rows, what)) != NES_OK) return rc;
   ConvPoolParams p;
   p.bias = bias; p.bias_noise = bias_noise; p.pout = pout; p.y = y;
   p.B = B; p.D = D; p.R = R;
@@ -595,11 +622,11 @@ static int run_conv_pool(const void* x_nhwc, const float* weight, const float* b
   // compile-time geometry for 13x13 inputs pooled to 5x5 (3x3 filters on the 13x13 maps of the small MNIST
   // network); every other covered shape takes the runtime-indexed form
   const bool fixed = (W == 13 && pl.Hp == 5 && pl.Wp == 5);
-  auto kernel = fixed ? conv_pool_tc_kernel<13, 5, 5, BF16> : conv_pool_tc_kernel<0, 0, 0, BF16>;
+  auto kernel = fixed ? conv_pool_tc_kernel<13, 5, 5, BF16, TERMS> : conv_pool_tc_kernel<0, 0, 0, BF16, TERMS>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
   const unsigned grid = (unsigned)(B < sm_count() ? B : sm_count());
-  kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, p);
+  kernel<<<grid, CP_THREADS, pl.smem, st>>>(map_x, map_f, map_x_lo, p);
   return check_launch(what);
 }
 
@@ -630,6 +657,20 @@ extern "C" int nes_permuted_conv_pool_fwd_bf16(const void* x_nhwc_bf16, const fl
                                                nes_stream_t stream) {
   return run_conv_pool<true>(x_nhwc_bf16, weight, bias, eps, bias_noise, pout, y, D, R, Cin, H, W, Cout, kh, kw, out_sp,
                              antithetic, scratch, scratch_bytes, as_stream(stream), "permuted_conv_pool_fwd_bf16");
+}
+
+extern "C" int64_t nes_permuted_conv_pool_fwd_bf16x3_scratch_bytes(int kh, int kw) {
+  if (kh <= 0 || kw <= 0) return 0;
+  return 2 * int64_t(kh) * kw * CP_M * 64;
+}
+
+extern "C" int nes_permuted_conv_pool_fwd_bf16x3(const void* x_hi_bf16, const void* x_lo_bf16, const float* weight, const float* bias,
+                                                 const float* eps, const float* bias_noise, const int16_t* pout, float* y,
+                                                 int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
+                                                 int out_sp, int antithetic, void* scratch, int64_t scratch_bytes,
+                                                 nes_stream_t stream) {
+  return run_conv_pool<true, 3>(x_hi_bf16, weight, bias, eps, bias_noise, pout, y, D, R, Cin, H, W, Cout, kh, kw, out_sp,
+                                antithetic, scratch, scratch_bytes, as_stream(stream), "permuted_conv_pool_fwd_bf16x3", x_lo_bf16);
 }
 
 extern "C" int nes_permuted_conv_pool_fwd_bf16x2(const void* x_pairs_bf16, const float* weight, const float* bias,

@@ -149,8 +149,10 @@ __global__ void grad_from_out_hist_kernel(const float* __restrict__ G, const flo
 // block reads all of eps from L2), so the noise rows are dealt round-robin to PU_SGROUPS thread groups that
 // each walk their rows with PU_UNROLL 128-bit loads in flight per thread over 256 columns at a time; the
 // groups' partial sums meet in shared memory.  The remaining blocks own 32 columns of the bias gradient each.
-constexpr int PU_ROWS = 8, PU_THREADS = 512, PU_SGROUPS = 8, PU_COLS = 256, PU_UNROLL = 8;
+constexpr int PU_THREADS = 512, PU_SGROUPS = 8, PU_COLS = 256, PU_UNROLL = 8;
 
+// PU_ROWS = 8 output rows per block, or 4 when eight would leave most of the SMs without a block
+template <int PU_ROWS>
 __global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
     const float* __restrict__ eps, const float* __restrict__ w, const int16_t* __restrict__ pout,
     const float* __restrict__ weight, const float* __restrict__ beta, float* __restrict__ grad,
@@ -184,11 +186,17 @@ __global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
   __syncthreads();
   if (vec_pout && k0 + PU_ROWS <= out) {
     for (int64_t d = t; d < D; d += PU_THREADS) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(pout + d * out + k0));
+      uint32_t q[PU_ROWS / 2];
+      if (PU_ROWS == 8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(pout + d * out + k0));
+        q[0] = v.x; q[1] = v.y; q[PU_ROWS / 2 - 2] = v.z; q[PU_ROWS / 2 - 1] = v.w;
+      } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(pout + d * out + k0));
+        q[0] = v.x; q[1] = v.y;
+      }
       const float wd = __ldg(w + d);
-      const uint32_t q[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < PU_ROWS / 2; ++u) {
         const int s0 = int(q[u] & 0xFFFFu), s1 = int(q[u] >> 16);
         if (s0 < out_sp) atomicAdd(&Gs[s0 * PU_ROWS + 2 * u], wd);
         if (s1 < out_sp) atomicAdd(&Gs[s1 * PU_ROWS + 2 * u + 1], wd);
@@ -234,9 +242,12 @@ __global__ void __launch_bounds__(PU_THREADS) permuted_update_out_kernel(
         for (int i = 0; i < PU_UNROLL; ++i) {
           const int s = sb + i * PU_SGROUPS;
           if (s < out_sp) {
-            const float4 g0 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS);
-            const float4 g1 = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS + 4);
-            const float g[PU_ROWS] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float g[PU_ROWS];
+#pragma unroll
+            for (int u4 = 0; u4 < PU_ROWS; u4 += 4) {
+              const float4 gv = *reinterpret_cast<const float4*>(Gs + s * PU_ROWS + u4);
+              g[u4] = gv.x; g[u4 + 1] = gv.y; g[u4 + 2] = gv.z; g[u4 + 3] = gv.w;
+            }
 #pragma unroll
             for (int u = 0; u < PU_ROWS; ++u) {
               a[u][0] = fmaf(g[u], ev[i].x, a[u][0]); a[u][1] = fmaf(g[u], ev[i].y, a[u][1]);
@@ -599,16 +610,18 @@ extern "C" int nes_permuted_update_out(const float* eps, const float* w, const i
   NES_REQUIRE((l1 == 0.f && l2 == 0.f) || weight, NES_ERR_BAD_ARG, "permuted_update_out: l1/l2 given without weight");
   NES_REQUIRE((bias_noise == nullptr) == (bias_grad == nullptr), NES_ERR_BAD_ARG,
               "permuted_update_out: bias_noise and bias_grad go together");
-  const size_t smem = (size_t(out_sp) * PU_ROWS + size_t(PU_SGROUPS) * PU_ROWS * PU_COLS) * sizeof(float);
+  const int rows = (ceil_div(out, 8) * 2 <= sm_count()) ? 4 : 8;       // more, smaller blocks while the grid is far below the SM count
+  const size_t smem = (size_t(out_sp) * rows + size_t(PU_SGROUPS) * rows * PU_COLS) * sizeof(float);
   NES_REQUIRE(smem <= 200 * 1024, NES_ERR_UNSUPPORTED, "permuted_update_out: out_sp=%d needs %zu B of shared memory", out_sp, smem);
   const size_t smem_all = smem;
+  auto kern = rows == 4 ? permuted_update_out_kernel<4> : permuted_update_out_kernel<8>;
   if (smem_all > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(permuted_update_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_all);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_all);
     if (e != cudaSuccess) return fail(NES_ERR_UNSUPPORTED, "permuted_update_out: %zu B of shared memory refused", smem_all);
   }
-  const int gblocks = ceil_div(out, PU_ROWS);
+  const int gblocks = ceil_div(out, rows);
   const int bblocks = bias_grad ? ceil_div(out, 32) : 0;
-  permuted_update_out_kernel<<<gblocks + bblocks, PU_THREADS, smem_all, as_stream(stream)>>>(
+  kern<<<gblocks + bblocks, PU_THREADS, smem_all, as_stream(stream)>>>(
       eps, w, pout, (l1 != 0.f || l2 != 0.f) ? weight : nullptr, bias_noise, grad, bias_grad, D, out, out_sp,
       int64_t(in) * ksize, gblocks, l1, l2,
       ((int64_t(in) * ksize) % 4 == 0 && aligned16(eps)) ? 1 : 0, (out % 8 == 0 && aligned16(pout)) ? 1 : 0);

@@ -611,3 +611,42 @@ def test_split_bf16_is_not_taken_for_uncovered_geometries():
     layer.perturbed_flag = True
     with pytest.raises(NotImplementedError):
         layer.forward(torch.zeros(4, 64, 8, 8, device=DEV))
+
+
+@pytest.mark.parametrize("cout,out_sp,hw,k,R,anti,bias,D", [
+    (64, 0, 13, 3, 2, True, True, 5), (64, 0.5, 13, 3, 4, True, True, 3), (40, 0, 12, 3, 1, False, False, 7),
+    (64, 0, 13, 3, 3, True, True, 210),
+])
+def test_permuted_conv_pool_split_bf16_holds_the_fp32_bar(cout, out_sp, hw, k, R, anti, bias, D):
+    """Fused Conv + ReLU + MaxPool2d(2) in the three-product split-bf16 form: 1e-4 against the oracle on an fp32
+    input (split into hi + lo bf16 parts on the way in), 1e-3 on the perturbation term alone."""
+    from nesgpu_b200 import base
+    from oracle import perturbed_ref as O
+    from gpu_util import set_params
+    cin = 32
+    g = torch.Generator().manual_seed(cout + hw + D + 1)
+    layer = base.PermutedConv2d(cin, cout, k, D, bias=bias, antithetic=anti, permutation="out", out_sparsity=out_sp,
+                                options={"tc": "bf16x3", "fuse": "relu_maxpool2"}).to(DEV)
+    osp = layer.out_sparsity
+    x = torch.randn(R * D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g) * .1 if bias else None
+    eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g) if bias else None
+    pout = torch.stack([torch.randperm(cout, generator=g) for _ in range(D)]).short()
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise, layer.output_permutations = G(eps), (G(beta) if bias else None), G(pout)
+    zb, zbeta = (b if bias else torch.zeros(cout)), (beta if bias else torch.zeros(D, cout))
+    pre = O.permuted_conv2d_forward(x, W, zb, eps, zbeta, None, pout, D, 1, 0, 1, anti)
+    want = torch.nn.functional.max_pool2d(torch.relu(pre), 2)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    assert layer.last_path == "bf16x3" and _flag(_C()) == 0
+    assert_close(y, want, tol=1e-4, what="split-bf16 fused layer")
+    layer.weight_noise = G(torch.zeros_like(eps))
+    with torch.no_grad():
+        y0 = layer.forward(G(x))
+    want0 = torch.nn.functional.max_pool2d(torch.relu(O.permuted_conv2d_forward(x, W, zb, torch.zeros_like(eps), zbeta, None, pout,
+                                                                                D, 1, 0, 1, anti)), 2)
+    assert_close(y - y0, want - want0, tol=1e-3, what="perturbation term")
