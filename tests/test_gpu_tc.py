@@ -60,7 +60,7 @@ def test_linear_tc_rejects_unaligned_k():
 
 
 # ------------------------------------------------------------------ tensor-core convolutions (TF32 mode)
-# Stated reduced-precision mode: operands rounded to TF32.  Bar 2e-2 (north-star); measured ~5e-4.
+# Stated reduced-precision mode: operands rounded to TF32.  Bar 2e-2; measured ~5e-4.
 TC_CONV_TOL = 5e-3
 
 
