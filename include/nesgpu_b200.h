@@ -391,6 +391,11 @@ int nes_permuted_update(const float* eps, const float* w, const int16_t* pin, co
                         float l1, float l2, void* scratch, int64_t scratch_bytes,
                         nes_stream_t stream);
 
+/* PerturbedAffine.forward (modules/base.py:437-444): y[i] = x[i] * scale[i % period] + shift[i % period], the
+ * (per-member) scale and shift tensors of `period` elements broadcast over the leading dimensions of x. */
+int nes_affine_fwd(const float* x, const float* scale, const float* shift, float* y, int64_t n, int64_t period,
+                   nes_stream_t stream);
+
 /* ----------------------------------------------- fp32: shared noise + member sign flips */
 
 /* SyntheticLinear.forward (modules/base.py:611-628):

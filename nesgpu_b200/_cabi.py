@@ -63,6 +63,7 @@ SIGNATURES = {
     "nes_permuted_update_out": [c_ptr] * 7 + [c_i64] + [c_int] * 4 + [c_f32, c_f32, c_ptr],
     "nes_permuted_update_scratch_bytes": [c_int] * 4,
     "nes_permuted_update": [c_ptr] * 7 + [c_i64] + [c_int] * 5 + [c_f32, c_f32, c_ptr, c_i64, c_ptr],
+    "nes_affine_fwd": [c_ptr] * 4 + [c_i64, c_i64, c_ptr],
     "nes_synthetic_linear_fwd_scratch_bytes": [c_i64] * 3,
     "nes_synthetic_linear_fwd": [c_ptr] * 8 + [c_i64] * 4 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_synthetic_linear_fwd_tc_scratch_bytes": [c_i64] * 4 + [c_int],

@@ -1093,8 +1093,8 @@ class SyntheticConv2d(nn.Conv2d, _ConvMixin, Synthetic):
 
 class PerturbedAffine(nn.Module, Perturbed):
     """Per-member scale and shift, stored "direct" (``weight_noise = weight + noise``; reference
-    ``base.py:427-444``).  The forward is the reference's broadcast multiply-add; noise set-up and the
-    update go through the same kernels as the other dense-noise layers."""
+    ``base.py:427-444``).  Forward, noise set-up and update all run in the library; the update subtracts the
+    parameter row by row as the reference does."""
 
     def __init__(self, normalized_shape, directions, antithetic=False, options={"direct": True}):
         nn.Module.__init__(self)
@@ -1105,6 +1105,18 @@ class PerturbedAffine(nn.Module, Perturbed):
         Perturbed.__init__(self, directions, antithetic=antithetic, options=options)
 
     def forward(self, input):
-        if self.perturbed_flag:
-            return input * self.weight_noise + self.bias_noise
-        return input * self.weight + self.bias
+        scale, shift = (self.weight_noise, self.bias_noise) if self.perturbed_flag else (self.weight.detach(), self.bias.detach())
+        x = C.require_cuda(input, "input", _F32)
+        # scale / shift broadcast against the trailing dimensions of the input (the reference's `input * w + b`)
+        shape = torch.broadcast_shapes(tuple(x.shape), tuple(scale.shape))
+        if shape != tuple(x.shape):
+            x = x.expand(shape).contiguous()
+        tail = shape[len(shape) - scale.dim():] if scale.dim() else ()
+        if tuple(scale.shape) != tuple(tail):
+            scale, shift = scale.expand(tail).contiguous(), shift.expand(tail).contiguous()
+        scale = C.require_cuda(scale, "scale", _F32)
+        shift = C.require_cuda(shift, "shift", _F32)
+        y = torch.empty(shape, device=x.device, dtype=_F32)
+        C.call("nes_affine_fwd", C.ptr(x), C.ptr(scale), C.ptr(shift), C.ptr(y), y.numel(), max(scale.numel(), 1),
+               C.stream())
+        return y

@@ -21,7 +21,12 @@
 // residuals): relative error of a few 1e-6.  The filter builders write W_d twice (hi and lo copies of the
 // same layout), the layout pre-pass writes x twice, and per (tile, channel chunk) the producer fetches the
 // hi run and the lo run into two consecutive pipeline slots; tiles are 128 positions wide so that two slots
-// of each kind fit next to the two filter copies.
+// of each kind fit next to the two filter copies.  With at most 64 output channels the two filter parts are
+// STACKED into one M = 128 operand (rows 0-63 = W_hi, rows 64-127 = W_lo): an M = 128 instruction takes as long as
+// an M = 64 one, so two MMAs per K step (stacked filter on x_hi, stacked filter on x_lo) yield all four
+// products hi.hi + lo.hi + hi.lo + lo.lo instead of three MMAs for three, and the epilogue adds accumulator
+// rows c and c + 64 (the warp of the upper row hands its values to the warp of the lower row through shared
+// memory, hand-over by two mbarriers per warp pair, bounded like every other wait).
 #include <cuda_bf16.h>
 #include "tc_ptx.cuh"
 
@@ -44,6 +49,7 @@ struct ConvBfParams {
   int antithetic, sign_groups, units;
   int stages, kchunks, cchunks;
   long long lo_offset;           // three-term form: element offset of the lo copy of the staged input
+  int stacked;                   // three-term form with Cout <= 64: W_hi and W_lo stacked into one M = 128 operand
   const float* weight; const float* bias; const float* bias_noise; float* y;
   int noise_kind;                // 1 dense (D,Cout,Cin,ksz), 2 permuted (out_sp,in_sp,ksz) through omap / imap
   const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
@@ -92,7 +98,10 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B] (x 2 with TERMS == 3: hi, lo)
   const int wd_chunk_bytes = p.M * 128;
   const size_t wd_copy_bytes = size_t(p.kchunks) * wd_chunk_bytes;
-  unsigned char* stages_base = wd + (TERMS == 3 ? 2 : 1) * wd_copy_bytes;
+  const bool stacked = TERMS == 3 && p.stacked != 0;
+  // byte offset from a hi filter element to its lo partner: 64 rows further down the same chunk, or a whole copy on
+  const size_t lo_off = stacked ? size_t(64) * 128 : wd_copy_bytes;
+  unsigned char* stages_base = wd + ((TERMS == 3 && !stacked) ? 2 : 1) * wd_copy_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(stages_base + size_t(p.stages) * p.stage_bytes);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;     // [2]
@@ -100,7 +109,9 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   uint64_t* wd_ready = acc_empty + 2;
   uint64_t* wd_free = wd_ready + 1;
   uint64_t* tbl_ready = wd_free + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_ready + 1);
+  uint64_t* pair_ready = tbl_ready + 1;      // [4] stacked form: upper-row warp -> lower-row warp
+  uint64_t* pair_done = pair_ready + 4;      // [4] ... and back
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_done + 4);
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
@@ -117,10 +128,21 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
     mbar_init(tbl_ready, 8);
+    for (int i = 0; i < 4; ++i) { mbar_init(&pair_ready[i], 1); mbar_init(&pair_done[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // filter rows beyond Cout (padding up to M) stay zero for the whole kernel
-  if (p.M > p.Cout) {
+  if (stacked) {
+    const int padrows = 64 - p.Cout;                     // per half: rows [Cout, 64) and [64 + Cout, 128)
+    for (int e = threadIdx.x; e < p.kchunks * 2 * padrows * 8; e += BF_THREADS) {
+      const int jc = e / (2 * padrows * 8);
+      const int r = e - jc * 2 * padrows * 8;
+      const int rr = r / 8, g16 = r & 7;
+      const int n = (rr < padrows) ? p.Cout + rr : 64 + p.Cout + (rr - padrows);
+      *reinterpret_cast<uint4*>(wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 + (g16 << 4)) = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async_smem();
+  } else if (p.M > p.Cout) {
     for (int e = threadIdx.x; e < p.kchunks * (p.M - p.Cout) * 8; e += BF_THREADS) {
       const int jc = e / ((p.M - p.Cout) * 8);
       const int r = e - jc * (p.M - p.Cout) * 8;
@@ -212,8 +234,8 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
               for (int k = 0; k < 4; ++k) {
                 mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
                 accumulate = 1u;
-                // W_lo . x_hi on the same staged run
-                if (TERMS == 3) mma_bf16_lohi(tmem_d, al + wd_copy_units + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
+                // W_lo . x_hi on the same staged run (the stacked operand already holds W_lo in its upper rows)
+                if (TERMS == 3 && !stacked) mma_bf16_lohi(tmem_d, al + wd_copy_units + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
               }
             }
             mma_commit(&empty[st]);
@@ -298,7 +320,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             const float v = fmaf(s, ev[i], wv[i]);
             const __nv_bfloat16 vh = __float2bfloat16_rn(v);
             *reinterpret_cast<__nv_bfloat16*>(dst) = vh;
-            if (TERMS == 3) *reinterpret_cast<__nv_bfloat16*>(dst + wd_copy_bytes) = __float2bfloat16_rn(v - __bfloat162float(vh));
+            if (TERMS == 3) *reinterpret_cast<__nv_bfloat16*>(dst + lo_off) = __float2bfloat16_rn(v - __bfloat162float(vh));
           }
         }
       } else {
@@ -354,7 +376,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
 #pragma unroll
               for (int z = 0; z < 8; ++z) split_bf16(f[z], h[z], l[z]);
               *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(h[0], h[1]), pack_bf16(h[2], h[3]), pack_bf16(h[4], h[5]), pack_bf16(h[6], h[7]));
-              *reinterpret_cast<uint4*>(dst + wd_copy_bytes) = make_uint4(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]), pack_bf16(l[4], l[5]), pack_bf16(l[6], l[7]));
+              *reinterpret_cast<uint4*>(dst + lo_off) = make_uint4(pack_bf16(l[0], l[1]), pack_bf16(l[2], l[3]), pack_bf16(l[4], l[5]), pack_bf16(l[6], l[7]));
             } else {
               *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
             }
@@ -370,11 +392,19 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
         // between them): a thread holds one output channel (accumulator row) and 32 consecutive positions per
         // tcgen05.ld; the warp transposes that 32-position chunk through shared memory so that each store
         // instruction writes 32 consecutive positions of ONE channel plane (full 128-byte lines).
-        const bool owns = lane_has_row && chan < p.Cout;
-        const float add = owns ? add_s[chan] : 0.f;
+        // stacked form: accumulator rows 64-127 (lane quadrants 2, 3) hold the W_lo products of channels 0-63; their
+        // warps only hand values to the warp of the same column half that owns rows 0-63 of those channels
+        const bool upper = stacked && q >= 2;
+        const int out_chan = stacked ? ((q & 1) * 32 + lane) : chan;
+        const bool owns = lane_has_row && out_chan < p.Cout;
+        const float add = (owns && !upper) ? add_s[out_chan] : 0.f;
         const int rows_per_warp = (p.M == 128) ? 32 : 16;
-        const int chan0 = (p.M == 128) ? q * 32 : q * 16;
-        float* xp = xpose + size_t(warp - 2) * rows_per_warp * 33;
+        const int chan0 = stacked ? (q & 1) * 32 : ((p.M == 128) ? q * 32 : q * 16);
+        const int pair = (q & 1) + 2 * (warp >= 6 ? 1 : 0);                       // warps (4,2) (5,3) (8,6) (9,7)
+        // stacked form: the two warps of a pair share ONE buffer (the upper-row warp's values in, the lower-row warp's
+        // sums over them for the transposed store); otherwise every warp has its own
+        float* xp = xpose + size_t(stacked ? pair : warp - 2) * rows_per_warp * 33;
+        uint32_t pc = 0;                                                           // chunks handed over so far
         const int col_lo = (warp < 6) ? 0 : NT / 2, col_hi = col_lo + NT / 2;
         for (long long r = r0; r < r1 && ok; ++r) {
           const long long b = r * p.D + d;
@@ -387,6 +417,23 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               uint32_t acc[32];
               tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(NT) + uint32_t(c0), acc);
+              if (stacked) {
+                if (upper) {
+                  // wait until the partner has consumed the previous chunk, publish this one, and move on
+                  if (pc > 0 && !mbar_wait_relaxed(&pair_done[pair], (pc - 1) & 1, 3)) { ok = false; break; }
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]);
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&pair_ready[pair]);
+                  ++pc;
+                  continue;
+                }
+                if (!mbar_wait_relaxed(&pair_ready[pair], pc & 1, 3)) { ok = false; break; }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + xp[lane * 33 + j]);
+                __syncwarp();                              // every lane has taken its row: the buffer is this warp's now
+                ++pc;
+              }
               if (lane_has_row) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]) + add;
@@ -399,6 +446,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
                 for (int rl = 0; rl < rows_per_warp && chan0 + rl < p.Cout; ++rl) dst[size_t(rl) * HoWo] = xp[rl * 33 + lane];
               }
               __syncwarp();
+              if (stacked && lane == 0) mbar_arrive(&pair_done[pair]);      // the upper-row warp may publish its next chunk
             }
             tc_fence_before();
             __syncwarp();
@@ -511,6 +559,8 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   NES_REQUIRE(p.Ho > 0 && p.Wo > 0, NES_ERR_BAD_ARG, "%s: empty output", what);
   p.Hp = H + 2 * ph; p.Wp = W + 2 * pw;
   p.M = Cout <= 64 ? 64 : 128;
+  p.stacked = (terms == 3 && Cout <= 64) ? 1 : 0;
+  if (p.stacked) p.M = 128;
   p.tiles_img = ceil_div(p.Ho * p.Wp, NT);
   const int max_shift = (kh - 1) * dh * p.Wp + (kw - 1) * dw;
   p.img_rows = (p.Hp * p.Wp + 7) & ~7;
@@ -522,10 +572,10 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   p.units = int(D * p.sign_groups);
   p.cchunks = Cin / 64;
   p.kchunks = kh * kw * p.cchunks;
-  const size_t wd_bytes = size_t(terms == 3 ? 2 : 1) * p.kchunks * p.M * 128;
+  const size_t wd_bytes = size_t((terms == 3 && !p.stacked) ? 2 : 1) * p.kchunks * p.M * 128;
   const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
-  const size_t xpose_bytes = 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
-  const size_t fixed = 1024 + wd_bytes + 64 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
+  const size_t xpose_bytes = (p.stacked ? 4 : 8) * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
+  const size_t fixed = 1024 + wd_bytes + 128 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
   const size_t limit = 227 * 1024;
   NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
               "%s: the member filter (%zu bytes) plus two input stages (%d bytes each) do not fit in shared memory on the "
@@ -534,7 +584,7 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   if (stages > 6) stages = 6;
   if (terms == 3 && stages > 4) stages = 4;
   p.stages = stages;
-  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 7) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
+  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 15) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
             8 * size_t(kh) * kw + xpose_bytes;
   const int64_t copy_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
   p.lo_offset = copy_bytes / 2;                    // bf16 elements

@@ -321,6 +321,26 @@ extern "C" int nes_sparse_perturbed_linear_fwd(const float* x, const float* weig
                        as_stream(stream), "sparse_perturbed_linear_fwd");
 }
 
+// y[i] = x[i] * scale[i % period] + shift[i % period]: per-member scale and shift broadcast over the leading
+// dimensions of x (PerturbedAffine.forward, modules/base.py:437-444)
+__global__ void affine_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ shift,
+                              float* __restrict__ y, int64_t n, int64_t period) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t j = i % period;
+  y[i] = fmaf(x[i], __ldg(scale + j), __ldg(shift + j));
+}
+
+extern "C" int nes_affine_fwd(const float* x, const float* scale, const float* shift, float* y, int64_t n, int64_t period,
+                              nes_stream_t stream) {
+  NES_REQUIRE(n >= 0 && period > 0, NES_ERR_BAD_ARG, "affine_fwd: bad extent");
+  if (n == 0) return NES_OK;
+  NES_REQUIRE(x && scale && shift && y, NES_ERR_BAD_ARG, "affine_fwd: null pointer");
+  NES_REQUIRE(ceil_div<int64_t>(n, 256) <= INT32_MAX, NES_ERR_UNSUPPORTED, "affine_fwd: too large");
+  affine_kernel<<<(unsigned)ceil_div<int64_t>(n, 256), 256, 0, as_stream(stream)>>>(x, scale, shift, y, n, period);
+  return check_launch("affine_fwd");
+}
+
 extern "C" int64_t nes_synthetic_linear_fwd_scratch_bytes(int64_t D, int64_t R, int64_t out) {
   return D * R * out * (int64_t)sizeof(float);
 }
