@@ -89,6 +89,22 @@ __device__ __forceinline__ void split_bf16(float v, float& hi, float& lo) {
   lo = v - hi;
 }
 
+// Optional timeline (build with -DNES_CONV_TRACE): block 0 writes %globaltimer (ns) into slot [tile * 16 + phase]
+// for its first 64 tiles (phases 0-1 producer, 2-6 MMA issuer, 7-8 epilogue, 9-10 filter build of the tile's member).
+#ifdef NES_CONV_TRACE
+__device__ long long g_conv_trace[64 * 16];
+__device__ __forceinline__ void conv_trace(uint32_t tile, int phase) {
+  if (blockIdx.x == 0 && tile < 64) {
+    long long tns;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tns));
+    g_conv_trace[tile * 16 + phase] = tns;
+  }
+}
+#define CONV_TRACE(cond, tile, phase) do { if (cond) conv_trace(tile, phase); } while (0)
+#else
+#define CONV_TRACE(cond, tile, phase) do { } while (0)
+#endif
+
 template <int TERMS, int NT>
 __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfloat16* __restrict__ xs, const ConvBfParams p) {
   extern __shared__ unsigned char dyn_raw[];
@@ -109,9 +125,9 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   uint64_t* wd_ready = acc_empty + 2;
   uint64_t* wd_free = wd_ready + 1;
   uint64_t* tbl_ready = wd_free + 1;
-  uint64_t* pair_ready = tbl_ready + 1;      // [4] stacked form: upper-row warp -> lower-row warp
-  uint64_t* pair_done = pair_ready + 4;      // [4] ... and back
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_done + 4);
+  uint64_t* pair_ready = tbl_ready + 1;      // [8] stacked form, per epilogue warp: the partner's values are in its buffer
+  uint64_t* pair_done = pair_ready + 8;      // [8] ... and it has finished with them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_done + 8);
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
@@ -128,7 +144,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
     mbar_init(tbl_ready, 8);
-    for (int i = 0; i < 4; ++i) { mbar_init(&pair_ready[i], 1); mbar_init(&pair_done[i], 1); }
+    for (int i = 0; i < 8; ++i) { mbar_init(&pair_ready[i], 1); mbar_init(&pair_done[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // filter rows beyond Cout (padding up to M) stay zero for the whole kernel
@@ -162,7 +178,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------------------------ producer: one bulk copy per (tile, chunk)
-      uint32_t g = 0;
+      uint32_t g = 0, tt = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
         const long long d = u / p.sign_groups;
@@ -170,11 +186,12 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
         bf_unit_range(p, u % p.sign_groups, r0, r1, s);
         for (long long r = r0; r < r1 && ok; ++r) {
           const long long b = r * p.D + d;
-          for (int ti = 0; ti < p.tiles_img && ok; ++ti)
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++tt)
             for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
               const int st = g % p.stages;
               const uint32_t phs = (g / p.stages) & 1;
               if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
+              CONV_TRACE(cc == 0, tt, 0);
               const long long row0 = (b * p.cchunks + cc) * (long long)p.img_rows + (long long)ti * NT;
               mbar_expect_tx(&full[st], uint32_t(p.load_bytes));
               bulk_load_1d(stages_base + size_t(st) * p.stage_bytes, xs + row0 * 64, uint32_t(p.load_bytes), &full[st]);
@@ -184,6 +201,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
                 const int st2 = g % p.stages;
                 const uint32_t phs2 = (g / p.stages) & 1;
                 if (!mbar_wait(&empty[st2], phs2 ^ 1, 1)) { ok = false; break; }
+                CONV_TRACE(cc == 0, tt, 1);
                 mbar_expect_tx(&full[st2], uint32_t(p.load_bytes));
                 bulk_load_1d(stages_base + size_t(st2) * p.stage_bytes, xs + p.lo_offset + row0 * 64, uint32_t(p.load_bytes), &full[st2]);
               }
@@ -192,74 +210,78 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer
-      // D = fp32, A = B = bf16, both K-major, N = 256 pixels, M = filter rows
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(p.M >> 4) << 24);
-      const uint32_t desc_hi = uint32_t(smem_desc_sw128(0) >> 32);
-      const uint32_t desc_lo0 = uint32_t(smem_desc_sw128(0));
-      for (int tap = 0; tap < ksz; ++tap) {
-        const int i = tap / p.kw, j = tap - i * p.kw;
-        tap_off[2 * tap] = uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u;                  // pixel-row shift, in 16-byte units
-        tap_off[2 * tap + 1] = uint32_t(tap * p.cchunks) * uint32_t(wd_chunk_bytes >> 4);
-      }
-      const uint32_t wd_lo = desc_lo0 + (smem_u32(wd) >> 4);
-      const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
-      const uint32_t wd_copy_units = uint32_t(wd_copy_bytes >> 4);      // from the hi filter copy to the lo copy
-      uint32_t g = 0, t = 0, ul = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        long long r0, r1; float s;
-        bf_unit_range(p, u % p.sign_groups, r0, r1, s);
-        if (r1 <= r0) continue;
-        if (!mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+    // -------------------------------------------------------------------- MMA issuer: the whole warp runs this loop in
+    // converged control flow and one elected lane issues each instruction (see warp_mma_bf16)
+    // D = fp32, A = B = bf16, both K-major, N = NT positions, M = filter rows
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(NT >> 3) << 17) | (uint32_t(p.M >> 4) << 24);
+    const uint64_t desc0 = smem_desc_sw128(0);
+    const uint64_t wd_desc = desc0 + uint64_t(smem_u32(wd) >> 4);
+    const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
+    const uint32_t tap_step = uint32_t(p.cchunks) * cc_step;            // filter chunks of one tap
+    const uint32_t wd_copy_units = uint32_t(wd_copy_bytes >> 4);        // from the hi filter copy to the lo copy
+    uint32_t g = 0, t = 0, ul = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      long long r0, r1; float s;
+      bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 <= r0) continue;
+      if (!warp_mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+      tc_fence_after();
+      const long long ntiles = (r1 - r0) * p.tiles_img;
+      for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
+        const uint32_t buf = t & 1;
+        if (!warp_mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
         tc_fence_after();
-        const long long ntiles = (r1 - r0) * p.tiles_img;
-        for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
-          const uint32_t buf = t & 1;
-          if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        CONV_TRACE(lane == 0, t, 2);
+        const uint32_t tmem_d = tmem_base + buf * uint32_t(NT);
+        for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+          const int st = g % p.stages;
+          const uint32_t phs = (g / p.stages) & 1;
+          if (!warp_mbar_wait(&full[st], phs, 2)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * uint32_t(NT);
-          for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
-            const int st = g % p.stages;
-            const uint32_t phs = (g / p.stages) & 1;
-            if (!mbar_wait(&full[st], phs, 2)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t x_lo = desc_lo0 + (smem_u32(stages_base + size_t(st) * p.stage_bytes) >> 4);
-            const uint32_t w_lo = wd_lo + uint32_t(cc) * cc_step;
-            uint32_t accumulate = (cc > 0) ? 1u : 0u;
-            for (int tap = 0; tap < ksz; ++tap) {
-              const uint32_t bl = x_lo + tap_off[2 * tap], al = w_lo + tap_off[2 * tap + 1];
+          CONV_TRACE(lane == 0 && cc == 0, t, 3);
+          const uint64_t x_desc = desc0 + uint64_t(smem_u32(stages_base + size_t(st) * p.stage_bytes) >> 4);
+          const uint64_t w_desc = wd_desc + uint64_t(uint32_t(cc) * cc_step);
+          uint32_t accumulate = (cc > 0) ? 1u : 0u;
+          for (int i = 0, tap = 0; i < p.kh; ++i)
+            for (int j = 0; j < p.kw; ++j, ++tap) {
+              // pixel-row shift of the tap in 16-byte units (8 per 128-byte row); the tap's filter chunk
+              const uint64_t bl = x_desc + uint64_t(uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u);
+              const uint64_t al = w_desc + uint64_t(uint32_t(tap) * tap_step);
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
+                warp_mma_bf16(tmem_d, al + uint64_t(2 * k), bl + uint64_t(2 * k), idesc, accumulate);
                 accumulate = 1u;
                 // W_lo . x_hi on the same staged run (the stacked operand already holds W_lo in its upper rows)
-                if (TERMS == 3 && !stacked) mma_bf16_lohi(tmem_d, al + wd_copy_units + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
+                if (TERMS == 3 && !stacked) warp_mma_bf16(tmem_d, al + uint64_t(wd_copy_units + 2 * k), bl + uint64_t(2 * k), idesc, 1u);
               }
             }
-            mma_commit(&empty[st]);
-            if (TERMS == 3) {
-              // W_hi . x_lo: the lo run sits in the next slot
-              ++g;
-              const int st2 = g % p.stages;
-              const uint32_t phs2 = (g / p.stages) & 1;
-              if (!mbar_wait(&full[st2], phs2, 2)) { ok = false; break; }
-              tc_fence_after();
-              const uint32_t x2 = desc_lo0 + (smem_u32(stages_base + size_t(st2) * p.stage_bytes) >> 4);
-              for (int tap = 0; tap < ksz; ++tap) {
-                const uint32_t bl = x2 + tap_off[2 * tap], al = w_lo + tap_off[2 * tap + 1];
+          warp_mma_commit(&empty[st]);
+          CONV_TRACE(lane == 0 && cc == 0, t, 4);
+          if (TERMS == 3) {
+            // W_hi . x_lo: the lo run sits in the next slot
+            ++g;
+            const int st2 = g % p.stages;
+            const uint32_t phs2 = (g / p.stages) & 1;
+            if (!warp_mbar_wait(&full[st2], phs2, 2)) { ok = false; break; }
+            tc_fence_after();
+            CONV_TRACE(lane == 0 && cc == 0, t, 5);
+            const uint64_t x2 = desc0 + uint64_t(smem_u32(stages_base + size_t(st2) * p.stage_bytes) >> 4);
+            for (int i = 0, tap = 0; i < p.kh; ++i)
+              for (int j = 0; j < p.kw; ++j, ++tap) {
+                const uint64_t bl = x2 + uint64_t(uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u);
+                const uint64_t al = w_desc + uint64_t(uint32_t(tap) * tap_step);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) mma_bf16_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, 1u);
+                for (int k = 0; k < 4; ++k) warp_mma_bf16(tmem_d, al + uint64_t(2 * k), bl + uint64_t(2 * k), idesc, 1u);
               }
-              mma_commit(&empty[st2]);
-            }
+            warp_mma_commit(&empty[st2]);
+            CONV_TRACE(lane == 0 && cc == 0, t, 6);
           }
-          mma_commit(&acc_full[buf]);
         }
-        mma_commit(wd_free);
-        ++ul;
+        warp_mma_commit(&acc_full[buf]);
       }
+      warp_mma_commit(wd_free);
+      ++ul;
     }
   } else {
     // ---------------------------------------------------------------------- filter builders / epilogue
@@ -271,7 +293,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     const bool lane_has_row = (p.M == 128) || (lane < 16);
     const int HoWo = p.Ho * p.Wo;
     const int k8 = K / 8, c8n = p.Cin / 8;
-    uint32_t t = 0, ul = 0;
+    uint32_t t = 0, ul = 0, pc = 0;    // tiles, members, exchanged chunks so far
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
       const long long d = u / p.sign_groups;
@@ -293,6 +315,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       if (lane == 0) mbar_arrive(tbl_ready);
       if (!mbar_wait_relaxed(tbl_ready, ul & 1, 4)) { ok = false; break; }
       if (!mbar_wait_relaxed(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
+      CONV_TRACE(threadIdx.x == 128, t, 9);
 
       if (p.noise_kind == 1) {
         // dense member noise in its native (n, c, tap) order: coalesced reads, scattered 2-byte writes
@@ -386,25 +409,87 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(wd_ready);
+      CONV_TRACE(threadIdx.x == 128, t, 10);
 
-      {
+      if (stacked) {
+        // Epilogue, stacked form.  Accumulator rows 0-63 (lane quadrants 0, 1) hold the W_hi products of channels 0-63
+        // and rows 64-127 (quadrants 2, 3) the W_lo products of the same channels; a warp can only read its own
+        // quadrant, so the warp of quadrant q and the warp of quadrant q + 2 that share a column half exchange values
+        // through shared memory.  Of the half's four 16-column chunks the lower-row warp finishes chunks 0, 1 and the
+        // upper-row warp chunks 2, 3: each writes the chunks it does not finish into the partner's buffer, adds what
+        // the partner wrote into its own, transposes there and stores 16 consecutive positions of two channel planes
+        // per instruction.
+        const bool upper = q >= 2;
+        const int chan0 = (q & 1) * 32;
+        const bool owns = chan0 + lane < p.Cout;
+        const float add = owns ? add_s[chan0 + lane] : 0.f;
+        const int mine = warp - 2, theirs = upper ? mine + 2 : mine - 2;
+        float* my_buf = xpose + size_t(mine) * 32 * 17;
+        float* their_buf = xpose + size_t(theirs) * 32 * 17;
+        const int col_lo = (warp < 6) ? 0 : NT / 2;
+        const int pos = lane & 15, rsel = lane >> 4;
+        for (long long r = r0; r < r1 && ok; ++r) {
+          const long long b = r * p.D + d;
+          float* img = p.y + size_t(b) * p.Cout * HoWo;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++t) {
+            const uint32_t buf = t & 1;
+            if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
+            tc_fence_after();
+            CONV_TRACE(threadIdx.x == 128, t, 7);
+            const bool live = (timeouts_so_far() == timeouts_at_start);
+            const uint32_t tcol = tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(NT) + uint32_t(col_lo);
+#pragma unroll 1
+            for (int rnd = 0; rnd < NT / 64; ++rnd) {
+              const int give_c = ((upper ? 0 : NT / 64) + rnd) * 16, take_c = ((upper ? NT / 64 : 0) + rnd) * 16;
+              uint32_t gv[16], tv[16];
+              tmem_ld16_nowait(tcol + uint32_t(give_c), gv);
+              tmem_ld16_nowait(tcol + uint32_t(take_c), tv);
+              tmem_ld_wait();
+              // hand over: the partner must have finished with what it got last time
+              if (pc > 0 && !mbar_wait(&pair_done[theirs], (pc - 1) & 1, 3)) { ok = false; break; }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) their_buf[lane * 17 + j] = __uint_as_float(gv[j]);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&pair_ready[theirs]);
+              // finish: own rows + the partner's + bias terms, transposed through the same buffer
+              if (!mbar_wait(&pair_ready[mine], pc & 1, 3)) { ok = false; break; }
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(tv[j]) + my_buf[lane * 17 + j] + add;
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) my_buf[lane * 17 + j] = v[j];
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = my_buf[(2 * i + rsel) * 17 + pos];
+              const int qpos = ti * NT + col_lo + take_c + pos;
+              const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
+              if (live && oy < p.Ho && ox < p.Wo) {
+                float* dst = img + size_t(chan0 + rsel) * HoWo + oy * p.Wo + ox;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (chan0 + 2 * i + rsel < p.Cout) dst[size_t(2 * i) * HoWo] = v[i];
+              }
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&pair_done[mine]);
+              ++pc;
+            }
+            tc_fence_before();
+            __syncwarp();
+            CONV_TRACE(threadIdx.x == 128, t, 8);
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+        }
+      } else {
         // Epilogue (all eight builder warps; two warps share a TMEM lane quadrant and split the tile's columns
         // between them): a thread holds one output channel (accumulator row) and 32 consecutive positions per
         // tcgen05.ld; the warp transposes that 32-position chunk through shared memory so that each store
         // instruction writes 32 consecutive positions of ONE channel plane (full 128-byte lines).
-        // stacked form: accumulator rows 64-127 (lane quadrants 2, 3) hold the W_lo products of channels 0-63; their
-        // warps only hand values to the warp of the same column half that owns rows 0-63 of those channels
-        const bool upper = stacked && q >= 2;
-        const int out_chan = stacked ? ((q & 1) * 32 + lane) : chan;
-        const bool owns = lane_has_row && out_chan < p.Cout;
-        const float add = (owns && !upper) ? add_s[out_chan] : 0.f;
+        const bool owns = lane_has_row && chan < p.Cout;
+        const float add = owns ? add_s[chan] : 0.f;
         const int rows_per_warp = (p.M == 128) ? 32 : 16;
-        const int chan0 = stacked ? (q & 1) * 32 : ((p.M == 128) ? q * 32 : q * 16);
-        const int pair = (q & 1) + 2 * (warp >= 6 ? 1 : 0);                       // warps (4,2) (5,3) (8,6) (9,7)
-        // stacked form: the two warps of a pair share ONE buffer (the upper-row warp's values in, the lower-row warp's
-        // sums over them for the transposed store); otherwise every warp has its own
-        float* xp = xpose + size_t(stacked ? pair : warp - 2) * rows_per_warp * 33;
-        uint32_t pc = 0;                                                           // chunks handed over so far
+        const int chan0 = (p.M == 128) ? q * 32 : q * 16;
+        float* xp = xpose + size_t(warp - 2) * rows_per_warp * 33;
         const int col_lo = (warp < 6) ? 0 : NT / 2, col_hi = col_lo + NT / 2;
         for (long long r = r0; r < r1 && ok; ++r) {
           const long long b = r * p.D + d;
@@ -417,23 +502,6 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
             for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
               uint32_t acc[32];
               tmem_ld32(tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(NT) + uint32_t(c0), acc);
-              if (stacked) {
-                if (upper) {
-                  // wait until the partner has consumed the previous chunk, publish this one, and move on
-                  if (pc > 0 && !mbar_wait_relaxed(&pair_done[pair], (pc - 1) & 1, 3)) { ok = false; break; }
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]);
-                  __syncwarp();
-                  if (lane == 0) mbar_arrive(&pair_ready[pair]);
-                  ++pc;
-                  continue;
-                }
-                if (!mbar_wait_relaxed(&pair_ready[pair], pc & 1, 3)) { ok = false; break; }
-#pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = __float_as_uint(__uint_as_float(acc[j]) + xp[lane * 33 + j]);
-                __syncwarp();                              // every lane has taken its row: the buffer is this warp's now
-                ++pc;
-              }
               if (lane_has_row) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) xp[lane * 33 + j] = __uint_as_float(acc[j]) + add;
@@ -446,7 +514,6 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
                 for (int rl = 0; rl < rows_per_warp && chan0 + rl < p.Cout; ++rl) dst[size_t(rl) * HoWo] = xp[rl * 33 + lane];
               }
               __syncwarp();
-              if (stacked && lane == 0) mbar_arrive(&pair_done[pair]);      // the upper-row warp may publish its next chunk
             }
             tc_fence_before();
             __syncwarp();
@@ -574,8 +641,8 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   p.kchunks = kh * kw * p.cchunks;
   const size_t wd_bytes = size_t((terms == 3 && !p.stacked) ? 2 : 1) * p.kchunks * p.M * 128;
   const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
-  const size_t xpose_bytes = (p.stacked ? 4 : 8) * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
-  const size_t fixed = 1024 + wd_bytes + 128 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
+  const size_t xpose_bytes = p.stacked ? 8 * size_t(32) * 17 * sizeof(float) : 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
+  const size_t fixed = 1024 + wd_bytes + 192 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
   const size_t limit = 227 * 1024;
   NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
               "%s: the member filter (%zu bytes) plus two input stages (%d bytes each) do not fit in shared memory on the "
@@ -584,7 +651,7 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   if (stages > 6) stages = 6;
   if (terms == 3 && stages > 4) stages = 4;
   p.stages = stages;
-  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 15) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
+  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 23) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
             8 * size_t(kh) * kw + xpose_bytes;
   const int64_t copy_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
   p.lo_offset = copy_bytes / 2;                    // bf16 elements
@@ -624,6 +691,13 @@ static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStr
 
 }  // namespace tc
 }  // namespace nes
+
+#ifdef NES_CONV_TRACE
+// instrumented builds only: copies the 64 x 16 timeline slots of block 0 to host memory
+extern "C" int nes_debug_conv_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, nes::tc::g_conv_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 using namespace nes;
 using namespace nes::tc;

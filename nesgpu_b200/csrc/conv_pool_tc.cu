@@ -67,7 +67,6 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(c0), "r"(c1) : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // TW / THP / TWP: input width and pooled output size known at compile time (0 = taken from the parameters).
 // With them the W-channel warps read their whole accumulator row into registers with four wide loads
@@ -138,39 +137,37 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer
-      constexpr uint32_t idesc = BF16 ? idesc_bf16(CP_M, CP_N) : idesc_tf32(CP_M, CP_N);
-      bool ok = mbar_wait(filt_full, 0, 2);
-      const uint32_t filt_addr = smem_u32(filt);
-      int i = 0;
-      for (int64_t b = blockIdx.x; b < p.B && ok; b += gridDim.x, ++i) {
-        const int s = i % stages, a2 = i & 1;
-        ok = mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && mbar_wait(&full[s], (i / stages) & 1, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
-        const uint32_t acc = tmem_base + uint32_t(a2 * CP_N);
-        for (int t = 0; t < taps; ++t) {
-          const int ti = t / p.kw, tj = t - ti * p.kw;
+    // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
+    constexpr uint32_t idesc = BF16 ? idesc_bf16(CP_M, CP_N) : idesc_tf32(CP_M, CP_N);
+    bool ok = warp_mbar_wait(filt_full, 0, 2);
+    const uint32_t filt_addr = smem_u32(filt);
+    int i = 0;
+    for (int64_t b = blockIdx.x; b < p.B && ok; b += gridDim.x, ++i) {
+      const int s = i % stages, a2 = i & 1;
+      ok = warp_mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && warp_mbar_wait(&full[s], (i / stages) & 1, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
+      const uint32_t acc = tmem_base + uint32_t(a2 * CP_N);
+      for (int ti = 0, t = 0; ti < p.kh; ++ti)
+        for (int tj = 0; tj < p.kw; ++tj, ++t) {
           const uint32_t a_addr = filt_addr + uint32_t(t) * TAP_BYTES;
           const uint32_t b_addr = st + uint32_t(ti * p.W + tj) * ROW_BYTES;
           const uint64_t a = BF16 ? smem_desc_sw64(a_addr) : smem_desc_sw128(a_addr);
           const uint64_t bd = BF16 ? smem_desc_sw64(b_addr) : smem_desc_sw128(b_addr);
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
-            if (BF16) mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
-            else mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+            if (BF16) warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+            else warp_mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
             if (TERMS == 3) {
               // lo filter on the hi image, hi filter on the lo image (descriptor units are 16 bytes)
-              mma_bf16(acc, a + uint64_t(filt_copy >> 4) + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, 1u);
-              mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(half_bytes >> 4) + uint64_t(2 * k), idesc, 1u);
+              warp_mma_bf16(acc, a + uint64_t(filt_copy >> 4) + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, 1u);
+              warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(half_bytes >> 4) + uint64_t(2 * k), idesc, 1u);
             }
           }
         }
-        mma_commit(&empty[s]);
-        mma_commit(&acc_full[a2]);
-      }
+      warp_mma_commit(&empty[s]);
+      warp_mma_commit(&acc_full[a2]);
     }
   } else if (warp != 6 && warp != 7) {
     // Each W-channel quadrant is served by two warps (4 and 8 for lanes 0-31, 5 and 9 for lanes 32-63) that
@@ -301,16 +298,6 @@ constexpr int PAIR_N = 256;
 constexpr int PAIR_W = 13, PAIR_HP = 5, PAIR_WP = 5;
 constexpr int PAIR_STAGE_ROWS = 320;                 // 2 x 160 rows of 64 bytes
 
-__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                         const __grid_constant__ CUtensorMap map_f,
                                                                         const ConvPoolParams p) {
@@ -378,29 +365,28 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_bf16(CP_M, PAIR_N);
-      bool ok = mbar_wait(filt_full, 0, 2);
-      const uint32_t filt_addr = smem_u32(filt);
-      int i = 0;
-      for (int64_t pr = blockIdx.x; pr < pairs && ok; pr += gridDim.x, ++i) {
-        const int s = i % stages, a2 = i & 1;
-        ok = mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && mbar_wait(&full[s], (i / stages) & 1, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t st = smem_u32(stage0 + size_t(s) * STAGE_BYTES);
-        const uint32_t acc = tmem_base + uint32_t(a2 * PAIR_N);
-        for (int t = 0; t < taps; ++t) {
-          const int ti = t / p.kw, tj = t - ti * p.kw;
+    // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
+    constexpr uint32_t idesc = idesc_bf16(CP_M, PAIR_N);
+    bool ok = warp_mbar_wait(filt_full, 0, 2);
+    const uint32_t filt_addr = smem_u32(filt);
+    int i = 0;
+    for (int64_t pr = blockIdx.x; pr < pairs && ok; pr += gridDim.x, ++i) {
+      const int s = i % stages, a2 = i & 1;
+      ok = warp_mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && warp_mbar_wait(&full[s], (i / stages) & 1, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_u32(stage0 + size_t(s) * STAGE_BYTES);
+      const uint32_t acc = tmem_base + uint32_t(a2 * PAIR_N);
+      for (int ti = 0, t = 0; ti < p.kh; ++ti)
+        for (int tj = 0; tj < p.kw; ++tj, ++t) {
           const uint64_t a = smem_desc_sw64(filt_addr + uint32_t(t) * TAP_BYTES);
           const uint64_t bd = smem_desc_sw64(st + uint32_t(2 * (ti * PAIR_W + tj)) * 64u);
 #pragma unroll
           for (int k = 0; k < 2; ++k)
-            mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+            warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
         }
-        mma_commit(&empty[s]);
-        mma_commit(&acc_full[a2]);
-      }
+      warp_mma_commit(&empty[s]);
+      warp_mma_commit(&acc_full[a2]);
     }
   } else {
     const int q = warp & 3;

@@ -118,59 +118,53 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float*
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(p.Cout >> 3) << 17) | (uint32_t(128 >> 4) << 24);
-      // Descriptor arithmetic is hoisted out of the issue loop (a single thread issues every MMA, so each
-      // instruction saved there is on the critical path): per tap the A operand starts (shift * 128) bytes
-      // into the staged box and the B operand is filter chunk (tap, cc); both are offsets in 16-byte units
-      // on the low descriptor word.
-      const uint32_t desc_hi = uint32_t(smem_desc_sw128(0) >> 32);
-      const uint32_t desc_lo0 = uint32_t(smem_desc_sw128(0));
-      for (int tap = 0; tap < ksz; ++tap) {
-        const int i = tap / p.kw, j = tap - i * p.kw;
-        tap_off[2 * tap] = uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u;
-        tap_off[2 * tap + 1] = uint32_t(tap * p.cchunks) * uint32_t(wd_chunk_bytes >> 4);
-      }
-      const uint32_t wd_lo = desc_lo0 + (smem_u32(wd) >> 4);
-      const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
-      uint32_t g = 0, t = 0, ul = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        long long r0, r1; float s;
-        unit_range(p, u % p.sign_groups, r0, r1, s);
-        if (r1 <= r0) continue;
-        if (!mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+    // -------------------------------------------------------------------- MMA issuer: the whole warp runs this loop in
+    // converged control flow and one elected lane issues each instruction (see warp_mma_tf32)
+    // D = fp32, A = B = tf32, both K-major, M = 128 positions, N = output channels
+    const uint32_t idesc = idesc_tf32(128, p.Cout);
+    const uint64_t desc0 = smem_desc_sw128(0);
+    const uint64_t wd_desc = desc0 + uint64_t(smem_u32(wd) >> 4);
+    const uint32_t cc_step = uint32_t(wd_chunk_bytes >> 4);
+    const uint32_t tap_step = uint32_t(p.cchunks) * cc_step;            // filter chunks of one tap
+    uint32_t g = 0, t = 0, ul = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      long long r0, r1; float s;
+      unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 <= r0) continue;
+      if (!warp_mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+      tc_fence_after();
+      const long long ntiles = (r1 - r0) * p.tiles_img;
+      for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
+        const uint32_t buf = t & 1;
+        if (!warp_mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
         tc_fence_after();
-        const long long ntiles = (r1 - r0) * p.tiles_img;
-        for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
-          const uint32_t buf = t & 1;
-          if (!mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        const uint32_t tmem_d = tmem_base + buf * uint32_t(p.Cout);
+        for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
+          const int st = g % p.stages;
+          const uint32_t phs = (g / p.stages) & 1;
+          if (!warp_mbar_wait(&full[st], phs, 2)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * uint32_t(p.Cout);
-          for (int cc = 0; cc < p.cchunks; ++cc, ++g) {
-            const int st = g % p.stages;
-            const uint32_t phs = (g / p.stages) & 1;
-            if (!mbar_wait(&full[st], phs, 2)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t a_lo = desc_lo0 + (smem_u32(atiles + size_t(st) * p.stage_bytes) >> 4);
-            const uint32_t b_lo = wd_lo + uint32_t(cc) * cc_step;
-            uint32_t accumulate = (cc > 0) ? 1u : 0u;
-            for (int tap = 0; tap < ksz; ++tap) {
-              const uint32_t al = a_lo + tap_off[2 * tap], bl = b_lo + tap_off[2 * tap + 1];
+          const uint64_t x_desc = desc0 + uint64_t(smem_u32(atiles + size_t(st) * p.stage_bytes) >> 4);
+          const uint64_t w_desc = wd_desc + uint64_t(uint32_t(cc) * cc_step);
+          uint32_t accumulate = (cc > 0) ? 1u : 0u;
+          for (int i = 0, tap = 0; i < p.kh; ++i)
+            for (int j = 0; j < p.kw; ++j, ++tap) {
+              // pixel-row shift of the tap in 16-byte units (8 per 128-byte row); the tap's filter chunk
+              const uint64_t al = x_desc + uint64_t(uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u);
+              const uint64_t bl = w_desc + uint64_t(uint32_t(tap) * tap_step);
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                mma_tf32_lohi(tmem_d, al + 2 * k, bl + 2 * k, desc_hi, idesc, accumulate);
+                warp_mma_tf32(tmem_d, al + uint64_t(2 * k), bl + uint64_t(2 * k), idesc, accumulate);
                 accumulate = 1u;
               }
             }
-            mma_commit(&empty[st]);
-          }
-          mma_commit(&acc_full[buf]);
+          warp_mma_commit(&empty[st]);
         }
-        mma_commit(wd_free);
-        ++ul;
+        warp_mma_commit(&acc_full[buf]);
       }
+      warp_mma_commit(wd_free);
+      ++ul;
     }
   } else {
     // ---------------------------------------------------------------------- filter builders / epilogue

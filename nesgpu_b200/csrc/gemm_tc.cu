@@ -84,36 +84,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer
-      constexpr uint32_t idesc = BF16 ? idesc_bf16(BM, BN) : idesc_tf32(BM, BN);
-      bool ok = true;
-      for (int kt = 0; kt < nk && ok; ++kt) {
-        const int s = kt % stages;
-        const uint32_t ph = (kt / stages) & 1;
-        ok = mbar_wait(&full[s], ph, 2);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t st = smem_u32(tiles + size_t(s) * STAGE_BYTES);
-        const uint64_t a_hi = smem_desc_sw128(st), b_hi = smem_desc_sw128(st + TILE_BYTES);
+    // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
+    constexpr uint32_t idesc = BF16 ? idesc_bf16(BM, BN) : idesc_tf32(BM, BN);
+    bool ok = true;
+    for (int kt = 0; kt < nk && ok; ++kt) {
+      const int s = kt % stages;
+      const uint32_t ph = (kt / stages) & 1;
+      ok = warp_mbar_wait(&full[s], ph, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_u32(tiles + size_t(s) * STAGE_BYTES);
+      const uint64_t a_hi = smem_desc_sw128(st), b_hi = smem_desc_sw128(st + TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < BKE / 8; ++k) {            // advance 32 bytes (2 descriptor units) per K = 8
-          const uint64_t adv = uint64_t(k * 2);
-          if (TERMS == 3) {
-            const uint64_t a_lo = smem_desc_sw128(st + 2 * TILE_BYTES), b_lo = smem_desc_sw128(st + 3 * TILE_BYTES);
-            mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-            mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-            mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
-          } else if (BF16) {
-            mma_bf16(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          } else {
-            mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          }
+      for (int k = 0; k < BKE / 8; ++k) {            // advance 32 bytes (2 descriptor units) per K = 8
+        const uint64_t adv = uint64_t(k * 2);
+        if (TERMS == 3) {
+          const uint64_t a_lo = smem_desc_sw128(st + 2 * TILE_BYTES), b_lo = smem_desc_sw128(st + 3 * TILE_BYTES);
+          warp_mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          warp_mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+          warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+        } else if (BF16) {
+          warp_mma_bf16(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        } else {
+          warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
         }
-        mma_commit(&empty[s]);            // frees the stage once these MMAs have read it
       }
-      mma_commit(accum);                  // accumulator complete (or abandoned: epilogue checks the error word)
+      warp_mma_commit(&empty[s]);            // frees the stage once these MMAs have read it
     }
+    warp_mma_commit(accum);                  // accumulator complete (or abandoned: epilogue checks the error word)
   } else {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
     const int q = warp & 3;

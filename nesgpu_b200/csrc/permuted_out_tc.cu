@@ -32,7 +32,7 @@
 // by mbarriers: full (TMA bytes landed) -> split (hi/lo written, made visible to the async proxy) ->
 // tcgen05.commit -> empty.  Every mbarrier wait is bounded; a wait that runs out records a code (see
 // tc_ptx.cuh), the role stops issuing work and all threads still reach the two cluster barriers and the
-// common exit where tensor memory is freed.  No multicast loads.
+// common exit where tensor memory is freed.  Every TMA load targets one block only.
 #include <cuda.h>
 #include "tc_ptx.cuh"
 
@@ -58,17 +58,6 @@ struct PermOutParams {
   int vec_y, vec_pout, vec_beta, vec_bias;
   int local_gather;                         // 1: slices are pushed to the peers and the gather is local
 };
-
-__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -203,40 +192,38 @@ __global__ void __launch_bounds__(PO_THREADS, 1) permuted_linear_out_kernel(cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer
-      const uint32_t idesc = idesc_tf32(PO_BM, NC);
-      bool ok = true;
-      for (int kt = 0; kt < nk && ok; ++kt) {
-        const int s = kt % p.stages;
-        const uint32_t ph = (kt / p.stages) & 1;
-        ok = mbar_wait(&split[s], ph, 2);
-        if (!ok) break;
-        PO_TRACE(kt == 0, 5);
-        tc_fence_after();
-        const uint32_t st = smem_u32(tiles + size_t(s) * stage_bytes);
-        const uint64_t a_hi = smem_desc_sw128(st);
-        const uint64_t a_lo = smem_desc_sw128(st + PO_A_BYTES);
-        const uint32_t bt = st + (TERMS == 3 ? 2 : 1) * PO_A_BYTES;
-        const uint64_t b_hi = smem_desc_sw128(bt);
-        const uint64_t b_lo = smem_desc_sw128(bt + b_bytes);
+    // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
+    const uint32_t idesc = idesc_tf32(PO_BM, NC);
+    bool ok = true;
+    for (int kt = 0; kt < nk && ok; ++kt) {
+      const int s = kt % p.stages;
+      const uint32_t ph = (kt / p.stages) & 1;
+      ok = warp_mbar_wait(&split[s], ph, 2);
+      if (!ok) break;
+      PO_TRACE(lane == 0 && kt == 0, 5);
+      tc_fence_after();
+      const uint32_t st = smem_u32(tiles + size_t(s) * stage_bytes);
+      const uint64_t a_hi = smem_desc_sw128(st);
+      const uint64_t a_lo = smem_desc_sw128(st + PO_A_BYTES);
+      const uint32_t bt = st + (TERMS == 3 ? 2 : 1) * PO_A_BYTES;
+      const uint64_t b_hi = smem_desc_sw128(bt);
+      const uint64_t b_lo = smem_desc_sw128(bt + b_bytes);
 #pragma unroll
-        for (int k = 0; k < PO_BK / 8; ++k) {                   // 32 bytes (2 descriptor units) per K = 8
-          const uint64_t adv = uint64_t(k * 2);
-          const uint32_t first = (kt > 0 || k > 0) ? 1u : 0u;
-          if (TERMS == 3) {
-            mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, first);
-            mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-            mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
-          } else {
-            mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, first);
-          }
+      for (int k = 0; k < PO_BK / 8; ++k) {                   // 32 bytes (2 descriptor units) per K = 8
+        const uint64_t adv = uint64_t(k * 2);
+        const uint32_t first = (kt > 0 || k > 0) ? 1u : 0u;
+        if (TERMS == 3) {
+          warp_mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, first);
+          warp_mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+          warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+        } else {
+          warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, first);
         }
-        mma_commit(&empty[s]);
       }
-      mma_commit(accum);
-      PO_TRACE(true, 6);
+      warp_mma_commit(&empty[s]);
     }
+    warp_mma_commit(accum);
+    PO_TRACE(lane == 0, 6);
   } else {
     // ---- operand splitters, then the first half of the epilogue
     const int t = threadIdx.x - 64;                             // 0 .. PO_WORKERS-1
