@@ -21,12 +21,8 @@
 // residuals): relative error of a few 1e-6.  The filter builders write W_d twice (hi and lo copies of the
 // same layout), the layout pre-pass writes x twice, and per (tile, channel chunk) the producer fetches the
 // hi run and the lo run into two consecutive pipeline slots; tiles are 128 positions wide so that two slots
-// of each kind fit next to the two filter copies.  With at most 64 output channels the two filter parts are
-// STACKED into one M = 128 operand (rows 0-63 = W_hi, rows 64-127 = W_lo): an M = 128 instruction takes as long as
-// an M = 64 one, so two MMAs per K step (stacked filter on x_hi, stacked filter on x_lo) yield all four
-// products hi.hi + lo.hi + hi.lo + lo.lo instead of three MMAs for three, and the epilogue adds accumulator
-// rows c and c + 64 (the warp of the upper row hands its values to the warp of the lower row through shared
-// memory, hand-over by two mbarriers per warp pair, bounded like every other wait).
+// of each kind fit next to the two filter copies.  Permuted-noise layers with 64 input channels and at most 64 output
+// channels take the tensor-memory form of this product instead (conv_split_tmem_kernel below).
 #include <cuda_bf16.h>
 #include "tc_ptx.cuh"
 
@@ -49,7 +45,8 @@ struct ConvBfParams {
   int antithetic, sign_groups, units;
   int stages, kchunks, cchunks;
   long long lo_offset;           // three-term form: element offset of the lo copy of the staged input
-  int stacked;                   // three-term form with Cout <= 64: W_hi and W_lo stacked into one M = 128 operand
+  int tmem_filter;               // three-term form with the stacked [W_hi; W_lo] filter in tensor memory (conv_split_tmem_kernel)
+  int eps_rows, e_pitch;         // that form: rows of the shared noise kept in shared memory and their pitch in bytes
   const float* weight; const float* bias; const float* bias_noise; float* y;
   int noise_kind;                // 1 dense (D,Cout,Cin,ksz), 2 permuted (out_sp,in_sp,ksz) through omap / imap
   const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
@@ -114,10 +111,8 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   unsigned char* wd = dyn_raw + pad;                                   // [kchunks][M][128 B] (x 2 with TERMS == 3: hi, lo)
   const int wd_chunk_bytes = p.M * 128;
   const size_t wd_copy_bytes = size_t(p.kchunks) * wd_chunk_bytes;
-  const bool stacked = TERMS == 3 && p.stacked != 0;
-  // byte offset from a hi filter element to its lo partner: 64 rows further down the same chunk, or a whole copy on
-  const size_t lo_off = stacked ? size_t(64) * 128 : wd_copy_bytes;
-  unsigned char* stages_base = wd + ((TERMS == 3 && !stacked) ? 2 : 1) * wd_copy_bytes;
+  const size_t lo_off = wd_copy_bytes;                                 // from a hi filter element to its lo partner
+  unsigned char* stages_base = wd + (TERMS == 3 ? 2 : 1) * wd_copy_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(stages_base + size_t(p.stages) * p.stage_bytes);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_full = empty + p.stages;     // [2]
@@ -125,9 +120,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   uint64_t* wd_ready = acc_empty + 2;
   uint64_t* wd_free = wd_ready + 1;
   uint64_t* tbl_ready = wd_free + 1;
-  uint64_t* pair_ready = tbl_ready + 1;      // [8] stacked form, per epilogue warp: the partner's values are in its buffer
-  uint64_t* pair_done = pair_ready + 8;      // [8] ... and it has finished with them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_done + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_ready + 1);
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
@@ -144,21 +137,10 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
     mbar_init(tbl_ready, 8);
-    for (int i = 0; i < 8; ++i) { mbar_init(&pair_ready[i], 1); mbar_init(&pair_done[i], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // filter rows beyond Cout (padding up to M) stay zero for the whole kernel
-  if (stacked) {
-    const int padrows = 64 - p.Cout;                     // per half: rows [Cout, 64) and [64 + Cout, 128)
-    for (int e = threadIdx.x; e < p.kchunks * 2 * padrows * 8; e += BF_THREADS) {
-      const int jc = e / (2 * padrows * 8);
-      const int r = e - jc * 2 * padrows * 8;
-      const int rr = r / 8, g16 = r & 7;
-      const int n = (rr < padrows) ? p.Cout + rr : 64 + p.Cout + (rr - padrows);
-      *reinterpret_cast<uint4*>(wd + size_t(jc) * wd_chunk_bytes + (n >> 3) * 1024 + (n & 7) * 128 + (g16 << 4)) = make_uint4(0, 0, 0, 0);
-    }
-    fence_proxy_async_smem();
-  } else if (p.M > p.Cout) {
+  if (p.M > p.Cout) {
     for (int e = threadIdx.x; e < p.kchunks * (p.M - p.Cout) * 8; e += BF_THREADS) {
       const int jc = e / ((p.M - p.Cout) * 8);
       const int r = e - jc * (p.M - p.Cout) * 8;
@@ -252,8 +234,8 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
               for (int k = 0; k < 4; ++k) {
                 warp_mma_bf16(tmem_d, al + uint64_t(2 * k), bl + uint64_t(2 * k), idesc, accumulate);
                 accumulate = 1u;
-                // W_lo . x_hi on the same staged run (the stacked operand already holds W_lo in its upper rows)
-                if (TERMS == 3 && !stacked) warp_mma_bf16(tmem_d, al + uint64_t(wd_copy_units + 2 * k), bl + uint64_t(2 * k), idesc, 1u);
+                // W_lo . x_hi on the same staged run
+                if (TERMS == 3) warp_mma_bf16(tmem_d, al + uint64_t(wd_copy_units + 2 * k), bl + uint64_t(2 * k), idesc, 1u);
               }
             }
           warp_mma_commit(&empty[st]);
@@ -293,7 +275,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     const bool lane_has_row = (p.M == 128) || (lane < 16);
     const int HoWo = p.Ho * p.Wo;
     const int k8 = K / 8, c8n = p.Cin / 8;
-    uint32_t t = 0, ul = 0, pc = 0;    // tiles, members, exchanged chunks so far
+    uint32_t t = 0, ul = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
       const long long d = u / p.sign_groups;
@@ -411,76 +393,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       if (lane == 0) mbar_arrive(wd_ready);
       CONV_TRACE(threadIdx.x == 128, t, 10);
 
-      if (stacked) {
-        // Epilogue, stacked form.  Accumulator rows 0-63 (lane quadrants 0, 1) hold the W_hi products of channels 0-63
-        // and rows 64-127 (quadrants 2, 3) the W_lo products of the same channels; a warp can only read its own
-        // quadrant, so the warp of quadrant q and the warp of quadrant q + 2 that share a column half exchange values
-        // through shared memory.  Of the half's four 16-column chunks the lower-row warp finishes chunks 0, 1 and the
-        // upper-row warp chunks 2, 3: each writes the chunks it does not finish into the partner's buffer, adds what
-        // the partner wrote into its own, transposes there and stores 16 consecutive positions of two channel planes
-        // per instruction.
-        const bool upper = q >= 2;
-        const int chan0 = (q & 1) * 32;
-        const bool owns = chan0 + lane < p.Cout;
-        const float add = owns ? add_s[chan0 + lane] : 0.f;
-        const int mine = warp - 2, theirs = upper ? mine + 2 : mine - 2;
-        float* my_buf = xpose + size_t(mine) * 32 * 17;
-        float* their_buf = xpose + size_t(theirs) * 32 * 17;
-        const int col_lo = (warp < 6) ? 0 : NT / 2;
-        const int pos = lane & 15, rsel = lane >> 4;
-        for (long long r = r0; r < r1 && ok; ++r) {
-          const long long b = r * p.D + d;
-          float* img = p.y + size_t(b) * p.Cout * HoWo;
-          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++t) {
-            const uint32_t buf = t & 1;
-            if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
-            tc_fence_after();
-            CONV_TRACE(threadIdx.x == 128, t, 7);
-            const bool live = (timeouts_so_far() == timeouts_at_start);
-            const uint32_t tcol = tmem_base + (uint32_t(q * 32) << 16) + buf * uint32_t(NT) + uint32_t(col_lo);
-#pragma unroll 1
-            for (int rnd = 0; rnd < NT / 64; ++rnd) {
-              const int give_c = ((upper ? 0 : NT / 64) + rnd) * 16, take_c = ((upper ? NT / 64 : 0) + rnd) * 16;
-              uint32_t gv[16], tv[16];
-              tmem_ld16_nowait(tcol + uint32_t(give_c), gv);
-              tmem_ld16_nowait(tcol + uint32_t(take_c), tv);
-              tmem_ld_wait();
-              // hand over: the partner must have finished with what it got last time
-              if (pc > 0 && !mbar_wait(&pair_done[theirs], (pc - 1) & 1, 3)) { ok = false; break; }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) their_buf[lane * 17 + j] = __uint_as_float(gv[j]);
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&pair_ready[theirs]);
-              // finish: own rows + the partner's + bias terms, transposed through the same buffer
-              if (!mbar_wait(&pair_ready[mine], pc & 1, 3)) { ok = false; break; }
-              float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(tv[j]) + my_buf[lane * 17 + j] + add;
-              __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 16; ++j) my_buf[lane * 17 + j] = v[j];
-              __syncwarp();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = my_buf[(2 * i + rsel) * 17 + pos];
-              const int qpos = ti * NT + col_lo + take_c + pos;
-              const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
-              if (live && oy < p.Ho && ox < p.Wo) {
-                float* dst = img + size_t(chan0 + rsel) * HoWo + oy * p.Wo + ox;
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  if (chan0 + 2 * i + rsel < p.Cout) dst[size_t(2 * i) * HoWo] = v[i];
-              }
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&pair_done[mine]);
-              ++pc;
-            }
-            tc_fence_before();
-            __syncwarp();
-            CONV_TRACE(threadIdx.x == 128, t, 8);
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          }
-        }
-      } else {
+      {
         // Epilogue (all eight builder warps; two warps share a TMEM lane quadrant and split the tile's columns
         // between them): a thread holds one output channel (accumulator row) and 32 consecutive positions per
         // tcgen05.ld; the warp transposes that 32-position chunk through shared memory so that each store
@@ -529,6 +442,359 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, uint32_t(2 * NT));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Split-bf16 convolution with the member filter in TENSOR MEMORY (permuted-noise layers, Cin = 64, at most 64 output
+// channels, at most 9 taps).  The two bf16 parts of the filter are stacked into one M = 128 operand (rows 0-63 = W_hi,
+// rows 64-127 = W_lo of the same channels), so two MMAs per K step (on x_hi and on x_lo) give all four partial
+// products, and that operand lives in tensor memory: lane = filter row, 8 columns (16 bf16) per K step, 36 K steps =
+// 288 columns next to two accumulators of SP_NT = 96 columns.  An MMA then reads only its B operand (the staged
+// positions) from shared memory.  With both operands in shared memory an M = 128, N = 128 instruction needs the
+// whole shared-memory bandwidth (8 KB per 64 cycles), and the bulk copies and the epilogue's transposes compete
+// for it: measured 4.3 us per 128-position tile against 2.9 us of tensor-pipe time.  Shared memory now only holds
+// the input pipeline (up to 8 slots), the per-member tables and the epilogue's exchange buffers.
+//
+// Roles as in conv_bf16_kernel.  The eight builder warps write the filter with tcgen05.st: the thread of tensor-memory
+// lane r forms W_d[r mod 64, :] = W + s * eps[omap] for 32 channels of one tap at a time and keeps its hi or its lo
+// part; the two warps of a lane quadrant take half of the (tap, channel half) groups each.  Where the values come
+// from: the shared noise eps (out_sp rows, the same for every member; a member only chooses which row goes where)
+// is copied into shared memory once per block, and the 32 x 32 W tile of a group arrives by one TMA tile load into
+// a ring of three tiles per warp pair (the warp of rows c and the warp of rows c + 64 read the same tile), issued
+// three groups ahead and across member boundaries.  Plain loads were tried first: a warp gets one 512-byte load
+// instruction through every ~90 cycles (measured), which made the build 13 us per member.  Epilogue: accumulator
+// rows c and c + 64 are added by the two warps (lane quadrants q and q + 2) that share a column half; each writes the
+// 16-column chunks it does not finish into its partner's buffer, adds what the partner wrote into its own, transposes
+// there and stores 16 consecutive positions of two channel planes per instruction.  A half has three chunks: each
+// warp finishes one, the third alternates between them from tile to tile.
+constexpr int SP_NT = 96;
+constexpr int SP_A_COL = 224;          // first tensor-memory column of the filter operand
+constexpr int SP_WRING = 3;            // W tiles in flight per builder warp pair
+
+__global__ void __launch_bounds__(BF_THREADS, 1) conv_split_tmem_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                        const __nv_bfloat16* __restrict__ xs, const ConvBfParams p) {
+  constexpr int NT = SP_NT;
+  extern __shared__ unsigned char dyn_raw[];
+  const unsigned int timeouts_at_start = timeouts_so_far();
+  const uint32_t raw = smem_u32(dyn_raw);
+  const uint32_t pad = ((raw + 1023u) & ~1023u) - raw;
+  unsigned char* stages_base = dyn_raw + pad;
+  unsigned char* wring = stages_base + size_t(p.stages) * p.stage_bytes;     // [4 pairs][SP_WRING][32 rows x 128 B], swizzled
+  unsigned char* eps_s = wring + 4 * SP_WRING * 4096;                         // [eps_rows][e_pitch]
+  uint64_t* full = reinterpret_cast<uint64_t*>(eps_s + size_t(p.eps_rows) * p.e_pitch);
+  uint64_t* empty = full + p.stages;
+  uint64_t* acc_full = empty + p.stages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint64_t* wd_ready = acc_empty + 2;
+  uint64_t* wd_free = wd_ready + 1;
+  uint64_t* tbl_ready = wd_free + 1;
+  uint64_t* pair_ready = tbl_ready + 1;      // [8] per epilogue warp: the partner's values are in its buffer
+  uint64_t* pair_done = pair_ready + 8;      // [8] ... and it has finished with them
+  uint64_t* wfree = pair_done + 8;           // [4 pairs][SP_WRING] both warps of the pair have read the W tile
+  uint64_t* wfull = wfree + 4 * SP_WRING;    // [4 pairs][SP_WRING] a W tile has landed
+  uint64_t* eps_full = wfull + 4 * SP_WRING; // the noise rows have landed (once)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(eps_full + 1);
+  const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
+  const int table_bytes = table_maps_bytes + 4 * p.Cout;
+  unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
+  float* xchg = reinterpret_cast<float*>(tables + 2 * size_t(table_bytes));      // [8 warps][32][17]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ksz = p.kh * p.kw;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    mbar_init(wd_ready, 8);
+    mbar_init(wd_free, 1);
+    mbar_init(tbl_ready, 8);
+    for (int i = 0; i < 8; ++i) { mbar_init(&pair_ready[i], 1); mbar_init(&pair_done[i], 1); }
+    for (int i = 0; i < 4 * SP_WRING; ++i) { mbar_init(&wfull[i], 1); mbar_init(&wfree[i], 2); }
+    mbar_init(eps_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ producer: the noise rows once, then the hi run
+      // and the lo run of every tile
+      if (p.eps_rows > 0) {
+        const uint32_t row_bytes = uint32_t(ksz) * 256u;
+        mbar_expect_tx(eps_full, uint32_t(p.eps_rows) * row_bytes);
+        for (int r = 0; r < p.eps_rows; ++r)
+          bulk_load_1d(eps_s + size_t(r) * p.e_pitch, p.noise_t + size_t(r) * ksz * 64, row_bytes, eps_full);
+      }
+      uint32_t g = 0, tt = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        const long long d = u / p.sign_groups;
+        long long r0, r1; float s;
+        bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+        for (long long r = r0; r < r1 && ok; ++r) {
+          const long long b = r * p.D + d;
+          for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++tt) {
+            const long long row0 = b * (long long)p.img_rows + (long long)ti * NT;
+            for (int half = 0; half < 2; ++half, ++g) {
+              const int st = g % p.stages;
+              const uint32_t phs = (g / p.stages) & 1;
+              if (!mbar_wait(&empty[st], phs ^ 1, 1)) { ok = false; break; }
+              CONV_TRACE(true, tt, half);
+              mbar_expect_tx(&full[st], uint32_t(p.load_bytes));
+              bulk_load_1d(stages_base + size_t(st) * p.stage_bytes, xs + (half ? p.lo_offset : 0) + row0 * 64, uint32_t(p.load_bytes), &full[st]);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------------- MMA issuer: the whole warp runs this loop in
+    // converged control flow and one elected lane issues each instruction
+    const uint32_t idesc = idesc_bf16(128, NT);
+    const uint64_t desc0 = smem_desc_sw128(0);
+    const uint32_t a_col0 = tmem_base + uint32_t(SP_A_COL);
+    // pixel-row shift of every tap in 16-byte units (8 per 128-byte row), kept in registers: the issue loop below is
+    // straight-line code, so that the instructions between two MMAs do not outlast the MMA itself (48 cycles)
+    uint32_t xoff[9];
+#pragma unroll
+    for (int tap = 0; tap < 9; ++tap) {
+      const int i = tap / p.kw, j = tap - i * p.kw;
+      xoff[tap] = uint32_t(i * p.dh * p.Wp + j * p.dw) * 8u;
+    }
+    uint32_t g = 0, t = 0, ul = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      long long r0, r1; float s;
+      bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 <= r0) continue;
+      if (!warp_mbar_wait(wd_ready, ul & 1, 2)) { ok = false; break; }
+      tc_fence_after();
+      const long long ntiles = (r1 - r0) * p.tiles_img;
+      for (long long ti = 0; ti < ntiles && ok; ++ti, ++t) {
+        const uint32_t buf = t & 1;
+        if (!warp_mbar_wait(&acc_empty[buf], ((t >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        tc_fence_after();
+        CONV_TRACE(lane == 0, t, 2);
+        const uint32_t tmem_d = tmem_base + buf * uint32_t(NT);
+        for (int half = 0; half < 2; ++half, ++g) {
+          const int st = g % p.stages;
+          const uint32_t phs = (g / p.stages) & 1;
+          if (!warp_mbar_wait(&full[st], phs, 2)) { ok = false; break; }
+          CONV_TRACE(lane == 0, t, 3 + 2 * half);
+          const uint64_t x_desc = desc0 + uint64_t(smem_u32(stages_base + size_t(st) * p.stage_bytes) >> 4);
+#pragma unroll
+          for (int tap = 0; tap < 9; ++tap) {
+            if (tap < ksz) {
+              // 4 K steps of 8 tensor-memory columns per tap; only the tile's very first MMA overwrites the accumulator
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                warp_mma_bf16_tmem_a(tmem_d, a_col0 + uint32_t(tap * 32 + 8 * k), x_desc + uint64_t(xoff[tap] + 2 * k), idesc,
+                                     (tap == 0 && k == 0) ? uint32_t(half) : 1u);
+            }
+          }
+          warp_mma_commit(&empty[st]);
+          CONV_TRACE(lane == 0, t, 4 + 2 * half);
+        }
+        warp_mma_commit(&acc_full[buf]);
+      }
+      warp_mma_commit(wd_free);
+      ++ul;
+    }
+  } else {
+    // ---------------------------------------------------------------------- filter builders / epilogue
+    const int bt = threadIdx.x - 64;            // builder thread 0..255
+    const int q = warp & 3;                     // tensor-memory lane quadrant of this warp
+    const int hsel = (warp - 2) >> 2;           // which of the quadrant's two warps
+    const int frow = q * 32 + lane;             // filter row = tensor-memory lane
+    const bool lo_part = frow >= 64;
+    const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
+    const int HoWo = p.Ho * p.Wo;
+    // epilogue roles
+    const bool upper = q >= 2;
+    const int chan0 = (q & 1) * 32;
+    const int mine = warp - 2, theirs = upper ? mine + 2 : mine - 2;
+    float* my_buf = xchg + size_t(mine) * 32 * 17;
+    float* their_buf = xchg + size_t(theirs) * 32 * 17;
+    const int col_lo = hsel * (NT / 2);
+    const int pos = lane & 15, rsel = lane >> 4;
+    // filter build: the pair's ring of W tiles and its barriers; every member takes the same ksz groups in the same
+    // order, so the tiles are a fixed cyclic sequence and can be requested across member boundaries
+    const int pair = (q & 1) + 2 * hsel;
+    unsigned char* wtiles = wring + size_t(pair) * SP_WRING * 4096;
+    uint64_t* wbar = wfull + pair * SP_WRING;
+    uint64_t* wdone = wfree + pair * SP_WRING;
+    uint32_t my_groups = 0;                     // groups this pair consumes in the whole kernel (32-bit: cheap % and /)
+    for (int u = blockIdx.x; u < p.units; u += gridDim.x) {
+      long long r0, r1; float s;
+      bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 > r0) my_groups += uint32_t(ksz);
+    }
+    auto request_w = [&](uint32_t nseq) {      // one lane of the pair: group number nseq of the pair's sequence
+      const int G = hsel * ksz + int(nseq % uint32_t(ksz));
+      const int slot = int(nseq % uint32_t(SP_WRING));
+      mbar_expect_tx(&wbar[slot], 4096u);
+      tma_load_2d(wtiles + size_t(slot) * 4096, &map_w, &wbar[slot], (G >> 1) * 64 + (G & 1) * 32, chan0);
+    };
+    if (!upper && lane == 0)
+      for (uint32_t i = 0; i < uint32_t(SP_WRING) && i < my_groups; ++i) request_w(i);
+    uint32_t n_w = 0;                           // groups consumed so far
+    uint32_t t = 0, ul = 0, n_give = 0, n_take = 0;
+    bool ok = true;
+    if (p.eps_rows > 0 && !mbar_wait_relaxed(eps_full, 0, 4)) ok = false;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      const long long d = u / p.sign_groups;
+      long long r0, r1; float s;
+      bf_unit_range(p, u % p.sign_groups, r0, r1, s);
+      if (r1 <= r0) continue;
+      unsigned char* tb = tables + size_t(ul & 1) * table_bytes;
+      int16_t* omap_s = reinterpret_cast<int16_t*>(tb);
+      int16_t* imap_s = omap_s + p.Cout;
+      float* add_s = reinterpret_cast<float*>(tb + table_maps_bytes);
+      for (int c = bt; c < p.Cout; c += 256) {
+        omap_s[c] = p.omap[d * p.Cout + c];
+        float a = p.bias ? __ldg(p.bias + c) : 0.f;
+        if (p.bias_noise) a += s * __ldg(p.bias_noise + d * p.Cout + c);
+        add_s[c] = a;
+      }
+      for (int c = bt; c < p.Cin; c += 256) imap_s[c] = p.imap[d * p.Cin + c];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tbl_ready);
+      if (!mbar_wait_relaxed(tbl_ready, ul & 1, 4)) { ok = false; break; }
+      if (!mbar_wait_relaxed(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
+      tc_fence_after();
+      CONV_TRACE(threadIdx.x == 128, t, 9);
+      {
+        // 2 * ksz groups of (tap, 32 channels) = 16 tensor-memory columns each, ksz of them per warp pair.  This
+        // thread's row: W from the tile (16-byte chunk z of row r sits at chunk z ^ (r & 7)), eps from the resident rows
+        const bool has_row = chan0 + lane < p.Cout;
+        const int so = (has_row && p.eps_rows > 0) ? int(omap_s[chan0 + lane]) : -1;
+        // A tile is requested again (for the group SP_WRING further on) once both warps have read it.  The two warps
+        // take turns with the requests, and each request is made one group late, when the partner has long arrived:
+        // the warps never wait for each other here, and the few hundred ns a request costs its issuer are spread.
+        auto rerequest = [&](uint32_t m) -> bool {
+          if (upper != ((m & 1u) != 0) || m + SP_WRING >= my_groups) return true;
+          const bool done = mbar_wait(&wdone[m % SP_WRING], (m / SP_WRING) & 1u, 4);
+          if (__all_sync(0xffffffffu, done ? 1 : 0) == 0) return false;
+          if (lane == 0) request_w(m + SP_WRING);
+          return true;
+        };
+        int pending = -1;
+#pragma unroll 1
+        for (int gi = 0; gi < ksz; ++gi, ++n_w) {
+          const int G = hsel * ksz + gi;
+          const int tap = G >> 1, c0 = (G & 1) * 32;
+          const int slot = int(n_w % SP_WRING);
+          if (!mbar_wait(&wbar[slot], (n_w / SP_WRING) & 1u, 4)) { ok = false; break; }
+          CONV_TRACE(threadIdx.x == 128 && ul == 1, 40 + gi, 11);
+          const unsigned char* wrow = wtiles + size_t(slot) * 4096 + lane * 128;
+          const unsigned char* erow = eps_s + size_t(so < 0 ? 0 : so) * p.e_pitch + tap * 256 + c0 * 4;
+          uint32_t w16[16];
+#pragma unroll
+          for (int z = 0; z < 8; ++z) {
+            const float4 w = *reinterpret_cast<const float4*>(wrow + ((z ^ (lane & 7)) << 4));
+            float4 e = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (so >= 0) e = *reinterpret_cast<const float4*>(erow + 16 * z);
+            const float f0 = fmaf(s, e.x, w.x), f1 = fmaf(s, e.y, w.y), f2 = fmaf(s, e.z, w.z), f3 = fmaf(s, e.w, w.w);
+            // hi = the two values rounded to bf16 (one packed conversion); lo = what that rounding left over
+            uint32_t p01 = pack_bf16(f0, f1), p23 = pack_bf16(f2, f3);
+            if (lo_part) {
+              p01 = pack_bf16(f0 - __uint_as_float(p01 << 16), f1 - __uint_as_float(p01 & 0xffff0000u));
+              p23 = pack_bf16(f2 - __uint_as_float(p23 << 16), f3 - __uint_as_float(p23 & 0xffff0000u));
+            }
+            w16[2 * z] = p01;
+            w16[2 * z + 1] = p23;
+          }
+          tmem_st16(lane_base + uint32_t(SP_A_COL + G * 16), w16);
+          CONV_TRACE(threadIdx.x == 128 && ul == 1, 40 + gi, 12);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&wdone[slot]);             // this warp has read the tile
+          if (pending >= 0 && !rerequest(uint32_t(pending))) { ok = false; break; }
+          pending = int(n_w);
+          CONV_TRACE(threadIdx.x == 128 && ul == 1, 40 + gi, 13);
+        }
+        if (ok && pending >= 0 && !rerequest(uint32_t(pending))) ok = false;
+        tmem_st_wait();
+        if (!ok) break;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wd_ready);
+      CONV_TRACE(threadIdx.x == 128, t, 10);
+
+      const float add = (chan0 + lane < p.Cout) ? add_s[chan0 + lane] : 0.f;
+      for (long long r = r0; r < r1 && ok; ++r) {
+        const long long b = r * p.D + d;
+        float* img = p.y + size_t(b) * p.Cout * HoWo;
+        for (int ti = 0; ti < p.tiles_img && ok; ++ti, ++t) {
+          const uint32_t buf = t & 1;
+          if (!mbar_wait_relaxed(&acc_full[buf], (t >> 1) & 1, 3)) { ok = false; break; }
+          tc_fence_after();
+          CONV_TRACE(threadIdx.x == 128, t, 7);
+          const bool live = (timeouts_so_far() == timeouts_at_start);
+          const uint32_t tcol = lane_base + buf * uint32_t(NT) + uint32_t(col_lo);
+          // chunk 0 is finished by the lower-row warp, chunk 1 by the upper-row warp, chunk 2 by one of them in turn
+          const bool takes_third = (upper == ((t & 1) != 0));
+          uint32_t c_own[16], c_other[16], c_third[16];
+          tmem_ld16_nowait(tcol + (upper ? 16u : 0u), c_own);
+          tmem_ld16_nowait(tcol + (upper ? 0u : 16u), c_other);
+          tmem_ld16_nowait(tcol + 32u, c_third);
+          tmem_ld_wait();
+#pragma unroll
+          for (int step = 0; step < 3 && ok; ++step) {
+            // step 0: hand chunk `other` over; step 1: finish chunk `own`; step 2: the third chunk, either way
+            const bool give = (step == 0) || (step == 2 && !takes_third);
+            const uint32_t* src = (step == 0) ? c_other : (step == 1 ? c_own : c_third);
+            if (give) {
+              if (n_give > 0 && !mbar_wait(&pair_done[theirs], (n_give - 1) & 1, 3)) { ok = false; break; }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) their_buf[lane * 17 + j] = __uint_as_float(src[j]);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&pair_ready[theirs]);
+              ++n_give;
+            } else {
+              if (!mbar_wait(&pair_ready[mine], n_take & 1, 3)) { ok = false; break; }
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(src[j]) + my_buf[lane * 17 + j] + add;
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) my_buf[lane * 17 + j] = v[j];
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = my_buf[(2 * i + rsel) * 17 + pos];
+              const int chunk = (step == 1) ? (upper ? 1 : 0) : 2;
+              const int qpos = ti * NT + col_lo + chunk * 16 + pos;
+              const int oy = qpos / p.Wp, ox = qpos - oy * p.Wp;
+              if (live && oy < p.Ho && ox < p.Wo) {
+                float* dst = img + size_t(chan0 + rsel) * HoWo + oy * p.Wo + ox;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (chan0 + 2 * i + rsel < p.Cout) dst[size_t(2 * i) * HoWo] = v[i];
+              }
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&pair_done[mine]);
+              ++n_take;
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          CONV_TRACE(threadIdx.x == 128, t, 8);
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+      }
+      ++ul;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512u);
   }
 }
 
@@ -611,9 +877,19 @@ static int64_t bf_align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
 struct ConvBfPlan { ConvBfParams p; size_t smem; int64_t x_bytes, map_bytes, filt_bytes; };
 
+// form 0: filter in shared memory (conv_bf16_kernel); form 1: three-term form with the filter in tensor memory
+// form 1 additionally needs identity input channels (no input permutation, in_sp == Cin) and the noise rows to fit in
+// shared memory beside the pipeline (80 KB at most: 32 rows of a 3x3 filter)
+static bool tmem_form_covers(int Cin, int Cout, int kh, int kw, int eps_rows) {
+  return Cin == 64 && Cout <= 64 && kh * kw <= 9 && eps_rows >= 0 && size_t(eps_rows) * (size_t(kh) * kw * 256 + 16) <= 80 * 1024;
+}
+
 static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
-                          int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what, int terms = 1) {
-  const int NT = terms == 3 ? BF_NT3 : BF_NT;
+                          int sh, int sw, int ph, int pw, int dh, int dw, int antithetic, const char* what, int terms = 1,
+                          int form = 0, int eps_rows = 0) {
+  NES_REQUIRE(form == 0 || (terms == 3 && tmem_form_covers(Cin, Cout, kh, kw, eps_rows)), NES_ERR_UNSUPPORTED,
+              "%s: the tensor-memory filter form needs Cin = 64, Cout <= 64, at most 9 taps and at most 80 KB of noise rows", what);
+  const int NT = form == 1 ? SP_NT : (terms == 3 ? BF_NT3 : BF_NT);
   NES_REQUIRE(D >= 0 && R >= 0 && Cin > 0 && H > 0 && W > 0 && Cout > 0 && kh > 0 && kw > 0 && ph >= 0 && pw >= 0 &&
               dh > 0 && dw > 0, NES_ERR_BAD_ARG, "%s: bad geometry", what);
   NES_REQUIRE(sh == 1 && sw == 1, NES_ERR_UNSUPPORTED, "%s: the bf16 tensor-core path needs stride 1", what);
@@ -626,8 +902,10 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   NES_REQUIRE(p.Ho > 0 && p.Wo > 0, NES_ERR_BAD_ARG, "%s: empty output", what);
   p.Hp = H + 2 * ph; p.Wp = W + 2 * pw;
   p.M = Cout <= 64 ? 64 : 128;
-  p.stacked = (terms == 3 && Cout <= 64) ? 1 : 0;
-  if (p.stacked) p.M = 128;
+  p.tmem_filter = form;
+  p.eps_rows = form == 1 ? eps_rows : 0;
+  p.e_pitch = kh * kw * 256 + 16;                    // 16 bytes more than a row: rows start in different bank groups
+  if (form == 1) p.M = 128;
   p.tiles_img = ceil_div(p.Ho * p.Wp, NT);
   const int max_shift = (kh - 1) * dh * p.Wp + (kw - 1) * dw;
   p.img_rows = (p.Hp * p.Wp + 7) & ~7;
@@ -639,10 +917,13 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   p.units = int(D * p.sign_groups);
   p.cchunks = Cin / 64;
   p.kchunks = kh * kw * p.cchunks;
-  const size_t wd_bytes = size_t((terms == 3 && !p.stacked) ? 2 : 1) * p.kchunks * p.M * 128;
+  const size_t wd_bytes = form == 1 ? 0 : size_t(terms == 3 ? 2 : 1) * p.kchunks * p.M * 128;
   const size_t table_bytes = (((2 * (size_t(Cout) + Cin)) + 15) & ~size_t(15)) + 4 * size_t(Cout);
-  const size_t xpose_bytes = p.stacked ? 8 * size_t(32) * 17 * sizeof(float) : 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
-  const size_t fixed = 1024 + wd_bytes + 192 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
+  // form 1: the epilogue's exchange buffers [8 warps][32][17], the ring of W tiles [4 pairs][SP_WRING][4096 B] and the
+  // resident noise rows
+  const size_t xpose_bytes = form == 1 ? 8 * size_t(32) * 17 * sizeof(float) + 4 * size_t(SP_WRING) * 4096 + size_t(p.eps_rows) * p.e_pitch
+                                       : 8 * size_t(p.M == 128 ? 32 : 16) * 33 * sizeof(float);
+  const size_t fixed = 1024 + wd_bytes + 400 + 16 + 16 + 2 * table_bytes + 8 * size_t(kh) * kw + xpose_bytes;
   const size_t limit = 227 * 1024;
   NES_REQUIRE(fixed + 2 * (size_t(p.stage_bytes) + 16) <= limit, NES_ERR_UNSUPPORTED,
               "%s: the member filter (%zu bytes) plus two input stages (%d bytes each) do not fit in shared memory on the "
@@ -650,8 +931,12 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
   int stages = int((limit - fixed) / (size_t(p.stage_bytes) + 16));
   if (stages > 6) stages = 6;
   if (terms == 3 && stages > 4) stages = 4;
+  if (form == 1) {                                  // hi / lo slot pairs, up to four tiles in flight
+    stages = int((limit - fixed) / (size_t(p.stage_bytes) + 16)) & ~1;
+    if (stages > 8) stages = 8;
+  }
   p.stages = stages;
-  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 23) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
+  pl.smem = 1024 + wd_bytes + size_t(stages) * p.stage_bytes + (2 * stages + 48) * sizeof(uint64_t) + 16 + 16 + 2 * table_bytes +
             8 * size_t(kh) * kw + xpose_bytes;
   const int64_t copy_bytes = bf_align256(D * R * int64_t(p.cchunks) * p.img_rows * 128 + int64_t(p.stage_bytes));
   p.lo_offset = copy_bytes / 2;                    // bf16 elements
@@ -680,11 +965,30 @@ static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStr
   }
   int rc = check_launch(what);
   if (rc != NES_OK) return rc;
+  int grid = p.units < sm_count() ? p.units : sm_count();
+  if (grid < 1) grid = 1;
+  if (p.tmem_filter) {
+    // W re-ordered to (n, tap, c): a (Cout, K) fp32 matrix read in tiles of 32 rows x 32 channels, 128-byte swizzle
+    EncodeTiledFn fn = encode_fn();
+    NES_REQUIRE(fn != nullptr, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", what);
+    CUtensorMap map_w;
+    const cuuint64_t K = cuuint64_t(p.kh) * p.kw * 64;
+    cuuint64_t dims[2] = {K, (cuuint64_t)p.Cout};
+    cuuint64_t strides[1] = {K * sizeof(float)};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&map_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(p.weight_t), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    NES_REQUIRE(r == CUDA_SUCCESS, NES_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
+    cudaError_t e = cudaFuncSetAttribute(conv_split_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+    conv_split_tmem_kernel<<<grid, BF_THREADS, pl.smem, st>>>(map_w, static_cast<const __nv_bfloat16*>(x_staged), p);
+    return check_launch(what);
+  }
   auto kern = terms == 3 ? conv_bf16_kernel<3, BF_NT3> : conv_bf16_kernel<1, BF_NT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
-  int grid = p.units < sm_count() ? p.units : sm_count();
-  if (grid < 1) grid = 1;
   kern<<<grid, BF_THREADS, pl.smem, st>>>(static_cast<const __nv_bfloat16*>(x_staged), p);
   return check_launch(what);
 }
@@ -776,7 +1080,11 @@ static int permuted_conv_bf16(int terms, const float* x, const float* weight, co
                               int in_sp, int out_sp, int antithetic,
                               void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
   ConvBfPlan pl;
-  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16", terms);
+  // the three-term form keeps the filter in tensor memory where that form covers the layer
+  const int form = (terms == 3 && sh == 1 && sw == 1 && pin == nullptr && in_sp == Cin &&
+                    tmem_form_covers(Cin, Cout, kh, kw, out_sp)) ? 1 : 0;
+  int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16", terms, form,
+                          out_sp);
   if (rc != NES_OK) return rc;
   if (D == 0 || R == 0) return NES_OK;
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_conv2d_fwd_bf16: null pointer");
