@@ -91,7 +91,8 @@ __global__ void sample_bits_kernel(const __half* __restrict__ p, const float* __
 // up to a multiple of 2^-16 (p = 0 never, p = 1 always).  The comparison runs on all 32 columns at once,
 // bit-sliced: the thresholds are held as 16 bit-planes (plane j, bit i = bit j of T_i), a random word
 // supplies bit j of all 32 uniforms, and from the top plane down a column is decided at the first plane
-// where its uniform and its threshold differ.  Two Philox-4x32-10 calls per word (counter = (column
+// where its uniform and its threshold differ.  Two Philox-4x32 calls of seven rounds per word (the kernel is bound by
+// this integer arithmetic; seven is the smallest count the generator's authors report as passing BigCrush; counter = (column
 // group, row, member)) give eight words: word k is bit 15-k of the uniforms, and the same word rotated
 // by k+1 columns is bit 7-k, so each U is sixteen independent random bits (its low byte is made of bits
 // that serve as high-byte bits of other columns; it only matters when the high bytes of U and T agree).
@@ -117,8 +118,8 @@ struct BitDrawer {
 
   __device__ inline uint32_t draw(const Philox& ph, int64_t q, int64_t y, int64_t x) const {
     uint32_t r[8];
-    ph(uint32_t(q * 2), uint32_t(y), uint32_t(x), 5u, r);
-    ph(uint32_t(q * 2 + 1), uint32_t(y), uint32_t(x), 5u, r + 4);
+    ph.rounds<7>(uint32_t(q * 2), uint32_t(y), uint32_t(x), 5u, r);
+    ph.rounds<7>(uint32_t(q * 2 + 1), uint32_t(y), uint32_t(x), 5u, r + 4);
     uint32_t und = ~0u, res = always;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {

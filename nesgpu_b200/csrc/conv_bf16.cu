@@ -800,65 +800,83 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_split_tmem_kernel(const __
 
 // x (B,C,H,W) fp32 -> staged bf16 layout: for every image and 64-channel chunk a run of img_rows pixel rows
 // (zero-padded image, pitch Wp, 128 bytes = 64 bf16 channels per row), 16-byte groups permuted by (row mod 8)
-// as the 128-byte shared-memory swizzle does.  One block per (image, chunk), strips of 4 padded rows.
-constexpr int BF_STRIP = 4;
+// as the 128-byte shared-memory swizzle does.  With SPLIT the lo copy (the bf16 rounding of what the hi copy left
+// over) is written `lo_units` 16-byte units behind the hi copy, in the same layout.
+//
+// A streaming pass without block-wide synchronisation: one warp per (image, chunk, padded image row, run of 32
+// pixels).  A lane reads its pixel from the 64 channel planes (64 coalesced 128-byte loads per warp, all in flight
+// together), converts, and writes its 128-byte row into the warp's shared-memory tile; the warp then reads the tile
+// back so that eight consecutive lanes hold one row and stores four whole rows (512 contiguous bytes) per instruction.
+constexpr int STAGE_WARPS = 8;
 
-// With SPLIT the lo copy (the bf16 rounding of what the hi copy left over) is written `lo_words` 32-bit words
-// behind the hi copy, in the same layout.
-template <bool VEC, bool SPLIT>
-__global__ void __launch_bounds__(256) stage_input_bf16_kernel(const float* __restrict__ x, uint32_t* __restrict__ out,
-                                                               int C, int H, int W, int Hp, int Wp, int ph, int pw,
-                                                               int img_rows, long long lo_words) {
-  extern __shared__ float tile[];                 // [64][pitch]
-  const int pitch = (BF_STRIP * Wp) | 1;
-  const size_t b = blockIdx.y;
-  const int cc = blockIdx.x;
+template <bool SPLIT>
+__global__ void __launch_bounds__(STAGE_WARPS * 32) stage_rows_bf16_kernel(const float* __restrict__ x, uint4* __restrict__ out,
+                                                                         int C, int H, int W, int Hp, int Wp, int ph, int pw,
+                                                                         int cchunks, int img_rows, long long lo_units,
+                                                                         int runs, long long jobs) {
+  __shared__ uint4 tiles[STAGE_WARPS][32 * 8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float* src = x + (b * size_t(C) + size_t(cc) * 64) * H * W;
-  uint32_t* dst = out + (b * gridDim.x + cc) * size_t(img_rows) * 32;      // 32 packed pairs per row
-  for (int y0 = 0; y0 < Hp; y0 += BF_STRIP) {
-    const int rows = (Hp - y0 < BF_STRIP) ? (Hp - y0) : BF_STRIP;
-    for (int e = threadIdx.x; e < 64 * pitch; e += 256) tile[e] = 0.f;
-    __syncthreads();
-    for (int ch = warp; ch < 64; ch += 8) {
-      const float* plane = src + size_t(ch) * H * W;
-      if (VEC) {
-        const int w4 = W >> 2;
-        for (int g = lane; g < rows * w4; g += 32) {
-          const int rr = g / w4, x4 = (g - rr * w4) * 4;
-          const int yy = y0 + rr - ph;
-          if (yy >= 0 && yy < H) {
-            const float4 v = __ldcs(reinterpret_cast<const float4*>(plane + size_t(yy) * W + x4));
-            float* tp = tile + ch * pitch + rr * Wp + pw + x4;
-            tp[0] = v.x; tp[1] = v.y; tp[2] = v.z; tp[3] = v.w;
-          }
+  uint4* tile = tiles[warp];
+  const long long nwarps = (long long)gridDim.x * STAGE_WARPS;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const size_t plane = size_t(H) * W;
+  for (long long job = (long long)blockIdx.x * STAGE_WARPS + warp; job < jobs; job += nwarps) {
+    const int xr = int(job % runs);
+    const long long jr = job / runs;
+    const int yp = int(jr % Hp);
+    const long long bc = jr / Hp;                       // image * cchunks + chunk
+    const int cc = int(bc % cchunks);
+    const long long b = bc / cchunks;
+    uint4* drow = out + (size_t(bc) * img_rows + size_t(yp) * Wp) * 8;      // eight 16-byte units per staged row
+    const int yy = yp - ph;
+    if (yy < 0 || yy >= H) {
+      if (xr == 0)
+        for (int i = lane; i < Wp * 8; i += 32) {
+          drow[i] = zero;
+          if (SPLIT) drow[i + lo_units] = zero;
         }
-      } else {
-        for (int g = lane; g < rows * W; g += 32) {
-          const int rr = g / W, xx = g - rr * W;
-          const int yy = y0 + rr - ph;
-          if (yy >= 0 && yy < H) tile[ch * pitch + rr * Wp + pw + xx] = __ldcs(plane + size_t(yy) * W + xx);
+      continue;
+    }
+    if (xr == 0)
+      for (int i = lane; i < pw * 8; i += 32) {            // the padding pixels left and right of the row
+        drow[i] = zero;
+        drow[size_t(pw + W) * 8 + i] = zero;
+        if (SPLIT) { drow[i + lo_units] = zero; drow[size_t(pw + W) * 8 + i + lo_units] = zero; }
+      }
+    const int x0 = xr * 32;
+    const int xx = x0 + lane;
+    const bool valid = xx < W;
+    const float* src = x + ((size_t(b) * C + size_t(cc) * 64) * H + yy) * W + xx;
+    float v[64];
+#pragma unroll
+    for (int c = 0; c < 64; ++c) v[c] = valid ? __ldcs(src + size_t(c) * plane) : 0.f;
+    const int row0 = yp * Wp + pw + x0;                // staged row of the run's first pixel (img_rows is a multiple of 8)
+    uint4* d0 = drow + size_t(pw + x0) * 8;
+#pragma unroll
+    for (int part = 0; part < (SPLIT ? 2 : 1); ++part) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        uint32_t w[4];
+#pragma unroll
+        for (int z = 0; z < 4; ++z) {
+          const float a = v[8 * g + 2 * z], bb = v[8 * g + 2 * z + 1];
+          uint32_t pk = pack_bf16(a, bb);
+          if (part == 1) pk = pack_bf16(a - __uint_as_float(pk << 16), bb - __uint_as_float(pk & 0xffff0000u));
+          w[z] = pk;
         }
+        tile[lane * 8 + (g ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
       }
-    }
-    __syncthreads();
-    const int first = y0 * Wp;
-    for (int r = warp; r < rows * Wp; r += 8) {
-      const int row = first + r;
-      // lane holds channels 2*lane, 2*lane+1 -> 4-byte unit `lane` of the row; units 4g..4g+3 form 16-byte group g
-      const size_t o = size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3));
-      const float v0 = tile[(2 * lane) * pitch + r], v1 = tile[(2 * lane + 1) * pitch + r];
-      if (SPLIT) {
-        float h0, l0, h1, l1;
-        split_bf16(v0, h0, l0);
-        split_bf16(v1, h1, l1);
-        dst[o] = pack_bf16(h0, h1);
-        dst[o + lo_words] = pack_bf16(l0, l1);
-      } else {
-        dst[o] = pack_bf16(v0, v1);
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = (lane >> 3) + 4 * it;            // pixel of the run; eight lanes per row
+        const int pos = lane & 7;                      // 16-byte position in the staged row
+        const int chunk = pos ^ ((row0 + r) & 7);      // the channel group that belongs there
+        const uint4 val = tile[r * 8 + (chunk ^ (r & 7))];
+        if (x0 + r < W) d0[size_t(r) * 8 + pos + (part ? lo_units : 0)] = val;
       }
+      __syncwarp();
     }
-    __syncthreads();
   }
 }
 
@@ -950,19 +968,15 @@ static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStr
   ConvBfParams& p = pl.p;
   const int64_t B = p.D * p.R;
   NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
-  const size_t tsmem = size_t(64) * ((BF_STRIP * p.Wp) | 1) * sizeof(float);
-  NES_REQUIRE(tsmem <= 48 * 1024, NES_ERR_UNSUPPORTED, "%s: image row too wide for the layout pre-pass (%zu bytes)", what, tsmem);
-  dim3 tgrid((unsigned)p.cchunks, (unsigned)B);
-  const bool vec = p.W % 4 == 0 && aligned16(x);
-  const long long lo_words = p.lo_offset / 2;
-  uint32_t* xo = static_cast<uint32_t*>(x_staged);
-  if (terms == 3) {
-    if (vec) stage_input_bf16_kernel<true, true><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, lo_words);
-    else stage_input_bf16_kernel<false, true><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, lo_words);
-  } else {
-    if (vec) stage_input_bf16_kernel<true, false><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, 0);
-    else stage_input_bf16_kernel<false, false><<<tgrid, 256, tsmem, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows, 0);
-  }
+  const int runs = ceil_div(p.W, 32);
+  const long long jobs = B * int64_t(p.cchunks) * p.Hp * runs;          // one warp per (image, chunk, padded row, 32 pixels)
+  const long long lo_units = p.lo_offset / 8;                           // bf16 elements -> 16-byte units
+  long long sblocks = (jobs + STAGE_WARPS - 1) / STAGE_WARPS;
+  if (sblocks > 16LL * sm_count()) sblocks = 16LL * sm_count();
+  if (sblocks < 1) sblocks = 1;
+  uint4* xo = static_cast<uint4*>(x_staged);
+  if (terms == 3) stage_rows_bf16_kernel<true><<<(unsigned)sblocks, STAGE_WARPS * 32, 0, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.cchunks, p.img_rows, lo_units, runs, jobs);
+  else stage_rows_bf16_kernel<false><<<(unsigned)sblocks, STAGE_WARPS * 32, 0, st>>>(x, xo, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.cchunks, p.img_rows, 0, runs, jobs);
   int rc = check_launch(what);
   if (rc != NES_OK) return rc;
   int grid = p.units < sm_count() ? p.units : sm_count();
@@ -1032,7 +1046,6 @@ extern "C" int nes_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, 
   ConvBfPlan pl;
   if (Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || dh <= 0 || dw <= 0) return 0;
   if (dh > 8 || dw > 8) return 0;
-  if (size_t(64) * ((BF_STRIP * (W + 2 * pw)) | 1) * sizeof(float) > 48 * 1024) return 0;
   return plan_conv_bf16(pl, 1, 1, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, 0, "conv2d_fwd_bf16x3", 3) == NES_OK ? 1 : 0;
 }
 

@@ -538,6 +538,9 @@ def test_permuted_linear_out_cluster_kernel_refuses_uncovered_shapes():
 @pytest.mark.parametrize("mode,in_sp,out_sp,R,anti,hw,k,pad,cout,cin", [
     ("out", 0, 0.5, 1, False, 13, 3, 1, 64, 64), ("in", 0, 0, 2, True, 9, 3, 1, 32, 64), ("both", 0, 0, 3, True, 8, 3, 0, 64, 64),
     ("out", 0, 0, 2, True, 33, 1, 0, 128, 128), ("auto", 0.5, 0, 1, False, 20, 3, 2, 24, 64), ("out", 0, 0, 2, True, 32, 3, 1, 64, 64),
+    # the form with the filter in tensor memory (64 input channels, <= 64 output channels, noise rows within 80 KB):
+    # antithetic pairs over several tiles, a 1x1 filter with a ragged channel count and an odd repeat count
+    ("out", 0, 0.25, 2, True, 32, 3, 1, 32, 64), ("out", 0, 0.5, 3, True, 10, 1, 0, 24, 64), ("out", 0, 0.125, 1, False, 17, 2, 1, 56, 64),
 ])
 def test_permuted_conv_split_bf16_holds_the_fp32_bar(mode, in_sp, out_sp, R, anti, hw, k, pad, cout, cin):
     """Default mode of a covered geometry: three bf16 products on hi/lo splits; 1e-4 on the output and 1e-3 on the
@@ -574,6 +577,35 @@ def test_permuted_conv_split_bf16_holds_the_fp32_bar(mode, in_sp, out_sp, R, ant
         y32 = layer.forward(G(x))
     assert layer.last_path == "fp32"
     assert_close(y32, want, tol=1e-4, what="CUDA-core conv")
+
+
+def test_permuted_conv_split_bf16_many_members_per_block():
+    """More members than SMs: a block builds several member filters in turn (the W tile ring runs across members)."""
+    from nesgpu_b200 import base, _cabi as C
+    from oracle import perturbed_ref as O
+    from gpu_util import set_params
+    D, cin, cout, hw, k = 333, 64, 64, 8, 3
+    g = torch.Generator().manual_seed(77)
+    layer = base.PermutedConv2d(cin, cout, k, D, padding=1, antithetic=False, permutation="out", out_sparsity=0.5).to(DEV)
+    osp = layer.out_sparsity
+    x = torch.randn(D, cin, hw, hw, generator=g)
+    W = torch.randn(cout, cin, k, k, generator=g) / (cin * k * k) ** .5
+    b = torch.randn(cout, generator=g)
+    eps = 0.05 * torch.randn(osp, cin, k, k, generator=g)
+    beta = 0.02 * torch.randn(D, cout, generator=g)
+    pout = _perms(g, D, cout)
+    set_params(layer, W, b)
+    layer.weight_noise, layer.bias_noise = G(eps), G(beta)
+    layer.output_permutations = G(pout)
+    with torch.no_grad():
+        layer.perturbed_flag = True
+        y = layer.forward(G(x))
+    torch.cuda.synchronize()
+    assert layer.last_path == "bf16x3" and _flag(C) == 0
+    want = O.permuted_conv2d_forward(x, W, b, eps, beta, None, pout, D, 1, 1, 1, False)
+    assert_close(y, want, tol=1e-4, what="split-bf16 conv, 333 members")
+    basey = torch.nn.functional.conv2d(x, W, b, 1, 1)
+    assert_close(y.cpu() - basey, want - basey, tol=1e-3, what="perturbation term")
 
 
 def test_perturbed_conv_split_bf16_holds_the_fp32_bar():
