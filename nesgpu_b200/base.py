@@ -689,7 +689,7 @@ class _ConvMixin:
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        suffix = self._tensor_core_mode(geom) if x.shape[0] <= 65535 else None
+        suffix = self._tensor_core_mode(geom)
         self.last_path = {None: "fp32", "tc": "tf32"}.get(suffix, suffix)
         if suffix and x.shape[0]:
             buf, nbytes = self._tc_scratch(x, R, geom, suffix)
@@ -925,7 +925,7 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        suffix = self._tensor_core_mode(geom) if x.shape[0] <= 65535 else None
+        suffix = self._tensor_core_mode(geom)
         if suffix in ("bf16", "bf16x3") and pin is None and self.in_sparsity % 8:
             suffix = None if self.options.get("tc", "auto") == "auto" else suffix
         self.last_path = {None: "fp32", "tc": "tf32"}.get(suffix, suffix)

@@ -967,7 +967,6 @@ static int plan_conv_bf16(ConvBfPlan& pl, int64_t D, int64_t R, int Cin, int H, 
 static int run_conv_bf16(ConvBfPlan& pl, const float* x, void* x_staged, cudaStream_t st, const char* what, int terms = 1) {
   ConvBfParams& p = pl.p;
   const int64_t B = p.D * p.R;
-  NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
   const int runs = ceil_div(p.W, 32);
   const long long jobs = B * int64_t(p.cchunks) * p.Hp * runs;          // one warp per (image, chunk, padded row, 32 pixels)
   const long long lo_units = p.lo_offset / 8;                           // bf16 elements -> 16-byte units

@@ -318,55 +318,64 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float*
 // x (B,C,H,W) -> the staged layout the kernel above copies from: for every image and 32-channel chunk a
 // run of img_rows pixel rows (zero-padded image, pitch Wp, 128 bytes = 32 channels per row), values rounded
 // to TF32, 16-byte groups of each row permuted by (row mod 8) exactly as the 128-byte shared-memory swizzle
-// does.  One block per (image, channel chunk) walks the image in strips of STRIP padded rows: each warp
-// reads whole image rows of one channel with 128-bit loads (contiguous in NCHW), the strip is transposed in
-// shared memory, and every warp store writes one 128-byte pixel row of a contiguous run.
-constexpr int STRIP = 4;
+// does.
+constexpr int STAGE_WARPS = 8;
 
-template <bool VEC>
-__global__ void __launch_bounds__(256) stage_input_tf32_kernel(const float* __restrict__ x, float* __restrict__ out,
-                                                               int C, int H, int W, int Hp, int Wp, int ph, int pw,
-                                                               int img_rows) {
-  extern __shared__ float tile[];                 // [32][pitch], pitch odd: conflict-free transposed reads
-  const int pitch = (STRIP * Wp) | 1;
-  const size_t b = blockIdx.y;
-  const int cc = blockIdx.x;
+// One warp per (image, chunk, padded image row, run of 32 pixels), no block-wide synchronisation: a lane reads its pixel
+// from the 32 channel planes (32 coalesced 128-byte loads per warp in flight together), rounds to TF32 and writes its
+// 128-byte row into the warp's shared-memory tile; the warp reads the tile back so that eight consecutive lanes hold
+// one row and stores four whole rows (512 contiguous bytes) per instruction.
+__global__ void __launch_bounds__(STAGE_WARPS * 32) stage_rows_tf32_kernel(const float* __restrict__ x, uint4* __restrict__ out,
+                                                                         int C, int H, int W, int Hp, int Wp, int ph, int pw,
+                                                                         int cchunks, int img_rows, int runs, long long jobs) {
+  __shared__ uint4 tiles[STAGE_WARPS][32 * 8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const float* src = x + (b * size_t(C) + size_t(cc) * 32) * H * W;
-  float* dst = out + (b * gridDim.x + cc) * size_t(img_rows) * 32;
-  for (int y0 = 0; y0 < Hp; y0 += STRIP) {
-    const int rows = (Hp - y0 < STRIP) ? (Hp - y0) : STRIP;
-    // zero the strip (padding), then drop the interior values in
-    for (int e = threadIdx.x; e < 32 * pitch; e += 256) tile[e] = 0.f;
-    __syncthreads();
-    for (int ch = warp; ch < 32; ch += 8) {
-      const float* plane = src + size_t(ch) * H * W;
-      if (VEC) {
-        const int w4 = W >> 2;
-        for (int g = lane; g < rows * w4; g += 32) {
-          const int rr = g / w4, x4 = (g - rr * w4) * 4;
-          const int yy = y0 + rr - ph;
-          if (yy >= 0 && yy < H) {
-            const float4 v = __ldcs(reinterpret_cast<const float4*>(plane + size_t(yy) * W + x4));
-            float* t = tile + ch * pitch + rr * Wp + pw + x4;
-            t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
-          }
-        }
-      } else {
-        for (int g = lane; g < rows * W; g += 32) {
-          const int rr = g / W, xx = g - rr * W;
-          const int yy = y0 + rr - ph;
-          if (yy >= 0 && yy < H) tile[ch * pitch + rr * Wp + pw + xx] = __ldcs(plane + size_t(yy) * W + xx);
-        }
+  uint4* tile = tiles[warp];
+  const long long nwarps = (long long)gridDim.x * STAGE_WARPS;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  const size_t plane = size_t(H) * W;
+  for (long long job = (long long)blockIdx.x * STAGE_WARPS + warp; job < jobs; job += nwarps) {
+    const int xr = int(job % runs);
+    const long long jr = job / runs;
+    const int yp = int(jr % Hp);
+    const long long bc = jr / Hp;                       // image * cchunks + chunk
+    const int cc = int(bc % cchunks);
+    const long long b = bc / cchunks;
+    uint4* drow = out + (size_t(bc) * img_rows + size_t(yp) * Wp) * 8;      // eight 16-byte units per staged row
+    const int yy = yp - ph;
+    if (yy < 0 || yy >= H) {
+      if (xr == 0)
+        for (int i = lane; i < Wp * 8; i += 32) drow[i] = zero;
+      continue;
+    }
+    if (xr == 0)
+      for (int i = lane; i < pw * 8; i += 32) {            // the padding pixels left and right of the row
+        drow[i] = zero;
+        drow[size_t(pw + W) * 8 + i] = zero;
       }
+    const int x0 = xr * 32;
+    const int xx = x0 + lane;
+    const bool valid = xx < W;
+    const float* src = x + ((size_t(b) * C + size_t(cc) * 32) * H + yy) * W + xx;
+    float v[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[c] = valid ? __ldcs(src + size_t(c) * plane) : 0.f;
+    const int row0 = yp * Wp + pw + x0;                // staged row of the run's first pixel (img_rows is a multiple of 8)
+    uint4* d0 = drow + size_t(pw + x0) * 8;
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      tile[lane * 8 + (g ^ (lane & 7))] = make_uint4(__float_as_uint(round_tf32(v[4 * g])), __float_as_uint(round_tf32(v[4 * g + 1])),
+                                                      __float_as_uint(round_tf32(v[4 * g + 2])), __float_as_uint(round_tf32(v[4 * g + 3])));
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = (lane >> 3) + 4 * it;              // pixel of the run; eight lanes per row
+      const int pos = lane & 7;                        // 16-byte position in the staged row
+      const int chunk = pos ^ ((row0 + r) & 7);        // the channel group that belongs there
+      const uint4 val = tile[r * 8 + (chunk ^ (r & 7))];
+      if (x0 + r < W) d0[size_t(r) * 8 + pos] = val;
     }
-    __syncthreads();
-    const int first = y0 * Wp;
-    for (int r = warp; r < rows * Wp; r += 8) {
-      const int row = first + r;                       // row inside this image/chunk run (run starts at a multiple of 8)
-      dst[size_t(row) * 32 + ((((lane >> 2) ^ (row & 7)) << 2) | (lane & 3))] = round_tf32(tile[lane * pitch + r]);
-    }
-    __syncthreads();
+    __syncwarp();
   }
 }
 
@@ -434,14 +443,13 @@ static int plan_conv_tc(ConvTcPlan& pl, int64_t D, int64_t R, int Cin, int H, in
 static int run_conv_tc(ConvTcPlan& pl, const float* x, float* x_nhwc, cudaStream_t st, const char* what) {
   ConvTcParams& p = pl.p;
   const int64_t B = p.D * p.R;
-  NES_REQUIRE(B <= 65535, NES_ERR_UNSUPPORTED, "%s: more than 65535 images per call on the tensor-core path", what);
-  const size_t tsmem = size_t(32) * ((STRIP * p.Wp) | 1) * sizeof(float);
-  NES_REQUIRE(tsmem <= 48 * 1024, NES_ERR_UNSUPPORTED, "%s: image row too wide for the layout pre-pass (%zu bytes)", what, tsmem);
-  dim3 tgrid((unsigned)p.cchunks, (unsigned)B);
-  if (p.W % 4 == 0 && aligned16(x))
-    stage_input_tf32_kernel<true><<<tgrid, 256, tsmem, st>>>(x, x_nhwc, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
-  else
-    stage_input_tf32_kernel<false><<<tgrid, 256, tsmem, st>>>(x, x_nhwc, p.Cin, p.H, p.W, p.Hp, p.Wp, p.ph, p.pw, p.img_rows);
+  const int runs = ceil_div(p.W, 32);
+  const long long jobs = B * int64_t(p.cchunks) * p.Hp * runs;          // one warp per (image, chunk, padded row, 32 pixels)
+  long long sblocks = (jobs + STAGE_WARPS - 1) / STAGE_WARPS;
+  if (sblocks > 16LL * sm_count()) sblocks = 16LL * sm_count();
+  if (sblocks < 1) sblocks = 1;
+  stage_rows_tf32_kernel<<<(unsigned)sblocks, STAGE_WARPS * 32, 0, st>>>(x, reinterpret_cast<uint4*>(x_nhwc), p.Cin, p.H, p.W, p.Hp, p.Wp,
+                                                                        p.ph, p.pw, p.cchunks, p.img_rows, runs, jobs);
   int rc = check_launch(what);
   if (rc != NES_OK) return rc;
 
