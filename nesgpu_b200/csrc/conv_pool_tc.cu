@@ -100,7 +100,13 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   uint64_t* zeps_full = acc_full + 4;                 // [zbufs] eps rows in shared memory (64 threads)
   uint64_t* zeps_empty = acc_full + 6;                // [zbufs] ... and consumed (128 threads)
   uint64_t* filt_full = acc_full + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 9);
+  uint64_t* a_ready = acc_full + 9;                   // TERMS == 3: the hi filter has been copied to tensor memory (4 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 10);
+  // TERMS == 3: the hi part of the stacked filter is ALSO kept in tensor memory (144 columns behind the two
+  // accumulators) and two of the three MMAs per K step take it from there: with A and B both in shared memory an
+  // M = N = 128 MMA needs 8 KB of operands per 64 cycles, all the shared-memory bandwidth there is
+  constexpr uint32_t A_COL = 2 * CP_N;
+  constexpr uint32_t TMEM_COLS = TERMS == 3 ? 512 : 2 * CP_N;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -108,9 +114,10 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 192); }
     for (int s = 0; s < zbufs; ++s) { mbar_init(&zeps_full[s], 64); mbar_init(&zeps_empty[s], 128); }
     mbar_init(filt_full, 1);
+    mbar_init(a_ready, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 2 * CP_N);
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -140,32 +147,58 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
     // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
     constexpr uint32_t idesc = BF16 ? idesc_bf16(CP_M, CP_N) : idesc_tf32(CP_M, CP_N);
     bool ok = warp_mbar_wait(filt_full, 0, 2);
-    const uint32_t filt_addr = smem_u32(filt);
+    if (TERMS == 3 && ok) {
+      ok = warp_mbar_wait(a_ready, 0, 2);
+      tc_fence_after();
+    }
+    const uint32_t a_tmem = tmem_base + A_COL;
+    // Straight-line issue: a single warp issues roughly one instruction every four cycles, so descriptor arithmetic
+    // between two MMAs must stay well below the 64 cycles an MMA takes.  Descriptors are a constant plus a 16-byte
+    // unit offset: the filter's offsets are compile-time constants once the tap loop is unrolled, the image's
+    // per-tap row shifts are kept in registers.
+    const uint64_t a_desc0 = BF16 ? smem_desc_sw64(smem_u32(filt)) : smem_desc_sw128(smem_u32(filt));
+    const uint64_t b_desc0 = BF16 ? smem_desc_sw64(smem_u32(stage0)) : smem_desc_sw128(smem_u32(stage0));
+    uint32_t boff[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      const int ti = t / p.kw, tj = t - ti * p.kw;
+      boff[t] = uint32_t((ti * p.W + tj) * ROW_BYTES) >> 4;
+    }
+    // the MMAs of one tap: descriptor units are 16 bytes, one K step is 32 bytes
+    auto issue_tap = [&](uint32_t acc, uint64_t bd, int t) {
+      const uint64_t a = a_desc0 + uint64_t(uint32_t(t) * uint32_t(TAP_BYTES >> 4));
+#pragma unroll
+      for (int k = 0; k < KSTEPS; ++k) {
+        const uint32_t first = (t > 0 || k > 0) ? 1u : 0u;
+        if (TERMS == 3) {
+          // hi filter (tensor memory: 8 columns per K step) on the hi image, lo filter (shared memory) on the hi
+          // image, hi filter on the lo image
+          const uint32_t a_hi = a_tmem + uint32_t(t * (KSTEPS * 8) + 8 * k);
+          warp_mma_bf16_tmem_a(acc, a_hi, bd + uint64_t(2 * k), idesc, first);
+          warp_mma_bf16(acc, a + uint64_t(filt_copy >> 4) + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, 1u);
+          warp_mma_bf16_tmem_a(acc, a_hi, bd + uint64_t(half_bytes >> 4) + uint64_t(2 * k), idesc, 1u);
+        } else if (BF16) {
+          warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, first);
+        } else {
+          warp_mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, first);
+        }
+      }
+    };
     int i = 0;
     for (int64_t b = blockIdx.x; b < p.B && ok; b += gridDim.x, ++i) {
       const int s = i % stages, a2 = i & 1;
       ok = warp_mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && warp_mbar_wait(&full[s], (i / stages) & 1, 2);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t st = smem_u32(stage0 + size_t(s) * stage_bytes);
+      const uint64_t b_desc = b_desc0 + uint64_t(uint32_t(s) * uint32_t(stage_bytes >> 4));
       const uint32_t acc = tmem_base + uint32_t(a2 * CP_N);
-      for (int ti = 0, t = 0; ti < p.kh; ++ti)
-        for (int tj = 0; tj < p.kw; ++tj, ++t) {
-          const uint32_t a_addr = filt_addr + uint32_t(t) * TAP_BYTES;
-          const uint32_t b_addr = st + uint32_t(ti * p.W + tj) * ROW_BYTES;
-          const uint64_t a = BF16 ? smem_desc_sw64(a_addr) : smem_desc_sw128(a_addr);
-          const uint64_t bd = BF16 ? smem_desc_sw64(b_addr) : smem_desc_sw128(b_addr);
 #pragma unroll
-          for (int k = 0; k < KSTEPS; ++k) {
-            if (BF16) warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
-            else warp_mma_tf32(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
-            if (TERMS == 3) {
-              // lo filter on the hi image, hi filter on the lo image (descriptor units are 16 bytes)
-              warp_mma_bf16(acc, a + uint64_t(filt_copy >> 4) + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, 1u);
-              warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(half_bytes >> 4) + uint64_t(2 * k), idesc, 1u);
-            }
-          }
-        }
+      for (int t = 0; t < 9; ++t)
+        if (t < taps) issue_tap(acc, b_desc + uint64_t(boff[t]), t);
+      for (int t = 9; t < taps; ++t) {                       // filters with more than nine taps: offsets on the fly
+        const int ti = t / p.kw, tj = t - ti * p.kw;
+        issue_tap(acc, b_desc + uint64_t(uint32_t((ti * p.W + tj) * ROW_BYTES) >> 4), t);
+      }
       warp_mma_commit(&empty[s]);
       warp_mma_commit(&acc_full[a2]);
     }
@@ -175,6 +208,28 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
     const int q = warp & 3;                        // TMEM lane quadrant of this warp
     const int half = warp >> 3;                    // 0: first share of the windows, 1: second share
     const uint32_t lane_addr = tmem_base + (uint32_t(q * 32) << 16);
+    if (TERMS == 3 && warp < 6) {
+      // warps 2-5 (one per lane quadrant) copy the hi filter from shared memory to tensor memory, once: the thread of
+      // filter row r reads its 64-byte row of every tap (16-byte chunk c sits at chunk c ^ ((r >> 1) & 3), the
+      // 64-byte swizzle of the load) and writes 16 columns = 32 channels
+      if (mbar_wait_relaxed(filt_full, 0, 4)) {
+        const int r = q * 32 + lane;
+        for (int t = 0; t < taps; ++t) {
+          const unsigned char* row = filt + size_t(t) * TAP_BYTES + size_t(r) * ROW_BYTES;
+          uint32_t w16[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(row + ((c ^ ((r >> 1) & 3)) << 4));
+            w16[4 * c] = v.x; w16[4 * c + 1] = v.y; w16[4 * c + 2] = v.z; w16[4 * c + 3] = v.w;
+          }
+          tmem_st16(lane_addr + A_COL + uint32_t(t * 16), w16);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+      }
+    }
     if (q >= 2) {
       // ---- eps channels: accumulator rows -> shared memory [position][channel]
       const int ch = (q - 2) * 32 + lane;
@@ -281,7 +336,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_tc_kernel(const __gri
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * CP_N);
+    tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -368,23 +423,36 @@ __global__ void __launch_bounds__(CP_THREADS, 1) conv_pool_pair_kernel(const __g
     // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
     constexpr uint32_t idesc = idesc_bf16(CP_M, PAIR_N);
     bool ok = warp_mbar_wait(filt_full, 0, 2);
-    const uint32_t filt_addr = smem_u32(filt);
+    // straight-line issue (see conv_pool_tc_kernel): descriptor = constant + offset in 16-byte units
+    const uint64_t a_desc0 = smem_desc_sw64(smem_u32(filt));
+    const uint64_t b_desc0 = smem_desc_sw64(smem_u32(stage0));
+    uint32_t boff[9];
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      const int ti = t / p.kw, tj = t - ti * p.kw;
+      boff[t] = uint32_t(2 * (ti * PAIR_W + tj) * 64) >> 4;
+    }
+    auto issue_tap = [&](uint32_t acc, uint64_t bd, int t) {
+      const uint64_t a = a_desc0 + uint64_t(uint32_t(t) * uint32_t(TAP_BYTES >> 4));
+#pragma unroll
+      for (int k = 0; k < 2; ++k)
+        warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
+    };
     int i = 0;
     for (int64_t pr = blockIdx.x; pr < pairs && ok; pr += gridDim.x, ++i) {
       const int s = i % stages, a2 = i & 1;
       ok = warp_mbar_wait(&acc_empty[a2], ((i >> 1) & 1) ^ 1, 2) && warp_mbar_wait(&full[s], (i / stages) & 1, 2);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t st = smem_u32(stage0 + size_t(s) * STAGE_BYTES);
+      const uint64_t b_desc = b_desc0 + uint64_t(uint32_t(s) * uint32_t(STAGE_BYTES >> 4));
       const uint32_t acc = tmem_base + uint32_t(a2 * PAIR_N);
-      for (int ti = 0, t = 0; ti < p.kh; ++ti)
-        for (int tj = 0; tj < p.kw; ++tj, ++t) {
-          const uint64_t a = smem_desc_sw64(filt_addr + uint32_t(t) * TAP_BYTES);
-          const uint64_t bd = smem_desc_sw64(st + uint32_t(2 * (ti * PAIR_W + tj)) * 64u);
 #pragma unroll
-          for (int k = 0; k < 2; ++k)
-            warp_mma_bf16(acc, a + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (t > 0 || k > 0) ? 1u : 0u);
-        }
+      for (int t = 0; t < 9; ++t)
+        if (t < taps) issue_tap(acc, b_desc + uint64_t(boff[t]), t);
+      for (int t = 9; t < taps; ++t) {
+        const int ti = t / p.kw, tj = t - ti * p.kw;
+        issue_tap(acc, b_desc + uint64_t(uint32_t(2 * (ti * PAIR_W + tj) * 64) >> 4), t);
+      }
       warp_mma_commit(&empty[s]);
       warp_mma_commit(&acc_full[a2]);
     }

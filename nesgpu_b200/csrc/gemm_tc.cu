@@ -86,20 +86,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
   } else if (warp == 1) {
     // ---- MMA issuer: the whole warp runs this loop in converged control flow, one elected lane issues
     constexpr uint32_t idesc = BF16 ? idesc_bf16(BM, BN) : idesc_tf32(BM, BN);
+    // descriptors are a constant plus an offset in 16-byte units: the stage's tiles lie TILE_BYTES apart
+    const uint64_t desc0 = smem_desc_sw128(smem_u32(tiles));
+    constexpr uint32_t TILE_UNITS = TILE_BYTES >> 4;
     bool ok = true;
+    int s = 0;
+    uint32_t ph = 0;
     for (int kt = 0; kt < nk && ok; ++kt) {
-      const int s = kt % stages;
-      const uint32_t ph = (kt / stages) & 1;
       ok = warp_mbar_wait(&full[s], ph, 2);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t st = smem_u32(tiles + size_t(s) * STAGE_BYTES);
-      const uint64_t a_hi = smem_desc_sw128(st), b_hi = smem_desc_sw128(st + TILE_BYTES);
+      const uint64_t a_hi = desc0 + uint64_t(uint32_t(s) * uint32_t(STAGE_BYTES >> 4));
+      const uint64_t b_hi = a_hi + TILE_UNITS;
 #pragma unroll
       for (int k = 0; k < BKE / 8; ++k) {            // advance 32 bytes (2 descriptor units) per K = 8
         const uint64_t adv = uint64_t(k * 2);
         if (TERMS == 3) {
-          const uint64_t a_lo = smem_desc_sw128(st + 2 * TILE_BYTES), b_lo = smem_desc_sw128(st + 3 * TILE_BYTES);
+          const uint64_t a_lo = a_hi + 2 * TILE_UNITS, b_lo = a_hi + 3 * TILE_UNITS;
           warp_mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           warp_mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
           warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
@@ -110,6 +113,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
         }
       }
       warp_mma_commit(&empty[s]);            // frees the stage once these MMAs have read it
+      if (++s == stages) { s = 0; ph ^= 1u; }
     }
     warp_mma_commit(accum);                  // accumulator complete (or abandoned: epilogue checks the error word)
   } else {
