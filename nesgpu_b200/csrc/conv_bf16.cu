@@ -52,6 +52,7 @@ struct ConvBfParams {
   const float* noise; const int16_t* omap; const int16_t* imap; int in_sp;
   const float* weight_t; const float* noise_t;    // (n, tap, c) re-ordered fp32 copies for noise_kind 2
   int identity_in;
+  int dense_vec;                 // dense noise: weight and noise are 16-byte aligned (vector path of the filter build)
 };
 
 __device__ __forceinline__ void bf_unit_range(const ConvBfParams& p, int sg, long long& r0, long long& r1, float& s) {
@@ -299,7 +300,41 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       if (!mbar_wait_relaxed(wd_free, (ul & 1) ^ 1, 4)) { ok = false; break; }
       CONV_TRACE(threadIdx.x == 128, t, 9);
 
-      if (p.noise_kind == 1) {
+      if (p.noise_kind == 1 && ksz == 9 && p.dense_vec) {
+        // dense member noise in its native (n, c, tap) order, 3x3 filters: a thread takes four consecutive channels
+        // of one filter row = 36 consecutive floats (nine 16-byte loads of W and of E_d, all in flight together); with
+        // the loops unrolled every element's tap and channel are compile-time constants, and the four channels of a
+        // tap go to shared memory as one 8-byte store per copy
+        const int quads_per_row = p.Cin >> 2;
+        const int nquads = p.Cout * quads_per_row;
+        const float4* W4 = reinterpret_cast<const float4*>(p.weight);
+        const float4* E4 = reinterpret_cast<const float4*>(p.noise + size_t(d) * p.Cout * K);
+        for (int quad = bt; quad < nquads; quad += 256) {
+          const int n = quad / quads_per_row, c0 = (quad - n * quads_per_row) * 4;
+          float f[36];
+#pragma unroll
+          for (int i = 0; i < 9; ++i) {
+            const float4 w = __ldg(W4 + size_t(quad) * 9 + i);
+            const float4 e = __ldcs(E4 + size_t(quad) * 9 + i);
+            f[4 * i] = fmaf(s, e.x, w.x); f[4 * i + 1] = fmaf(s, e.y, w.y);
+            f[4 * i + 2] = fmaf(s, e.z, w.z); f[4 * i + 3] = fmaf(s, e.w, w.w);
+          }
+          unsigned char* rowp = wd + (n >> 3) * 1024 + (n & 7) * 128;
+#pragma unroll
+          for (int tap = 0; tap < 9; ++tap) {
+            const int kk = tap * p.Cin + c0;                 // element j of the run is channel j / 9, tap j % 9
+            const int jc = kk >> 6, col = kk & 63;
+            unsigned char* dst = rowp + size_t(jc) * wd_chunk_bytes + ((((col >> 3) ^ (n & 7))) << 4) + (col & 7) * 2;
+            const float v0 = f[tap], v1 = f[9 + tap], v2 = f[18 + tap], v3 = f[27 + tap];
+            const uint32_t p01 = pack_bf16(v0, v1), p23 = pack_bf16(v2, v3);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(p01, p23);
+            if (TERMS == 3)
+              *reinterpret_cast<uint2*>(dst + lo_off) =
+                  make_uint2(pack_bf16(v0 - __uint_as_float(p01 << 16), v1 - __uint_as_float(p01 & 0xffff0000u)),
+                             pack_bf16(v2 - __uint_as_float(p23 << 16), v3 - __uint_as_float(p23 & 0xffff0000u)));
+          }
+        }
+      } else if (p.noise_kind == 1) {
         // dense member noise in its native (n, c, tap) order: coalesced reads, scattered 2-byte writes
         const int total = p.Cout * K;
         const float* E = p.noise + size_t(d) * total;
@@ -1063,6 +1098,7 @@ static int perturbed_conv_bf16(int terms, const float* x, const float* weight, c
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 1; pl.p.noise = noise; pl.p.omap = nullptr; pl.p.imap = nullptr; pl.p.in_sp = Cin;
   pl.p.weight_t = nullptr; pl.p.noise_t = nullptr; pl.p.identity_in = 1;
+  pl.p.dense_vec = (aligned16(weight) && aligned16(noise)) ? 1 : 0;
   return run_conv_bf16(pl, x, scratch, as_stream(stream), "perturbed_conv2d_fwd_bf16", terms);
 }
 
@@ -1124,6 +1160,7 @@ static int permuted_conv_bf16(int terms, const float* x, const float* weight, co
   pl.p.weight = weight; pl.p.bias = bias; pl.p.bias_noise = bias_noise; pl.p.y = y;
   pl.p.noise_kind = 2; pl.p.noise = eps; pl.p.omap = omap; pl.p.imap = imap; pl.p.in_sp = in_sp;
   pl.p.weight_t = weight_t; pl.p.noise_t = eps_t; pl.p.identity_in = (pin == nullptr) ? 1 : 0;
+  pl.p.dense_vec = 0;
   return run_conv_bf16(pl, x, scratch, st, "permuted_conv2d_fwd_bf16", terms);
 }
 
