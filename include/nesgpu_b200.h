@@ -203,7 +203,8 @@ int nes_permuted_linear_fwd(const float* x, const float* weight, const float* bi
 /* The same layer without output permutations (pout == NULL) as ONE tensor-core product
  *   y = [ x | s(r) * xg ] . [ weight | eps ]^T + bias + s(r) * bias_noise[d]
  * (K = in + in_sp): a pre-pass writes the concatenated, TF32-rounded (mode 1), bf16 (mode 2; kind::f16
- * MMAs, relative error ~3e-3) or hi/lo-split (mode 3, fp32-level accuracy) operand into `scratch`, then
+ * MMAs, relative error ~3e-3) or hi/lo-split operand (mode 3: tf32 parts, 3xTF32; mode 4: bf16 parts, three
+ * kind::f16 products, half the operand bytes of mode 3; both at fp32-level accuracy) into `scratch`, then
  * the tcgen05 tile kernel of nes_linear_fwd_tc runs on it with the per-member bias term in its epilogue.  Rows of eps at or above out_sp count as zero.
  * Replaces the same reference lines (modules/base.py:487-508) for input-permuted layers. */
 int64_t nes_permuted_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out,

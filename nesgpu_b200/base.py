@@ -564,20 +564,21 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
     SINGLE_PRODUCT_MIN_ROWS = 64 * 128
 
     def _single_product_mode(self, rows, pout):
-        """Mode (1 = TF32, 2 = bf16, 3 = 3xTF32) of the one-product tensor-core forward, or 0 for the CUDA-core
-        kernels.
+        """Mode (1 = TF32, 2 = bf16, 3 = 3xTF32, 4 = split-bf16) of the one-product tensor-core forward, or 0 for the
+        CUDA-core kernels.
 
-        ``options["tc"]``: ``"3xtf32"`` / ``"tf32"`` / ``"bf16"`` force it, ``"fp32"`` forbids it; by default ("auto") the
-        error-compensated 3xTF32 form (fp32-level accuracy) is taken for batches of at least
-        ``SINGLE_PRODUCT_MIN_ROWS`` rows.  It needs a layer without output permutations."""
+        ``options["tc"]``: ``"bf16x3"`` / ``"3xtf32"`` / ``"tf32"`` / ``"bf16"`` force it, ``"fp32"`` forbids it; by
+        default ("auto") the split-bf16 form (three products on bf16 hi / lo parts, fp32-level accuracy, half the
+        operand bytes of 3xTF32) is taken for batches of at least ``SINGLE_PRODUCT_MIN_ROWS`` rows.  It needs a layer
+        without output permutations."""
         mode = self.options.get("tc", "auto")
-        if mode not in ("auto", "fp32", "3xtf32", "tf32", "bf16"):
-            raise NotImplementedError('options["tc"] must be "auto", "3xtf32", "tf32", "bf16" or "fp32"')
+        if mode not in ("auto", "fp32", "bf16x3", "3xtf32", "tf32", "bf16"):
+            raise NotImplementedError('options["tc"] must be "auto", "bf16x3", "3xtf32", "tf32", "bf16" or "fp32"')
         if mode == "fp32" or pout is not None or rows == 0:
             return 0
         if mode == "auto":
-            return 3 if rows >= self.SINGLE_PRODUCT_MIN_ROWS else 0
-        return {"3xtf32": 3, "tf32": 1, "bf16": 2}[mode]
+            return 4 if rows >= self.SINGLE_PRODUCT_MIN_ROWS else 0
+        return {"bf16x3": 4, "3xtf32": 3, "tf32": 1, "bf16": 2}[mode]
 
     def _cluster_kernel_mode(self, x, R, pin):
         """Mode (3 = 3xTF32, 1 = TF32) of the one-launch tensor-core forward for layers without input
@@ -606,7 +607,7 @@ class PermutedLinear(nn.Linear, _LinearMixin, Permuted):
         mode = self._single_product_mode(x.shape[0], pout)
         cluster_mode = self._cluster_kernel_mode(x, R, pin)
         self.last_path = ("3xtf32" if cluster_mode == 3 else "tf32") if cluster_mode else (
-            {1: "tf32", 2: "bf16", 3: "3xtf32"}[mode] if mode else "fp32")
+            {1: "tf32", 2: "bf16", 3: "3xtf32", 4: "bf16x3"}[mode] if mode else "fp32")
         if cluster_mode:
             C.call("nes_permuted_linear_out_fwd_tc", C.ptr(x), C.ptr(_opt(self.weight)), C.ptr(_opt(self.bias)),
                    C.ptr(eps), C.ptr(beta), C.ptr(pout), C.ptr(y), self.directions, R, self.in_features,

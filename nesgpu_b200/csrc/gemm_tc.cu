@@ -103,9 +103,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_tf32_kernel(const __grid_con
         const uint64_t adv = uint64_t(k * 2);
         if (TERMS == 3) {
           const uint64_t a_lo = a_hi + 2 * TILE_UNITS, b_lo = a_hi + 3 * TILE_UNITS;
-          warp_mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          warp_mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-          warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+          if (BF16) {
+            warp_mma_bf16(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            warp_mma_bf16(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+            warp_mma_bf16(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+          } else {
+            warp_mma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            warp_mma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+            warp_mma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+          }
         } else if (BF16) {
           warp_mma_bf16(tmem_base, a_hi + adv, b_hi + adv, idesc, (kt > 0 || k > 0) ? 1u : 0u);
         } else {
@@ -231,6 +237,13 @@ __global__ void __launch_bounds__(256) permuted_operand_kernel(const float* __re
         w.x = *reinterpret_cast<uint32_t*>(&p0);
         w.y = *reinterpret_cast<uint32_t*>(&p1);
         *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(hi) + b * K2 + k0) = w;
+        if (lo) {                  // split form: what the bf16 rounding left over, again as bf16
+          p0 = __floats2bfloat162_rn(a[0] - __uint_as_float(w.x << 16), a[1] - __uint_as_float(w.x & 0xffff0000u));
+          p1 = __floats2bfloat162_rn(a[2] - __uint_as_float(w.y << 16), a[3] - __uint_as_float(w.y & 0xffff0000u));
+          w.x = *reinterpret_cast<uint32_t*>(&p0);
+          w.y = *reinterpret_cast<uint32_t*>(&p1);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(lo) + b * K2 + k0) = w;
+        }
       } else {
         float h[4];
 #pragma unroll
@@ -255,7 +268,9 @@ __global__ void permuted_filter_kernel(const float* __restrict__ w, const float*
   if (k < in) a = w[o * in + k];
   else if (k < in + in_sp && o < out_sp) a = eps[o * in_sp + (k - in)];
   if (BF16) {
-    reinterpret_cast<__nv_bfloat16*>(hi)[i] = __float2bfloat16_rn(a);
+    const __nv_bfloat16 h = __float2bfloat16_rn(a);
+    reinterpret_cast<__nv_bfloat16*>(hi)[i] = h;
+    if (lo) reinterpret_cast<__nv_bfloat16*>(lo)[i] = __float2bfloat16_rn(a - __bfloat162float(h));
   } else {
     const float h = round_tf32(a);
     hi[i] = h;
@@ -328,22 +343,28 @@ static int run_gemm(const float* a_hi, const float* a_lo, const float* b_hi, con
                     const RowTerm& rt, float* y, int64_t M, int64_t N, int64_t K, int mode, cudaStream_t st, const char* what) {
   int rc;
   Maps maps;
-  const bool bf16 = (mode == 2);
+  // modes: 1 TF32, 2 bf16, 3 3xTF32 (tf32 hi / lo splits), 4 split-bf16 (bf16 hi / lo splits, three products)
+  const bool bf16 = (mode == 2 || mode == 4);
+  const bool three = (mode == 3 || mode == 4);
   if ((rc = make_map(&maps.a_hi, a_hi, M, K, BM, what, bf16)) != NES_OK) return rc;
   if ((rc = make_map(&maps.b_hi, b_hi, N, K, BN, what, bf16)) != NES_OK) return rc;
-  if (mode == 3) {
-    if ((rc = make_map(&maps.a_lo, a_lo, M, K, BM, what)) != NES_OK) return rc;
-    if ((rc = make_map(&maps.b_lo, b_lo, N, K, BN, what)) != NES_OK) return rc;
+  if (three) {
+    if ((rc = make_map(&maps.a_lo, a_lo, M, K, BM, what, bf16)) != NES_OK) return rc;
+    if ((rc = make_map(&maps.b_lo, b_lo, N, K, BN, what, bf16)) != NES_OK) return rc;
   } else {
     maps.a_lo = maps.a_hi;
     maps.b_lo = maps.b_hi;
   }
-  const int stages = (mode == 3) ? 3 : 4;
-  const int stage_bytes = (mode == 3 ? 4 : 2) * TILE_BYTES;
+  const int stages = three ? 3 : 4;
+  const int stage_bytes = (three ? 4 : 2) * TILE_BYTES;
   const size_t smem = 1024 + size_t(stages) * stage_bytes + (2 * stages + 1) * sizeof(uint64_t) + 16;
   dim3 grid((unsigned)ceil_div<int64_t>(M, BM), (unsigned)ceil_div<int64_t>(N, BN));
   cudaError_t e;
-  if (mode == 3) {
+  if (mode == 4) {
+    e = cudaFuncSetAttribute(gemm_tf32_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
+    gemm_tf32_kernel<3, true><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
+  } else if (mode == 3) {
     e = cudaFuncSetAttribute(gemm_tf32_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "%s: shared memory opt-in failed: %s", what, cudaGetErrorString(e));
     gemm_tf32_kernel<3><<<grid, NTHREADS, smem, st>>>(maps, bias, rt, y, int(M), int(N), int(K), stages);
@@ -467,15 +488,15 @@ extern "C" int nes_synthetic_linear_fwd_tc(const float* x, const float* weight, 
 
 // row length of the concatenated operand: a multiple of 16 bytes (4 fp32 / 8 bf16)
 static int64_t permuted_k2(int64_t in, int64_t in_sp, int mode) {
-  return mode == 2 ? ((in + in_sp + 7) & ~int64_t(7)) : ((in + in_sp + 3) & ~int64_t(3));
+  return (mode == 2 || mode == 4) ? ((in + in_sp + 7) & ~int64_t(7)) : ((in + in_sp + 3) & ~int64_t(3));
 }
 
 extern "C" int64_t nes_permuted_linear_fwd_tc_scratch_bytes(int64_t D, int64_t R, int64_t in, int64_t out, int64_t in_sp, int mode) {
   if (D <= 0 || R <= 0 || out <= 0 || in < 0 || in_sp < 0) return 0;
   const int64_t K2 = permuted_k2(in, in_sp, mode);
-  const int64_t esz = mode == 2 ? 2 : 4;
+  const int64_t esz = (mode == 2 || mode == 4) ? 2 : 4;
   const int64_t a = align256(D * R * K2 * esz), b = align256(out * K2 * esz);
-  return mode == 3 ? 2 * (a + b) : (a + b);
+  return (mode == 3 || mode == 4) ? 2 * (a + b) : (a + b);
 }
 
 extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, const float* bias, const float* eps,
@@ -485,7 +506,8 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
                                           nes_stream_t stream) {
   NES_REQUIRE(D >= 0 && R >= 0 && in >= 0 && out >= 0 && in_sp >= 0 && out_sp >= 0 && out_sp <= out, NES_ERR_BAD_ARG,
               "permuted_linear_fwd_tc: bad extent");
-  NES_REQUIRE(mode == 1 || mode == 2 || mode == 3, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: mode must be 1 (TF32), 2 (bf16) or 3 (3xTF32)");
+  NES_REQUIRE(mode >= 1 && mode <= 4, NES_ERR_BAD_ARG,
+              "permuted_linear_fwd_tc: mode must be 1 (TF32), 2 (bf16), 3 (3xTF32) or 4 (split-bf16, three products)");
   if (D == 0 || R == 0 || out == 0) return NES_OK;
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: null pointer");
   NES_REQUIRE(pin || in_sp == in, NES_ERR_BAD_ARG, "permuted_linear_fwd_tc: in_sp != in without input permutations");
@@ -498,19 +520,20 @@ extern "C" int nes_permuted_linear_fwd_tc(const float* x, const float* weight, c
               "permuted_linear_fwd_tc: scratch needs %lld bytes, 256-byte aligned", (long long)need);
   cudaStream_t st = as_stream(stream);
   unsigned char* sp = static_cast<unsigned char*>(scratch);
-  const int64_t esz = mode == 2 ? 2 : 4;
+  const bool half_words = (mode == 2 || mode == 4), split = (mode == 3 || mode == 4);
+  const int64_t esz = half_words ? 2 : 4;
   const int64_t a_bytes = align256(B * K2 * esz), b_bytes = align256(out * K2 * esz);
   float* a_hi = reinterpret_cast<float*>(sp);
   float* b_hi = reinterpret_cast<float*>(sp + a_bytes);
-  float* a_lo = mode == 3 ? reinterpret_cast<float*>(sp + a_bytes + b_bytes) : nullptr;
-  float* b_lo = mode == 3 ? reinterpret_cast<float*>(sp + 2 * a_bytes + b_bytes) : nullptr;
+  float* a_lo = split ? reinterpret_cast<float*>(sp + a_bytes + b_bytes) : nullptr;
+  float* b_lo = split ? reinterpret_cast<float*>(sp + 2 * a_bytes + b_bytes) : nullptr;
   const unsigned blocks = (unsigned)(B < int64_t(sm_count()) * 16 ? B : int64_t(sm_count()) * 16);
   const unsigned fblocks = (unsigned)ceil_div<int64_t>(out * K2, 256);
-  if (mode == 2) permuted_operand_kernel<true><<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
+  if (half_words) permuted_operand_kernel<true><<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
   else permuted_operand_kernel<false><<<blocks, 256, 0, st>>>(x, pin, a_hi, a_lo, B, D, R, int(in), int(in_sp), int(K2), antithetic);
   int rc = check_launch("permuted_linear_fwd_tc(operand)");
   if (rc != NES_OK) return rc;
-  if (mode == 2) permuted_filter_kernel<true><<<fblocks, 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
+  if (half_words) permuted_filter_kernel<true><<<fblocks, 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
   else permuted_filter_kernel<false><<<fblocks, 256, 0, st>>>(weight, eps, b_hi, b_lo, out, out_sp, int(in), int(in_sp), int(K2));
   rc = check_launch("permuted_linear_fwd_tc(filter)");
   if (rc != NES_OK) return rc;

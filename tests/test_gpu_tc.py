@@ -250,13 +250,13 @@ def test_config3_permuted_conv_bf16_full_size():
 
 # ---- PermutedLinear as one tensor-core product ----------------------------------------------------
 
-@pytest.mark.parametrize("tc,tol", [("3xtf32", 1e-4), ("tf32", 2e-2), ("bf16", 2e-2)])
+@pytest.mark.parametrize("tc,tol", [("bf16x3", 1e-4), ("3xtf32", 1e-4), ("tf32", 2e-2), ("bf16", 2e-2)])
 @pytest.mark.parametrize("mode,in_sp,out_sp,R,anti,in_f,out_f,bias", [
     ("in", 0, 0, 2, True, 200, 136, True), ("in", 0.1, 0, 3, True, 203, 70, True),
     ("in", 0, 0, 1, False, 64, 10, False), ("in", 0.5, 0, 4, True, 1600, 128, True),
 ])
 def test_permuted_linear_single_product(tc, tol, mode, in_sp, out_sp, R, anti, in_f, out_f, bias):
-    """options["tc"] forces the one-product form; 3xTF32 holds the fp32 bar, TF32 is the stated 2e-2 mode."""
+    """options["tc"] forces the one-product form; split-bf16 and 3xTF32 hold the fp32 bar, TF32 and bf16 are the stated 2e-2 modes."""
     from nesgpu_b200 import base
     from oracle import perturbed_ref as O
     from gpu_util import G, set_params
@@ -301,7 +301,7 @@ def test_permuted_linear_auto_takes_single_product_for_large_batches():
     pin = torch.stack([torch.randperm(in_f, generator=g) for _ in range(D)]).short()
     set_params(layer, W, b)
     layer.weight_noise, layer.bias_noise, layer.input_permutations = G(eps), G(beta), G(pin)
-    assert layer._single_product_mode(R * D, None) == 3 and layer._single_product_mode(64, None) == 0
+    assert layer._single_product_mode(R * D, None) == 4 and layer._single_product_mode(64, None) == 0
     with torch.no_grad():
         layer.perturbed_flag = True
         y = layer.forward(G(x))
