@@ -439,12 +439,17 @@ class PermutedConv64(Workload):
         mode = self.mode()
         bf = mode in ("bf16", "bf16x3")
         peak = peaks["bf16_sustained"] if bf else peaks["bf16_sustained"] / 2
-        kernel = {"tf32": "conv_tf32_kernel (tcgen05 kind::tf32) + stage_input_tf32_kernel",
-                  "bf16": "conv_bf16_kernel<1> (tcgen05 kind::f16) + stage_input_bf16_kernel",
-                  "bf16x3": "conv_bf16_kernel<3> (tcgen05 kind::f16, three products on bf16 hi/lo splits) + stage_input_bf16_kernel",
+        dense = self.name == "perturbed_conv_64"
+        kernel = {"tf32": "conv_tf32_kernel (tcgen05 kind::tf32) + stage_rows_tf32_kernel",
+                  "bf16": "conv_bf16_kernel<1> (tcgen05 kind::f16) + stage_rows_bf16_kernel",
+                  "bf16x3": ("conv_bf16_kernel<3> (tcgen05 kind::f16, three products on bf16 hi/lo splits, operands in shared memory)"
+                             if dense else
+                             "conv_split_tmem_kernel (tcgen05 kind::f16, stacked hi/lo filter operand in tensor memory, two MMAs per "
+                             "K step on the hi and lo input copies)") + " + stage_rows_bf16_kernel",
                   }.get(mode, "gemm_kernel<ConvProb<...>> (implicit-GEMM conv on CUDA cores)")
         note = {"tf32": "TF32 operands (stated reduced precision, bar 2e-2)", "bf16": "bf16 operands (stated reduced precision, bar 2e-2)",
-                "bf16x3": "split-bf16 three-product form: holds the fp32 bar (rel err ~5e-6); the tensor pipe issues 3x the algorithmic flops",
+                "bf16x3": "split-bf16 form: holds the fp32 bar (rel err ~5e-6); the tensor pipe executes 3-4 partial products per "
+                          "algorithmic product",
                 }.get(mode, "fp32 CUDA-core path (exact-fp32 parity)")
         return {"kernel": kernel + ", forward phase", "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(ach / peak, 4), "peak_source": peaks["source"] + (" bf16 sustained" if bf else " bf16 sustained / 2 taken as TF32"),
