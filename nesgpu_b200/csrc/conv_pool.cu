@@ -127,6 +127,112 @@ __global__ void __launch_bounds__(CP_WARPS * 32) shared_conv_pool_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Table form of the same layer.  Before the bias term, a stored value only depends on (channel c, noise map so,
+// pooled pixel): pooled_max(conv(x, W)[c] + s * conv(x, eps)[so]).  With 1024 members and 32 channels an image has
+// 32768 (member, channel) pairs but only Cout x (out_sp + 1) such maps, so a block first builds the table of pooled
+// maps for ONE image and TB_CG channels in shared memory -- [channel][noise map, or none][pooled pixel], fp32 -- and
+// then every member only looks its values up, adds its bias term, applies the ReLU, converts and stores: about six
+// instructions per stored value instead of about forty (four gathered noise reads, four FMAs and the pooling per
+// value).  The arithmetic is the same as in shared_conv_pool_kernel, operation for operation.  A block takes 16
+// channels and half of the pooled pixels (the table of more does not fit): 16 bf16 channels are one 32-byte sector,
+// and a block has to write whole sectors -- with 8 channels per block the other half of every sector arrived from
+// another block much later and the bf16 forms ran 30 % slower than the kernel above.  A lane of the second phase owns
+// two neighbouring channels of one pooled pixel: stores are 4 bytes (bf16 pairs) or 8 bytes wide, eight lanes per pixel.
+constexpr int TB_CG = 16;         // channels per block
+constexpr int TB_SPLIT = 2;       // pixel ranges per image and channel group
+constexpr int TB_THREADS = 1024;
+
+template <int MODE>
+__global__ void __launch_bounds__(TB_THREADS) shared_conv_pool_table_kernel(
+    const float* __restrict__ z, const float* __restrict__ bias, const float* __restrict__ bias_noise,
+    const int16_t* __restrict__ pout, typename OutType<MODE>::type* __restrict__ y, int64_t R, int64_t D, int Cout, int osp,
+    int Ho, int Wo, int antithetic, int members_per_block) {
+  typedef typename OutType<MODE>::type out_t;
+  extern __shared__ __align__(16) float table[];                  // [TB_CG][osp + 1][npix]
+  const int hw = Ho * Wo;
+  const int Hp = Ho / 2, Wp = Wo / 2, pooled = Hp * Wp;
+  const int nslots = osp + 1;                                     // slot osp: the channel carries no noise
+  const int64_t r = blockIdx.x;
+  const int cbase = blockIdx.y * TB_CG;
+  const int part = blockIdx.z % TB_SPLIT;                         // which range of the pooled pixels
+  const int per_part = (pooled + TB_SPLIT - 1) / TB_SPLIT;
+  const int pix0 = part * per_part;
+  const int npix = (pix0 + per_part < pooled ? pix0 + per_part : pooled) - pix0;
+  const int64_t d0 = int64_t(blockIdx.z / TB_SPLIT) * members_per_block;
+  const int nm = int((d0 + members_per_block < D ? d0 + members_per_block : D) - d0);
+  const float sgn = anti_sign(r, R, antithetic);
+  const float* zr = z + r * int64_t(Cout + osp) * hw;
+  // phase 1: the pooled maps.  p00 is even (2 * px and 2 * py * Wo are), so the window's rows are read as pairs
+  // when Wo is even too
+  const bool pairs = (Wo % 2 == 0) && ((reinterpret_cast<uintptr_t>(zr) & 7u) == 0) && (hw % 2 == 0);
+  for (int e = threadIdx.x; e < nslots * npix; e += TB_THREADS) {
+    const int so = e / npix, pl = e - so * npix;
+    const int pp = pix0 + pl;
+    const int py = pp / Wp, px = pp - py * Wp;
+    const int p00 = (2 * py) * Wo + 2 * px;
+    float n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
+    if (so < osp) {
+      const float* np = zr + size_t(Cout + so) * hw + p00;
+      if (pairs) {
+        const float2 a = *reinterpret_cast<const float2*>(np), b = *reinterpret_cast<const float2*>(np + Wo);
+        n0 = a.x; n1 = a.y; n2 = b.x; n3 = b.y;
+      } else {
+        n0 = np[0]; n1 = np[1]; n2 = np[Wo]; n3 = np[Wo + 1];
+      }
+    }
+#pragma unroll
+    for (int cl = 0; cl < TB_CG; ++cl) {
+      const float* wp = zr + size_t(cbase + cl) * hw + p00;
+      float b0, b1, b2, b3;
+      if (pairs) {
+        const float2 a = *reinterpret_cast<const float2*>(wp), b = *reinterpret_cast<const float2*>(wp + Wo);
+        b0 = a.x; b1 = a.y; b2 = b.x; b3 = b.y;
+      } else {
+        b0 = wp[0]; b1 = wp[1]; b2 = wp[Wo]; b3 = wp[Wo + 1];
+      }
+      table[(cl * nslots + so) * npix + pl] =
+          fmaxf(fmaxf(fmaf(sgn, n0, b0), fmaf(sgn, n1, b1)), fmaxf(fmaf(sgn, n2, b2), fmaf(sgn, n3, b3)));
+    }
+  }
+  __syncthreads();
+  // phase 2: a warp takes members in turn; lane = (pixel slot, channel pair)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int cp = lane & 7, ps = lane >> 3;
+  const int c0 = cbase + 2 * cp;
+  const int64_t member_stride = int64_t(pooled) * Cout;
+  const int64_t lo_off = R * D * member_stride;                   // split form: the lo copy follows the hi copy
+  const float bias0 = bias ? bias[c0] : 0.f, bias1 = bias ? bias[c0 + 1] : 0.f;
+  for (int m = warp; m < nm; m += TB_THREADS / 32) {
+    const int64_t d = d0 + m;
+    int so0 = pout ? int(pout[d * Cout + c0]) : c0, so1 = pout ? int(pout[d * Cout + c0 + 1]) : c0 + 1;
+    if (so0 >= osp) so0 = osp;
+    if (so1 >= osp) so1 = osp;
+    const float add0 = bias0 + (bias_noise ? sgn * bias_noise[d * Cout + c0] : 0.f);
+    const float add1 = bias1 + (bias_noise ? sgn * bias_noise[d * Cout + c0 + 1] : 0.f);
+    const float* t0 = table + ((2 * cp) * nslots + so0) * npix;
+    const float* t1 = table + ((2 * cp + 1) * nslots + so1) * npix;
+    // MODE 3: images b = 2q and 2q + 1 share rows, [q][pooled pixel][image][channel]
+    const int64_t b = r * D + d;
+    out_t* o = (MODE == 3) ? y + (((b >> 1) * pooled) * 2 + (b & 1)) * Cout + c0 : y + b * member_stride + c0;
+    const int64_t pix = (MODE == 3) ? 2 * int64_t(Cout) : int64_t(Cout);
+    for (int pl = ps; pl < npix; pl += 4) {
+      const float v0 = fmaxf(t0[pl] + add0, 0.f), v1 = fmaxf(t1[pl] + add1, 0.f);
+      out_t* op = o + (pix0 + pl) * pix;
+      if constexpr (MODE == 0) {
+        *reinterpret_cast<float2*>(op) = make_float2(v0, v1);
+      } else if constexpr (MODE == 1) {
+        *reinterpret_cast<float2*>(op) = make_float2(round_to_tf32(v0), round_to_tf32(v1));
+      } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+        *reinterpret_cast<__nv_bfloat162*>(op) = h;
+        if constexpr (MODE == 4)
+          *reinterpret_cast<__nv_bfloat162*>(op + lo_off) = __floats2bfloat162_rn(v0 - __low2float(h), v1 - __high2float(h));
+      }
+    }
+  }
+}
+
 }  // namespace nes
 
 using namespace nes;
@@ -144,6 +250,34 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   NES_REQUIRE(z && y, NES_ERR_BAD_ARG, "shared_conv_pool_fwd: null pointer");
   NES_REQUIRE(R <= INT32_MAX && Cout <= 32767, NES_ERR_UNSUPPORTED, "shared_conv_pool_fwd: extent too large");
   const int64_t hw = int64_t(Ho) * Wo;
+  cudaStream_t st = as_stream(stream);
+  {
+    // table form: Cout a multiple of TB_CG, the table of one channel group and pixel range within shared memory, 8-byte
+    // aligned stores
+    const int64_t pooled_t = int64_t(Ho / 2) * (Wo / 2);
+    const size_t tbytes = size_t(TB_CG) * size_t(out_sp + 1) * size_t(ceil_div<int64_t>(pooled_t, TB_SPLIT)) * sizeof(float);
+    if (Cout % TB_CG == 0 && tbytes <= 200 * 1024 && (reinterpret_cast<uintptr_t>(y) & 7u) == 0 && Cout / TB_CG <= 65535) {
+      // members per block: all of them unless that leaves SMs idle
+      const int64_t groups = R * (Cout / TB_CG) * TB_SPLIT;
+      int64_t chunks = 1;
+      while (groups * chunks < sm_count() && D / (chunks * 2) >= 64) chunks *= 2;
+      const int64_t per_t = ceil_div<int64_t>(D, chunks);
+      dim3 tgrid((unsigned)R, (unsigned)(Cout / TB_CG), (unsigned)(ceil_div<int64_t>(D, per_t) * TB_SPLIT));
+      cudaError_t te;
+#define NES_LAUNCH_SHARED_CONV_POOL_TABLE(MODE, T)                                                                       \
+  te = cudaFuncSetAttribute(shared_conv_pool_table_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tbytes); \
+  if (te != cudaSuccess) return fail(NES_ERR_LAUNCH, "shared_conv_pool_fwd: shared memory opt-in failed: %s", cudaGetErrorString(te)); \
+  shared_conv_pool_table_kernel<MODE><<<tgrid, TB_THREADS, tbytes, st>>>(z, bias, bias_noise, pout, static_cast<T*>(y), R, D, Cout, \
+                                                                        out_sp, Ho, Wo, antithetic, int(per_t))
+      if (out_mode == 4) { NES_LAUNCH_SHARED_CONV_POOL_TABLE(4, __nv_bfloat16); }
+      else if (out_mode == 3) { NES_LAUNCH_SHARED_CONV_POOL_TABLE(3, __nv_bfloat16); }
+      else if (out_mode == 2) { NES_LAUNCH_SHARED_CONV_POOL_TABLE(2, __nv_bfloat16); }
+      else if (out_mode == 1) { NES_LAUNCH_SHARED_CONV_POOL_TABLE(1, float); }
+      else { NES_LAUNCH_SHARED_CONV_POOL_TABLE(0, float); }
+#undef NES_LAUNCH_SHARED_CONV_POOL_TABLE
+      return check_launch("shared_conv_pool_fwd(table)");
+    }
+  }
   const size_t limit = 220 * 1024;
   const size_t plane_bytes = ((size_t(Cout) * size_t(hw | 1) + size_t(hw) * size_t(out_sp | 1) + 1) & ~size_t(1)) * sizeof(float);
   const size_t member_bytes = size_t(Cout) * 10;                // one float2 and one int16 per channel
@@ -168,7 +302,6 @@ extern "C" int nes_shared_conv_pool_fwd(const float* z, const float* bias, const
   const size_t smem = plane_bytes + size_t(per) * member_bytes + 16;
   dim3 grid((unsigned)R, (unsigned)ceil_div<int64_t>(D, per));
   cudaError_t e;
-  cudaStream_t st = as_stream(stream);
 #define NES_LAUNCH_SHARED_CONV_POOL(MODE, T)                                                                             \
   e = cudaFuncSetAttribute(shared_conv_pool_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
   if (e != cudaSuccess) return fail(NES_ERR_LAUNCH, "shared_conv_pool_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); \
