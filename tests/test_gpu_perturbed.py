@@ -456,6 +456,8 @@ def test_population_model_end_to_end(base):
     (1, 32, 0, 28, 3, 0, 3, False, True),      # first layer of the small CNN
     (3, 40, 0.5, 15, 3, 1, 4, True, True),     # odd output size (floor pooling), sparsity, antithetic halves
     (2, 8, 0, 9, 2, 0, 1, True, False),
+    # 16-channel multiples take the table form: odd map width (no paired loads), sparsity, antithetic halves, no bias
+    (3, 48, 0.5, 15, 3, 1, 4, True, True), (2, 16, 0.25, 11, 2, 0, 2, True, False),
 ])
 def test_shared_input_conv_relu_pool(base, cin, cout, out_sp, hw, k, pad, R, anti, bias):
     """options shared_input + fuse: every member sees the same images; result equals the oracle's layer on the
