@@ -65,10 +65,31 @@ def takes_shared_input(perturbed_model):
 PAIRS_PER_CHUNK = 65536      # member-example pairs per forward call: launches amortised, activations bounded (a few GB)
 
 
-def auto_chunk(directions, examples):
+def auto_chunk(directions, examples, sms=None):
     """Examples per forward call such that a call evaluates about ``PAIRS_PER_CHUNK`` member-example pairs
-    (64 for 1024 members; the whole minibatch for small populations, where launches would dominate)."""
-    return max(1, min(int(examples), PAIRS_PER_CHUNK // max(int(directions), 1)))
+    (64 for 1024 members; the whole minibatch for small populations, where launches would dominate).
+
+    With ``sms`` (the GPU's SM count) the size is adjusted by up to a quarter either way so that the calls fill whole
+    waves: the layer kernels work through a call in tiles of 128 batch rows, one tile per SM at a time, and a call of
+    64 x 1024 rows is 512 tiles = 3.46 waves of 148 SMs, while 74 x 1024 rows are exactly four.  Among the even sizes
+    in range (antithetic layers halve every call) the one with the fewest waves over the whole minibatch wins; ties go
+    to the size nearest the plain choice."""
+    base = max(1, min(int(examples), PAIRS_PER_CHUNK // max(int(directions), 1)))
+    if not sms or base >= int(examples) or base < 8:
+        return base
+    best, best_cost = base, None
+    for c in range(max(2, (base * 3) // 4), (base * 5) // 4 + 1):
+        if c % 2:
+            continue
+        cost, left = 0, int(examples)
+        while left > 0:
+            n = min(c, left)
+            tiles = -(-n * int(directions) // 128)
+            cost += -(-tiles // int(sms))
+            left -= n
+        if best_cost is None or cost < best_cost or (cost == best_cost and abs(c - base) < abs(best - base)):
+            best, best_cost = c, cost
+    return best
 
 
 _side_streams = {}
@@ -96,7 +117,11 @@ def population_fitness(perturbed_model, inputs, labels, directions, chunk=None, 
     bf16 mode and cost 0.9 ms in the TF32 mode, whose fp32 activations are four times larger."""
     R = inputs.shape[0]
     if chunk is None:
-        chunk = auto_chunk(directions, R)
+        # whole waves per call pay when the calls run one after another (measured on the small CNN: 7.90 -> 7.67 ms);
+        # with several streams equal calls balance the streams better (5.39 -> 5.56 ms with the adjusted size)
+        one_stream = inputs.is_cuda and int(streams) <= 1
+        sms = torch.cuda.get_device_properties(inputs.device).multi_processor_count if one_stream else None
+        chunk = auto_chunk(directions, R, sms)
     shared = takes_shared_input(perturbed_model)
     starts = list(range(0, R, chunk))
     lanes = _streams(inputs.device, max(1, min(int(streams), len(starts)))) if inputs.is_cuda else [None]

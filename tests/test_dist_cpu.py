@@ -114,3 +114,5 @@ def test_auto_chunk():
     from nesgpu_b200 import es
     assert es.auto_chunk(1024, 256) == 64 and es.auto_chunk(64, 256) == 256 and es.auto_chunk(8192, 256) == 8
     assert es.auto_chunk(100000, 256) == 1 and es.auto_chunk(1, 7) == 7 and es.auto_chunk(65536, 256) == 1
+    # with the SM count the calls fill whole waves of 128-row tiles: 74 x 1024 rows = 592 tiles = 4 x 148
+    assert es.auto_chunk(1024, 256, 148) == 74 and es.auto_chunk(64, 256, 148) == 256 and es.auto_chunk(8192, 256, 148) == 8
