@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
-  uint32_t* tap_off = reinterpret_cast<uint32_t*>(tables + 2 * size_t(table_bytes));
-  float* xpose = reinterpret_cast<float*>(tap_off + 2 * p.kh * p.kw);     // [8 warps][rows per warp][33] epilogue transpose
+  // [8 warps][rows per warp][33] epilogue transpose (8 bytes per tap of spare room lie in front of it)
+  float* xpose = reinterpret_cast<float*>(tables + 2 * size_t(table_bytes) + 8 * size_t(p.kh) * p.kw);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksz = p.kh * p.kw;

@@ -73,7 +73,6 @@ __global__ void __launch_bounds__(CONV_THREADS, 1) conv_tf32_kernel(const float*
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;    // two parities
-  uint32_t* tap_off = reinterpret_cast<uint32_t*>(tables + 2 * size_t(table_bytes));   // [ksz][2] descriptor offsets
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ksz = p.kh * p.kw;
