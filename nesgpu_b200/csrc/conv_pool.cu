@@ -203,13 +203,25 @@ __global__ void __launch_bounds__(TB_THREADS) shared_conv_pool_table_kernel(
   const int64_t member_stride = int64_t(pooled) * Cout;
   const int64_t lo_off = R * D * member_stride;                   // split form: the lo copy follows the hi copy
   const float bias0 = bias ? bias[c0] : 0.f, bias1 = bias ? bias[c0 + 1] : 0.f;
+  // a member's noise-map indices and bias terms come from global memory: the next member's are requested before
+  // this member's look-ups start, so that their latency is not paid per member
+  auto member_terms = [&](int m, int& so0, int& so1, float& a0, float& a1) {
+    const int64_t d = d0 + m;
+    so0 = pout ? int(pout[d * Cout + c0]) : c0;
+    so1 = pout ? int(pout[d * Cout + c0 + 1]) : c0 + 1;
+    a0 = bias_noise ? bias_noise[d * Cout + c0] : 0.f;
+    a1 = bias_noise ? bias_noise[d * Cout + c0 + 1] : 0.f;
+  };
+  int nso0 = 0, nso1 = 0;
+  float na0 = 0.f, na1 = 0.f;
+  if (warp < nm) member_terms(warp, nso0, nso1, na0, na1);
   for (int m = warp; m < nm; m += TB_THREADS / 32) {
     const int64_t d = d0 + m;
-    int so0 = pout ? int(pout[d * Cout + c0]) : c0, so1 = pout ? int(pout[d * Cout + c0 + 1]) : c0 + 1;
+    int so0 = nso0, so1 = nso1;
+    const float add0 = bias0 + sgn * na0, add1 = bias1 + sgn * na1;
+    if (m + TB_THREADS / 32 < nm) member_terms(m + TB_THREADS / 32, nso0, nso1, na0, na1);
     if (so0 >= osp) so0 = osp;
     if (so1 >= osp) so1 = osp;
-    const float add0 = bias0 + (bias_noise ? sgn * bias_noise[d * Cout + c0] : 0.f);
-    const float add1 = bias1 + (bias_noise ? sgn * bias_noise[d * Cout + c0 + 1] : 0.f);
     const float* t0 = table + ((2 * cp) * nslots + so0) * npix;
     const float* t1 = table + ((2 * cp + 1) * nslots + so1) * npix;
     // MODE 3: images b = 2q and 2q + 1 share rows, [q][pooled pixel][image][channel]
