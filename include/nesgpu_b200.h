@@ -356,6 +356,12 @@ int nes_permuted_conv2d_fwd_bf16(const float* x, const float* weight, const floa
  * (modules/base.py:410-425, 557-588). */
 int nes_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, int kh, int kw, int sh, int sw,
                                     int ph, int pw, int dh, int dw);
+/* The same question for a permuted-noise layer (nes_permuted_conv2d_fwd_bf16x3): output-permuted layers with 64 input
+ * channels, at most 64 output channels and at most 9 taps keep the member filter in tensor memory, which covers
+ * larger images than the shared-memory form. */
+int nes_permuted_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, int kh, int kw, int sh, int sw,
+                                             int ph, int pw, int dh, int dw, int in_sp, int out_sp,
+                                             int input_permutations);
 int64_t nes_conv2d_fwd_bf16x3_scratch_bytes(int64_t D, int64_t R, int Cin, int H, int W, int Cout, int kh, int kw,
                                             int ph, int pw);
 int nes_perturbed_conv2d_fwd_bf16x3(const float* x, const float* weight, const float* bias,

@@ -56,6 +56,7 @@ SIGNATURES = {
     "nes_perturbed_conv2d_fwd_bf16": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_bf16": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
     "nes_conv2d_fwd_bf16x3_supported": [c_int] * 12,
+    "nes_permuted_conv2d_fwd_bf16x3_supported": [c_int] * 15,
     "nes_conv2d_fwd_bf16x3_scratch_bytes": [c_i64, c_i64] + [c_int] * 8,
     "nes_perturbed_conv2d_fwd_bf16x3": [c_ptr] * 6 + [c_i64] * 2 + [c_int] * 12 + [c_int, c_ptr, c_i64, c_ptr],
     "nes_permuted_conv2d_fwd_bf16x3": [c_ptr] * 8 + [c_i64] * 2 + [c_int] * 12 + [c_int] * 3 + [c_ptr, c_i64, c_ptr],
@@ -118,6 +119,7 @@ _RETURNS = {
     "nes_bin_weighted_sum_scratch_bytes": c_i64,
     "nes_permuted_linear_out_fwd_tc_supported": c_int,
     "nes_conv2d_fwd_bf16x3_supported": c_int,
+    "nes_permuted_conv2d_fwd_bf16x3_supported": c_int,
     "nes_conv2d_fwd_bf16x3_scratch_bytes": c_i64,
     "nes_binarized_update_scratch_bytes": c_i64,
     "nes_binarized_linear_fwd_scratch_bytes": c_i64,

@@ -659,7 +659,7 @@ class _ConvMixin:
                x.shape[0], *geom, C.stream())
         return y
 
-    def _tensor_core_mode(self, geom=None):
+    def _tensor_core_mode(self, geom=None, permuted=None):
         """``options["tc"]`` -> entry-point suffix of the tcgen05 path, or None for the CUDA-core kernel.
 
         ``"auto"`` (default) and ``"bf16x3"``: the split-bf16 three-product form, which holds the fp32 bar (relative
@@ -671,8 +671,13 @@ class _ConvMixin:
         if mode not in ("auto", "fp32", "tf32", "bf16", "bf16x3"):
             raise NotImplementedError('options["tc"] for convolutions must be "auto", "fp32", "bf16x3", "tf32" or "bf16"')
         if mode in ("auto", "bf16x3"):
-            covered = geom is not None and C.call("nes_conv2d_fwd_bf16x3_supported", geom[0], geom[1], geom[2], geom[3],
-                                                  *geom[4:12]) == 1
+            if geom is None:
+                covered = False
+            elif permuted is not None:          # (in_sparsity, out_sparsity, has input permutations)
+                covered = C.call("nes_permuted_conv2d_fwd_bf16x3_supported", geom[0], geom[1], geom[2], geom[3], *geom[4:12],
+                                 int(permuted[0]), int(permuted[1]), 1 if permuted[2] else 0) == 1
+            else:
+                covered = C.call("nes_conv2d_fwd_bf16x3_supported", geom[0], geom[1], geom[2], geom[3], *geom[4:12]) == 1
             if covered:
                 return "bf16x3"
             if mode == "bf16x3":
@@ -926,7 +931,7 @@ class PermutedConv2d(nn.Conv2d, _ConvMixin, Permuted):
         R = self._repeats(x.shape[0])
         beta = C.require_cuda(self.bias_noise, "bias_noise", _F32) if self.bias is not None else None
         y = torch.empty((x.shape[0], self.out_channels) + out_hw, device=x.device, dtype=_F32)
-        suffix = self._tensor_core_mode(geom)
+        suffix = self._tensor_core_mode(geom, (self.in_sparsity, self.out_sparsity, pin is not None))
         if suffix in ("bf16", "bf16x3") and pin is None and self.in_sparsity % 8:
             suffix = None if self.options.get("tc", "auto") == "auto" else suffix
         self.last_path = {None: "fp32", "tc": "tf32"}.get(suffix, suffix)

@@ -1083,6 +1083,19 @@ extern "C" int nes_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, 
   return plan_conv_bf16(pl, 1, 1, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, 0, "conv2d_fwd_bf16x3", 3) == NES_OK ? 1 : 0;
 }
 
+// The same question for a permuted-noise layer: output-permuted layers with 64 input channels may also take the form
+// with the filter in tensor memory, which needs far less shared memory (larger images fit).
+extern "C" int nes_permuted_conv2d_fwd_bf16x3_supported(int Cin, int H, int W, int Cout, int kh, int kw, int sh, int sw,
+                                                        int ph, int pw, int dh, int dw, int in_sp, int out_sp,
+                                                        int input_permutations) {
+  if (nes_conv2d_fwd_bf16x3_supported(Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw)) return 1;
+  if (Cin <= 0 || H <= 0 || W <= 0 || Cout <= 0 || kh <= 0 || kw <= 0 || ph < 0 || pw < 0 || dh <= 0 || dw <= 0) return 0;
+  if (dh > 8 || dw > 8 || input_permutations || in_sp != Cin || !tmem_form_covers(Cin, Cout, kh, kw, out_sp)) return 0;
+  ConvBfPlan pl;
+  return plan_conv_bf16(pl, 1, 1, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, 0, "permuted_conv2d_fwd_bf16x3", 3, 1, out_sp) == NES_OK
+             ? 1 : 0;
+}
+
 static int perturbed_conv_bf16(int terms, const float* x, const float* weight, const float* bias,
                                const float* noise, const float* bias_noise, float* y,
                                int64_t D, int64_t R, int Cin, int H, int W, int Cout,
@@ -1129,10 +1142,14 @@ static int permuted_conv_bf16(int terms, const float* x, const float* weight, co
                               void* scratch, int64_t scratch_bytes, nes_stream_t stream) {
   ConvBfPlan pl;
   // the three-term form keeps the filter in tensor memory where that form covers the layer
-  const int form = (terms == 3 && sh == 1 && sw == 1 && pin == nullptr && in_sp == Cin &&
-                    tmem_form_covers(Cin, Cout, kh, kw, out_sp)) ? 1 : 0;
+  int form = (terms == 3 && sh == 1 && sw == 1 && pin == nullptr && in_sp == Cin &&
+              tmem_form_covers(Cin, Cout, kh, kw, out_sp)) ? 1 : 0;
   int rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16", terms, form,
                           out_sp);
+  if (rc == NES_ERR_UNSUPPORTED && form == 1) {           // the other form may still fit
+    form = 0;
+    rc = plan_conv_bf16(pl, D, R, Cin, H, W, Cout, kh, kw, sh, sw, ph, pw, dh, dw, antithetic, "permuted_conv2d_fwd_bf16", terms, 0, 0);
+  }
   if (rc != NES_OK) return rc;
   if (D == 0 || R == 0) return NES_OK;
   NES_REQUIRE(x && weight && eps && y, NES_ERR_BAD_ARG, "permuted_conv2d_fwd_bf16: null pointer");

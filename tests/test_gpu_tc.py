@@ -541,6 +541,8 @@ def test_permuted_linear_out_cluster_kernel_refuses_uncovered_shapes():
     # the form with the filter in tensor memory (64 input channels, <= 64 output channels, noise rows within 80 KB):
     # antithetic pairs over several tiles, a 1x1 filter with a ragged channel count and an odd repeat count
     ("out", 0, 0.25, 2, True, 32, 3, 1, 32, 64), ("out", 0, 0.5, 3, True, 10, 1, 0, 24, 64), ("out", 0, 0.125, 1, False, 17, 2, 1, 56, 64),
+    # an image too large for the form with the filter in shared memory: only the tensor-memory form covers it
+    ("out", 0, 0.5, 1, False, 64, 3, 1, 64, 64),
 ])
 def test_permuted_conv_split_bf16_holds_the_fp32_bar(mode, in_sp, out_sp, R, anti, hw, k, pad, cout, cin):
     """Default mode of a covered geometry: three bf16 products on hi/lo splits; 1e-4 on the output and 1e-3 on the
