@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
 #pragma unroll
           for (int i = 0; i < 9; ++i) {
             const float4 w = __ldg(W4 + size_t(quad) * 9 + i);
-            const float4 e = __ldcs(E4 + size_t(quad) * 9 + i);
+            const float4 e = __ldg(E4 + size_t(quad) * 9 + i);      // cached: the nine loads of a thread share lines with its neighbours
             f[4 * i] = fmaf(s, e.x, w.x); f[4 * i + 1] = fmaf(s, e.y, w.y);
             f[4 * i + 2] = fmaf(s, e.z, w.z); f[4 * i + 3] = fmaf(s, e.w, w.w);
           }
