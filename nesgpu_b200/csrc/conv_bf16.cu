@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
   uint64_t* wd_ready = acc_empty + 2;
   uint64_t* wd_free = wd_ready + 1;
   uint64_t* tbl_ready = wd_free + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tbl_ready + 1);
+  uint64_t* stage_bar = tbl_ready + 1;       // dense filter build: all eight builder warps have reached the same point
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_bar + 1);
   const int table_maps_bytes = ((2 * (p.Cout + p.Cin)) + 15) & ~15;
   const int table_bytes = table_maps_bytes + 4 * p.Cout;
   unsigned char* tables = reinterpret_cast<unsigned char*>(tmem_slot) + 16;
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     mbar_init(wd_ready, 8);
     mbar_init(wd_free, 1);
     mbar_init(tbl_ready, 8);
+    mbar_init(stage_bar, 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // filter rows beyond Cout (padding up to M) stay zero for the whole kernel
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
     const bool lane_has_row = (p.M == 128) || (lane < 16);
     const int HoWo = p.Ho * p.Wo;
     const int k8 = K / 8, c8n = p.Cin / 8;
-    uint32_t t = 0, ul = 0;
+    uint32_t t = 0, ul = 0, n_stage_sync = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
       const long long d = u / p.sign_groups;
@@ -301,39 +303,77 @@ __global__ void __launch_bounds__(BF_THREADS, 1) conv_bf16_kernel(const __nv_bfl
       CONV_TRACE(threadIdx.x == 128, t, 9);
 
       if (p.noise_kind == 1 && ksz == 9 && p.dense_vec) {
-        // dense member noise in its native (n, c, tap) order, 3x3 filters: a thread takes four consecutive channels
-        // of one filter row = 36 consecutive floats (nine 16-byte loads of W and of E_d, all in flight together); with
-        // the loops unrolled every element's tap and channel are compile-time constants, and the four channels of a
-        // tap go to shared memory as one 8-byte store per copy
+        // dense member noise in its native (n, c, tap) order, 3x3 filters.  The filter W + s E_d is formed element by
+        // element in stream order (W has the same order): coalesced 16-byte loads, 1008 of them per round, the sums
+        // parked in the epilogue's transpose buffers (idle during the build).  After a block-wide hand-over a thread
+        // takes four consecutive channels of one filter row = 36 consecutive floats from there (conflict-free at a
+        // 144-byte stride); with the loops unrolled every element's tap and channel are compile-time constants, and
+        // the four channels of a tap go to the filter image as one 8-byte store per copy.  (Reading the 36 floats
+        // straight from global memory made every load instruction touch 36 lines: 16-20 us per member.)
+        constexpr int QR = 112;                                  // quads (of 9 float4) per round
         const int quads_per_row = p.Cin >> 2;
         const int nquads = p.Cout * quads_per_row;
+        const int total4 = nquads * 9;
         const float4* W4 = reinterpret_cast<const float4*>(p.weight);
         const float4* E4 = reinterpret_cast<const float4*>(p.noise + size_t(d) * p.Cout * K);
-        for (int quad = bt; quad < nquads; quad += 256) {
-          const int n = quad / quads_per_row, c0 = (quad - n * quads_per_row) * 4;
-          float f[36];
+        float4* staging = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xpose) + ((16u - (smem_u32(xpose) & 15u)) & 15u));
+        auto block_sync = [&]() -> bool {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(stage_bar);
+          const bool done = mbar_wait(stage_bar, n_stage_sync & 1, 4);
+          ++n_stage_sync;
+          return __all_sync(0xffffffffu, done ? 1 : 0) != 0;
+        };
+        float4 wv[4], ev[4];
+        auto fetch = [&](int base4) {
 #pragma unroll
-          for (int i = 0; i < 9; ++i) {
-            const float4 w = __ldg(W4 + size_t(quad) * 9 + i);
-            const float4 e = __ldg(E4 + size_t(quad) * 9 + i);      // cached: the nine loads of a thread share lines with its neighbours
-            f[4 * i] = fmaf(s, e.x, w.x); f[4 * i + 1] = fmaf(s, e.y, w.y);
-            f[4 * i + 2] = fmaf(s, e.z, w.z); f[4 * i + 3] = fmaf(s, e.w, w.w);
+          for (int i = 0; i < 4; ++i) {
+            const int idx = base4 + bt + 256 * i;
+            const bool in = bt + 256 * i < QR * 9 && idx < total4;
+            wv[i] = in ? __ldg(W4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ev[i] = in ? __ldcs(E4 + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
           }
-          unsigned char* rowp = wd + (n >> 3) * 1024 + (n & 7) * 128;
+        };
+        fetch(0);
+        // the buffers may still serve another warp's epilogue of the previous member: everybody arrives here first
+        bool fine = block_sync();
+        for (int q0 = 0; q0 < nquads && fine; q0 += QR) {
 #pragma unroll
-          for (int tap = 0; tap < 9; ++tap) {
-            const int kk = tap * p.Cin + c0;                 // element j of the run is channel j / 9, tap j % 9
-            const int jc = kk >> 6, col = kk & 63;
-            unsigned char* dst = rowp + size_t(jc) * wd_chunk_bytes + ((((col >> 3) ^ (n & 7))) << 4) + (col & 7) * 2;
-            const float v0 = f[tap], v1 = f[9 + tap], v2 = f[18 + tap], v3 = f[27 + tap];
-            const uint32_t p01 = pack_bf16(v0, v1), p23 = pack_bf16(v2, v3);
-            *reinterpret_cast<uint2*>(dst) = make_uint2(p01, p23);
-            if (TERMS == 3)
-              *reinterpret_cast<uint2*>(dst + lo_off) =
-                  make_uint2(pack_bf16(v0 - __uint_as_float(p01 << 16), v1 - __uint_as_float(p01 & 0xffff0000u)),
-                             pack_bf16(v2 - __uint_as_float(p23 << 16), v3 - __uint_as_float(p23 & 0xffff0000u)));
+          for (int i = 0; i < 4; ++i) {
+            const int li = bt + 256 * i;
+            if (li < QR * 9)
+              staging[li] = make_float4(fmaf(s, ev[i].x, wv[i].x), fmaf(s, ev[i].y, wv[i].y), fmaf(s, ev[i].z, wv[i].z),
+                                        fmaf(s, ev[i].w, wv[i].w));
           }
+          if (q0 + QR < nquads) fetch((q0 + QR) * 9);            // the next round's loads travel during this round
+          if (!block_sync()) { fine = false; break; }
+          const int quad = q0 + bt;
+          if (bt < QR && quad < nquads) {
+            const int n = quad / quads_per_row, c0 = (quad - n * quads_per_row) * 4;
+            float f[36];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+              const float4 v = staging[bt * 9 + i];
+              f[4 * i] = v.x; f[4 * i + 1] = v.y; f[4 * i + 2] = v.z; f[4 * i + 3] = v.w;
+            }
+            unsigned char* rowp = wd + (n >> 3) * 1024 + (n & 7) * 128;
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) {
+              const int kk = tap * p.Cin + c0;                 // element j of the run is channel j / 9, tap j % 9
+              const int jc = kk >> 6, col = kk & 63;
+              unsigned char* dst = rowp + size_t(jc) * wd_chunk_bytes + ((((col >> 3) ^ (n & 7))) << 4) + (col & 7) * 2;
+              const float v0 = f[tap], v1 = f[9 + tap], v2 = f[18 + tap], v3 = f[27 + tap];
+              const uint32_t p01 = pack_bf16(v0, v1), p23 = pack_bf16(v2, v3);
+              *reinterpret_cast<uint2*>(dst) = make_uint2(p01, p23);
+              if (TERMS == 3)
+                *reinterpret_cast<uint2*>(dst + lo_off) =
+                    make_uint2(pack_bf16(v0 - __uint_as_float(p01 << 16), v1 - __uint_as_float(p01 & 0xffff0000u)),
+                               pack_bf16(v2 - __uint_as_float(p23 << 16), v3 - __uint_as_float(p23 & 0xffff0000u)));
+            }
+          }
+          if (!block_sync()) { fine = false; break; }            // the staging area is free again
         }
+        if (!fine) { ok = false; break; }
       } else if (p.noise_kind == 1) {
         // dense member noise in its native (n, c, tap) order: coalesced reads, scattered 2-byte writes
         const int total = p.Cout * K;
