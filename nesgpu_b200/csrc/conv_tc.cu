@@ -13,7 +13,7 @@
 //      all taps: the im2col expansion happens in shared memory, not in L2 traffic.  The copy is stored
 //      chunk-major and already in the 128-byte-swizzled byte order of the shared-memory tile, so a run
 //      is one contiguous range fetched by a single bulk async copy (cp.async.bulk + mbarrier);
-//   3. one thread issues tcgen05.mma (kind::tf32, M = 128 positions, N = Cout, K = 8): per tap the A
+//   3. one warp (converged, an elected lane) issues tcgen05.mma (kind::tf32, M = 128 positions, N = Cout, K = 8): per tap the A
 //      descriptor simply starts (shift * 128 bytes) further into the same staged box (the box itself
 //      starts on a 1024-byte boundary, so the swizzle pattern stays aligned and the descriptor's base
 //      offset is 0); accumulators alternate between two tiles in tensor memory, so that

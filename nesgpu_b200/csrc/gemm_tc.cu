@@ -3,13 +3,15 @@
 // Blackwell execution model, written directly in PTX:
 //   * operands travel global -> shared memory as 128-byte-swizzled tiles by TMA
 //     (cp.async.bulk.tensor.2d, one elected producer thread, mbarrier transaction counts);
-//   * one elected thread issues tcgen05.mma (kind::tf32, M = 128, N = 128, K = 8 per
-//     instruction) with both operands read from shared memory through matrix descriptors and
-//     the fp32 accumulator tile (128 lanes x 128 columns) living in tensor memory;
+//   * one warp runs the MMA loop in converged control flow and an elected lane issues tcgen05.mma
+//     (kind::tf32, M = 128, N = 128, K = 8 per instruction) with both operands read from shared memory
+//     through matrix descriptors and the fp32 accumulator tile (128 lanes x 128 columns) living in
+//     tensor memory;
 //   * tcgen05.commit hands shared-memory stages back to the producer and signals the epilogue;
 //   * four epilogue warps read the accumulator with tcgen05.ld (one TMEM lane = one output
 //     row per thread), add the bias and store.
-// With BF16 the operands are bf16 (64 elements per 128-byte row, kind::f16 with K = 16, TERMS = 1 only).
+// With BF16 the operands are bf16 (64 elements per 128-byte row, kind::f16 with K = 16); TERMS = 3 with BF16 is the
+// split-bf16 form: the same three products on bf16 hi / lo parts, half the operand bytes of 3xTF32.
 // Precision modes: TERMS = 1 is plain TF32 (inputs rounded to 10 mantissa bits; relative error
 // ~1e-3, for callers that state it).  TERMS = 3 is the error-compensated 3xTF32 scheme: every
 // operand is split beforehand into hi = tf32(a) and lo = a - hi, and the kernel accumulates
